@@ -1,0 +1,231 @@
+"""Functional Qwen3-MoE decoder in plain PyTorch: the numerical oracle for every CUDA kernel and the engine
+behind the CPU/gloo configuration.
+
+Math (all taken from the reference kernels' behaviour, not their code): RMSNorm eps 1e-6, per-head RMSNorm on Q
+and K before RoPE (kernels/k1_attn_prologue.cu:524-604), NeoX rotate-half RoPE with theta 1e6, grouped-query
+causal attention, router = softmax over all experts in fp32, top-k, renormalise the k weights to sum 1
+(kernels/k4_router.cu:67-132), SwiGLU experts ``down(silu(gate x) * up x)`` (kernels/k5_experts.cu:91-149),
+untied lm_head after a final RMSNorm (kernels/decode_step.cu:144-185).
+
+Tensor parallelism follows kernels/decode_step_tp8.cu:18-41 (partial o_proj / down outputs summed over the TP
+group); expert parallelism routes each token from its home rank to the ranks that own its experts and back.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Optional, Tuple
+
+import torch
+
+from ..config import ModelConfig
+from ..parallel.collectives import Collectives
+from .weights import LayerWeights, ModelWeights
+
+
+def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
+    xf = x.float()
+    inv = torch.rsqrt(xf.pow(2).mean(dim=-1, keepdim=True) + eps)
+    return xf * inv * w.float()
+
+
+def rope_tables(positions: torch.Tensor, head_dim: int, theta: float) -> Tuple[torch.Tensor, torch.Tensor]:
+    half = head_dim // 2
+    inv_freq = theta ** (-torch.arange(0, half, dtype=torch.float32, device=positions.device) / half)
+    ang = positions.float()[:, None] * inv_freq[None, :]
+    return ang.cos(), ang.sin()
+
+
+def apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """NeoX rotate-half on ``x[T, heads, hd]``: pairs (d, d + hd/2)."""
+    half = x.shape[-1] // 2
+    x1, x2 = x[..., :half], x[..., half:]
+    c, s = cos[:, None, :], sin[:, None, :]
+    return torch.cat([x1 * c - x2 * s, x2 * c + x1 * s], dim=-1)
+
+
+def route(h: torch.Tensor, router_w: torch.Tensor, top_k: int, renorm: bool = True):
+    """Router: fp32 softmax over all experts, top-k, optional renormalisation. Returns ``(idx, w, logits)``."""
+    logits = h.float() @ router_w.float().t()
+    probs = torch.softmax(logits, dim=-1)
+    w, idx = torch.topk(probs, top_k, dim=-1)
+    if renorm:
+        w = w / w.sum(dim=-1, keepdim=True)
+    return idx, w, logits
+
+
+@dataclass
+class RouteRecord:
+    """Expert choice of one token in one layer (global expert ids and renormalised weights)."""
+    layer: int
+    experts: List[int]
+    weights: List[float]
+
+
+class TorchKV:
+    """Contiguous KV cache ``[layers, kv_heads_local, max_seq, hd]`` for the PyTorch path."""
+
+    def __init__(self, n_layers: int, n_kv: int, max_seq: int, hd: int, dtype, device):
+        self.k = torch.zeros(n_layers, n_kv, max_seq, hd, dtype=dtype, device=device)
+        self.v = torch.zeros_like(self.k)
+        self.len = 0
+        self.max_seq = max_seq
+
+    def reset(self) -> None:
+        self.len = 0
+
+
+def _attention(q: torch.Tensor, kc: torch.Tensor, vc: torch.Tensor, positions: torch.Tensor,
+               extra_mask: Optional[torch.Tensor]) -> torch.Tensor:
+    """q[T, nq, hd]; kc/vc[nkv, S, hd] (S = cached length incl. the new tokens); causal w.r.t. ``positions``.
+
+    ``extra_mask[T, T_new]`` (bool, True = visible) replaces causality among the new tokens for tree verify."""
+    T, nq, hd = q.shape
+    nkv, S, _ = kc.shape
+    g = nq // nkv
+    qf = q.float().reshape(T, nkv, g, hd).permute(1, 2, 0, 3)                     # [nkv, g, T, hd]
+    scores = torch.einsum("kgtd,ksd->kgts", qf, kc.float()) * (hd ** -0.5)
+    kpos = torch.arange(S, device=q.device)
+    visible = kpos[None, :] <= positions[:, None]                                  # [T, S]
+    if extra_mask is not None:
+        t_new = extra_mask.shape[1]
+        visible = visible.clone()
+        visible[:, S - t_new:] = extra_mask
+    scores = scores.masked_fill(~visible[None, None], float("-inf"))
+    p = torch.softmax(scores, dim=-1)
+    out = torch.einsum("kgts,ksd->kgtd", p, vc.float())
+    return out.permute(2, 0, 1, 3).reshape(T, nq * hd)
+
+
+def _experts_local(h: torch.Tensor, lw: LayerWeights, idx: torch.Tensor, w: torch.Tensor, expert0: int,
+                   n_local: int) -> torch.Tensor:
+    """Sum over the (token, slot) pairs whose expert is held locally; ``idx`` holds global expert ids."""
+    out = torch.zeros(h.shape[0], lw.w_d.data.shape[-2], dtype=torch.float32, device=h.device)
+    local = idx - expert0
+    for e in torch.unique(local[(local >= 0) & (local < n_local)]).tolist():
+        tok, slot = torch.nonzero(local == e, as_tuple=True)
+        x = h[tok].float()
+        wgu = lw.w_gu.select(e).dequant()
+        I = wgu.shape[0] // 2
+        gu = x @ wgu.t()
+        a = torch.nn.functional.silu(gu[:, :I]) * gu[:, I:]
+        y = a @ lw.w_d.select(e).dequant().t()
+        out.index_add_(0, tok, y * w[tok, slot].float()[:, None])
+    return out
+
+
+class Qwen3MoE:
+    """One rank's model. ``forward`` runs ``T`` new tokens (prefill chunk, decode step or verify window)."""
+
+    def __init__(self, weights: ModelWeights, comm: Optional[Collectives] = None, compute_dtype=torch.float32):
+        self.w = weights
+        self.cfg: ModelConfig = weights.cfg
+        self.par = weights.par
+        self.geom = weights.geom
+        self.comm = comm if comm is not None else Collectives(weights.par)
+        self.compute_dtype = compute_dtype
+        self.last_routes: List[RouteRecord] = []
+        self.aux_taps: dict = {}
+
+    def new_cache(self, max_seq: int, dtype=torch.float32, device=None) -> TorchKV:
+        device = device if device is not None else self.w.embed.device
+        return TorchKV(self.cfg.n_layers, self.geom.nkv_local, max_seq, self.cfg.head_dim, dtype, device)
+
+    # ---------------------------------------------------------------------------------------------------------
+    def _moe(self, L: int, h: torch.Tensor, lw: LayerWeights, record: bool) -> torch.Tensor:
+        cfg, par, geom = self.cfg, self.par, self.geom
+        if par.ep == 1:
+            idx, w, _ = route(h, lw.router, cfg.top_k, cfg.norm_topk_prob)
+            if record:
+                self.last_routes.append(RouteRecord(L, idx[-1].tolist(), w[-1].tolist()))
+            y = _experts_local(h, lw, idx, w, 0, cfg.n_experts)
+            return self.comm.all_reduce_tp(y)
+        # expert parallel: home rank of token m is m % world -----------------------------------------------
+        world, rank = par.world, par.rank
+        T = h.shape[0]
+        home = torch.arange(T, device=h.device) % world
+        mine = torch.nonzero(home == rank, as_tuple=True)[0]
+        idx, w, _ = route(h[mine], lw.router, cfg.top_k, cfg.norm_topk_prob)
+        n_el = geom.n_experts_local
+        owner = idx // n_el                                                     # [Tm, k]
+        flat_tok = mine[:, None].expand_as(idx).reshape(-1)
+        flat_owner, flat_idx, flat_w = owner.reshape(-1), idx.reshape(-1), w.reshape(-1)
+        order = torch.argsort(flat_owner, stable=True)
+        send_counts = torch.bincount(flat_owner, minlength=world).tolist()
+        # dispatch: hidden row, expert id and weight travel together (2 extra fp32 columns)
+        payload = torch.cat([h[flat_tok[order]].float(), flat_idx[order, None].float(),
+                             flat_w[order, None].float()], dim=1)
+        recv, recv_counts = self.comm.all_to_all_rows(payload, send_counts)
+        rh, ridx, rw = recv[:, :-2], recv[:, -2].long(), recv[:, -1]
+        yo = torch.zeros(rh.shape[0], cfg.hidden, dtype=torch.float32, device=h.device)
+        if rh.shape[0]:
+            yo = _experts_local(rh, lw, ridx[:, None], rw[:, None], geom.expert0, n_el)
+        # combine: rows go back to their home rank in the order they came
+        back, _ = self.comm.all_to_all_rows(yo, recv_counts)
+        y_mine = torch.zeros(mine.shape[0], cfg.hidden, dtype=torch.float32, device=h.device)
+        if back.shape[0]:
+            slot_of = torch.arange(mine.shape[0], device=h.device)[:, None].expand_as(idx).reshape(-1)[order]
+            y_mine.index_add_(0, slot_of, back)
+        # every rank needs every token for the next attention block
+        y = torch.zeros(T, cfg.hidden, dtype=torch.float32, device=h.device)
+        y[mine] = y_mine
+        y = self.comm.all_reduce_world(y)
+        if record:
+            last_home = (T - 1) % world
+            rec = torch.zeros(2 * cfg.top_k, dtype=torch.float32, device=h.device)
+            if rank == last_home:
+                rec[: cfg.top_k] = idx[-1].float()
+                rec[cfg.top_k:] = w[-1].float()
+            rec = self.comm.all_reduce_world(rec)
+            self.last_routes.append(RouteRecord(L, rec[: cfg.top_k].long().tolist(), rec[cfg.top_k:].tolist()))
+        return y
+
+    def forward_hidden(self, tokens: torch.Tensor, cache: TorchKV, positions: Optional[torch.Tensor] = None,
+                       tree_mask: Optional[torch.Tensor] = None, commit: bool = True,
+                       record_routes: bool = True, aux_layers: Tuple[int, ...] = ()) -> torch.Tensor:
+        """Runs the decoder stack over ``tokens[T]`` whose KV rows are written at ``cache.len ...``; returns the
+        final-normed hidden states ``[T, H]``. ``commit=False`` leaves ``cache.len`` unchanged (verify window)."""
+        cfg, geom = self.cfg, self.geom
+        T = tokens.shape[0]
+        start = cache.len
+        if start + T > cache.max_seq:
+            raise ValueError("KV cache overflow")
+        if positions is None:
+            positions = torch.arange(start, start + T, device=tokens.device)
+        cos, sin = rope_tables(positions, cfg.head_dim, cfg.rope_theta)
+        x = self.w.embed[tokens].float()
+        self.last_routes = []
+        self.aux_taps = {}
+        hd = cfg.head_dim
+        for L, lw in enumerate(self.w.layers):
+            h = rmsnorm(x, lw.in_ln, cfg.rms_eps)
+            qkv = h @ lw.wqkv.dequant().t()
+            nq, nkv = geom.nq_local, geom.nkv_local
+            q = qkv[:, : nq * hd].reshape(T, nq, hd)
+            k = qkv[:, nq * hd: (nq + nkv) * hd].reshape(T, nkv, hd)
+            v = qkv[:, (nq + nkv) * hd:].reshape(T, nkv, hd)
+            q = apply_rope(rmsnorm(q, lw.q_norm, cfg.rms_eps), cos, sin)
+            k = apply_rope(rmsnorm(k, lw.k_norm, cfg.rms_eps), cos, sin)
+            cache.k[L, :, start:start + T] = k.permute(1, 0, 2).to(cache.k.dtype)
+            cache.v[L, :, start:start + T] = v.permute(1, 0, 2).to(cache.v.dtype)
+            attn = _attention(q, cache.k[L, :, : start + T], cache.v[L, :, : start + T], positions, tree_mask)
+            o = attn @ lw.wo.dequant().t()
+            x = x + self.comm.all_reduce_tp(o)
+            h2 = rmsnorm(x, lw.post_ln, cfg.rms_eps)
+            x = x + self._moe(L, h2, lw, record_routes)
+            if L in aux_layers:
+                self.aux_taps[L] = x.clone()
+        if commit:
+            cache.len = start + T
+        return rmsnorm(x, self.w.final_norm, cfg.rms_eps)
+
+    def logits(self, hidden: torch.Tensor) -> torch.Tensor:
+        """Full-vocabulary logits ``[T, V]`` (gathered from the vocabulary shards)."""
+        local = hidden.float() @ self.w.lm_head.dequant().t()
+        return self.comm.gather_logits(local, self.cfg.vocab, self.geom.vocab_chunk)
+
+    def greedy(self, hidden: torch.Tensor) -> torch.Tensor:
+        local = hidden.float() @ self.w.lm_head.dequant().t()
+        return self.comm.argmax_sharded(local, self.geom.vocab0)[1]
+
+    def forward(self, tokens: torch.Tensor, cache: TorchKV, **kw) -> torch.Tensor:
+        return self.logits(self.forward_hidden(tokens, cache, **kw))

@@ -1,0 +1,217 @@
+"""The inference engine: prefill, single-token decode, generation loop, device-timed steps and per-token
+expert-routing telemetry.
+
+Two backends share this front end: ``torch`` runs the functional PyTorch model (CPU/gloo configuration, and
+the oracle on GPU), ``cuda`` runs the sm_100a kernel pipeline of :mod:`..runtime.gpu_decoder` under a CUDA
+graph. The reference has no engine object: its drivers are ``main()`` functions that replay one layer of dummy
+weights 94 times, never append to the KV cache across steps and have no sampler beyond argmax
+(kernels/decode_step_tp8.cu:50-54, 1155-1184).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Callable, List, Optional, Sequence
+
+import torch
+
+from ..config import EngineConfig, ModelConfig, ParallelConfig, QuantConfig, get_model_config
+from ..models.qwen3_moe import Qwen3MoE, RouteRecord
+from ..models.weights import ModelWeights, random_sharded_weights, random_state_dict, shard_state_dict
+from ..parallel.collectives import Collectives
+from ..utils.timing import StepTimer
+from .sampler import Sampler, SamplingParams
+
+
+@dataclass
+class PrefillOutput:
+    n_prompt_tokens: int
+    seconds: float
+    next_token: int
+    logits: Optional[torch.Tensor] = None
+
+
+@dataclass
+class StepOutput:
+    index: int
+    token_id: int
+    seconds: float
+    routes: List[RouteRecord] = field(default_factory=list)
+
+
+@dataclass
+class GenerationResult:
+    prompt_tokens: int
+    tokens: List[int]
+    ttft_s: float
+    step_seconds: List[float]
+    routes: List[List[RouteRecord]]
+    spec_proposed: int = 0
+    spec_accepted: int = 0
+
+    @property
+    def decode_tok_per_s(self) -> float:
+        t = sum(self.step_seconds)
+        return (len(self.step_seconds) / t) if t > 0 else 0.0
+
+
+def expert_gpu(expert_id: int, cfg: ModelConfig, par: ParallelConfig) -> int:
+    """GPU that serves an expert: its owner under expert parallelism; under pure tensor parallelism every rank
+    holds a slice of every expert and the home convention ``expert % world`` of the reference server is kept
+    (server/topology.py:45-64)."""
+    if par.ep > 1:
+        return expert_id // (cfg.n_experts // par.ep)
+    return expert_id % max(par.world, 1)
+
+
+class InferenceEngine:
+    """One rank of the engine. All ranks of a parallel run call the same methods in the same order."""
+
+    def __init__(self, cfg: EngineConfig, weights: ModelWeights, comm: Optional[Collectives] = None,
+                 device=None):
+        self.cfg = cfg
+        self.weights = weights
+        self.device = torch.device(device if device is not None else weights.embed.device)
+        self.comm = comm if comm is not None else Collectives(cfg.parallel)
+        backend = cfg.backend
+        if backend == "auto":
+            backend = "cuda" if self.device.type == "cuda" else "torch"
+        self.backend = backend
+        self.model = Qwen3MoE(weights, self.comm)
+        kv_dtype = {"fp32": torch.float32, "bf16": torch.bfloat16}[cfg.quant.kv]
+        self.gpu = None
+        if backend == "cuda":
+            from .gpu_decoder import GpuDecoder            # imports the compiled kernels; fails loudly if absent
+            self.gpu = GpuDecoder(cfg, weights, self.comm, self.device)
+            self.cache = None
+        else:
+            self.cache = self.model.new_cache(cfg.max_seq, kv_dtype, self.device)
+        self.sampler = Sampler()
+        self._last_token: Optional[int] = None
+        self._index = 0
+        self._timer = StepTimer(self.device)
+
+    # construction ------------------------------------------------------------------------------------------
+    @classmethod
+    def build(cls, model: str = "tiny", *, tp: int = 1, ep: int = 1, rank: int = 0, world: Optional[int] = None,
+              weights: str = "fp32", kv: Optional[str] = None, device="cpu", backend: str = "auto",
+              max_seq: int = 2048, seed: int = 0, n_layers: Optional[int] = None, distinct_layers: int = 0,
+              state_dict=None, checkpoint: Optional[str] = None, comm: str = "auto",
+              use_graph: bool = True) -> "InferenceEngine":
+        """Public constructor. Weight source, in order: ``state_dict`` (HF names), ``checkpoint`` (safetensors
+        directory), else random init (host-side and layout-independent for small models, streamed on the
+        device otherwise)."""
+        mcfg = get_model_config(model, n_layers)
+        world = world if world is not None else max(tp, ep)
+        par = ParallelConfig(tp=tp, ep=ep, rank=rank, world=world)
+        par.validate(mcfg)
+        q = QuantConfig(weights=weights, kv=kv or ("fp32" if weights == "fp32" else "bf16"))
+        ecfg = EngineConfig(model=mcfg, parallel=par, quant=q, max_seq=max_seq, seed=seed, backend=backend,
+                            distinct_layers=distinct_layers, comm=comm, use_graph=use_graph)
+        if state_dict is not None or checkpoint is not None:
+            w = shard_state_dict(state_dict if state_dict is not None else checkpoint, mcfg, par, q, device=device)
+        elif mcfg.total_params() <= 300_000_000:
+            w = shard_state_dict(random_state_dict(mcfg, seed), mcfg, par, q, device=device)
+        else:
+            w = random_sharded_weights(mcfg, par, q, device, seed, distinct_layers)
+        return cls(ecfg, w, device=device)
+
+    # state ---------------------------------------------------------------------------------------------------
+    @property
+    def seq_len(self) -> int:
+        return self.gpu.seq_len if self.gpu is not None else self.cache.len
+
+    def reset(self) -> None:
+        if self.gpu is not None:
+            self.gpu.reset()
+        else:
+            self.cache.reset()
+        self._last_token = None
+        self._index = 0
+
+    def set_sampling(self, params: SamplingParams) -> None:
+        self.sampler = Sampler(params)
+
+    # forward passes ------------------------------------------------------------------------------------------
+    def prefill(self, token_ids: Sequence[int], return_logits: bool = False) -> PrefillOutput:
+        """Process the prompt, fill the KV cache, return the first generated token (device-timed)."""
+        toks = torch.as_tensor(list(token_ids), dtype=torch.long, device=self.device)
+        self._timer.start()
+        if self.gpu is not None:
+            nxt, logits = self.gpu.prefill(toks, self.sampler, return_logits)
+        else:
+            hidden = self.model.forward_hidden(toks, self.cache)
+            nxt, logits = self._pick(hidden[-1:], return_logits)
+        seconds = self._timer.stop()
+        self._last_token = int(nxt)
+        self._index = 0
+        return PrefillOutput(len(toks), seconds, int(nxt), logits)
+
+    def _pick(self, hidden_last: torch.Tensor, return_logits: bool):
+        if self.sampler.params.greedy and not return_logits:
+            return int(self.model.greedy(hidden_last)[0]), None
+        logits = self.model.logits(hidden_last)
+        tok = self.sampler.sample(logits[0])
+        if self.cfg.parallel.world > 1 and not self.sampler.params.greedy:
+            # all ranks must continue with the same token: rank 0's draw wins
+            t = tok.reshape(1).clone()
+            torch.distributed.broadcast(t, src=0)
+            tok = t[0]
+        return int(tok), (logits if return_logits else None)
+
+    def decode_step(self, token: Optional[int] = None, return_logits: bool = False) -> StepOutput:
+        """Feed one token (default: the previously generated one) and produce the next."""
+        tok = self._last_token if token is None else token
+        if tok is None:
+            raise RuntimeError("decode_step before prefill")
+        if self.gpu is not None:
+            out_tok, seconds, routes = self.gpu.decode_step(tok, self.sampler)
+        else:
+            t = torch.tensor([tok], dtype=torch.long, device=self.device)
+            self._timer.start()
+            hidden = self.model.forward_hidden(t, self.cache)
+            out_tok, _ = self._pick(hidden, return_logits)
+            seconds = self._timer.stop()
+            routes = list(self.model.last_routes)
+        self._last_token = int(out_tok)
+        i = self._index
+        self._index += 1
+        return StepOutput(i, int(out_tok), seconds, routes)
+
+    def logits_for(self, tokens: Sequence[int], commit: bool = True, tree_mask=None, positions=None,
+                   aux_layers=()) -> torch.Tensor:
+        """Logits ``[T, V]`` of a window of new tokens (speculative verify); PyTorch path."""
+        if self.gpu is not None:
+            return self.gpu.logits_for(tokens, commit=commit, tree_mask=tree_mask, positions=positions)
+        t = torch.as_tensor(list(tokens), dtype=torch.long, device=self.device)
+        hidden = self.model.forward_hidden(t, self.cache, positions=positions, tree_mask=tree_mask,
+                                           commit=commit, aux_layers=tuple(aux_layers))
+        return self.model.logits(hidden)
+
+    def rollback(self, seq_len: int) -> None:
+        """Drop KV rows beyond ``seq_len`` (rejected draft tokens)."""
+        if self.gpu is not None:
+            self.gpu.rollback(seq_len)
+        else:
+            self.cache.len = seq_len
+
+    # generation ----------------------------------------------------------------------------------------------
+    def generate(self, prompt_ids: Sequence[int], max_new_tokens: int, *, eos: Optional[int] = None,
+                 sampling: Optional[SamplingParams] = None,
+                 on_token: Optional[Callable[[StepOutput], None]] = None) -> GenerationResult:
+        if sampling is not None:
+            self.set_sampling(sampling)
+        self.reset()
+        pre = self.prefill(prompt_ids)
+        tokens = [pre.next_token]
+        secs: List[float] = []
+        routes: List[List[RouteRecord]] = [list(self.model.last_routes) if self.gpu is None else self.gpu.last_routes()]
+        if on_token is not None:
+            on_token(StepOutput(-1, pre.next_token, pre.seconds, routes[0]))
+        while len(tokens) < max_new_tokens and (eos is None or tokens[-1] != eos):
+            st = self.decode_step()
+            tokens.append(st.token_id)
+            secs.append(st.seconds)
+            routes.append(st.routes)
+            if on_token is not None:
+                on_token(st)
+        return GenerationResult(len(prompt_ids), tokens, pre.seconds, secs, routes)

@@ -1,0 +1,57 @@
+"""Reference model: parameter accounting, layout invariants, KV-cache consistency (CPU)."""
+import torch
+
+from inferencehackathon_b200 import TINY, QWEN3_235B_A22B, QWEN3_30B_A3B, ParallelConfig, QuantConfig
+from inferencehackathon_b200.models.qwen3_moe import Qwen3MoE
+from inferencehackathon_b200.models.weights import random_state_dict, shard_state_dict, shard_geometry
+from inferencehackathon_b200.runtime.engine import InferenceEngine
+
+
+def test_param_counts():
+    assert 234e9 < QWEN3_235B_A22B.total_params() < 236e9
+    assert 21e9 < QWEN3_235B_A22B.active_params() < 23e9
+    assert 30e9 < QWEN3_30B_A3B.total_params() < 31e9
+
+
+def test_geometry_tp8_replicates_kv():
+    g = shard_geometry(QWEN3_235B_A22B, ParallelConfig(tp=8, rank=5, world=8))
+    assert (g.nq_local, g.nkv_local, g.kv_head0, g.inter_local) == (8, 1, 2, 192)
+    assert g.vocab_local == 18992
+    g = shard_geometry(QWEN3_235B_A22B, ParallelConfig(tp=2, ep=8, rank=5, world=8))
+    assert (g.nq_local, g.nkv_local, g.n_experts_local, g.expert0, g.inter_local) == (32, 2, 16, 80, 1536)
+
+
+def test_incremental_decode_matches_full_prefill():
+    sd = random_state_dict(TINY, 0)
+    w = shard_state_dict(sd, TINY, ParallelConfig(), QuantConfig("fp32", kv="fp32"))
+    m = Qwen3MoE(w)
+    toks = torch.randint(0, TINY.vocab, (12,), generator=torch.Generator().manual_seed(1))
+    c1 = m.new_cache(32)
+    full = m.forward(toks, c1)
+    c2 = m.new_cache(32)
+    m.forward(toks[:8], c2)
+    outs = [m.forward(toks[i:i + 1], c2) for i in range(8, 12)]
+    inc = torch.cat(outs)
+    assert torch.allclose(full[8:], inc, atol=2e-4, rtol=1e-4)
+
+
+def test_generate_greedy_deterministic():
+    e = InferenceEngine.build("tiny", weights="fp32", max_seq=128)
+    prompt = torch.randint(0, TINY.vocab, (32,), generator=torch.Generator().manual_seed(0)).tolist()
+    a = e.generate(prompt, 16)
+    b = e.generate(prompt, 16)
+    assert a.tokens == b.tokens and len(a.tokens) == 16
+    assert len(a.routes[1]) == TINY.n_layers and len(a.routes[1][0].experts) == TINY.top_k
+    assert abs(sum(a.routes[1][0].weights) - 1.0) < 1e-5
+
+
+def test_fp8_block_weights_close_to_fp32():
+    sd = random_state_dict(TINY, 0)
+    w32 = shard_state_dict(sd, TINY, ParallelConfig(), QuantConfig("fp32", kv="fp32"))
+    w8 = shard_state_dict(sd, TINY, ParallelConfig(), QuantConfig("fp8_block", kv="fp32"))
+    a, b = w32.layers[0].wqkv.dequant(), w8.layers[0].wqkv.dequant()
+    assert w8.layers[0].wqkv.is_fp8 and (a - b).abs().max() < 0.07 * a.abs().max()
+    toks = torch.arange(8)
+    m32, m8 = Qwen3MoE(w32), Qwen3MoE(w8)
+    l32, l8 = m32.forward(toks, m32.new_cache(16)), m8.forward(toks, m8.new_cache(16))
+    assert torch.nn.functional.cosine_similarity(l32.flatten(), l8.flatten(), dim=0) > 0.98
