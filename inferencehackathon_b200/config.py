@@ -75,9 +75,14 @@ TINY = ModelConfig(name="tiny-qwen3-moe", hidden=256, n_layers=4, n_q_heads=8, n
 QWEN3_30B_A3B = ModelConfig(name="qwen3-30b-a3b", hidden=2048, n_layers=48, n_q_heads=32, n_kv_heads=4,
                             head_dim=128, n_experts=128, top_k=8, moe_inter=768, vocab=151936)
 QWEN3_235B_A22B = ModelConfig()
+# head_dim-128 miniature for GPU kernel tests
+SMALL = ModelConfig(name="small-qwen3-moe", hidden=512, n_layers=2, n_q_heads=8, n_kv_heads=2, head_dim=128,
+                    n_experts=16, top_k=4, moe_inter=256, vocab=4096)
 
 MODEL_PRESETS = {
     "tiny": TINY,
+    "small": SMALL,
+    SMALL.name: SMALL,
     TINY.name: TINY,
     "qwen3-30b-a3b": QWEN3_30B_A3B,
     "qwen3-235b-a22b": QWEN3_235B_A22B,

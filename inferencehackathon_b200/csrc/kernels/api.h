@@ -1,0 +1,121 @@
+// C ABI of the sm_100a kernel library (loaded from Python with ctypes; every entry launches on the given
+// stream and returns a cudaError_t value, 0 = success). All pointers are device pointers unless noted.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define IHB_MAX_RANKS 8
+#define IHB_MAX_TOPK 8
+
+enum { IHB_W_FP8 = 0, IHB_W_BF16 = 1 };
+enum { IHB_EPI_STORE = 0, IHB_EPI_ROUTER = 1, IHB_EPI_ARGMAX = 2, IHB_EPI_AR_NORM = 3 };
+
+// Cross-GPU state of the fused all-reduce epilogues. With nranks == 1 only slots_local and epoch are used.
+// Multicast mode: *_mc are NVLS multicast addresses of the same symmetric buffers (one store reaches every
+// GPU); peer mode (*_mc == NULL): *_peer[r] is rank r's buffer mapped into this process.
+typedef struct {
+  int nranks;
+  int rank;
+  float* slots_local;                        // [2][nranks * ks][H] fp32 partials, double buffered by epoch parity
+  float* slots_mc;
+  float* slots_peer[IHB_MAX_RANKS];
+  unsigned* flag_local;                      // monotonic arrival counter
+  unsigned* flag_mc;
+  unsigned* flag_peer[IHB_MAX_RANKS];
+  unsigned long long* arg_slots_local;       // [2][nranks] packed (value, token) for the sharded head
+  unsigned long long* arg_slots_mc;
+  unsigned long long* arg_slots_peer[IHB_MAX_RANKS];
+  unsigned* epoch;                           // local: number of collectives completed so far
+} IhbComm;
+
+typedef struct {
+  // weights
+  const uint8_t* W;        // [rows, K] e4m3 bytes or bf16, rows contiguous
+  const float* wscale;     // fp8: [ceil(rows / rb), nkb]
+  int wtype;               // IHB_W_*
+  int rows, K;
+  int rb, kb_shift, nkb;   // scale block: rb rows x (1 << kb_shift) columns
+  // input
+  const float* x;          // [K] fp32
+  // tiling (0 = choose)
+  int R, S, grid, ks;      // rows per tile, ring stages, CTAs, K-split (AR_NORM only)
+  int epi;                 // IHB_EPI_*
+  float* out;              // STORE / ROUTER / (ARGMAX, optional): [rows] fp32
+  unsigned* counter;       // last-CTA election word (zero before the first launch)
+  unsigned* err;           // device error word (0 = none)
+  // ROUTER
+  int top_k, renorm;
+  int* sel_idx;            // [top_k]
+  float* sel_w;            // [top_k]
+  // ARGMAX
+  unsigned long long* argmax_partial;   // [grid]
+  int vocab0;
+  int* cur_token;          // next input token
+  int* pos;                // position counter, incremented by the tail
+  int* token_ring;         // optional ring of generated tokens indexed by position
+  int token_ring_size;
+  const int* forced;       // optional: tokens that override the argmax while position + 1 < *n_forced (prompt replay)
+  const int* n_forced;
+  // AR_NORM
+  float* resid;            // [rows] residual stream, updated in place
+  const float* gamma;      // [rows] weight of the norm that follows
+  float* xn_out;           // [rows] normed output
+  float eps;
+  IhbComm comm;
+} IhbGemvArgs;
+
+int ihb_gemv(IhbGemvArgs* args, int use_pdl, cudaStream_t stream);
+
+// MoE expert kernels (M = 1). Expert ids / weights come from device memory (the router tail wrote them).
+typedef struct {
+  const uint8_t* Wgu;      // [E_local, 2 * I, H]: gate rows then up rows
+  const float* gu_scale;   // fp8: [E_local, ceil(2 I / rb), nkb]
+  const uint8_t* Wd;       // [E_local, H, I]
+  const float* d_scale;    // fp8: [E_local, ceil(H / d_rb), d_nkb]
+  int wtype;
+  int H, I, E_local, expert0, top_k;
+  int gu_rb, gu_kb_shift, gu_nkb;
+  int d_rb, d_kb_shift, d_nkb;
+  const float* x;          // [H] normed hidden
+  const int* sel_idx;      // [top_k] global expert ids
+  const float* sel_w;      // [top_k]
+  float* act;              // [top_k, I] fp32 SwiGLU activations (scratch between the two kernels)
+  int R_gu, R_d, S, grid;
+  unsigned* counter;
+  unsigned* err;
+  // down projection epilogue = AR_NORM
+  float* resid;
+  const float* gamma;
+  float* xn_out;
+  float eps;
+  IhbComm comm;
+} IhbMoeArgs;
+
+int ihb_moe_gateup(IhbMoeArgs* args, int use_pdl, cudaStream_t stream);
+int ihb_moe_down(IhbMoeArgs* args, int use_pdl, cudaStream_t stream);
+
+// Embedding gather + first RMSNorm: resid = embed[*token]; xn = rmsnorm(resid) * gamma.
+int ihb_embed_norm(const void* embed, int embed_is_bf16, const int* token, int H, const float* gamma, float eps,
+                   float* resid, float* xn, int use_pdl, cudaStream_t stream);
+
+// Per-head QK RMSNorm + NeoX RoPE at position *pos; writes q in place and K/V (bf16) into the cache row *pos.
+// qkv: [(nq + 2 nkv) * 128] fp32 (Q heads, K heads, V heads); cos/sin: [max_seq, 64] fp32 tables.
+int ihb_qk_norm_rope_kv(float* qkv, int nq, int nkv, const float* q_gamma, const float* k_gamma, float eps,
+                        const float* cos_t, const float* sin_t, const int* pos, void* k_cache, void* v_cache,
+                        int max_seq, int use_pdl, cudaStream_t stream);
+
+// Split-KV GQA flash-decode over positions [0, *pos] with an in-kernel merge by the last CTA of each KV head.
+// q: [nq, 128] fp32 (already normed + roped); k_cache/v_cache: [nkv, max_seq, 128] bf16; out: [nq, 128] fp32.
+// scratch: nq * nsplit * 130 floats (partial acc, m, l); counters: nq unsigned, zero before the first launch.
+int ihb_flash_decode(const float* q, const void* k_cache, const void* v_cache, int nq, int nkv, int max_seq,
+                     const int* pos, int nsplit, float* scratch, unsigned* counters, float* out, int use_pdl,
+                     cudaStream_t stream);
+size_t ihb_flash_decode_scratch_floats(int nq, int nsplit);
+
+#ifdef __cplusplus
+}
+#endif

@@ -1,0 +1,308 @@
+// Decode-side attention kernels, head_dim = 128, sm_100a:
+//   embed_norm          token embedding gather + first RMSNorm
+//   qk_norm_rope_kv     per-head RMSNorm of Q and K, NeoX RoPE, KV-cache append (bf16)
+//   flash_decode        split-KV GQA single-query attention; the last CTA of each head group merges the split
+//                       partials in the same launch (the reference needs a second kernel,
+//                       kernels/k2_flash_decode.cu:90-195) and every K/V row is read once for all query heads of
+//                       its group (the reference re-reads it per 4 heads, kernels/decode_step_tp8.cu:1798-1802).
+// The position counter lives in device memory so that a captured CUDA graph replays without host updates.
+#include "common.cuh"
+#include "api.h"
+
+namespace ihb {
+
+constexpr int HD = 128;
+
+// ---------------------------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) embed_norm_kernel(const void* __restrict__ embed, int is_bf16,
+                                                         const int* __restrict__ token, int H,
+                                                         const float* __restrict__ gamma, float eps,
+                                                         float* __restrict__ resid, float* __restrict__ xn) {
+  __shared__ float red[8];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int tok = ld_cg_i(token);
+  const int tid = threadIdx.x;
+  float ss = 0.f;
+  for (int i = tid; i < H; i += 256) {
+    float v;
+    if (is_bf16) v = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(embed)[static_cast<size_t>(tok) * H + i]);
+    else v = reinterpret_cast<const float*>(embed)[static_cast<size_t>(tok) * H + i];
+    resid[i] = v;
+    ss += v * v;
+  }
+  ss = warp_sum(ss);
+  if ((tid & 31) == 0) red[tid >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int w = 0; w < 8; ++w) tot += red[w];
+  const float rinv = rsqrtf(tot / static_cast<float>(H) + eps);
+  for (int i = tid; i < H; i += 256) xn[i] = resid[i] * rinv * gamma[i];
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// One warp per head. Lane owns channels d = lane + 32 j (j = 0..3); RoPE pairs (d, d + 64) are (j, j + 2).
+__global__ void __launch_bounds__(32) qk_norm_rope_kv_kernel(float* __restrict__ qkv, int nq, int nkv,
+                                                             const float* __restrict__ q_gamma,
+                                                             const float* __restrict__ k_gamma, float eps,
+                                                             const float* __restrict__ cos_t,
+                                                             const float* __restrict__ sin_t,
+                                                             const int* __restrict__ pos_p,
+                                                             __nv_bfloat16* __restrict__ k_cache,
+                                                             __nv_bfloat16* __restrict__ v_cache, int max_seq) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int head = blockIdx.x;
+  const int lane = threadIdx.x;
+  int pos = ld_cg_i(pos_p);
+  if (pos >= max_seq) pos = max_seq - 1;   // cache full: keep overwriting the last row instead of running past it
+  if (head >= nq + nkv) {                  // V head: copy into the cache
+    const int kvh = head - nq - nkv;
+    const float* v = qkv + static_cast<size_t>(head) * HD;
+    __nv_bfloat16* dst = v_cache + (static_cast<size_t>(kvh) * max_seq + pos) * HD;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) dst[lane + 32 * j] = __float2bfloat16(ld_cg_f(v + lane + 32 * j));
+    return;
+  }
+  float* x = qkv + static_cast<size_t>(head) * HD;
+  const float* gamma = head < nq ? q_gamma : k_gamma;
+  float v[4];
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    v[j] = ld_cg_f(x + lane + 32 * j);
+    ss += v[j] * v[j];
+  }
+  ss = warp_sum(ss);
+  const float rinv = rsqrtf(ss / static_cast<float>(HD) + eps);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) v[j] = v[j] * rinv * gamma[lane + 32 * j];
+  float o[4];
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    const float c = cos_t[static_cast<size_t>(pos) * (HD / 2) + lane + 32 * j];
+    const float s = sin_t[static_cast<size_t>(pos) * (HD / 2) + lane + 32 * j];
+    o[j] = v[j] * c - v[j + 2] * s;
+    o[j + 2] = v[j + 2] * c + v[j] * s;
+  }
+  if (head < nq) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) x[lane + 32 * j] = o[j];
+  } else {
+    __nv_bfloat16* dst = k_cache + (static_cast<size_t>(head - nq) * max_seq + pos) * HD;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) dst[lane + 32 * j] = __float2bfloat16(o[j]);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// flash decode. grid = (nsplit, nkv, q_per_kv / GQ); block = 128 threads (4 warps x 32 positions).
+// scratch layout per (head, split): [128 acc][m][l]  (FD_REC floats)
+// ---------------------------------------------------------------------------------------------------------------------
+constexpr int FD_WARPS = 4;
+constexpr int FD_BLOCK = FD_WARPS * 32;     // positions per CTA iteration
+constexpr int FD_REC = HD + 2;
+
+template <int GQ>
+__global__ void __launch_bounds__(FD_WARPS * 32) flash_decode_kernel(
+    const float* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
+    const __nv_bfloat16* __restrict__ v_cache, int nq, int nkv, int max_seq, const int* __restrict__ pos_p,
+    int nsplit, float* __restrict__ scratch, unsigned* __restrict__ counters, float* __restrict__ out) {
+  __shared__ __align__(16) float q_s[GQ][HD];
+  __shared__ __align__(16) float p_s[FD_WARPS][GQ][32];
+  __shared__ float m_s[FD_WARPS][GQ], l_s[FD_WARPS][GQ];
+  __shared__ __align__(16) float acc_s[FD_WARPS][GQ][HD];
+  __shared__ int s_last;
+  pdl_wait();
+  pdl_launch_dependents();
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int split = blockIdx.x, kvh = blockIdx.y, grp = blockIdx.z;
+  const int q_per_kv = nq / nkv;
+  const int head0 = kvh * q_per_kv + grp * GQ;
+  int n = ld_cg_i(pos_p) + 1;
+  if (n > max_seq) n = max_seq;
+  const float qscale = 0.08838834764831845f * 1.4426950408889634f;   // 1/sqrt(128) * log2(e)
+  for (int i = tid; i < GQ * HD; i += FD_WARPS * 32)
+    q_s[i / HD][i % HD] = ld_cg_f(q + static_cast<size_t>(head0) * HD + i) * qscale;
+  __syncthreads();
+
+  float m[GQ], l[GQ], acc[GQ][4];
+#pragma unroll
+  for (int g = 0; g < GQ; ++g) {
+    m[g] = -INFINITY;
+    l[g] = 0.f;
+    acc[g][0] = acc[g][1] = acc[g][2] = acc[g][3] = 0.f;
+  }
+  const __nv_bfloat16* kbase = k_cache + static_cast<size_t>(kvh) * max_seq * HD;
+  const __nv_bfloat16* vbase = v_cache + static_cast<size_t>(kvh) * max_seq * HD;
+
+  for (int b0 = split * FD_BLOCK; b0 < n; b0 += nsplit * FD_BLOCK) {
+    const int base = b0 + warp * 32;
+    if (base >= n) break;
+    const int p = base + lane;
+    const bool valid = p < n;
+    float s[GQ];
+#pragma unroll
+    for (int g = 0; g < GQ; ++g) s[g] = 0.f;
+    if (valid) {
+      const uint4* kr = reinterpret_cast<const uint4*>(kbase + static_cast<size_t>(p) * HD);
+#pragma unroll 4
+      for (int c = 0; c < HD / 8; ++c) {
+        const uint4 kv = kr[c];
+        float kf[8];
+        kf[0] = __uint_as_float(kv.x << 16); kf[1] = __uint_as_float(kv.x & 0xffff0000u);
+        kf[2] = __uint_as_float(kv.y << 16); kf[3] = __uint_as_float(kv.y & 0xffff0000u);
+        kf[4] = __uint_as_float(kv.z << 16); kf[5] = __uint_as_float(kv.z & 0xffff0000u);
+        kf[6] = __uint_as_float(kv.w << 16); kf[7] = __uint_as_float(kv.w & 0xffff0000u);
+#pragma unroll
+        for (int g = 0; g < GQ; ++g) {
+          const float4 qa = *reinterpret_cast<const float4*>(&q_s[g][c * 8]);
+          const float4 qb = *reinterpret_cast<const float4*>(&q_s[g][c * 8 + 4]);
+          s[g] = fmaf(kf[0], qa.x, s[g]); s[g] = fmaf(kf[1], qa.y, s[g]);
+          s[g] = fmaf(kf[2], qa.z, s[g]); s[g] = fmaf(kf[3], qa.w, s[g]);
+          s[g] = fmaf(kf[4], qb.x, s[g]); s[g] = fmaf(kf[5], qb.y, s[g]);
+          s[g] = fmaf(kf[6], qb.z, s[g]); s[g] = fmaf(kf[7], qb.w, s[g]);
+        }
+      }
+    }
+#pragma unroll
+    for (int g = 0; g < GQ; ++g) {
+      const float sv = valid ? s[g] : -INFINITY;
+      const float mnew = fmaxf(m[g], warp_max(sv));     // finite: lane 0 of the chunk is always valid
+      const float corr = exp2f(m[g] - mnew);
+      const float pv = valid ? exp2f(sv - mnew) : 0.f;
+      m[g] = mnew;
+      l[g] = l[g] * corr + pv;                           // per-lane partial sum, combined at the end
+      acc[g][0] *= corr; acc[g][1] *= corr; acc[g][2] *= corr; acc[g][3] *= corr;
+      p_s[warp][g][lane] = pv;
+    }
+    __syncwarp();
+    const int cnt = min(32, n - base);
+    for (int j = 0; j < cnt; ++j) {
+      const uint2 vv = *reinterpret_cast<const uint2*>(vbase + static_cast<size_t>(base + j) * HD + lane * 4);
+      const float v0 = __uint_as_float(vv.x << 16), v1 = __uint_as_float(vv.x & 0xffff0000u);
+      const float v2 = __uint_as_float(vv.y << 16), v3 = __uint_as_float(vv.y & 0xffff0000u);
+#pragma unroll
+      for (int g = 0; g < GQ; ++g) {
+        const float pj = p_s[warp][g][j];
+        acc[g][0] = fmaf(pj, v0, acc[g][0]); acc[g][1] = fmaf(pj, v1, acc[g][1]);
+        acc[g][2] = fmaf(pj, v2, acc[g][2]); acc[g][3] = fmaf(pj, v3, acc[g][3]);
+      }
+    }
+    __syncwarp();
+  }
+
+  // combine the four warps of the CTA
+#pragma unroll
+  for (int g = 0; g < GQ; ++g) {
+    const float lt = warp_sum(l[g]);
+    if (lane == 0) { m_s[warp][g] = m[g]; l_s[warp][g] = lt; }
+    *reinterpret_cast<float4*>(&acc_s[warp][g][lane * 4]) = make_float4(acc[g][0], acc[g][1], acc[g][2], acc[g][3]);
+  }
+  __syncthreads();
+  for (int i = tid; i < GQ * HD; i += FD_WARPS * 32) {
+    const int g = i / HD, d = i % HD;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < FD_WARPS; ++w) M = fmaxf(M, m_s[w][g]);
+    float a = 0.f, L = 0.f;
+    if (M > -INFINITY) {
+#pragma unroll
+      for (int w = 0; w < FD_WARPS; ++w) {
+        const float f = exp2f(m_s[w][g] - M);     // exp2(-inf) = 0 for warps without positions
+        a += acc_s[w][g][d] * f;
+        L += l_s[w][g] * f;
+      }
+    }
+    float* rec = scratch + (static_cast<size_t>(head0 + g) * nsplit + split) * FD_REC;
+    rec[d] = a;
+    if (d == 0) { rec[HD] = M; rec[HD + 1] = L; }
+  }
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    unsigned* ctr = counters + kvh * gridDim.z + grp;
+    const unsigned old = atomicAdd(ctr, 1u);
+    s_last = (old == static_cast<unsigned>(nsplit) - 1u);
+    if (s_last) { *ctr = 0u; __threadfence(); }
+  }
+  __syncthreads();
+  if (!s_last) return;
+  // merge of the split partials by the last CTA of this (kv head, group)
+  for (int i = tid; i < GQ * HD; i += FD_WARPS * 32) {
+    const int g = i / HD, d = i % HD;
+    const float* recs = scratch + static_cast<size_t>(head0 + g) * nsplit * FD_REC;
+    float M = -INFINITY;
+    for (int sp = 0; sp < nsplit; ++sp) M = fmaxf(M, ld_cg_f(recs + sp * FD_REC + HD));
+    float a = 0.f, L = 0.f;
+    for (int sp = 0; sp < nsplit; ++sp) {
+      const float ms = ld_cg_f(recs + sp * FD_REC + HD);
+      if (ms > -INFINITY) {
+        const float f = exp2f(ms - M);
+        a += ld_cg_f(recs + sp * FD_REC + d) * f;
+        L += ld_cg_f(recs + sp * FD_REC + HD + 1) * f;
+      }
+    }
+    out[static_cast<size_t>(head0 + g) * HD + d] = a / L;
+  }
+}
+
+static void pdl_cfg(cudaLaunchConfig_t& cfg, cudaLaunchAttribute* attr, dim3 grid, dim3 block, int use_pdl,
+                    cudaStream_t stream) {
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = stream;
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = use_pdl ? 1 : 0;
+}
+
+}  // namespace ihb
+
+using namespace ihb;
+
+extern "C" int ihb_embed_norm(const void* embed, int embed_is_bf16, const int* token, int H, const float* gamma,
+                              float eps, float* resid, float* xn, int use_pdl, cudaStream_t stream) {
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  pdl_cfg(cfg, attr, dim3(1), dim3(256), use_pdl, stream);
+  return cudaLaunchKernelEx(&cfg, embed_norm_kernel, embed, embed_is_bf16, token, H, gamma, eps, resid, xn);
+}
+
+extern "C" int ihb_qk_norm_rope_kv(float* qkv, int nq, int nkv, const float* q_gamma, const float* k_gamma,
+                                   float eps, const float* cos_t, const float* sin_t, const int* pos, void* k_cache,
+                                   void* v_cache, int max_seq, int use_pdl, cudaStream_t stream) {
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  pdl_cfg(cfg, attr, dim3(nq + 2 * nkv), dim3(32), use_pdl, stream);
+  return cudaLaunchKernelEx(&cfg, qk_norm_rope_kv_kernel, qkv, nq, nkv, q_gamma, k_gamma, eps, cos_t, sin_t, pos,
+                            reinterpret_cast<__nv_bfloat16*>(k_cache), reinterpret_cast<__nv_bfloat16*>(v_cache),
+                            max_seq);
+}
+
+extern "C" size_t ihb_flash_decode_scratch_floats(int nq, int nsplit) {
+  return static_cast<size_t>(nq) * nsplit * FD_REC;
+}
+
+extern "C" int ihb_flash_decode(const float* q, const void* k_cache, const void* v_cache, int nq, int nkv,
+                                int max_seq, const int* pos, int nsplit, float* scratch, unsigned* counters,
+                                float* out, int use_pdl, cudaStream_t stream) {
+  if (nq % nkv || nsplit < 1) return cudaErrorInvalidValue;
+  const int q_per_kv = nq / nkv;
+  int gq = q_per_kv >= 8 ? 8 : q_per_kv;
+  if (q_per_kv % gq || (gq != 8 && gq != 4 && gq != 2 && gq != 1)) return cudaErrorInvalidValue;
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  pdl_cfg(cfg, attr, dim3(nsplit, nkv, q_per_kv / gq), dim3(FD_WARPS * 32), use_pdl, stream);
+  const __nv_bfloat16* kc = reinterpret_cast<const __nv_bfloat16*>(k_cache);
+  const __nv_bfloat16* vc = reinterpret_cast<const __nv_bfloat16*>(v_cache);
+  switch (gq) {
+    case 8: return cudaLaunchKernelEx(&cfg, flash_decode_kernel<8>, q, kc, vc, nq, nkv, max_seq, pos, nsplit, scratch, counters, out);
+    case 4: return cudaLaunchKernelEx(&cfg, flash_decode_kernel<4>, q, kc, vc, nq, nkv, max_seq, pos, nsplit, scratch, counters, out);
+    case 2: return cudaLaunchKernelEx(&cfg, flash_decode_kernel<2>, q, kc, vc, nq, nkv, max_seq, pos, nsplit, scratch, counters, out);
+    default: return cudaLaunchKernelEx(&cfg, flash_decode_kernel<1>, q, kc, vc, nq, nkv, max_seq, pos, nsplit, scratch, counters, out);
+  }
+}

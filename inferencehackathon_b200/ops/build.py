@@ -1,0 +1,104 @@
+"""In-tree build of the native libraries with nvcc / g++ for sm_100a.
+
+``libihb_kernels.so`` (CUDA kernels, plain C ABI, loaded with ctypes) and ``libihb_ctrl.so`` (C++ control
+plane: speculative acceptance, tree builder, routing optimiser/predictors/scheduler) are written next to this
+file so that they travel with the source tree. nvcc cross-compiles without a GPU.
+"""
+from __future__ import annotations
+
+import hashlib
+import os
+import subprocess
+import sys
+from typing import List
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+CSRC = os.path.join(os.path.dirname(HERE), "csrc")
+KERNEL_LIB = os.path.join(HERE, "libihb_kernels.so")
+CTRL_LIB = os.path.join(HERE, "libihb_ctrl.so")
+
+NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
+              "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]
+
+
+def _sources(sub: str, exts) -> List[str]:
+    d = os.path.join(CSRC, sub)
+    if not os.path.isdir(d):
+        return []
+    return sorted(os.path.join(d, f) for f in os.listdir(d) if f.endswith(tuple(exts)))
+
+
+def _digest(paths: List[str], extra: str) -> str:
+    h = hashlib.sha256(extra.encode())
+    for p in paths:
+        with open(p, "rb") as f:
+            h.update(p.encode())
+            h.update(f.read())
+    return h.hexdigest()
+
+
+def _stale(lib: str, digest: str) -> bool:
+    stamp = lib + ".stamp"
+    if not os.path.exists(lib) or not os.path.exists(stamp):
+        return True
+    with open(stamp) as f:
+        return f.read().strip() != digest
+
+
+def _run(cmd: List[str]) -> None:
+    r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if r.returncode != 0:
+        raise RuntimeError("build failed: " + " ".join(cmd) + "\n" + r.stdout)
+
+
+def build_kernels(force: bool = False, verbose: bool = False) -> str:
+    srcs = _sources("kernels", (".cu",))
+    deps = srcs + _sources("kernels", (".cuh", ".h"))
+    digest = _digest(deps, " ".join(NVCC_FLAGS))
+    if not force and not _stale(KERNEL_LIB, digest):
+        return KERNEL_LIB
+    nvcc = os.environ.get("NVCC", "nvcc")
+    objs = []
+    objdir = os.path.join(HERE, "build")
+    os.makedirs(objdir, exist_ok=True)
+    procs = []
+    for s in srcs:
+        o = os.path.join(objdir, os.path.basename(s) + ".o")
+        objs.append(o)
+        cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-c", s, "-o", o]
+        procs.append((cmd, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
+    for cmd, p in procs:
+        out, _ = p.communicate()
+        if verbose:
+            print(out)
+        if p.returncode != 0:
+            raise RuntimeError("build failed: " + " ".join(cmd) + "\n" + out)
+    _run([nvcc, "-shared", "-o", KERNEL_LIB] + objs + ["-lcuda"])
+    with open(KERNEL_LIB + ".stamp", "w") as f:
+        f.write(digest)
+    return KERNEL_LIB
+
+
+def build_ctrl(force: bool = False) -> str:
+    srcs = _sources("ctrl", (".cpp",))
+    if not srcs:
+        return ""
+    deps = srcs + _sources("ctrl", (".hpp", ".h"))
+    flags = ["-O2", "-std=c++17", "-fPIC", "-shared", "-Wall"]
+    digest = _digest(deps, " ".join(flags))
+    if not force and not _stale(CTRL_LIB, digest):
+        return CTRL_LIB
+    _run([os.environ.get("CXX", "g++")] + flags + srcs + ["-o", CTRL_LIB])
+    with open(CTRL_LIB + ".stamp", "w") as f:
+        f.write(digest)
+    return CTRL_LIB
+
+
+def build_all(force: bool = False, verbose: bool = False) -> None:
+    build_kernels(force, verbose)
+    build_ctrl(force)
+
+
+if __name__ == "__main__":
+    build_all(force="--force" in sys.argv, verbose="-v" in sys.argv)
+    print("built", KERNEL_LIB, CTRL_LIB if os.path.exists(CTRL_LIB) else "")

@@ -1,0 +1,181 @@
+"""ctypes bindings of the sm_100a kernel library (``libihb_kernels.so``, built in-tree by :mod:`.build`).
+
+The structures mirror ``csrc/kernels/api.h`` field by field. Launches go to ``torch.cuda.current_stream()`` so
+that they are captured by ``torch.cuda.graph``. The library is required on a GPU machine: a missing or
+unloadable ``.so`` raises instead of falling back to PyTorch ops.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from typing import Optional
+
+import torch
+
+from . import build as _build
+
+MAX_RANKS = 8
+W_FP8, W_BF16 = 0, 1
+EPI_STORE, EPI_ROUTER, EPI_ARGMAX, EPI_AR_NORM = 0, 1, 2, 3
+
+ERR_NAMES = {0: "none", 1: "pipeline full-barrier time-out", 2: "pipeline empty-barrier time-out",
+             3: "peer barrier time-out", 4: "grid counter time-out", 5: "tensor-memory time-out", 6: "bad arguments"}
+
+_vp = C.c_void_p
+
+
+class IhbComm(C.Structure):
+    _fields_ = [("nranks", C.c_int), ("rank", C.c_int),
+                ("slots_local", _vp), ("slots_mc", _vp), ("slots_peer", _vp * MAX_RANKS),
+                ("flag_local", _vp), ("flag_mc", _vp), ("flag_peer", _vp * MAX_RANKS),
+                ("arg_slots_local", _vp), ("arg_slots_mc", _vp), ("arg_slots_peer", _vp * MAX_RANKS),
+                ("epoch", _vp)]
+
+
+class IhbGemvArgs(C.Structure):
+    _fields_ = [("W", _vp), ("wscale", _vp), ("wtype", C.c_int), ("rows", C.c_int), ("K", C.c_int),
+                ("rb", C.c_int), ("kb_shift", C.c_int), ("nkb", C.c_int),
+                ("x", _vp),
+                ("R", C.c_int), ("S", C.c_int), ("grid", C.c_int), ("ks", C.c_int), ("epi", C.c_int),
+                ("out", _vp), ("counter", _vp), ("err", _vp),
+                ("top_k", C.c_int), ("renorm", C.c_int), ("sel_idx", _vp), ("sel_w", _vp),
+                ("argmax_partial", _vp), ("vocab0", C.c_int), ("cur_token", _vp), ("pos", _vp),
+                ("token_ring", _vp), ("token_ring_size", C.c_int), ("forced", _vp), ("n_forced", _vp),
+                ("resid", _vp), ("gamma", _vp), ("xn_out", _vp), ("eps", C.c_float),
+                ("comm", IhbComm)]
+
+
+class IhbMoeArgs(C.Structure):
+    _fields_ = [("Wgu", _vp), ("gu_scale", _vp), ("Wd", _vp), ("d_scale", _vp), ("wtype", C.c_int),
+                ("H", C.c_int), ("I", C.c_int), ("E_local", C.c_int), ("expert0", C.c_int), ("top_k", C.c_int),
+                ("gu_rb", C.c_int), ("gu_kb_shift", C.c_int), ("gu_nkb", C.c_int),
+                ("d_rb", C.c_int), ("d_kb_shift", C.c_int), ("d_nkb", C.c_int),
+                ("x", _vp), ("sel_idx", _vp), ("sel_w", _vp), ("act", _vp),
+                ("R_gu", C.c_int), ("R_d", C.c_int), ("S", C.c_int), ("grid", C.c_int),
+                ("counter", _vp), ("err", _vp),
+                ("resid", _vp), ("gamma", _vp), ("xn_out", _vp), ("eps", C.c_float),
+                ("comm", IhbComm)]
+
+
+_lib: Optional[C.CDLL] = None
+
+
+def load(build_if_missing: bool = True) -> C.CDLL:
+    """Load (building first if the sources changed and nvcc is present) the kernel library."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    path = _build.KERNEL_LIB
+    if build_if_missing:
+        try:
+            _build.build_kernels()
+        except Exception:
+            if not os.path.exists(path):
+                raise
+    if not os.path.exists(path):
+        raise RuntimeError(f"kernel library {path} is missing: run `python -m inferencehackathon_b200.ops.build`")
+    lib = C.CDLL(path)
+    lib.ihb_gemv.argtypes = [C.POINTER(IhbGemvArgs), C.c_int, _vp]
+    lib.ihb_moe_gateup.argtypes = [C.POINTER(IhbMoeArgs), C.c_int, _vp]
+    lib.ihb_moe_down.argtypes = [C.POINTER(IhbMoeArgs), C.c_int, _vp]
+    lib.ihb_embed_norm.argtypes = [_vp, C.c_int, _vp, C.c_int, _vp, C.c_float, _vp, _vp, C.c_int, _vp]
+    lib.ihb_qk_norm_rope_kv.argtypes = [_vp, C.c_int, C.c_int, _vp, _vp, C.c_float, _vp, _vp, _vp, _vp, _vp,
+                                        C.c_int, C.c_int, _vp]
+    lib.ihb_flash_decode.argtypes = [_vp, _vp, _vp, C.c_int, C.c_int, C.c_int, _vp, C.c_int, _vp, _vp, _vp,
+                                     C.c_int, _vp]
+    lib.ihb_flash_decode_scratch_floats.argtypes = [C.c_int, C.c_int]
+    lib.ihb_flash_decode_scratch_floats.restype = C.c_size_t
+    for name in ("ihb_gemv", "ihb_moe_gateup", "ihb_moe_down", "ihb_embed_norm", "ihb_qk_norm_rope_kv",
+                 "ihb_flash_decode"):
+        getattr(lib, name).restype = C.c_int
+    _lib = lib
+    return lib
+
+
+def available() -> bool:
+    return os.path.exists(_build.KERNEL_LIB)
+
+
+def stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def check(code: int, what: str) -> None:
+    if code != 0:
+        raise RuntimeError(f"{what}: CUDA error {code}")
+
+
+def ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def wtype_of(t: torch.Tensor) -> int:
+    if t.dtype == torch.float8_e4m3fn:
+        return W_FP8
+    if t.dtype == torch.bfloat16:
+        return W_BF16
+    raise TypeError(f"kernel weights must be float8_e4m3fn or bfloat16, got {t.dtype}")
+
+
+def kb_shift_of(kb: int) -> int:
+    s = kb.bit_length() - 1
+    if (1 << s) != kb or kb < 16:
+        raise ValueError("scale block width must be a power of two >= 16")
+    return s
+
+
+def single_comm(slots: torch.Tensor, epoch: torch.Tensor) -> IhbComm:
+    """Comm block for one GPU: the partial lands in a local slot buffer and the tail only adds the residual."""
+    cm = IhbComm()
+    cm.nranks, cm.rank = 1, 0
+    cm.slots_local = slots.data_ptr()
+    cm.epoch = epoch.data_ptr()
+    return cm
+
+
+def fill_weight(args, qw, prefix: str = "") -> None:
+    """Set the weight fields of a GEMV argument block from a QWeight."""
+    args.W = qw.data.data_ptr()
+    args.wtype = wtype_of(qw.data)
+    args.rows, args.K = qw.data.shape[-2], qw.data.shape[-1]
+    if qw.scale is not None:
+        args.wscale = qw.scale.data_ptr()
+        args.rb, args.kb_shift, args.nkb = qw.rb, kb_shift_of(qw.kb), qw.scale.shape[-1]
+
+
+def gemv(args: IhbGemvArgs, use_pdl: bool = False) -> None:
+    check(load().ihb_gemv(C.byref(args), int(use_pdl), stream_ptr()), "ihb_gemv")
+
+
+def moe_gateup(args: IhbMoeArgs, use_pdl: bool = False) -> None:
+    check(load().ihb_moe_gateup(C.byref(args), int(use_pdl), stream_ptr()), "ihb_moe_gateup")
+
+
+def moe_down(args: IhbMoeArgs, use_pdl: bool = False) -> None:
+    check(load().ihb_moe_down(C.byref(args), int(use_pdl), stream_ptr()), "ihb_moe_down")
+
+
+def embed_norm(embed: torch.Tensor, token: torch.Tensor, gamma: torch.Tensor, eps: float, resid: torch.Tensor,
+               xn: torch.Tensor, use_pdl: bool = False) -> None:
+    check(load().ihb_embed_norm(embed.data_ptr(), int(embed.dtype == torch.bfloat16), token.data_ptr(),
+                                embed.shape[1], gamma.data_ptr(), eps, resid.data_ptr(), xn.data_ptr(),
+                                int(use_pdl), stream_ptr()), "ihb_embed_norm")
+
+
+def qk_norm_rope_kv(qkv: torch.Tensor, nq: int, nkv: int, q_gamma, k_gamma, eps: float, cos_t, sin_t, pos,
+                    k_cache, v_cache, max_seq: int, use_pdl: bool = False) -> None:
+    check(load().ihb_qk_norm_rope_kv(qkv.data_ptr(), nq, nkv, q_gamma.data_ptr(), k_gamma.data_ptr(), eps,
+                                     cos_t.data_ptr(), sin_t.data_ptr(), pos.data_ptr(), k_cache.data_ptr(),
+                                     v_cache.data_ptr(), max_seq, int(use_pdl), stream_ptr()),
+          "ihb_qk_norm_rope_kv")
+
+
+def flash_decode_scratch_floats(nq: int, nsplit: int) -> int:
+    return int(load().ihb_flash_decode_scratch_floats(nq, nsplit))
+
+
+def flash_decode(q, k_cache, v_cache, nq: int, nkv: int, max_seq: int, pos, nsplit: int, scratch, counters, out,
+                 use_pdl: bool = False) -> None:
+    check(load().ihb_flash_decode(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), nq, nkv, max_seq,
+                                  pos.data_ptr(), nsplit, scratch.data_ptr(), counters.data_ptr(), out.data_ptr(),
+                                  int(use_pdl), stream_ptr()), "ihb_flash_decode")

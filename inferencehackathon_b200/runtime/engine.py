@@ -158,13 +158,14 @@ class InferenceEngine:
             tok = t[0]
         return int(tok), (logits if return_logits else None)
 
-    def decode_step(self, token: Optional[int] = None, return_logits: bool = False) -> StepOutput:
+    def decode_step(self, token: Optional[int] = None, return_logits: bool = False,
+                    want_routes: bool = True) -> StepOutput:
         """Feed one token (default: the previously generated one) and produce the next."""
         tok = self._last_token if token is None else token
         if tok is None:
             raise RuntimeError("decode_step before prefill")
         if self.gpu is not None:
-            out_tok, seconds, routes = self.gpu.decode_step(tok, self.sampler)
+            out_tok, seconds, routes = self.gpu.decode_step(tok, self.sampler, want_routes=want_routes)
         else:
             t = torch.tensor([tok], dtype=torch.long, device=self.device)
             self._timer.start()

@@ -1,0 +1,284 @@
+"""Decode pipeline on the sm_100a kernels: seven launches per layer, the whole token under one CUDA graph.
+
+Per layer: QKV GEMV -> QK-norm/RoPE/KV append -> split-KV flash decode -> o_proj GEMV fused with the
+all-reduce, residual add and post-attention RMSNorm -> router GEMV with softmax/top-k tail -> expert gate/up
+SwiGLU -> expert down projection fused with the all-reduce, residual add and the next layer's input RMSNorm.
+The head GEMV ends with the argmax, writes the next token and advances the position counter on the device, so a
+replayed graph needs no host input (the reference's graph replays a fixed dummy state,
+kernels/k6_graph_capture.cu:33-64; its eager path issues ~1100 launches per token,
+kernels/decode_step_tp8.cu:1193-1195).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from typing import List, Optional
+
+import torch
+
+from ..config import EngineConfig, env_flag
+from ..models.qwen3_moe import RouteRecord, rope_tables
+from ..models.weights import ModelWeights
+from ..ops import lib as K
+
+
+def _pick_ks(Kdim: int, celems: int) -> int:
+    ks = 1
+    while Kdim // ks // celems > 256 and ks < 8:
+        ks *= 2
+    return ks
+
+
+class GpuDecoder:
+    def __init__(self, cfg: EngineConfig, weights: ModelWeights, comm, device: torch.device):
+        if device.type != "cuda":
+            raise RuntimeError("the sm_100a decode path needs a CUDA device")
+        K.load()
+        self.cfg, self.w, self.device = cfg, weights, device
+        m, g = cfg.model, weights.geom
+        if m.head_dim != 128:
+            raise ValueError("the CUDA attention kernels are built for head_dim 128")
+        if weights.quant.weights not in ("bf16", "fp8_block"):
+            raise ValueError("the CUDA path stores weights as bf16 or block-scaled fp8")
+        self.H, self.nq, self.nkv, self.I = m.hidden, g.nq_local, g.nkv_local, g.inter_local
+        self.max_seq = cfg.max_seq
+        self.use_pdl = bool(env_flag("IHB_PDL", 1))
+        self.use_graph = cfg.use_graph and bool(env_flag("IHB_GRAPH", 1))
+        self.comm_ref = comm
+        self.n_launches_per_step = 0
+        dev = device
+        f32 = dict(dtype=torch.float32, device=dev)
+        i32 = dict(dtype=torch.int32, device=dev)
+        L = m.n_layers
+        self.resid = torch.zeros(self.H, **f32)
+        self.xn = torch.zeros(self.H, **f32)
+        self.qkv = torch.zeros((self.nq + 2 * self.nkv) * 128, **f32)
+        self.attn = torch.zeros(self.nq * 128, **f32)
+        self.act = torch.zeros(m.top_k * self.I, **f32)
+        self.router_logits = torch.zeros(L, m.n_experts, **f32)
+        self.sel_idx = torch.zeros(L, m.top_k, **i32)
+        self.sel_w = torch.zeros(L, m.top_k, **f32)
+        self.cur_token = torch.zeros(1, **i32)
+        self.pos = torch.zeros(1, **i32)
+        self.n_forced = torch.zeros(1, **i32)
+        self.forced = torch.zeros(self.max_seq + 1, **i32)
+        self.token_ring = torch.zeros(self.max_seq + 1, **i32)
+        self.counters = torch.zeros(8 + self.nq, dtype=torch.int32, device=dev)
+        self.err = torch.zeros(1, **i32)
+        self.epoch = torch.zeros(1, **i32)
+        self.argmax_partial = torch.zeros(1024, dtype=torch.int64, device=dev)
+        self.logits = torch.zeros(max(g.vocab_local, 1), **f32)
+        kv_shape = (L, self.nkv, self.max_seq, 128)
+        self.k_cache = torch.zeros(kv_shape, dtype=torch.bfloat16, device=dev)
+        self.v_cache = torch.zeros(kv_shape, dtype=torch.bfloat16, device=dev)
+        cos, sin = rope_tables(torch.arange(self.max_seq, device=dev), 128, m.rope_theta)
+        self.cos, self.sin = cos.contiguous(), sin.contiguous()
+        q_per_kv = self.nq // self.nkv
+        ngroups = max(1, q_per_kv // 8)
+        sms = torch.cuda.get_device_properties(dev).multi_processor_count
+        want = max(1, (2 * sms) // (self.nkv * ngroups))
+        self.nsplit = env_flag("IHB_FD_SPLITS", max(1, min((self.max_seq + 127) // 128, want)))
+        self.fd_scratch = torch.zeros(K.flash_decode_scratch_floats(self.nq, self.nsplit), **f32)
+        celems = 16 if weights.quant.weights == "fp8_block" else 8
+        self.ks_o = _pick_ks(self.nq * 128, celems)
+        self._setup_comm()
+        self._build_args()
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self._ev0 = torch.cuda.Event(enable_timing=True)
+        self._ev1 = torch.cuda.Event(enable_timing=True)
+        # pinned staging for the per-step host<->device traffic of the public decode_step API
+        self._tok_in = torch.zeros(1, dtype=torch.int32).pin_memory()
+        self._tok_out = torch.zeros(1, dtype=torch.int32).pin_memory()
+        self.h2d_bytes_per_step = self._tok_in.numel() * 4
+        self.d2h_bytes_per_step = self._tok_out.numel() * 4
+
+    # communication block -------------------------------------------------------------------------------------
+    def _setup_comm(self) -> None:
+        par = self.cfg.parallel
+        nslots = 2 * max(par.tp, 1) * max(self.ks_o, 1) * self.H
+        if par.world == 1:
+            self.slots = torch.zeros(nslots, dtype=torch.float32, device=self.device)
+            self.symm = None
+        else:
+            from ..parallel.symm import SymmetricComm
+            self.symm = SymmetricComm(par, self.device, slot_floats=nslots)
+            self.slots = self.symm.slots_local
+
+    def _comm(self) -> K.IhbComm:
+        if self.symm is None:
+            return K.single_comm(self.slots, self.epoch)
+        return self.symm.comm_block(self.epoch)
+
+    # argument blocks -----------------------------------------------------------------------------------------
+    def _gemv_args(self, qw, x, epi, **kw) -> K.IhbGemvArgs:
+        a = K.IhbGemvArgs()
+        K.fill_weight(a, qw)
+        a.x = x.data_ptr()
+        a.epi = epi
+        a.ks = kw.pop("ks", 1)
+        a.err = self.err.data_ptr()
+        a.counter = kw.pop("counter").data_ptr() if "counter" in kw else None
+        for k, v in kw.items():
+            setattr(a, k, v.data_ptr() if isinstance(v, torch.Tensor) else v)
+        return a
+
+    def _build_args(self) -> None:
+        m, w = self.cfg.model, self.w
+        from ..models.quant import QWeight
+        self.layer_args = []
+        ctr = self.counters
+        for L, lw in enumerate(w.layers):
+            nxt_gamma = w.layers[L + 1].in_ln if L + 1 < len(w.layers) else w.final_norm
+            qkv = self._gemv_args(lw.wqkv, self.xn, K.EPI_STORE, out=self.qkv)
+            oproj = self._gemv_args(lw.wo, self.attn, K.EPI_AR_NORM, ks=self.ks_o, counter=ctr[0:1],
+                                    resid=self.resid, gamma=lw.post_ln, xn_out=self.xn, eps=m.rms_eps)
+            oproj.comm = self._comm()
+            router = self._gemv_args(QWeight(lw.router), self.xn, K.EPI_ROUTER, counter=ctr[1:2],
+                                     out=self.router_logits[L], top_k=m.top_k, renorm=int(m.norm_topk_prob),
+                                     sel_idx=self.sel_idx[L], sel_w=self.sel_w[L])
+            moe = K.IhbMoeArgs()
+            moe.Wgu, moe.Wd = lw.w_gu.data.data_ptr(), lw.w_d.data.data_ptr()
+            moe.wtype = K.wtype_of(lw.w_gu.data)
+            moe.H, moe.I, moe.E_local = self.H, self.I, lw.w_gu.data.shape[0]
+            moe.expert0, moe.top_k = w.geom.expert0, m.top_k
+            if lw.w_gu.scale is not None:
+                moe.gu_scale, moe.d_scale = lw.w_gu.scale.data_ptr(), lw.w_d.scale.data_ptr()
+                moe.gu_rb, moe.gu_kb_shift, moe.gu_nkb = lw.w_gu.rb, K.kb_shift_of(lw.w_gu.kb), lw.w_gu.scale.shape[-1]
+                moe.d_rb, moe.d_kb_shift, moe.d_nkb = lw.w_d.rb, K.kb_shift_of(lw.w_d.kb), lw.w_d.scale.shape[-1]
+            moe.x, moe.act = self.xn.data_ptr(), self.act.data_ptr()
+            moe.sel_idx, moe.sel_w = self.sel_idx[L].data_ptr(), self.sel_w[L].data_ptr()
+            moe.counter, moe.err = ctr[2:3].data_ptr(), self.err.data_ptr()
+            moe.resid, moe.gamma, moe.xn_out, moe.eps = (self.resid.data_ptr(), nxt_gamma.data_ptr(),
+                                                         self.xn.data_ptr(), m.rms_eps)
+            moe.comm = self._comm()
+            self.layer_args.append((qkv, oproj, router, moe, lw))
+        self.head = self._gemv_args(w.lm_head, self.xn, K.EPI_ARGMAX, counter=ctr[3:4], out=self.logits,
+                                    argmax_partial=self.argmax_partial, vocab0=w.geom.vocab0,
+                                    cur_token=self.cur_token, pos=self.pos, token_ring=self.token_ring,
+                                    token_ring_size=self.token_ring.numel(), forced=self.forced,
+                                    n_forced=self.n_forced)
+        self.head.comm = self._comm()
+
+    # one token -------------------------------------------------------------------------------------------------
+    def _enqueue_step(self) -> None:
+        m, w, pdl = self.cfg.model, self.w, self.use_pdl
+        n = 0
+        K.embed_norm(w.embed, self.cur_token, w.layers[0].in_ln, m.rms_eps, self.resid, self.xn, False)
+        n += 1
+        fd_ctr = self.counters[8:]
+        for L, (qkv, oproj, router, moe, lw) in enumerate(self.layer_args):
+            K.gemv(qkv, pdl)
+            K.qk_norm_rope_kv(self.qkv, self.nq, self.nkv, lw.q_norm, lw.k_norm, m.rms_eps, self.cos, self.sin,
+                              self.pos, self.k_cache[L], self.v_cache[L], self.max_seq, pdl)
+            K.flash_decode(self.qkv, self.k_cache[L], self.v_cache[L], self.nq, self.nkv, self.max_seq, self.pos,
+                           self.nsplit, self.fd_scratch, fd_ctr, self.attn, pdl)
+            K.gemv(oproj, pdl)
+            K.gemv(router, pdl)
+            K.moe_gateup(moe, pdl)
+            K.moe_down(moe, pdl)
+            n += 7
+        K.gemv(self.head, pdl)
+        self.n_launches_per_step = n + 1
+
+    def _step(self) -> None:
+        if not self.use_graph:
+            self._enqueue_step()
+            return
+        if self.graph is None:
+            # warm up on a side stream (lazy module loading, attribute calls) and restore the state it advanced
+            state = (self.pos.clone(), self.cur_token.clone(), self.epoch.clone())
+            s = torch.cuda.Stream(device=self.device)
+            s.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(s):
+                self._enqueue_step()
+            torch.cuda.current_stream().wait_stream(s)
+            torch.cuda.synchronize()
+            self.pos.copy_(state[0]); self.cur_token.copy_(state[1]); self.epoch.copy_(state[2])
+            if self.symm is not None:
+                self.symm.barrier_host()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self._enqueue_step()
+            self.pos.copy_(state[0]); self.cur_token.copy_(state[1]); self.epoch.copy_(state[2])
+            self.graph = g
+        self.graph.replay()
+
+    # public ------------------------------------------------------------------------------------------------------
+    @property
+    def seq_len(self) -> int:
+        return int(self.pos.item())
+
+    def reset(self) -> None:
+        self.pos.zero_()
+        self.n_forced.zero_()
+        self.cur_token.zero_()
+
+    def rollback(self, seq_len: int) -> None:
+        self.pos.fill_(seq_len)
+
+    def check_error(self) -> None:
+        code = int(self.err.item())
+        if code:
+            self.err.zero_()
+            raise RuntimeError(f"device-side wait gave up: {K.ERR_NAMES.get(code, code)}")
+
+    def prefill(self, toks: torch.Tensor, sampler, return_logits: bool):
+        """Prompt processing by replaying the decode step once per prompt token with forced inputs (the
+        tensor-core prefill path replaces this for long prompts)."""
+        T = toks.shape[0]
+        if self.seq_len + T > self.max_seq:
+            raise ValueError("KV cache overflow")
+        start = self.seq_len
+        self.forced[start:start + T] = toks.to(torch.int32)
+        self.n_forced.fill_(start + T)
+        self.cur_token.copy_(self.forced[start:start + 1])
+        for _ in range(T):
+            self._step()
+        self.check_error()
+        nxt = int(self.cur_token.item())
+        logits = None
+        if return_logits or not sampler.params.greedy:
+            logits = self._full_logits()[None]
+            if not sampler.params.greedy:
+                nxt = int(sampler.sample(logits[0]))
+                self.cur_token.fill_(nxt)
+        return nxt, logits
+
+    def _full_logits(self) -> torch.Tensor:
+        local = self.logits[: self.w.geom.vocab_local].clone()
+        if self.cfg.parallel.world == 1:
+            return local
+        return self.comm_ref.gather_logits(local[None], self.cfg.model.vocab, self.w.geom.vocab_chunk)[0]
+
+    def decode_step(self, tok: int, sampler, timed: bool = True, want_routes: bool = True):
+        """One token through the public path: the input token goes host->device from pinned memory, the step
+        runs (graph replay), the produced token comes back device->host."""
+        self._tok_in[0] = tok
+        self._ev0.record()
+        self.cur_token.copy_(self._tok_in, non_blocking=True)
+        self._step()
+        self._tok_out.copy_(self.cur_token, non_blocking=True)
+        self._ev1.record()
+        self._ev1.synchronize()
+        seconds = self._ev0.elapsed_time(self._ev1) * 1e-3
+        out = int(self._tok_out[0])
+        if not sampler.params.greedy:
+            out = int(sampler.sample(self._full_logits()))
+            self.cur_token.fill_(out)
+        routes = self.last_routes() if want_routes else []
+        return out, seconds, routes
+
+    def _peek_token(self) -> int:
+        return int(self.cur_token.item())
+
+    def last_routes(self) -> List[RouteRecord]:
+        idx, w = self.sel_idx.cpu(), self.sel_w.cpu()
+        return [RouteRecord(L, idx[L].tolist(), w[L].tolist()) for L in range(idx.shape[0])]
+
+    def run_steps(self, n: int) -> None:
+        """Enqueue ``n`` decode steps without any host synchronisation (benchmark loop)."""
+        for _ in range(n):
+            self._step()
+
+    def logits_for(self, tokens, commit=True, tree_mask=None, positions=None):
+        raise NotImplementedError("window logits on the CUDA path come from the speculative verifier")
