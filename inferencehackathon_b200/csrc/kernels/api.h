@@ -116,6 +116,39 @@ int ihb_flash_decode(const float* q, const void* k_cache, const void* v_cache, i
                      cudaStream_t stream);
 size_t ihb_flash_decode_scratch_floats(int nq, int nsplit);
 
+// ---- tensor-core linear layers (tcgen05 / TMEM / TMA) ------------------------------------------------------------
+enum { IHB_TC_LINEAR = 0, IHB_TC_GATEUP = 1, IHB_TC_DOWN = 2 };
+
+// Y[t, r] = sum_k X[t, k] W[r, k] for T <= 128 tokens per call.
+//   LINEAR: W [rows, K];            X [T_total, K];          out [T, out_stride] fp32
+//   GATEUP: W [E][2][rows = I][K];  X [T_total, K];          out [top_k][T][I] = silu(gate) * up
+//   DOWN:   W [E][rows = H][K = I]; X [top_k][T_total][K];   out [T, out_stride] = sum over slots of w_slot * (...)
+// fp8: wscale [E][nrb][nkb_stride] (row blocks of rb rows, K blocks of 128), xscale [slots][nkb][T_total].
+typedef struct {
+  const void* W;
+  const float* wscale;
+  int wtype;               // IHB_W_FP8 | IHB_W_BF16 (activations have the same type)
+  int rows, K;
+  int rb, nrb, nkb_stride;
+  int n_experts, expert0, top_k;
+  const void* X;
+  const float* xscale;
+  int T, T_total, tok0;    // tokens in this call, rows of X, first token of this call
+  int mode;
+  const int* sel_idx;      // [top_k] global expert ids (GATEUP / DOWN)
+  const float* sel_w;      // [top_k]
+  float* out;
+  int out_stride;
+  float* partial;          // workspace of ihb_tc_partial_floats() floats when several units feed a tile
+  unsigned* tile_counters; // one per output tile, zero before the first launch
+  int ks, S, grid;         // K split / stages / CTAs (0 = choose)
+  int n_units;             // filled in by the launcher
+  unsigned* err;
+} IhbTcArgs;
+
+int ihb_tc_gemm(IhbTcArgs* args, int use_pdl, cudaStream_t stream);
+size_t ihb_tc_partial_floats(const IhbTcArgs* args);
+
 #ifdef __cplusplus
 }
 #endif

@@ -23,13 +23,18 @@ __global__ void __launch_bounds__(256) embed_norm_kernel(const void* __restrict_
   pdl_launch_dependents();
   const int tok = ld_cg_i(token);
   const int tid = threadIdx.x;
+  constexpr int MAXP = 32;                 // H <= 8192
+  float v[MAXP];
   float ss = 0.f;
-  for (int i = tid; i < H; i += 256) {
-    float v;
-    if (is_bf16) v = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(embed)[static_cast<size_t>(tok) * H + i]);
-    else v = reinterpret_cast<const float*>(embed)[static_cast<size_t>(tok) * H + i];
-    resid[i] = v;
-    ss += v * v;
+#pragma unroll
+  for (int j = 0; j < MAXP; ++j) {
+    const int i = tid + 256 * j;
+    v[j] = 0.f;
+    if (i < H) {
+      if (is_bf16) v[j] = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(embed)[static_cast<size_t>(tok) * H + i]);
+      else v[j] = reinterpret_cast<const float*>(embed)[static_cast<size_t>(tok) * H + i];
+    }
+    ss += v[j] * v[j];
   }
   ss = warp_sum(ss);
   if ((tid & 31) == 0) red[tid >> 5] = ss;
@@ -38,7 +43,14 @@ __global__ void __launch_bounds__(256) embed_norm_kernel(const void* __restrict_
 #pragma unroll
   for (int w = 0; w < 8; ++w) tot += red[w];
   const float rinv = rsqrtf(tot / static_cast<float>(H) + eps);
-  for (int i = tid; i < H; i += 256) xn[i] = resid[i] * rinv * gamma[i];
+#pragma unroll
+  for (int j = 0; j < MAXP; ++j) {
+    const int i = tid + 256 * j;
+    if (i < H) {
+      resid[i] = v[j];
+      xn[i] = v[j] * rinv * gamma[i];
+    }
+  }
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
@@ -147,9 +159,12 @@ __global__ void __launch_bounds__(FD_WARPS * 32) flash_decode_kernel(
     for (int g = 0; g < GQ; ++g) s[g] = 0.f;
     if (valid) {
       const uint4* kr = reinterpret_cast<const uint4*>(kbase + static_cast<size_t>(p) * HD);
-#pragma unroll 4
+      uint4 kreg[HD / 8];
+#pragma unroll
+      for (int c = 0; c < HD / 8; ++c) kreg[c] = kr[c];      // all 16 loads in flight before the first FMA
+#pragma unroll
       for (int c = 0; c < HD / 8; ++c) {
-        const uint4 kv = kr[c];
+        const uint4 kv = kreg[c];
         float kf[8];
         kf[0] = __uint_as_float(kv.x << 16); kf[1] = __uint_as_float(kv.x & 0xffff0000u);
         kf[2] = __uint_as_float(kv.y << 16); kf[3] = __uint_as_float(kv.y & 0xffff0000u);
@@ -179,15 +194,23 @@ __global__ void __launch_bounds__(FD_WARPS * 32) flash_decode_kernel(
     }
     __syncwarp();
     const int cnt = min(32, n - base);
-    for (int j = 0; j < cnt; ++j) {
-      const uint2 vv = *reinterpret_cast<const uint2*>(vbase + static_cast<size_t>(base + j) * HD + lane * 4);
-      const float v0 = __uint_as_float(vv.x << 16), v1 = __uint_as_float(vv.x & 0xffff0000u);
-      const float v2 = __uint_as_float(vv.y << 16), v3 = __uint_as_float(vv.y & 0xffff0000u);
+    for (int j0 = 0; j0 < cnt; j0 += 8) {
+      uint2 vreg[8];
 #pragma unroll
-      for (int g = 0; g < GQ; ++g) {
-        const float pj = p_s[warp][g][j];
-        acc[g][0] = fmaf(pj, v0, acc[g][0]); acc[g][1] = fmaf(pj, v1, acc[g][1]);
-        acc[g][2] = fmaf(pj, v2, acc[g][2]); acc[g][3] = fmaf(pj, v3, acc[g][3]);
+      for (int u = 0; u < 8; ++u) {
+        const int jj = min(j0 + u, cnt - 1);               // rows past the end repeat the last row; their p is 0
+        vreg[u] = *reinterpret_cast<const uint2*>(vbase + static_cast<size_t>(base + jj) * HD + lane * 4);
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const float v0 = __uint_as_float(vreg[u].x << 16), v1 = __uint_as_float(vreg[u].x & 0xffff0000u);
+        const float v2 = __uint_as_float(vreg[u].y << 16), v3 = __uint_as_float(vreg[u].y & 0xffff0000u);
+#pragma unroll
+        for (int g = 0; g < GQ; ++g) {
+          const float pj = p_s[warp][g][j0 + u];
+          acc[g][0] = fmaf(pj, v0, acc[g][0]); acc[g][1] = fmaf(pj, v1, acc[g][1]);
+          acc[g][2] = fmaf(pj, v2, acc[g][2]); acc[g][3] = fmaf(pj, v3, acc[g][3]);
+        }
       }
     }
     __syncwarp();
@@ -234,8 +257,10 @@ __global__ void __launch_bounds__(FD_WARPS * 32) flash_decode_kernel(
     const int g = i / HD, d = i % HD;
     const float* recs = scratch + static_cast<size_t>(head0 + g) * nsplit * FD_REC;
     float M = -INFINITY;
+#pragma unroll 8
     for (int sp = 0; sp < nsplit; ++sp) M = fmaxf(M, ld_cg_f(recs + sp * FD_REC + HD));
     float a = 0.f, L = 0.f;
+#pragma unroll 8
     for (int sp = 0; sp < nsplit; ++sp) {
       const float ms = ld_cg_f(recs + sp * FD_REC + HD);
       if (ms > -INFINITY) {

@@ -161,16 +161,14 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) gemv_kernel(const IhbGemvAr
       uint8_t* dst = ring.stages + static_cast<size_t>(st) * stage_stride;
       const uint32_t bytes = static_cast<uint32_t>(nrows) * row_bytes;
       if (lane == 0) {
-        mbar_expect_tx(&ring.full[st], bytes);
+        // weights and (fp8) the row block's scale row both arrive by bulk copy: the producer never waits on a load
+        const uint32_t sbytes = (WT == 0) ? static_cast<uint32_t>(a.nkb) * 4u : 0u;
+        mbar_arrive_expect_tx(&ring.full[st], bytes + sbytes);
         bulk_g2s(dst, a.W + static_cast<size_t>(row0) * row_bytes, bytes, &ring.full[st]);
+        if (WT == 0)
+          bulk_g2s(dst + stage_stride - 256, a.wscale + static_cast<size_t>(row0 / a.rb) * a.nkb, sbytes,
+                   &ring.full[st]);
       }
-      if (WT == 0) {
-        float* sc = reinterpret_cast<float*>(dst + stage_stride - 256);
-        const float* src = a.wscale + static_cast<size_t>(row0 / a.rb) * a.nkb;
-        for (int j = lane; j < a.nkb; j += 32) sc[j] = src[j];
-      }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&ring.full[st]);
     }
     // Error path: a wait above ran out after IHB_LOCAL_WAIT_NS, far longer than any copy takes, so nothing
     // issued by this warp is still in flight when it leaves.
@@ -311,7 +309,7 @@ extern "C" int ihb_gemv(IhbGemvArgs* args, int use_pdl, cudaStream_t stream) {
   const int ni = (nchunks + 31) / 32;
   if (ni > 16) return cudaErrorInvalidValue;
   if (a.wtype == IHB_W_FP8) {
-    if (a.kb_shift < 4 || a.nkb > 64 || a.rb <= 0) return cudaErrorInvalidValue;
+    if (a.kb_shift < 4 || a.nkb > 64 || (a.nkb & 3) || a.rb <= 0) return cudaErrorInvalidValue;   // scale rows: 16-byte multiples
   }
   const int row_bytes = a.K * esize;
   int sms = 148;

@@ -45,6 +45,11 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) moe_gateup_kernel(const Ihb
 
   if (warp == NCW) {
     pdl_wait();   // expert ids come from the router kernel
+    int my_e = 0;                              // lane s holds the local expert index of routing slot s
+    if (lane < a.top_k) {
+      my_e = ld_cg_i(a.sel_idx + lane) - a.expert0;
+      if (my_e < 0 || my_e >= a.E_local) my_e = 0;   // not held here (expert parallel): rows are read but ignored
+    }
     for (int it = 0; it < my_tiles && ok; ++it) {
       const int tile = blockIdx.x + it * gridDim.x;
       const int st = it % a.S;
@@ -53,29 +58,24 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) moe_gateup_kernel(const Ihb
       if (!ok) break;
       const int s = tile / tiles_per_slot;
       const int j0 = (tile % tiles_per_slot) * R;
-      int e = ld_cg_i(a.sel_idx + s) - a.expert0;
-      if (e < 0 || e >= a.E_local) e = 0;     // not held here (expert parallel): rows are read but ignored
+      const int e = __shfl_sync(0xffffffffu, my_e, s);
       uint8_t* dst = ring.stages + static_cast<size_t>(st) * stage_stride;
       const uint8_t* wg = a.Wgu + e * expert_bytes + static_cast<size_t>(j0) * row_bytes;
       const uint8_t* wu = wg + static_cast<size_t>(a.I) * row_bytes;
       const uint32_t bytes = static_cast<uint32_t>(R) * row_bytes;
       if (lane == 0) {
-        mbar_expect_tx(&ring.full[st], 2 * bytes);
+        const uint32_t sbytes = (WT == 0) ? static_cast<uint32_t>(a.gu_nkb) * 4u : 0u;
+        mbar_arrive_expect_tx(&ring.full[st], 2 * (bytes + sbytes));
         bulk_g2s(dst, wg, bytes, &ring.full[st]);
         bulk_g2s(dst + bytes, wu, bytes, &ring.full[st]);
-      }
-      if (WT == 0) {
-        float* sc = reinterpret_cast<float*>(dst + stage_stride - 512);
-        const float* base = a.gu_scale + static_cast<size_t>(e) * gu_nrb * a.gu_nkb;
-        const float* sg = base + static_cast<size_t>(j0 / a.gu_rb) * a.gu_nkb;
-        const float* su = base + static_cast<size_t>((a.I + j0) / a.gu_rb) * a.gu_nkb;
-        for (int j = lane; j < a.gu_nkb; j += 32) {
-          sc[j] = sg[j];
-          sc[64 + j] = su[j];
+        if (WT == 0) {
+          const float* base = a.gu_scale + static_cast<size_t>(e) * gu_nrb * a.gu_nkb;
+          bulk_g2s(dst + stage_stride - 512, base + static_cast<size_t>(j0 / a.gu_rb) * a.gu_nkb, sbytes,
+                   &ring.full[st]);
+          bulk_g2s(dst + stage_stride - 256, base + static_cast<size_t>((a.I + j0) / a.gu_rb) * a.gu_nkb, sbytes,
+                   &ring.full[st]);
         }
       }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&ring.full[st]);
     }
     return;
   }
@@ -145,6 +145,11 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) moe_down_kernel(const IhbMo
 
   if (warp == NCW) {
     pdl_wait();   // expert ids: written two kernels back, visible once the previous kernel has passed its own wait
+    int my_e = 0;
+    if (lane < k) {
+      my_e = ld_cg_i(a.sel_idx + lane) - a.expert0;
+      if (my_e < 0 || my_e >= a.E_local) my_e = 0;
+    }
     for (int it = 0; it < my_tiles && ok; ++it) {
       const int tile = blockIdx.x + it * gridDim.x;
       const int st = it % a.S;
@@ -154,25 +159,16 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) moe_down_kernel(const IhbMo
       const int o0 = tile * R;
       uint8_t* dst = ring.stages + static_cast<size_t>(st) * stage_stride;
       const uint32_t bytes = static_cast<uint32_t>(R) * row_bytes;
-      if (lane == 0) mbar_expect_tx(&ring.full[st], k * bytes);
+      const uint32_t sbytes = (WT == 0) ? static_cast<uint32_t>(a.d_nkb) * 4u : 0u;
+      if (lane == 0) mbar_arrive_expect_tx(&ring.full[st], k * (bytes + sbytes));
       __syncwarp();
       if (lane < k) {
-        int e = ld_cg_i(a.sel_idx + lane) - a.expert0;
-        if (e < 0 || e >= a.E_local) e = 0;
-        bulk_g2s(dst + lane * bytes, a.Wd + e * expert_bytes + static_cast<size_t>(o0) * row_bytes, bytes,
+        bulk_g2s(dst + lane * bytes, a.Wd + my_e * expert_bytes + static_cast<size_t>(o0) * row_bytes, bytes,
                  &ring.full[st]);
+        if (WT == 0)
+          bulk_g2s(dst + stage_stride - k * 256 + lane * 256,
+                   a.d_scale + (static_cast<size_t>(my_e) * d_nrb + o0 / a.d_rb) * a.d_nkb, sbytes, &ring.full[st]);
       }
-      if (WT == 0) {
-        float* sc = reinterpret_cast<float*>(dst + stage_stride - k * 256);
-        for (int s = 0; s < k; ++s) {
-          int e = ld_cg_i(a.sel_idx + s) - a.expert0;
-          if (e < 0 || e >= a.E_local) e = 0;
-          const float* src = a.d_scale + (static_cast<size_t>(e) * d_nrb + o0 / a.d_rb) * a.d_nkb;
-          for (int j = lane; j < a.d_nkb; j += 32) sc[s * 64 + j] = src[j];
-        }
-      }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&ring.full[st]);
     }
     return;
   }
@@ -275,7 +271,7 @@ extern "C" int ihb_moe_gateup(IhbMoeArgs* args, int use_pdl, cudaStream_t stream
   if (a.H % celems || a.top_k < 1 || a.top_k > IHB_MAX_TOPK) return cudaErrorInvalidValue;
   const int ni = (a.H / celems + 31) / 32;
   if (ni > 8) return cudaErrorInvalidValue;
-  if (a.wtype == IHB_W_FP8 && (a.gu_nkb > 64 || a.gu_kb_shift < 4)) return cudaErrorInvalidValue;
+  if (a.wtype == IHB_W_FP8 && (a.gu_nkb > 64 || (a.gu_nkb & 3) || a.gu_kb_shift < 4)) return cudaErrorInvalidValue;
   const int row_bytes = a.H * esize;
   const int sms = num_sms();
   if (a.R_gu <= 0) {
@@ -328,7 +324,7 @@ extern "C" int ihb_moe_down(IhbMoeArgs* args, int use_pdl, cudaStream_t stream) 
   const int celems = a.wtype == IHB_W_FP8 ? 16 : 8;
   const int k = a.top_k;
   if (a.I % celems || k < 1 || k > IHB_MAX_TOPK || (NCW % k) != 0) return cudaErrorInvalidValue;
-  if (a.wtype == IHB_W_FP8 && (a.d_nkb > 64 || a.d_kb_shift < 4)) return cudaErrorInvalidValue;
+  if (a.wtype == IHB_W_FP8 && (a.d_nkb > 64 || (a.d_nkb & 3) || a.d_kb_shift < 4)) return cudaErrorInvalidValue;
   const int nchunks = a.I / celems;
   // lanes per row: smallest power of two G with ceil(nchunks / G) <= 4
   int G = 1;

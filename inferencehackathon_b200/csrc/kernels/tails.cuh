@@ -51,16 +51,27 @@ __device__ __forceinline__ void tail_ar_norm(const ArNormTail& a, int tid, float
   }
   const int nslots = cm.nranks * a.ks;
   const float* slots = cm.slots_local + static_cast<size_t>(parity) * nslots * H;
-  float ss = 0.f;
-  for (int i = tid * 4; i < H; i += CONSUMER_THREADS * 4) {
-    float4 acc = *reinterpret_cast<const float4*>(a.resid + i);
-    for (int s = 0; s < nslots; ++s) {
-      const float4 v = ld_cg_f4(reinterpret_cast<const float4*>(slots + static_cast<size_t>(s) * H + i));
-      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
-    }
-    *reinterpret_cast<float4*>(a.resid + i) = acc;
-    ss += acc.x * acc.x + acc.y * acc.y + acc.z * acc.z + acc.w * acc.w;
+  constexpr int MAXV = 8;                       // H <= 8192: at most 8 float4 per thread, kept in registers
+  float4 acc[MAXV];
+#pragma unroll
+  for (int j = 0; j < MAXV; ++j) {
+    const int i = (tid + CONSUMER_THREADS * j) * 4;
+    acc[j] = (i < H) ? *reinterpret_cast<const float4*>(a.resid + i) : make_float4(0.f, 0.f, 0.f, 0.f);
   }
+  for (int s = 0; s < nslots; ++s) {
+#pragma unroll
+    for (int j = 0; j < MAXV; ++j) {
+      const int i = (tid + CONSUMER_THREADS * j) * 4;
+      if (i < H) {
+        const float4 v = ld_cg_f4(reinterpret_cast<const float4*>(slots + static_cast<size_t>(s) * H + i));
+        acc[j].x += v.x; acc[j].y += v.y; acc[j].z += v.z; acc[j].w += v.w;
+      }
+    }
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < MAXV; ++j)
+    ss += acc[j].x * acc[j].x + acc[j].y * acc[j].y + acc[j].z * acc[j].z + acc[j].w * acc[j].w;
   ss = warp_sum(ss);
   if ((tid & 31) == 0) red_smem[tid >> 5] = ss;
   named_bar_sync(1, CONSUMER_THREADS);
@@ -68,12 +79,15 @@ __device__ __forceinline__ void tail_ar_norm(const ArNormTail& a, int tid, float
 #pragma unroll
   for (int w = 0; w < NCW; ++w) tot += red_smem[w];
   const float rinv = rsqrtf(tot / static_cast<float>(H) + a.eps);
-  for (int i = tid * 4; i < H; i += CONSUMER_THREADS * 4) {
-    const float4 v = *reinterpret_cast<const float4*>(a.resid + i);
-    const float4 g = *reinterpret_cast<const float4*>(a.gamma + i);
-    float4 o;
-    o.x = v.x * rinv * g.x; o.y = v.y * rinv * g.y; o.z = v.z * rinv * g.z; o.w = v.w * rinv * g.w;
-    *reinterpret_cast<float4*>(a.xn_out + i) = o;
+#pragma unroll
+  for (int j = 0; j < MAXV; ++j) {
+    const int i = (tid + CONSUMER_THREADS * j) * 4;
+    if (i < H) {
+      const float4 g = *reinterpret_cast<const float4*>(a.gamma + i);
+      *reinterpret_cast<float4*>(a.resid + i) = acc[j];
+      *reinterpret_cast<float4*>(a.xn_out + i) =
+          make_float4(acc[j].x * rinv * g.x, acc[j].y * rinv * g.y, acc[j].z * rinv * g.z, acc[j].w * rinv * g.w);
+    }
   }
   if (tid == 0) *cm.epoch = epoch + 1u;
 }

@@ -1,0 +1,576 @@
+// Tensor-core linear layers for sm_100a: tcgen05.mma with TMEM accumulators, operands staged by TMA.
+//
+//   Y[t, r] = sum_k X[t, k] * W[r, k]        W: block-scaled e4m3 (128-wide K blocks) or bf16, K-major rows
+//                                            X: e4m3 with one scale per token per 128 channels, or bf16
+//
+// The WEIGHT rows are the MMA's M dimension (128 rows per tile = the 128 TMEM lanes) and the TOKENS are N
+// (16..128), so that one kernel serves single-token decode (N padded to 16), speculative verify windows and
+// prefill chunks, and a token count far below 128 wastes nothing but idle tensor-core columns. Per K block of
+// 128 bytes a stage holds a 128x128-byte weight tile and an Nx128-byte activation tile, both written by TMA
+// with the 128-byte swizzle that the shared-memory matrix descriptors name; one thread issues four MMAs
+// (K = 32 bytes each) per stage. For block-scaled fp8 every K block accumulates into its own TMEM buffer (two,
+// ping-pong) and the epilogue warps fold it into fp32 registers with scale_w[row block, k block] *
+// scale_x[token, k block]; bf16 accumulates the whole K range in TMEM.
+//
+// Work units are (row tile, K split[, routing slot]); when several units feed one output tile their partials
+// go through a small fp32 workspace and the last unit to arrive adds them in a fixed order (deterministic).
+//
+// The reference reaches tensor cores only through cuBLASLt calls at M = 16 (kernels/gemm_engine.cuh:48-125)
+// and one mma.sync prefill kernel (kernels/prefill_wgmma.cu:88-262).
+#include <cuda.h>
+#include "common.cuh"
+#include "api.h"
+#include "tails.cuh"
+
+namespace ihb {
+
+constexpr int TC_BM = 128;          // weight rows per tile (TMEM lanes)
+constexpr int TC_BKB = 128;         // bytes of K per stage
+constexpr int TC_THREADS = 192;     // warp 0: TMA, warp 1: MMA + TMEM allocation, warps 2-5: epilogue
+constexpr int TC_A_BYTES = TC_BM * TC_BKB;
+
+// ---- PTX wrappers ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* tm, int x, int y, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
+          smem_u32(dst)),
+      "l"(tm), "r"(smem_u32(bar)), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* tm, int x, int y, int z, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];" ::
+          "r"(smem_u32(dst)),
+      "l"(tm), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* tm, int x, int y, int z, int w,
+                                            uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], "
+      "[%2];" ::"r"(smem_u32(dst)),
+      "l"(tm), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z), "r"(w)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t* smem_dst, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_dst)),
+               "r"(ncols)
+               : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+template <int KIND>   // 0: e4m3 x e4m3, 1: bf16 x bf16; fp32 accumulate
+__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
+  if (KIND == 0) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc)
+        : "memory");
+  }
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* d) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) d[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory matrix descriptor of a K-major tile with 128-byte rows and the 128-byte swizzle: 8-row groups
+// 1024 bytes apart (stride byte offset), descriptor version 1, layout type 2.
+__device__ __forceinline__ uint64_t smem_desc_sw128(const void* tile) {
+  uint64_t d = (static_cast<uint64_t>(smem_u32(tile)) >> 4) & 0x3FFFull;
+  d |= 1ull << 16;                        // leading byte offset: unused for swizzled K-major operands
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;
+  d |= 1ull << 46;
+  d |= 2ull << 61;
+  return d;
+}
+
+// Wait with a time limit that also gives up when another role of this CTA has already failed.
+__device__ __forceinline__ bool tc_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, unsigned* err,
+                                        unsigned code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = globaltimer_ns();
+  unsigned spins = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++spins & 127u) == 0u) {
+      if (*abort_flag) return false;
+      if (globaltimer_ns() - t0 > IHB_LOCAL_WAIT_NS) {
+        *abort_flag = 1;
+        set_error(err, code);
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
+struct TcSmem {
+  uint64_t full[8];
+  uint64_t empty[8];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+  int last_flag;
+  int sel_e[IHB_MAX_TOPK];       // local expert index per routing slot
+  float sel_w[IHB_MAX_TOPK];
+};
+
+struct Unit {
+  int tile;      // output tile index (mode 0: row tile; mode 1: slot * jtiles + jt; mode 2: row tile)
+  int member;    // index of this unit among the units that add into the same tile
+  int row0;      // first weight row of the tile (mode 1: j0 inside the expert's gate block)
+  int slot;      // routing slot (modes 1, 2) else 0
+  int kb0, kb1;  // K blocks [kb0, kb1)
+};
+
+__device__ __forceinline__ Unit decode_unit(const IhbTcArgs& a, int u, int nkb_total) {
+  Unit un;
+  const int s = u % a.ks;
+  int rest = u / a.ks;
+  const int base = nkb_total / a.ks, rem = nkb_total % a.ks;
+  un.kb0 = s * base + min(s, rem);
+  un.kb1 = un.kb0 + base + (s < rem ? 1 : 0);
+  if (a.mode == IHB_TC_LINEAR) {
+    un.tile = rest; un.slot = 0; un.member = s; un.row0 = rest * TC_BM;
+  } else if (a.mode == IHB_TC_GATEUP) {
+    const int jtiles = (a.rows + TC_BM - 1) / TC_BM;      // rows = I
+    un.slot = rest / jtiles;
+    const int jt = rest % jtiles;
+    un.tile = rest; un.member = s; un.row0 = jt * TC_BM;
+  } else {   // DOWN: units ordered (tile, slot, split) so that a tile's members are contiguous
+    un.slot = rest % a.top_k;
+    un.tile = rest / a.top_k;
+    un.member = un.slot * a.ks + s;
+    un.row0 = un.tile * TC_BM;
+  }
+  return un;
+}
+
+// KIND 0 = block-scaled fp8, 1 = bf16. NT = token tile (MMA N). NA = A tiles per stage (2 for gate/up).
+template <int KIND, int NT, int NA>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const IhbTcArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  // 1024-byte alignment for the swizzled tiles
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  TcSmem& sh = *reinterpret_cast<TcSmem*>(smem);
+  const int esize = (KIND == 0) ? 1 : 2;
+  const int nkb_total = (a.K * esize + TC_BKB - 1) / TC_BKB;
+  const int nslot_x = (a.mode == IHB_TC_DOWN) ? a.top_k : 1;
+  float* xs_s = reinterpret_cast<float*>(smem + 1024);                     // [nslot_x][nkb_total][NT] (fp8 only)
+  const int xs_bytes = (KIND == 0) ? ((nslot_x * nkb_total * NT * 4 + 1023) & ~1023) : 0;
+  uint8_t* stages = smem + 1024 + xs_bytes;
+  constexpr int B_BYTES = NT * TC_BKB;
+  constexpr int STAGE_BYTES = NA * TC_A_BYTES + B_BYTES;
+  const int S = a.S;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  constexpr uint32_t TMEM_COLS_NEEDED = 2 * NA * NT;
+  constexpr uint32_t TMEM_COLS = TMEM_COLS_NEEDED <= 32 ? 32 : TMEM_COLS_NEEDED <= 64 ? 64
+                               : TMEM_COLS_NEEDED <= 128 ? 128 : TMEM_COLS_NEEDED <= 256 ? 256 : 512;
+
+  if (tid == 0) {
+    for (int s = 0; s < S; ++s) { mbar_init(&sh.full[s], 1); mbar_init(&sh.empty[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&sh.tmem_full[b], 1); mbar_init(&sh.tmem_empty[b], 4); }
+    sh.abort_flag = 0;
+    sh.last_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) tmem_alloc(&sh.tmem_base, TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = sh.tmem_base;
+  volatile int* abort_flag = &sh.abort_flag;
+
+  // Everything below reads outputs of earlier kernels (activations, expert ids).
+  pdl_wait();
+  pdl_launch_dependents();
+  if (a.mode != IHB_TC_LINEAR && tid < a.top_k) {
+    int e = ld_cg_i(a.sel_idx + tid) - a.expert0;
+    const bool here = (e >= 0 && e < a.n_experts);
+    sh.sel_e[tid] = here ? e : 0;
+    sh.sel_w[tid] = here ? ld_cg_f(a.sel_w + tid) : 0.f;
+  }
+  if (KIND == 0 && warp >= 2) {
+    // activation scales for every K block: global layout [slot][kb][T], padded here to NT columns
+    const int n = nslot_x * nkb_total * NT;
+    for (int i = tid - 64; i < n; i += 128) {
+      const int col = i % NT, r = i / NT;
+      xs_s[i] = (col < a.T) ? ld_cg_f(a.xscale + static_cast<size_t>(r) * a.T_total + a.tok0 + col) : 0.f;
+    }
+  }
+  __syncthreads();
+
+  const int total_units = a.n_units;
+  const uint32_t idesc = (1u << 4) | (KIND == 1 ? ((1u << 7) | (1u << 10)) : 0u) |
+                         (static_cast<uint32_t>(NT >> 3) << 17) | (static_cast<uint32_t>(TC_BM >> 4) << 24);
+  const int kx = TC_BKB / esize;     // K elements per block (tensor-map coordinate units)
+
+  if (warp == 0) {
+    // =============================== TMA producer ====================================================================
+    if (lane == 0) {
+      int g = 0;
+      bool ok = true;
+      for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
+        const Unit un = decode_unit(a, u, nkb_total);
+        const int e = (a.mode == IHB_TC_LINEAR) ? 0 : sh.sel_e[un.slot];
+        for (int kb = un.kb0; kb < un.kb1; ++kb, ++g) {
+          const int st = g % S;
+          if (g >= S) ok = tc_wait(&sh.empty[st], ((g / S) & 1u) ^ 1u, abort_flag, a.err, ERR_MBAR_EMPTY_TIMEOUT);
+          if (!ok) break;
+          uint8_t* sA = stages + static_cast<size_t>(st) * STAGE_BYTES;
+          uint8_t* sB = sA + NA * TC_A_BYTES;
+          mbar_arrive_expect_tx(&sh.full[st], STAGE_BYTES);
+          if (a.mode == IHB_TC_LINEAR) {
+            tma_load_2d(sA, &tmA, kb * kx, un.row0, &sh.full[st]);
+            tma_load_2d(sB, &tmB, kb * kx, a.tok0, &sh.full[st]);
+          } else if (a.mode == IHB_TC_GATEUP) {
+            tma_load_4d(sA, &tmA, kb * kx, un.row0, 0, e, &sh.full[st]);
+            if (NA == 2) tma_load_4d(sA + TC_A_BYTES, &tmA, kb * kx, un.row0, 1, e, &sh.full[st]);
+            tma_load_2d(sB, &tmB, kb * kx, a.tok0, &sh.full[st]);
+          } else {
+            tma_load_3d(sA, &tmA, kb * kx, un.row0, e, &sh.full[st]);
+            tma_load_3d(sB, &tmB, kb * kx, a.tok0, un.slot, &sh.full[st]);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // =============================== MMA issuer ========================================================================
+    if (lane == 0) {
+      int g = 0, ui = 0;
+      bool ok = true;
+      for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x, ++ui) {
+        const Unit un = decode_unit(a, u, nkb_total);
+        for (int kb = un.kb0; kb < un.kb1 && ok; ++kb, ++g) {
+          const int st = g % S;
+          ok = tc_wait(&sh.full[st], (g / S) & 1u, abort_flag, a.err, ERR_MBAR_FULL_TIMEOUT);
+          if (!ok) break;
+          const int j = (KIND == 0) ? g : ui;            // accumulator use counter
+          const int b = j & 1;
+          if ((KIND == 0 || kb == un.kb0) && j >= 2) {
+            ok = tc_wait(&sh.tmem_empty[b], ((j >> 1) & 1u) ^ 1u, abort_flag, a.err, ERR_TMEM_TIMEOUT);
+            if (!ok) break;
+          }
+          tc_fence_after();
+          const uint8_t* sA = stages + static_cast<size_t>(st) * STAGE_BYTES;
+          const uint64_t bdesc = smem_desc_sw128(sA + NA * TC_A_BYTES);
+#pragma unroll
+          for (int ai = 0; ai < NA; ++ai) {
+            const uint64_t adesc = smem_desc_sw128(sA + ai * TC_A_BYTES);
+            const uint32_t d = tmem_base + static_cast<uint32_t>(b * NA * NT + ai * NT);
+#pragma unroll
+            for (int k = 0; k < TC_BKB / 32; ++k) {
+              const uint32_t accf = (KIND == 0) ? (k > 0) : (kb > un.kb0 || k > 0);
+              tc_mma<KIND>(d, adesc + 2 * k, bdesc + 2 * k, idesc, accf);   // +32 bytes of K per step
+            }
+          }
+          tc_commit(&sh.empty[st]);                      // stage reusable once these MMAs have read it
+          if (KIND == 0 || kb == un.kb1 - 1) tc_commit(&sh.tmem_full[b]);
+        }
+      }
+    }
+  } else {
+    // =============================== epilogue warps (TMEM lane quarter = warp % 4) =================================================
+    const int quarter = warp & 3;
+    const int r_in_tile = quarter * 32 + lane;
+    const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+    const int etid = tid - 64;                         // 0..127
+    int g = 0, ui = 0;
+    bool ok = true;
+    for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x, ++ui) {
+      const Unit un = decode_unit(a, u, nkb_total);
+      const int e = (a.mode == IHB_TC_LINEAR) ? 0 : sh.sel_e[un.slot];
+      float acc[NA][NT];
+#pragma unroll
+      for (int ai = 0; ai < NA; ++ai)
+#pragma unroll
+        for (int n = 0; n < NT; ++n) acc[ai][n] = 0.f;
+      if (KIND == 0) {
+        // weight scale rows of this thread's weight row(s)
+        const float* wsp[NA];
+#pragma unroll
+        for (int ai = 0; ai < NA; ++ai) {
+          int wr = un.row0 + r_in_tile;
+          if (wr >= a.rows) wr = a.rows - 1;
+          if (a.mode == IHB_TC_GATEUP) wr += ai * a.rows;      // up rows follow the gate rows
+          wsp[ai] = a.wscale + (static_cast<size_t>(e) * a.nrb + wr / a.rb) * a.nkb_stride;
+        }
+        float ws_next[NA];
+#pragma unroll
+        for (int ai = 0; ai < NA; ++ai) ws_next[ai] = __ldg(wsp[ai] + un.kb0);
+        const float* xsl = xs_s + static_cast<size_t>(a.mode == IHB_TC_DOWN ? un.slot : 0) * nkb_total * NT;
+        for (int kb = un.kb0; kb < un.kb1 && ok; ++kb, ++g) {
+          float ws[NA];
+#pragma unroll
+          for (int ai = 0; ai < NA; ++ai) {
+            ws[ai] = ws_next[ai];
+            if (kb + 1 < un.kb1) ws_next[ai] = __ldg(wsp[ai] + kb + 1);
+          }
+          const int b = g & 1;
+          ok = tc_wait(&sh.tmem_full[b], (g >> 1) & 1u, abort_flag, a.err, ERR_TMEM_TIMEOUT);
+          if (!ok) break;
+          tc_fence_after();
+          const float* xk = xsl + static_cast<size_t>(kb) * NT;
+#pragma unroll
+          for (int ai = 0; ai < NA; ++ai) {
+#pragma unroll
+            for (int c = 0; c < NT; c += 16) {
+              float d[16];
+              tmem_ld16(lane_addr + static_cast<uint32_t>(b * NA * NT + ai * NT + c), d);
+#pragma unroll
+              for (int n = 0; n < 16; ++n) acc[ai][c + n] = fmaf(d[n], ws[ai] * xk[c + n], acc[ai][c + n]);
+            }
+          }
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&sh.tmem_empty[b]);
+        }
+      } else {
+        g += un.kb1 - un.kb0;
+        const int b = ui & 1;
+        ok = tc_wait(&sh.tmem_full[b], (ui >> 1) & 1u, abort_flag, a.err, ERR_TMEM_TIMEOUT);
+        if (ok) {
+          tc_fence_after();
+#pragma unroll
+          for (int ai = 0; ai < NA; ++ai)
+#pragma unroll
+            for (int c = 0; c < NT; c += 16) tmem_ld16(lane_addr + static_cast<uint32_t>(b * NA * NT + ai * NT + c), &acc[ai][c]);
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&sh.tmem_empty[b]);
+        }
+      }
+      if (!ok) break;
+
+      // ---- combine the units that feed this output tile -------------------------------------------------------------------
+      const int members = (a.mode == IHB_TC_DOWN) ? a.top_k * a.ks : a.ks;
+      const float wslot = (a.mode == IHB_TC_DOWN) ? sh.sel_w[un.slot] : 1.f;
+      bool finisher = true;
+      if (members > 1) {
+        float* part = a.partial + (static_cast<size_t>(un.tile) * members + un.member) * (NA * a.T * TC_BM);
+#pragma unroll
+        for (int ai = 0; ai < NA; ++ai)
+#pragma unroll
+          for (int n = 0; n < NT; ++n)
+            if (n < a.T) part[(ai * a.T + n) * TC_BM + r_in_tile] = acc[ai][n] * wslot;
+        __threadfence();
+        named_bar_sync(2, 128);
+        if (etid == 0) {
+          const unsigned old = atomicAdd(a.tile_counters + un.tile, 1u);
+          const int last = (old == static_cast<unsigned>(members) - 1u);
+          if (last) { a.tile_counters[un.tile] = 0u; __threadfence(); }
+          sh.last_flag = last;
+        }
+        named_bar_sync(2, 128);
+        finisher = sh.last_flag != 0;
+        if (finisher) {
+          const float* p0 = a.partial + static_cast<size_t>(un.tile) * members * (NA * a.T * TC_BM);
+#pragma unroll
+          for (int ai = 0; ai < NA; ++ai)
+#pragma unroll
+            for (int n = 0; n < NT; ++n) {
+              if (n < a.T) {
+                float s = 0.f;
+                for (int mbr = 0; mbr < members; ++mbr)
+                  s += ld_cg_f(p0 + (static_cast<size_t>(mbr) * NA * a.T + ai * a.T + n) * TC_BM + r_in_tile);
+                acc[ai][n] = s;
+              }
+            }
+        }
+        named_bar_sync(2, 128);      // last_flag is rewritten by the next unit
+      } else if (a.mode == IHB_TC_DOWN) {
+#pragma unroll
+        for (int n = 0; n < NT; ++n) acc[0][n] *= wslot;
+      }
+      if (!finisher) continue;
+
+      // ---- epilogue on the finished tile: this thread owns weight row `row` for every token ----------------------------
+      const int row = un.row0 + r_in_tile;
+      if (a.mode == IHB_TC_GATEUP) {
+        // SwiGLU; `out` is [slot][T][I] fp32
+        if (row < a.rows) {
+#pragma unroll
+          for (int n = 0; n < NT; ++n)
+            if (n < a.T) a.out[(static_cast<size_t>(un.slot) * a.T + n) * a.rows + row] = silu(acc[0][n]) * acc[NA - 1][n];
+        }
+      } else {
+        if (row < a.rows) {
+#pragma unroll
+          for (int n = 0; n < NT; ++n)
+            if (n < a.T) a.out[static_cast<size_t>(n) * a.out_stride + row] = acc[0][n];
+        }
+      }
+    }
+  }
+
+  // ---- teardown: every role arrives here, also after a time-out ------------------------------------------------------------------
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---- host side ------------------------------------------------------------------------------------------------------------------
+
+static CUresult encode_map(CUtensorMap* tm, int is_fp8, void* base, int rank, const cuuint64_t* dims,
+                           const cuuint64_t* strides_bytes, const cuuint32_t* box) {
+  cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+  return cuTensorMapEncodeTiled(tm, is_fp8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, base,
+                                dims, strides_bytes, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+}
+
+template <int KIND, int NT, int NA>
+static cudaError_t launch_tc(const CUtensorMap& tmA, const CUtensorMap& tmB, const IhbTcArgs& a, int grid, int smem,
+                             int use_pdl, cudaStream_t stream) {
+  cudaError_t e = cudaFuncSetAttribute(tc_gemm_kernel<KIND, NT, NA>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) return e;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(TC_THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = use_pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, tc_gemm_kernel<KIND, NT, NA>, tmA, tmB, a);
+}
+
+}  // namespace ihb
+
+using namespace ihb;
+
+extern "C" size_t ihb_tc_partial_floats(const IhbTcArgs* a) {
+  const int tiles_rows = (a->rows + TC_BM - 1) / TC_BM;
+  const int tiles = a->mode == IHB_TC_GATEUP ? a->top_k * tiles_rows : tiles_rows;
+  const int members = a->mode == IHB_TC_DOWN ? a->top_k * a->ks : a->ks;
+  const int na = a->mode == IHB_TC_GATEUP ? 2 : 1;
+  return members > 1 ? static_cast<size_t>(tiles) * members * na * a->T * TC_BM : 0;
+}
+
+// Picks the K split so that the grid has about two waves of units, encodes the tensor maps and launches.
+extern "C" int ihb_tc_gemm(IhbTcArgs* args, int use_pdl, cudaStream_t stream) {
+  IhbTcArgs a = *args;
+  const int is_fp8 = a.wtype == IHB_W_FP8;
+  const int esize = is_fp8 ? 1 : 2;
+  if (a.T < 1 || a.T > 128 || a.rows < 1 || a.K < 1 || (a.K * esize) % 16) return cudaErrorInvalidValue;
+  if (is_fp8 && (a.rb < 1 || a.wscale == nullptr || a.xscale == nullptr)) return cudaErrorInvalidValue;
+  if (a.mode != IHB_TC_LINEAR && (a.top_k < 1 || a.top_k > IHB_MAX_TOPK)) return cudaErrorInvalidValue;
+  const int nt = a.T <= 16 ? 16 : a.T <= 32 ? 32 : a.T <= 64 ? 64 : 128;
+  if (a.mode == IHB_TC_GATEUP && nt > 64) return cudaErrorInvalidValue;   // two accumulators per token column
+  const int na = a.mode == IHB_TC_GATEUP ? 2 : 1;
+  const int nkb_total = (a.K * esize + TC_BKB - 1) / TC_BKB;
+  const int tiles_rows = (a.rows + TC_BM - 1) / TC_BM;
+  int sms = 148;
+  {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  const int base_units = a.mode == IHB_TC_LINEAR ? tiles_rows : a.top_k * tiles_rows;
+  if (a.ks <= 0) {
+    int ks = (2 * sms + base_units - 1) / base_units;
+    if (ks > nkb_total) ks = nkb_total;
+    if (ks > 16) ks = 16;
+    if (ks < 1) ks = 1;
+    a.ks = ks;
+  }
+  if (a.ks > nkb_total) a.ks = nkb_total;
+  a.n_units = base_units * a.ks;
+  const int members = a.mode == IHB_TC_DOWN ? a.top_k * a.ks : a.ks;
+  if (members > 1 && (a.partial == nullptr || a.tile_counters == nullptr)) return cudaErrorInvalidValue;
+
+  // tensor maps -----------------------------------------------------------------------------------------------------------
+  alignas(64) CUtensorMap tmA, tmB;
+  const cuuint64_t Kd = static_cast<cuuint64_t>(a.K);
+  const cuuint64_t rowb = Kd * esize;
+  const cuuint32_t kbox = TC_BKB / esize;
+  CUresult r;
+  if (a.mode == IHB_TC_LINEAR) {
+    cuuint64_t dims[2] = {Kd, static_cast<cuuint64_t>(a.rows)};
+    cuuint64_t str[1] = {rowb};
+    cuuint32_t box[2] = {kbox, TC_BM};
+    r = encode_map(&tmA, is_fp8, const_cast<void*>(a.W), 2, dims, str, box);
+  } else if (a.mode == IHB_TC_GATEUP) {       // [E][2][I][K]
+    cuuint64_t dims[4] = {Kd, static_cast<cuuint64_t>(a.rows), 2, static_cast<cuuint64_t>(a.n_experts)};
+    cuuint64_t str[3] = {rowb, rowb * a.rows, rowb * a.rows * 2};
+    cuuint32_t box[4] = {kbox, TC_BM, 1, 1};
+    r = encode_map(&tmA, is_fp8, const_cast<void*>(a.W), 4, dims, str, box);
+  } else {                                    // [E][H][I]
+    cuuint64_t dims[3] = {Kd, static_cast<cuuint64_t>(a.rows), static_cast<cuuint64_t>(a.n_experts)};
+    cuuint64_t str[2] = {rowb, rowb * a.rows};
+    cuuint32_t box[3] = {kbox, TC_BM, 1};
+    r = encode_map(&tmA, is_fp8, const_cast<void*>(a.W), 3, dims, str, box);
+  }
+  if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
+  if (a.mode == IHB_TC_DOWN) {                // X: [top_k][T][K]
+    cuuint64_t dims[3] = {Kd, static_cast<cuuint64_t>(a.T_total), static_cast<cuuint64_t>(a.top_k)};
+    cuuint64_t str[2] = {rowb, rowb * a.T_total};
+    cuuint32_t box[3] = {kbox, static_cast<cuuint32_t>(nt), 1};
+    r = encode_map(&tmB, is_fp8, const_cast<void*>(a.X), 3, dims, str, box);
+  } else {
+    cuuint64_t dims[2] = {Kd, static_cast<cuuint64_t>(a.T_total)};
+    cuuint64_t str[1] = {rowb};
+    cuuint32_t box[2] = {kbox, static_cast<cuuint32_t>(nt)};
+    r = encode_map(&tmB, is_fp8, const_cast<void*>(a.X), 2, dims, str, box);
+  }
+  if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
+
+  // shared memory ------------------------------------------------------------------------------------------------------------
+  const int nslot_x = a.mode == IHB_TC_DOWN ? a.top_k : 1;
+  const int xs_bytes = is_fp8 ? ((nslot_x * nkb_total * nt * 4 + 1023) & ~1023) : 0;
+  const int stage_bytes = na * TC_A_BYTES + nt * TC_BKB;
+  int S = (200 * 1024 - 2048 - xs_bytes) / stage_bytes;
+  if (S > 8) S = 8;
+  if (a.S > 0 && a.S < S) S = a.S;
+  if (S < 2) return cudaErrorInvalidValue;
+  a.S = S;
+  const int smem = 1024 /*align slack*/ + 1024 + xs_bytes + S * stage_bytes;
+  int grid = a.grid > 0 ? a.grid : sms;
+  if (grid > a.n_units) grid = a.n_units;
+
+#define TC_GO(KIND, NT, NA) return launch_tc<KIND, NT, NA>(tmA, tmB, a, grid, smem, use_pdl, stream)
+  if (is_fp8) {
+    if (na == 1) {
+      switch (nt) { case 16: TC_GO(0, 16, 1); case 32: TC_GO(0, 32, 1); case 64: TC_GO(0, 64, 1); default: TC_GO(0, 128, 1); }
+    } else {
+      switch (nt) { case 16: TC_GO(0, 16, 2); case 32: TC_GO(0, 32, 2); default: TC_GO(0, 64, 2); }
+    }
+  } else {
+    if (na == 1) {
+      switch (nt) { case 16: TC_GO(1, 16, 1); case 32: TC_GO(1, 32, 1); case 64: TC_GO(1, 64, 1); default: TC_GO(1, 128, 1); }
+    } else {
+      switch (nt) { case 16: TC_GO(1, 16, 2); case 32: TC_GO(1, 32, 2); default: TC_GO(1, 64, 2); }
+    }
+  }
+#undef TC_GO
+}

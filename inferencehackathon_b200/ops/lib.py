@@ -57,6 +57,19 @@ class IhbMoeArgs(C.Structure):
                 ("comm", IhbComm)]
 
 
+TC_LINEAR, TC_GATEUP, TC_DOWN = 0, 1, 2
+
+
+class IhbTcArgs(C.Structure):
+    _fields_ = [("W", _vp), ("wscale", _vp), ("wtype", C.c_int), ("rows", C.c_int), ("K", C.c_int),
+                ("rb", C.c_int), ("nrb", C.c_int), ("nkb_stride", C.c_int),
+                ("n_experts", C.c_int), ("expert0", C.c_int), ("top_k", C.c_int),
+                ("X", _vp), ("xscale", _vp), ("T", C.c_int), ("T_total", C.c_int), ("tok0", C.c_int),
+                ("mode", C.c_int), ("sel_idx", _vp), ("sel_w", _vp),
+                ("out", _vp), ("out_stride", C.c_int), ("partial", _vp), ("tile_counters", _vp),
+                ("ks", C.c_int), ("S", C.c_int), ("grid", C.c_int), ("n_units", C.c_int), ("err", _vp)]
+
+
 _lib: Optional[C.CDLL] = None
 
 
@@ -85,6 +98,10 @@ def load(build_if_missing: bool = True) -> C.CDLL:
                                      C.c_int, _vp]
     lib.ihb_flash_decode_scratch_floats.argtypes = [C.c_int, C.c_int]
     lib.ihb_flash_decode_scratch_floats.restype = C.c_size_t
+    lib.ihb_tc_gemm.argtypes = [C.POINTER(IhbTcArgs), C.c_int, _vp]
+    lib.ihb_tc_gemm.restype = C.c_int
+    lib.ihb_tc_partial_floats.argtypes = [C.POINTER(IhbTcArgs)]
+    lib.ihb_tc_partial_floats.restype = C.c_size_t
     for name in ("ihb_gemv", "ihb_moe_gateup", "ihb_moe_down", "ihb_embed_norm", "ihb_qk_norm_rope_kv",
                  "ihb_flash_decode"):
         getattr(lib, name).restype = C.c_int
@@ -133,14 +150,29 @@ def single_comm(slots: torch.Tensor, epoch: torch.Tensor) -> IhbComm:
     return cm
 
 
+def kernel_scale(qw) -> torch.Tensor:
+    """Block scales in the kernels' layout: each scale row padded to a multiple of 4 floats, because scale rows
+    travel to shared memory by bulk copy (16-byte granules). Cached on the QWeight."""
+    ks = getattr(qw, "_kscale", None)
+    if ks is None:
+        sc = qw.scale
+        pad = (-sc.shape[-1]) % 4
+        ks = torch.nn.functional.pad(sc, (0, pad)).contiguous() if pad else sc.contiguous()
+        if ks.shape[-1] > 64:
+            raise ValueError("at most 64 scale blocks along K")
+        qw._kscale = ks
+    return ks
+
+
 def fill_weight(args, qw, prefix: str = "") -> None:
     """Set the weight fields of a GEMV argument block from a QWeight."""
     args.W = qw.data.data_ptr()
     args.wtype = wtype_of(qw.data)
     args.rows, args.K = qw.data.shape[-2], qw.data.shape[-1]
     if qw.scale is not None:
-        args.wscale = qw.scale.data_ptr()
-        args.rb, args.kb_shift, args.nkb = qw.rb, kb_shift_of(qw.kb), qw.scale.shape[-1]
+        ks = kernel_scale(qw)
+        args.wscale = ks.data_ptr()
+        args.rb, args.kb_shift, args.nkb = qw.rb, kb_shift_of(qw.kb), ks.shape[-1]
 
 
 def gemv(args: IhbGemvArgs, use_pdl: bool = False) -> None:
@@ -179,3 +211,26 @@ def flash_decode(q, k_cache, v_cache, nq: int, nkv: int, max_seq: int, pos, nspl
     check(load().ihb_flash_decode(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), nq, nkv, max_seq,
                                   pos.data_ptr(), nsplit, scratch.data_ptr(), counters.data_ptr(), out.data_ptr(),
                                   int(use_pdl), stream_ptr()), "ihb_flash_decode")
+
+
+def tc_gemm(args: IhbTcArgs, use_pdl: bool = False) -> None:
+    check(load().ihb_tc_gemm(C.byref(args), int(use_pdl), stream_ptr()), "ihb_tc_gemm")
+
+
+def tc_partial_floats(args: IhbTcArgs) -> int:
+    return int(load().ihb_tc_partial_floats(C.byref(args)))
+
+
+def tc_fill_weight(args: IhbTcArgs, qw) -> None:
+    """Weight fields of a tensor-core GEMM block; ``qw.data`` is ``[rows, K]`` or ``[E, rows, K]``
+    (gate/up weights: ``[E, 2 * I, K]`` with ``rows = I``, set by the caller)."""
+    args.W = qw.data.data_ptr()
+    args.wtype = wtype_of(qw.data)
+    args.rows, args.K = qw.data.shape[-2], qw.data.shape[-1]
+    args.n_experts = qw.data.shape[0] if qw.data.dim() == 3 else 1
+    if qw.scale is not None:
+        if qw.kb != 128:
+            raise ValueError("the tensor-core path needs 128-wide K scale blocks")
+        ks = kernel_scale(qw)
+        args.wscale = ks.data_ptr()
+        args.rb, args.nrb, args.nkb_stride = qw.rb, ks.shape[-2], ks.shape[-1]

@@ -142,9 +142,10 @@ class GpuDecoder:
             moe.H, moe.I, moe.E_local = self.H, self.I, lw.w_gu.data.shape[0]
             moe.expert0, moe.top_k = w.geom.expert0, m.top_k
             if lw.w_gu.scale is not None:
-                moe.gu_scale, moe.d_scale = lw.w_gu.scale.data_ptr(), lw.w_d.scale.data_ptr()
-                moe.gu_rb, moe.gu_kb_shift, moe.gu_nkb = lw.w_gu.rb, K.kb_shift_of(lw.w_gu.kb), lw.w_gu.scale.shape[-1]
-                moe.d_rb, moe.d_kb_shift, moe.d_nkb = lw.w_d.rb, K.kb_shift_of(lw.w_d.kb), lw.w_d.scale.shape[-1]
+                gsc, dsc = K.kernel_scale(lw.w_gu), K.kernel_scale(lw.w_d)
+                moe.gu_scale, moe.d_scale = gsc.data_ptr(), dsc.data_ptr()
+                moe.gu_rb, moe.gu_kb_shift, moe.gu_nkb = lw.w_gu.rb, K.kb_shift_of(lw.w_gu.kb), gsc.shape[-1]
+                moe.d_rb, moe.d_kb_shift, moe.d_nkb = lw.w_d.rb, K.kb_shift_of(lw.w_d.kb), dsc.shape[-1]
             moe.x, moe.act = self.xn.data_ptr(), self.act.data_ptr()
             moe.sel_idx, moe.sel_w = self.sel_idx[L].data_ptr(), self.sel_w[L].data_ptr()
             moe.counter, moe.err = ctr[2:3].data_ptr(), self.err.data_ptr()

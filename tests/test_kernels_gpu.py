@@ -141,8 +141,8 @@ def test_lm_head_argmax(fp8):
 @pytest.mark.parametrize("H,I,E,k", [(4096, 1536, 8, 8), (2048, 192, 16, 8), (512, 256, 16, 4), (2048, 768, 8, 8),
                                      (2048, 96, 8, 8)])
 def test_moe_gateup_down(fp8, H, I, E, k):
-    if fp8 and I % 16:
-        pytest.skip("fp8 rows are consumed in 16-element chunks")
+    if not fp8 and H > 2048:
+        pytest.skip("bf16 activations of this width do not fit the register fragment")
     lib = _K()
     g = torch.Generator(device=_dev()).manual_seed(H + I)
     wgu = _rand_q(2 * I, H, fp8, g, lead=(E,))
@@ -160,9 +160,10 @@ def test_moe_gateup_down(fp8, H, I, E, k):
     a.Wgu, a.Wd, a.wtype = wgu.data.data_ptr(), wd.data.data_ptr(), lib.wtype_of(wgu.data)
     a.H, a.I, a.E_local, a.expert0, a.top_k = H, I, E, 0, k
     if fp8:
-        a.gu_scale, a.d_scale = wgu.scale.data_ptr(), wd.scale.data_ptr()
-        a.gu_rb, a.gu_kb_shift, a.gu_nkb = wgu.rb, lib.kb_shift_of(wgu.kb), wgu.scale.shape[-1]
-        a.d_rb, a.d_kb_shift, a.d_nkb = wd.rb, lib.kb_shift_of(wd.kb), wd.scale.shape[-1]
+        gsc, dsc = lib.kernel_scale(wgu), lib.kernel_scale(wd)
+        a.gu_scale, a.d_scale = gsc.data_ptr(), dsc.data_ptr()
+        a.gu_rb, a.gu_kb_shift, a.gu_nkb = wgu.rb, lib.kb_shift_of(wgu.kb), gsc.shape[-1]
+        a.d_rb, a.d_kb_shift, a.d_nkb = wd.rb, lib.kb_shift_of(wd.kb), dsc.shape[-1]
     a.x, a.sel_idx, a.sel_w, a.act = x.data_ptr(), sel.data_ptr(), sw.data_ptr(), act.data_ptr()
     a.counter, a.err = st["counter"].data_ptr(), st["err"].data_ptr()
     a.resid, a.gamma, a.xn_out, a.eps = resid.data_ptr(), gamma.data_ptr(), xn.data_ptr(), 1e-6
