@@ -144,6 +144,8 @@ typedef struct {
   int ks, S, grid;         // K split / stages / CTAs (0 = choose)
   int n_units;             // filled in by the launcher
   unsigned* err;
+  int tiled;               // 1: W is pre-tiled [matrix][k block][rows padded to 8][128 B] in swizzled order
+  int x_rows1;             // 1 (needs tiled, T == 1): X is [slots][K padded to 128 B], one plain row per slot
 } IhbTcArgs;
 
 int ihb_tc_gemm(IhbTcArgs* args, int use_pdl, cudaStream_t stream);

@@ -261,8 +261,8 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) gemv_kernel(const IhbGemvAr
   named_bar_sync(1, CONSUMER_THREADS);
   if (!s_last) return;
   if (EPI == IHB_EPI_AR_NORM) {
-    ArNormTail t{a.comm, a.rows, a.ks, a.resid, a.gamma, a.xn_out, a.eps, a.err};
-    tail_ar_norm(t, tid, red_f);
+    ArNormTail t{a.comm, a.rows, a.ks, a.resid, a.gamma, a.xn_out, a.eps, a.err, nullptr, nullptr, 0};
+    tail_ar_norm<CONSUMER_THREADS, 1>(t, tid, red_f);
   }
   if (EPI == IHB_EPI_ROUTER) { if (warp == 0) tail_router(a, lane); }
   if (EPI == IHB_EPI_ARGMAX) tail_argmax(a, tid, red_u, gridDim.x);

@@ -237,8 +237,8 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) moe_down_kernel(const IhbMo
   }
   named_bar_sync(1, CONSUMER_THREADS);
   if (!s_last) return;
-  ArNormTail t{a.comm, a.H, 1, a.resid, a.gamma, a.xn_out, a.eps, a.err};
-  tail_ar_norm(t, tid, red_f);
+  ArNormTail t{a.comm, a.H, 1, a.resid, a.gamma, a.xn_out, a.eps, a.err, nullptr, nullptr, 0};
+  tail_ar_norm<CONSUMER_THREADS, 1>(t, tid, red_f);
 }
 
 static int num_sms() {

@@ -35,11 +35,36 @@ struct ArNormTail {
   float* xn_out;
   float eps;
   unsigned* err;
+  // optional copy of the normed vector as the tensor-core kernels' activation operand: plain row of e4m3
+  // bytes with one fp32 scale per 128 channels (xq_fp8 = 1), or a bf16 row (xq_fp8 = 0); nullptr = none
+  uint8_t* xq;
+  float* xs;
+  int xq_fp8;
 };
+
+// Quantise 4 consecutive values per lane (a warp = one group of 128 channels) to e4m3 with scale amax / 448.
+__device__ __forceinline__ void quant_group128(float4 v, uint8_t* dst4, float* scale_out, int lane) {
+  float m = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+  m = warp_max(m);
+  const float s = fmaxf(m, 1e-12f) * (1.f / 448.f);
+  const float inv = 1.f / s;
+  const __nv_fp8x2_storage_t lo = __nv_cvt_float2_to_fp8x2(make_float2(v.x * inv, v.y * inv), __NV_SATFINITE, __NV_E4M3);
+  const __nv_fp8x2_storage_t hi = __nv_cvt_float2_to_fp8x2(make_float2(v.z * inv, v.w * inv), __NV_SATFINITE, __NV_E4M3);
+  *reinterpret_cast<uint32_t*>(dst4) = static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
+  if (lane == 0) *scale_out = s;
+}
+__device__ __forceinline__ void store_bf16x4(float4 v, uint8_t* dst8) {
+  const __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+  uint2 o;
+  o.x = *reinterpret_cast<const uint32_t*>(&a);
+  o.y = *reinterpret_cast<const uint32_t*>(&b);
+  *reinterpret_cast<uint2*>(dst8) = o;
+}
 
 // Runs in the consumer threads of the last CTA: cross-GPU arrive/wait, sum of all slots in slot order,
 // residual add, RMSNorm. Every rank sums the same values in the same order, so the replicated residual stream
 // stays bitwise identical across ranks.
+template <int NTHR, int BAR>
 __device__ __forceinline__ void tail_ar_norm(const ArNormTail& a, int tid, float* red_smem) {
   const IhbComm& cm = a.comm;
   const int H = a.H;
@@ -47,21 +72,21 @@ __device__ __forceinline__ void tail_ar_norm(const ArNormTail& a, int tid, float
   const int parity = epoch & 1u;
   if (cm.nranks > 1) {
     if (tid == 0) peer_barrier(cm, (epoch + 1u) * static_cast<unsigned>(cm.nranks), a.err);
-    named_bar_sync(1, CONSUMER_THREADS);
+    named_bar_sync(BAR, NTHR);
   }
   const int nslots = cm.nranks * a.ks;
   const float* slots = cm.slots_local + static_cast<size_t>(parity) * nslots * H;
-  constexpr int MAXV = 8;                       // H <= 8192: at most 8 float4 per thread, kept in registers
+  constexpr int MAXV = 8192 / 4 / NTHR;          // H <= 8192: float4s per thread, kept in registers
   float4 acc[MAXV];
 #pragma unroll
   for (int j = 0; j < MAXV; ++j) {
-    const int i = (tid + CONSUMER_THREADS * j) * 4;
+    const int i = (tid + NTHR * j) * 4;
     acc[j] = (i < H) ? *reinterpret_cast<const float4*>(a.resid + i) : make_float4(0.f, 0.f, 0.f, 0.f);
   }
   for (int s = 0; s < nslots; ++s) {
 #pragma unroll
     for (int j = 0; j < MAXV; ++j) {
-      const int i = (tid + CONSUMER_THREADS * j) * 4;
+      const int i = (tid + NTHR * j) * 4;
       if (i < H) {
         const float4 v = ld_cg_f4(reinterpret_cast<const float4*>(slots + static_cast<size_t>(s) * H + i));
         acc[j].x += v.x; acc[j].y += v.y; acc[j].z += v.z; acc[j].w += v.w;
@@ -74,19 +99,24 @@ __device__ __forceinline__ void tail_ar_norm(const ArNormTail& a, int tid, float
     ss += acc[j].x * acc[j].x + acc[j].y * acc[j].y + acc[j].z * acc[j].z + acc[j].w * acc[j].w;
   ss = warp_sum(ss);
   if ((tid & 31) == 0) red_smem[tid >> 5] = ss;
-  named_bar_sync(1, CONSUMER_THREADS);
+  named_bar_sync(BAR, NTHR);
   float tot = 0.f;
 #pragma unroll
-  for (int w = 0; w < NCW; ++w) tot += red_smem[w];
+  for (int w = 0; w < NTHR / 32; ++w) tot += red_smem[w];
   const float rinv = rsqrtf(tot / static_cast<float>(H) + a.eps);
 #pragma unroll
   for (int j = 0; j < MAXV; ++j) {
-    const int i = (tid + CONSUMER_THREADS * j) * 4;
+    const int i = (tid + NTHR * j) * 4;
     if (i < H) {
       const float4 g = *reinterpret_cast<const float4*>(a.gamma + i);
       *reinterpret_cast<float4*>(a.resid + i) = acc[j];
-      *reinterpret_cast<float4*>(a.xn_out + i) =
-          make_float4(acc[j].x * rinv * g.x, acc[j].y * rinv * g.y, acc[j].z * rinv * g.z, acc[j].w * rinv * g.w);
+      const float4 o = make_float4(acc[j].x * rinv * g.x, acc[j].y * rinv * g.y, acc[j].z * rinv * g.z,
+                                   acc[j].w * rinv * g.w);
+      *reinterpret_cast<float4*>(a.xn_out + i) = o;
+      if (a.xq != nullptr) {          // H is a multiple of 128, so a warp is entirely inside or outside
+        if (a.xq_fp8) quant_group128(o, a.xq + i, a.xs + (i >> 7), tid & 31);
+        else store_bf16x4(o, a.xq + 2 * i);
+      }
     }
   }
   if (tid == 0) *cm.epoch = epoch + 1u;

@@ -17,120 +17,22 @@
 //
 // The reference reaches tensor cores only through cuBLASLt calls at M = 16 (kernels/gemm_engine.cuh:48-125)
 // and one mma.sync prefill kernel (kernels/prefill_wgmma.cu:88-262).
-#include <cuda.h>
-#include "common.cuh"
-#include "api.h"
+#include <string.h>
+#include "tc_common.cuh"
 #include "tails.cuh"
 
 namespace ihb {
 
-constexpr int TC_BM = 128;          // weight rows per tile (TMEM lanes)
-constexpr int TC_BKB = 128;         // bytes of K per stage
-constexpr int TC_THREADS = 192;     // warp 0: TMA, warp 1: MMA + TMEM allocation, warps 2-5: epilogue
-constexpr int TC_A_BYTES = TC_BM * TC_BKB;
-
-// ---- PTX wrappers ------------------------------------------------------------------------------------------------
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* tm, int x, int y, uint64_t* bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
-          smem_u32(dst)),
-      "l"(tm), "r"(smem_u32(bar)), "r"(x), "r"(y)
-      : "memory");
-}
-__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* tm, int x, int y, int z, uint64_t* bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];" ::
-          "r"(smem_u32(dst)),
-      "l"(tm), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
-      : "memory");
-}
-__device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* tm, int x, int y, int z, int w,
-                                            uint64_t* bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], "
-      "[%2];" ::"r"(smem_u32(dst)),
-      "l"(tm), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z), "r"(w)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_alloc(uint32_t* smem_dst, uint32_t ncols) {
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_dst)),
-               "r"(ncols)
-               : "memory");
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
-               : "memory");
-}
-template <int KIND>   // 0: e4m3 x e4m3, 1: bf16 x bf16; fp32 accumulate
-__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
-  if (KIND == 0) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
-        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc)
-        : "memory");
-  } else {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
-        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc)
-        : "memory");
-  }
-}
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* d) {
-  uint32_t r[16];
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr)
-      : "memory");
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-  for (int i = 0; i < 16; ++i) d[i] = __uint_as_float(r[i]);
-}
-
-// Shared-memory matrix descriptor of a K-major tile with 128-byte rows and the 128-byte swizzle: 8-row groups
-// 1024 bytes apart (stride byte offset), descriptor version 1, layout type 2.
-__device__ __forceinline__ uint64_t smem_desc_sw128(const void* tile) {
-  uint64_t d = (static_cast<uint64_t>(smem_u32(tile)) >> 4) & 0x3FFFull;
-  d |= 1ull << 16;                        // leading byte offset: unused for swizzled K-major operands
-  d |= static_cast<uint64_t>(1024 >> 4) << 32;
-  d |= 1ull << 46;
-  d |= 2ull << 61;
-  return d;
-}
-
-// Wait with a time limit that also gives up when another role of this CTA has already failed.
-__device__ __forceinline__ bool tc_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, unsigned* err,
-                                        unsigned code) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const unsigned long long t0 = globaltimer_ns();
-  unsigned spins = 0;
-  while (!mbar_try_wait(bar, parity)) {
-    if ((++spins & 127u) == 0u) {
-      if (*abort_flag) return false;
-      if (globaltimer_ns() - t0 > IHB_LOCAL_WAIT_NS) {
-        *abort_flag = 1;
-        set_error(err, code);
-        return false;
-      }
-    }
-  }
-  return true;
-}
+constexpr int TC_PRODUCERS = 3;     // a thread gets one bulk/TMA copy accepted every ~0.3 us whatever its size, so
+                                    // three producer warps take the stages round-robin
+constexpr int TC_MMA_WARP = 3;
+constexpr int TC_THREADS = 256;     // warps 0-2: TMA producers, warp 3: MMA + TMEM allocation, warps 4-7: epilogue
 
 struct TcSmem {
   uint64_t full[8];
   uint64_t empty[8];
-  uint64_t tmem_full[2];
-  uint64_t tmem_empty[2];
+  uint64_t tmem_full[8];
+  uint64_t tmem_empty[8];
   uint32_t tmem_base;
   int abort_flag;
   int last_flag;
@@ -187,18 +89,26 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   constexpr int STAGE_BYTES = NA * TC_A_BYTES + B_BYTES;
   const int S = a.S;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  constexpr uint32_t TMEM_COLS_NEEDED = 2 * NA * NT;
+  // With few token columns an MMA is over in a handful of cycles but its result takes a pipeline latency to
+  // land, so MMAs chained on ONE accumulator run at latency, not throughput. The four K steps of a stage
+  // therefore go to SUB = 4 separate accumulators (added up by the epilogue) when N is small.
+  constexpr int SUB = (NT <= 32) ? 4 : 1;
+  constexpr int BUF_COLS = NA * SUB * NT;
+  // accumulator ring in tensor memory: up to 8 buffers (512 columns in total)
+  constexpr int NBUF = (512 / BUF_COLS) >= 8 ? 8 : (512 / BUF_COLS);
+  static_assert(NBUF >= 2, "need two accumulator buffers");
+  constexpr uint32_t TMEM_COLS_NEEDED = NBUF * BUF_COLS;
   constexpr uint32_t TMEM_COLS = TMEM_COLS_NEEDED <= 32 ? 32 : TMEM_COLS_NEEDED <= 64 ? 64
                                : TMEM_COLS_NEEDED <= 128 ? 128 : TMEM_COLS_NEEDED <= 256 ? 256 : 512;
 
   if (tid == 0) {
     for (int s = 0; s < S; ++s) { mbar_init(&sh.full[s], 1); mbar_init(&sh.empty[s], 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(&sh.tmem_full[b], 1); mbar_init(&sh.tmem_empty[b], 4); }
+    for (int b = 0; b < NBUF; ++b) { mbar_init(&sh.tmem_full[b], 1); mbar_init(&sh.tmem_empty[b], 4); }
     sh.abort_flag = 0;
     sh.last_flag = 0;
     fence_mbar_init();
   }
-  if (warp == 1) tmem_alloc(&sh.tmem_base, TMEM_COLS);
+  if (warp == TC_MMA_WARP) tmem_alloc(&sh.tmem_base, TMEM_COLS);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -214,10 +124,18 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     sh.sel_e[tid] = here ? e : 0;
     sh.sel_w[tid] = here ? ld_cg_f(a.sel_w + tid) : 0.f;
   }
-  if (KIND == 0 && warp >= 2) {
+  if (a.x_rows1) {
+    // single-token mode copies only row 0 of each activation tile: clear the other rows once
+    for (int i = tid; i < S * (B_BYTES / 16); i += TC_THREADS) {
+      const int st = i / (B_BYTES / 16), o = i % (B_BYTES / 16);
+      *reinterpret_cast<uint4*>(stages + static_cast<size_t>(st) * STAGE_BYTES + NA * TC_A_BYTES + o * 16) = make_uint4(0, 0, 0, 0);
+    }
+    fence_proxy_async_smem();
+  }
+  if (KIND == 0 && warp >= 4) {
     // activation scales for every K block: global layout [slot][kb][T], padded here to NT columns
     const int n = nslot_x * nkb_total * NT;
-    for (int i = tid - 64; i < n; i += 128) {
+    for (int i = tid - 128; i < n; i += 128) {
       const int col = i % NT, r = i / NT;
       xs_s[i] = (col < a.T) ? ld_cg_f(a.xscale + static_cast<size_t>(r) * a.T_total + a.tok0 + col) : 0.f;
     }
@@ -228,9 +146,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const uint32_t idesc = (1u << 4) | (KIND == 1 ? ((1u << 7) | (1u << 10)) : 0u) |
                          (static_cast<uint32_t>(NT >> 3) << 17) | (static_cast<uint32_t>(TC_BM >> 4) << 24);
   const int kx = TC_BKB / esize;     // K elements per block (tensor-map coordinate units)
+  const int rows_p8 = (a.rows + 7) & ~7;
 
-  if (warp == 0) {
-    // =============================== TMA producer ====================================================================
+  if (warp < TC_PRODUCERS) {
+    // =============================== TMA producers: warp p feeds the stages with g % 3 == p ============================
     if (lane == 0) {
       int g = 0;
       bool ok = true;
@@ -238,27 +157,53 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const Unit un = decode_unit(a, u, nkb_total);
         const int e = (a.mode == IHB_TC_LINEAR) ? 0 : sh.sel_e[un.slot];
         for (int kb = un.kb0; kb < un.kb1; ++kb, ++g) {
+          if (g % TC_PRODUCERS != warp) continue;
           const int st = g % S;
           if (g >= S) ok = tc_wait(&sh.empty[st], ((g / S) & 1u) ^ 1u, abort_flag, a.err, ERR_MBAR_EMPTY_TIMEOUT);
           if (!ok) break;
           uint8_t* sA = stages + static_cast<size_t>(st) * STAGE_BYTES;
           uint8_t* sB = sA + NA * TC_A_BYTES;
-          mbar_arrive_expect_tx(&sh.full[st], STAGE_BYTES);
-          if (a.mode == IHB_TC_LINEAR) {
-            tma_load_2d(sA, &tmA, kb * kx, un.row0, &sh.full[st]);
-            tma_load_2d(sB, &tmB, kb * kx, a.tok0, &sh.full[st]);
-          } else if (a.mode == IHB_TC_GATEUP) {
-            tma_load_4d(sA, &tmA, kb * kx, un.row0, 0, e, &sh.full[st]);
-            if (NA == 2) tma_load_4d(sA + TC_A_BYTES, &tmA, kb * kx, un.row0, 1, e, &sh.full[st]);
-            tma_load_2d(sB, &tmB, kb * kx, a.tok0, &sh.full[st]);
+          if (a.tiled) {
+            // Pre-tiled weights: [matrix][k block][rows padded to 8][128 B], already in the swizzled order, so a
+            // tile of this K block is ONE contiguous run of up to 16 KB.
+            const int rows_here = min(TC_BM, rows_p8 - un.row0);
+            const uint32_t abytes = static_cast<uint32_t>(rows_here) * TC_BKB;
+            const uint32_t bbytes = a.x_rows1 ? TC_BKB : B_BYTES;
+            mbar_arrive_expect_tx(&sh.full[st], NA * abytes + bbytes);
+            const size_t panel = static_cast<size_t>(rows_p8) * TC_BKB;                 // one K block of one matrix
+            const size_t mat = (a.mode == IHB_TC_GATEUP) ? static_cast<size_t>(e) * 2 : static_cast<size_t>(e);
+            const uint8_t* src = reinterpret_cast<const uint8_t*>(a.W) + (mat * nkb_total + kb) * panel +
+                                 static_cast<size_t>(un.row0) * TC_BKB;
+            bulk_g2s(sA, src, abytes, &sh.full[st]);
+            if (NA == 2) bulk_g2s(sA + TC_A_BYTES, src + static_cast<size_t>(nkb_total) * panel, abytes, &sh.full[st]);
+            if (a.x_rows1) {
+              // one token: row 0 of the (pre-zeroed) activation tile; the swizzle of row 0 is the identity
+              const uint8_t* xs = reinterpret_cast<const uint8_t*>(a.X) +
+                                  (static_cast<size_t>(a.mode == IHB_TC_DOWN ? un.slot : 0) * nkb_total + kb) * TC_BKB;
+              bulk_g2s(sB, xs, TC_BKB, &sh.full[st]);
+            } else if (a.mode == IHB_TC_DOWN) {
+              tma_load_3d(sB, &tmB, kb * kx, a.tok0, un.slot, &sh.full[st]);
+            } else {
+              tma_load_2d(sB, &tmB, kb * kx, a.tok0, &sh.full[st]);
+            }
           } else {
-            tma_load_3d(sA, &tmA, kb * kx, un.row0, e, &sh.full[st]);
-            tma_load_3d(sB, &tmB, kb * kx, a.tok0, un.slot, &sh.full[st]);
+            mbar_arrive_expect_tx(&sh.full[st], STAGE_BYTES);
+            if (a.mode == IHB_TC_LINEAR) {
+              tma_load_2d(sA, &tmA, kb * kx, un.row0, &sh.full[st]);
+              tma_load_2d(sB, &tmB, kb * kx, a.tok0, &sh.full[st]);
+            } else if (a.mode == IHB_TC_GATEUP) {
+              tma_load_4d(sA, &tmA, kb * kx, un.row0, 0, e, &sh.full[st]);
+              if (NA == 2) tma_load_4d(sA + TC_A_BYTES, &tmA, kb * kx, un.row0, 1, e, &sh.full[st]);
+              tma_load_2d(sB, &tmB, kb * kx, a.tok0, &sh.full[st]);
+            } else {
+              tma_load_3d(sA, &tmA, kb * kx, un.row0, e, &sh.full[st]);
+              tma_load_3d(sB, &tmB, kb * kx, a.tok0, un.slot, &sh.full[st]);
+            }
           }
         }
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == TC_MMA_WARP) {
     // =============================== MMA issuer ========================================================================
     if (lane == 0) {
       int g = 0, ui = 0;
@@ -270,9 +215,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           ok = tc_wait(&sh.full[st], (g / S) & 1u, abort_flag, a.err, ERR_MBAR_FULL_TIMEOUT);
           if (!ok) break;
           const int j = (KIND == 0) ? g : ui;            // accumulator use counter
-          const int b = j & 1;
-          if ((KIND == 0 || kb == un.kb0) && j >= 2) {
-            ok = tc_wait(&sh.tmem_empty[b], ((j >> 1) & 1u) ^ 1u, abort_flag, a.err, ERR_TMEM_TIMEOUT);
+          const int b = j % NBUF;
+          if ((KIND == 0 || kb == un.kb0) && j >= NBUF) {
+            ok = tc_wait(&sh.tmem_empty[b], ((j / NBUF) & 1u) ^ 1u, abort_flag, a.err, ERR_TMEM_TIMEOUT);
             if (!ok) break;
           }
           tc_fence_after();
@@ -281,10 +226,11 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 #pragma unroll
           for (int ai = 0; ai < NA; ++ai) {
             const uint64_t adesc = smem_desc_sw128(sA + ai * TC_A_BYTES);
-            const uint32_t d = tmem_base + static_cast<uint32_t>(b * NA * NT + ai * NT);
 #pragma unroll
             for (int k = 0; k < TC_BKB / 32; ++k) {
-              const uint32_t accf = (KIND == 0) ? (k > 0) : (kb > un.kb0 || k > 0);
+              const int sub = (SUB == 1) ? 0 : k;
+              const uint32_t d = tmem_base + static_cast<uint32_t>(b * BUF_COLS + (ai * SUB + sub) * NT);
+              const uint32_t accf = (KIND == 0) ? (SUB == 1 && k > 0) : (kb > un.kb0 || (SUB == 1 && k > 0));
               tc_mma<KIND>(d, adesc + 2 * k, bdesc + 2 * k, idesc, accf);   // +32 bytes of K per step
             }
           }
@@ -298,7 +244,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const int quarter = warp & 3;
     const int r_in_tile = quarter * 32 + lane;
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
-    const int etid = tid - 64;                         // 0..127
+    const int etid = tid - 128;                        // 0..127
     int g = 0, ui = 0;
     bool ok = true;
     for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x, ++ui) {
@@ -330,8 +276,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             ws[ai] = ws_next[ai];
             if (kb + 1 < un.kb1) ws_next[ai] = __ldg(wsp[ai] + kb + 1);
           }
-          const int b = g & 1;
-          ok = tc_wait(&sh.tmem_full[b], (g >> 1) & 1u, abort_flag, a.err, ERR_TMEM_TIMEOUT);
+          const int b = g % NBUF;
+          ok = tc_wait(&sh.tmem_full[b], (g / NBUF) & 1u, abort_flag, a.err, ERR_TMEM_TIMEOUT);
           if (!ok) break;
           tc_fence_after();
           const float* xk = xsl + static_cast<size_t>(kb) * NT;
@@ -340,7 +286,14 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 #pragma unroll
             for (int c = 0; c < NT; c += 16) {
               float d[16];
-              tmem_ld16(lane_addr + static_cast<uint32_t>(b * NA * NT + ai * NT + c), d);
+              tmem_ld16(lane_addr + static_cast<uint32_t>(b * BUF_COLS + ai * SUB * NT + c), d);
+#pragma unroll
+              for (int sub = 1; sub < SUB; ++sub) {
+                float d2[16];
+                tmem_ld16(lane_addr + static_cast<uint32_t>(b * BUF_COLS + (ai * SUB + sub) * NT + c), d2);
+#pragma unroll
+                for (int n = 0; n < 16; ++n) d[n] += d2[n];
+              }
 #pragma unroll
               for (int n = 0; n < 16; ++n) acc[ai][c + n] = fmaf(d[n], ws[ai] * xk[c + n], acc[ai][c + n]);
             }
@@ -351,14 +304,23 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
       } else {
         g += un.kb1 - un.kb0;
-        const int b = ui & 1;
-        ok = tc_wait(&sh.tmem_full[b], (ui >> 1) & 1u, abort_flag, a.err, ERR_TMEM_TIMEOUT);
+        const int b = ui % NBUF;
+        ok = tc_wait(&sh.tmem_full[b], (ui / NBUF) & 1u, abort_flag, a.err, ERR_TMEM_TIMEOUT);
         if (ok) {
           tc_fence_after();
 #pragma unroll
           for (int ai = 0; ai < NA; ++ai)
 #pragma unroll
-            for (int c = 0; c < NT; c += 16) tmem_ld16(lane_addr + static_cast<uint32_t>(b * NA * NT + ai * NT + c), &acc[ai][c]);
+            for (int c = 0; c < NT; c += 16) {
+              tmem_ld16(lane_addr + static_cast<uint32_t>(b * BUF_COLS + ai * SUB * NT + c), &acc[ai][c]);
+#pragma unroll
+              for (int sub = 1; sub < SUB; ++sub) {
+                float d2[16];
+                tmem_ld16(lane_addr + static_cast<uint32_t>(b * BUF_COLS + (ai * SUB + sub) * NT + c), d2);
+#pragma unroll
+                for (int n = 0; n < 16; ++n) acc[ai][c + n] += d2[n];
+              }
+            }
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(&sh.tmem_empty[b]);
@@ -430,7 +392,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   // ---- teardown: every role arrives here, also after a time-out ------------------------------------------------------------------
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) {
+  if (warp == TC_MMA_WARP) {
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
@@ -515,7 +477,11 @@ extern "C" int ihb_tc_gemm(IhbTcArgs* args, int use_pdl, cudaStream_t stream) {
   const cuuint64_t rowb = Kd * esize;
   const cuuint32_t kbox = TC_BKB / esize;
   CUresult r;
-  if (a.mode == IHB_TC_LINEAR) {
+  memset(&tmA, 0, sizeof(tmA));
+  memset(&tmB, 0, sizeof(tmB));
+  if (a.tiled) {
+    r = CUDA_SUCCESS;
+  } else if (a.mode == IHB_TC_LINEAR) {
     cuuint64_t dims[2] = {Kd, static_cast<cuuint64_t>(a.rows)};
     cuuint64_t str[1] = {rowb};
     cuuint32_t box[2] = {kbox, TC_BM};
@@ -532,7 +498,10 @@ extern "C" int ihb_tc_gemm(IhbTcArgs* args, int use_pdl, cudaStream_t stream) {
     r = encode_map(&tmA, is_fp8, const_cast<void*>(a.W), 3, dims, str, box);
   }
   if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
-  if (a.mode == IHB_TC_DOWN) {                // X: [top_k][T][K]
+  if (a.x_rows1) {
+    if (a.T != 1 || !a.tiled) return cudaErrorInvalidValue;
+    r = CUDA_SUCCESS;
+  } else if (a.mode == IHB_TC_DOWN) {                // X: [top_k][T][K]
     cuuint64_t dims[3] = {Kd, static_cast<cuuint64_t>(a.T_total), static_cast<cuuint64_t>(a.top_k)};
     cuuint64_t str[2] = {rowb, rowb * a.T_total};
     cuuint32_t box[3] = {kbox, static_cast<cuuint32_t>(nt), 1};

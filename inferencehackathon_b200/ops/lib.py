@@ -67,7 +67,8 @@ class IhbTcArgs(C.Structure):
                 ("X", _vp), ("xscale", _vp), ("T", C.c_int), ("T_total", C.c_int), ("tok0", C.c_int),
                 ("mode", C.c_int), ("sel_idx", _vp), ("sel_w", _vp),
                 ("out", _vp), ("out_stride", C.c_int), ("partial", _vp), ("tile_counters", _vp),
-                ("ks", C.c_int), ("S", C.c_int), ("grid", C.c_int), ("n_units", C.c_int), ("err", _vp)]
+                ("ks", C.c_int), ("S", C.c_int), ("grid", C.c_int), ("n_units", C.c_int), ("err", _vp),
+                ("tiled", C.c_int), ("x_rows1", C.c_int)]
 
 
 _lib: Optional[C.CDLL] = None
@@ -234,3 +235,26 @@ def tc_fill_weight(args: IhbTcArgs, qw) -> None:
         ks = kernel_scale(qw)
         args.wscale = ks.data_ptr()
         args.rb, args.nrb, args.nkb_stride = qw.rb, ks.shape[-2], ks.shape[-1]
+
+
+def tile_weight(data: torch.Tensor) -> torch.Tensor:
+    """Repack ``data[..., rows, K]`` (e4m3 or bf16) into the tensor-core kernels' HBM layout
+    ``[..., k block, rows padded to 8, 128 B]`` with the 16-byte chunks of every row XOR-swizzled by
+    ``row % 8``: a 128-row tile of one 128-byte K block is then one contiguous 16 KB run that a single bulk
+    copy drops into shared memory in exactly the order the MMA's 128-byte-swizzle descriptor expects."""
+    *lead, rows, K = data.shape
+    raw = data.contiguous().view(torch.uint8).reshape(*lead, rows, -1)
+    rowb = raw.shape[-1]
+    nkb = (rowb + 127) // 128
+    rows_p8 = (rows + 7) // 8 * 8
+    raw = torch.nn.functional.pad(raw, (0, nkb * 128 - rowb, 0, rows_p8 - rows))
+    v = raw.reshape(*lead, rows_p8 // 8, 8, nkb, 8, 16)                 # [.., grp, r, kb, chunk, 16]
+    r = torch.arange(8, device=data.device)
+    c = torch.arange(8, device=data.device)
+    src_chunk = (c[None, :] ^ r[:, None])                                # dst chunk c of row r holds src chunk c ^ r
+    idx = src_chunk[None, :, None, :, None].expand(v.shape[-5], 8, nkb, 8, 16)
+    for _ in lead:
+        idx = idx[None]
+    v = torch.gather(v, -2, idx.expand(v.shape))
+    out = v.permute(*range(len(lead)), len(lead) + 2, len(lead), len(lead) + 1, len(lead) + 3, len(lead) + 4)
+    return out.contiguous().reshape(*lead, nkb, rows_p8, 128)

@@ -47,10 +47,17 @@ def _common(lib, a, T):
     return err, n
 
 
+def _pad_rows128(x):
+    """[.., K] activations as plain rows padded to a multiple of 128 bytes (single-token kernel input)."""
+    raw = x.contiguous().view(torch.uint8).reshape(*x.shape[:-1], -1)
+    return torch.nn.functional.pad(raw, (0, (-raw.shape[-1]) % 128)).contiguous()
+
+
 @pytest.mark.parametrize("fp8", [True, False])
+@pytest.mark.parametrize("tiled", [False, True])
 @pytest.mark.parametrize("rows,K,T,ks", [(256, 512, 1, 1), (1280, 4096, 1, 0), (4096, 1024, 5, 4), (640, 2048, 17, 0),
-                                         (200, 768, 40, 2), (512, 4096, 128, 1)])
-def test_tc_linear(fp8, rows, K, T, ks):
+                                         (200, 768, 40, 2), (512, 4096, 128, 1), (4096, 192, 1, 0)])
+def test_tc_linear(fp8, tiled, rows, K, T, ks):
     lib = _K()
     g = torch.Generator(device=_dev()).manual_seed(rows + K + T)
     qw = _weights(rows, K, fp8, g)
@@ -59,6 +66,12 @@ def test_tc_linear(fp8, rows, K, T, ks):
     a = lib.IhbTcArgs()
     lib.tc_fill_weight(a, qw)
     a.X, a.mode, a.out, a.out_stride, a.ks = xq.data_ptr(), lib.TC_LINEAR, out.data_ptr(), rows, ks
+    if tiled:
+        wt = lib.tile_weight(qw.data)
+        a.W, a.tiled = wt.data_ptr(), 1
+        if T == 1:
+            xrow = _pad_rows128(xq[0])
+            a.X, a.x_rows1 = xrow.data_ptr(), 1
     if fp8:
         a.xscale = xs.data_ptr()
     a.T, a.T_total, a.tok0 = T, T, 0
@@ -79,8 +92,9 @@ def test_tc_linear(fp8, rows, K, T, ks):
 
 
 @pytest.mark.parametrize("fp8", [True, False])
+@pytest.mark.parametrize("tiled", [False, True])
 @pytest.mark.parametrize("H,I,E,k,T", [(1024, 256, 8, 4, 1), (2048, 192, 16, 8, 1), (1024, 768, 8, 8, 3)])
-def test_tc_moe_gateup_down(fp8, H, I, E, k, T):
+def test_tc_moe_gateup_down(fp8, tiled, H, I, E, k, T):
     lib = _K()
     d = _dev()
     g = torch.Generator(device=d).manual_seed(H + I + T)
@@ -97,6 +111,12 @@ def test_tc_moe_gateup_down(fp8, H, I, E, k, T):
     a.rows = I
     a.expert0, a.top_k, a.sel_idx, a.sel_w = 0, k, sel.data_ptr(), sw.data_ptr()
     a.X, a.mode, a.out, a.out_stride = xq.data_ptr(), lib.TC_GATEUP, act.data_ptr(), I
+    if tiled:
+        wgt = lib.tile_weight(wgu.data.reshape(E, 2, I, H))
+        a.W, a.tiled = wgt.data_ptr(), 1
+        if T == 1:
+            xrow = _pad_rows128(xq[0])
+            a.X, a.x_rows1 = xrow.data_ptr(), 1
     if fp8:
         a.xscale = xs.data_ptr()
     a.T, a.T_total, a.tok0, a.err = T, T, 0, err.data_ptr()
@@ -119,6 +139,12 @@ def test_tc_moe_gateup_down(fp8, H, I, E, k, T):
     lib.tc_fill_weight(b, wd)
     b.expert0, b.top_k, b.sel_idx, b.sel_w = 0, k, sel.data_ptr(), sw.data_ptr()
     b.X, b.mode, b.out, b.out_stride = aq.data_ptr(), lib.TC_DOWN, out.data_ptr(), H
+    if tiled:
+        wdt = lib.tile_weight(wd.data)
+        b.W, b.tiled = wdt.data_ptr(), 1
+        if T == 1:
+            arow = _pad_rows128(aq[:, 0])
+            b.X, b.x_rows1 = arow.data_ptr(), 1
     if fp8:
         b.xscale = asc.data_ptr()
     b.T, b.T_total, b.tok0, b.err = T, T, 0, err.data_ptr()
