@@ -99,8 +99,11 @@ int ihb_moe_gateup(IhbMoeArgs* args, int use_pdl, cudaStream_t stream);
 int ihb_moe_down(IhbMoeArgs* args, int use_pdl, cudaStream_t stream);
 
 // Embedding gather + first RMSNorm: resid = embed[*token]; xn = rmsnorm(resid) * gamma.
+// xq / xs (optional): the normed vector again as a tensor-core activation row (e4m3 + scale per 128 channels when
+// xq_fp8, else bf16).
 int ihb_embed_norm(const void* embed, int embed_is_bf16, const int* token, int H, const float* gamma, float eps,
-                   float* resid, float* xn, int use_pdl, cudaStream_t stream);
+                   float* resid, float* xn, unsigned char* xq, float* xs, int xq_fp8, int use_pdl,
+                   cudaStream_t stream);
 
 // Per-head QK RMSNorm + NeoX RoPE at position *pos; writes q in place and K/V (bf16) into the cache row *pos.
 // qkv: [(nq + 2 nkv) * 128] fp32 (Q heads, K heads, V heads); cos/sin: [max_seq, 64] fp32 tables.
@@ -110,10 +113,11 @@ int ihb_qk_norm_rope_kv(float* qkv, int nq, int nkv, const float* q_gamma, const
 
 // Split-KV GQA flash-decode over positions [0, *pos] with an in-kernel merge by the last CTA of each KV head.
 // q: [nq, 128] fp32 (already normed + roped); k_cache/v_cache: [nkv, max_seq, 128] bf16; out: [nq, 128] fp32.
+// out_q / out_s (optional): the output again as the o_proj kernel's activation row (one scale per head).
 // scratch: nq * nsplit * 130 floats (partial acc, m, l); counters: nq unsigned, zero before the first launch.
 int ihb_flash_decode(const float* q, const void* k_cache, const void* v_cache, int nq, int nkv, int max_seq,
-                     const int* pos, int nsplit, float* scratch, unsigned* counters, float* out, int use_pdl,
-                     cudaStream_t stream);
+                     const int* pos, int nsplit, float* scratch, unsigned* counters, float* out, unsigned char* out_q,
+                     float* out_s, int out_fp8, int use_pdl, cudaStream_t stream);
 size_t ihb_flash_decode_scratch_floats(int nq, int nsplit);
 
 // ---- tensor-core linear layers (tcgen05 / TMEM / TMA) ------------------------------------------------------------
@@ -150,6 +154,56 @@ typedef struct {
 
 int ihb_tc_gemm(IhbTcArgs* args, int use_pdl, cudaStream_t stream);
 size_t ihb_tc_partial_floats(const IhbTcArgs* args);
+
+// ---- single-token tensor-core linear layers with fused epilogues (the decode hot path) ----------------------------
+enum { IHB_DEC_STORE = 0, IHB_DEC_AR_NORM = 1, IHB_DEC_ARGMAX = 2, IHB_DEC_ACT = 3 };
+
+// y[r] = sum_k x[k] W[r, k] for ONE token. Weights are pre-tiled for HBM streaming:
+//   W: [matrix][row tile][k block][rows of the tile, padded to 8][128 B], 16-byte chunks XOR-swizzled by row % 8
+//   (matrix = expert, or expert * 2 + {gate, up}); a row tile's K blocks are contiguous, so one bulk copy moves
+//   two of them (32 KB) into shared memory in the order the MMA descriptor expects.
+//   X: [slots][k blocks * 128 B] plain activation rows (e4m3 or bf16), xscale [slots][k blocks] (e4m3 only).
+// mode LINEAR + epi STORE / AR_NORM / ARGMAX; mode GATEUP + epi ACT (SwiGLU, then re-quantised per 128 rows as
+// the down projection's input); mode DOWN + epi AR_NORM (sum over routing slots, weighted).
+typedef struct {
+  const void* W;
+  const float* wscale;     // e4m3: [matrix rows / rb][nkb_stride] per expert: [E][nrb][nkb_stride]
+  int wtype;
+  int rows, K;
+  int rb, nrb, nkb_stride;
+  int n_experts, expert0, top_k;
+  const void* X;
+  const float* xscale;
+  int mode, epi;
+  const int* sel_idx;
+  const float* sel_w;
+  float* out;              // STORE: [rows] fp32; ARGMAX: optional logits [rows]
+  unsigned char* act_q;    // ACT: [top_k][ceil(I * esize / 128) * 128 B]
+  float* act_s;            // ACT (e4m3): [top_k][ceil(I / 128)]
+  float* partial;          // ihb_tc_dec_partial_floats() floats (several units per output tile)
+  unsigned* tile_counters; // one per output tile, zero before the first launch
+  int ks, S, grid, n_units;
+  unsigned* counter;       // last-CTA election (AR_NORM, ARGMAX), zero before the first launch
+  unsigned* err;
+  unsigned long long* argmax_partial;   // [grid]
+  int vocab0;
+  int* cur_token;
+  int* pos;
+  int* token_ring;
+  int token_ring_size;
+  const int* forced;
+  const int* n_forced;
+  float* resid;            // AR_NORM: as in IhbGemvArgs
+  const float* gamma;
+  float* xn_out;
+  float eps;
+  unsigned char* xq;       // AR_NORM: normed vector as the next tensor-core kernel's activation row (optional)
+  float* xs;
+  IhbComm comm;
+} IhbTcDecArgs;
+
+int ihb_tc_decode(IhbTcDecArgs* args, int use_pdl, cudaStream_t stream);
+size_t ihb_tc_dec_partial_floats(const IhbTcDecArgs* args);
 
 #ifdef __cplusplus
 }

@@ -8,6 +8,7 @@
 // The position counter lives in device memory so that a captured CUDA graph replays without host updates.
 #include "common.cuh"
 #include "api.h"
+#include "tails.cuh"
 
 namespace ihb {
 
@@ -17,24 +18,31 @@ constexpr int HD = 128;
 __global__ void __launch_bounds__(256) embed_norm_kernel(const void* __restrict__ embed, int is_bf16,
                                                          const int* __restrict__ token, int H,
                                                          const float* __restrict__ gamma, float eps,
-                                                         float* __restrict__ resid, float* __restrict__ xn) {
+                                                         float* __restrict__ resid, float* __restrict__ xn,
+                                                         uint8_t* __restrict__ xq, float* __restrict__ xs, int xq_fp8) {
   __shared__ float red[8];
   pdl_wait();
   pdl_launch_dependents();
   const int tok = ld_cg_i(token);
   const int tid = threadIdx.x;
-  constexpr int MAXP = 32;                 // H <= 8192
-  float v[MAXP];
+  constexpr int MAXV = 8;                  // H <= 8192, multiple of 4: float4 j of thread t covers (t + 256 j) * 4
+  float4 v[MAXV];
   float ss = 0.f;
 #pragma unroll
-  for (int j = 0; j < MAXP; ++j) {
-    const int i = tid + 256 * j;
-    v[j] = 0.f;
+  for (int j = 0; j < MAXV; ++j) {
+    const int i = (tid + 256 * j) * 4;
+    v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
     if (i < H) {
-      if (is_bf16) v[j] = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(embed)[static_cast<size_t>(tok) * H + i]);
-      else v[j] = reinterpret_cast<const float*>(embed)[static_cast<size_t>(tok) * H + i];
+      if (is_bf16) {
+        const uint2 r = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(embed) +
+                                                        static_cast<size_t>(tok) * H + i);
+        v[j] = make_float4(__uint_as_float(r.x << 16), __uint_as_float(r.x & 0xffff0000u),
+                           __uint_as_float(r.y << 16), __uint_as_float(r.y & 0xffff0000u));
+      } else {
+        v[j] = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(embed) + static_cast<size_t>(tok) * H + i);
+      }
     }
-    ss += v[j] * v[j];
+    ss += v[j].x * v[j].x + v[j].y * v[j].y + v[j].z * v[j].z + v[j].w * v[j].w;
   }
   ss = warp_sum(ss);
   if ((tid & 31) == 0) red[tid >> 5] = ss;
@@ -44,11 +52,17 @@ __global__ void __launch_bounds__(256) embed_norm_kernel(const void* __restrict_
   for (int w = 0; w < 8; ++w) tot += red[w];
   const float rinv = rsqrtf(tot / static_cast<float>(H) + eps);
 #pragma unroll
-  for (int j = 0; j < MAXP; ++j) {
-    const int i = tid + 256 * j;
+  for (int j = 0; j < MAXV; ++j) {
+    const int i = (tid + 256 * j) * 4;
     if (i < H) {
-      resid[i] = v[j];
-      xn[i] = v[j] * rinv * gamma[i];
+      const float4 g = *reinterpret_cast<const float4*>(gamma + i);
+      const float4 o = make_float4(v[j].x * rinv * g.x, v[j].y * rinv * g.y, v[j].z * rinv * g.z, v[j].w * rinv * g.w);
+      *reinterpret_cast<float4*>(resid + i) = v[j];
+      *reinterpret_cast<float4*>(xn + i) = o;
+      if (xq != nullptr) {                 // needs H % 128 == 0: a warp covers one group of 128 channels
+        if (xq_fp8) quant_group128(o, xq + i, xs + (i >> 7), tid & 31);
+        else store_bf16x4(o, xq + 2 * i);
+      }
     }
   }
 }
@@ -120,7 +134,9 @@ template <int GQ>
 __global__ void __launch_bounds__(FD_WARPS * 32) flash_decode_kernel(
     const float* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
     const __nv_bfloat16* __restrict__ v_cache, int nq, int nkv, int max_seq, const int* __restrict__ pos_p,
-    int nsplit, float* __restrict__ scratch, unsigned* __restrict__ counters, float* __restrict__ out) {
+    int nsplit, float* __restrict__ scratch, unsigned* __restrict__ counters, float* __restrict__ out,
+    uint8_t* __restrict__ out_q, float* __restrict__ out_s, int out_fp8) {
+  __shared__ float red_m[FD_WARPS];
   __shared__ __align__(16) float q_s[GQ][HD];
   __shared__ __align__(16) float p_s[FD_WARPS][GQ][32];
   __shared__ float m_s[FD_WARPS][GQ], l_s[FD_WARPS][GQ];
@@ -269,7 +285,24 @@ __global__ void __launch_bounds__(FD_WARPS * 32) flash_decode_kernel(
         L += ld_cg_f(recs + sp * FD_REC + HD + 1) * f;
       }
     }
-    out[static_cast<size_t>(head0 + g) * HD + d] = a / L;
+    const float o = a / L;
+    out[static_cast<size_t>(head0 + g) * HD + d] = o;
+    if (out_q != nullptr) {
+      // one iteration of this loop is one head = one group of 128 channels of the o_proj input row
+      if (out_fp8) {
+        const float mx = warp_max(fabsf(o));
+        if (lane == 0) red_m[warp] = mx;
+        __syncthreads();
+        const float amax = fmaxf(fmaxf(red_m[0], red_m[1]), fmaxf(red_m[2], red_m[3]));
+        const float sc = fmaxf(amax, 1e-12f) * (1.f / 448.f);
+        out_q[static_cast<size_t>(head0 + g) * HD + d] =
+            static_cast<uint8_t>(__nv_cvt_float_to_fp8(o / sc, __NV_SATFINITE, __NV_E4M3));
+        if (tid == 0) out_s[head0 + g] = sc;
+        __syncthreads();
+      } else {
+        reinterpret_cast<__nv_bfloat16*>(out_q)[static_cast<size_t>(head0 + g) * HD + d] = __float2bfloat16(o);
+      }
+    }
   }
 }
 
@@ -290,11 +323,13 @@ static void pdl_cfg(cudaLaunchConfig_t& cfg, cudaLaunchAttribute* attr, dim3 gri
 using namespace ihb;
 
 extern "C" int ihb_embed_norm(const void* embed, int embed_is_bf16, const int* token, int H, const float* gamma,
-                              float eps, float* resid, float* xn, int use_pdl, cudaStream_t stream) {
+                              float eps, float* resid, float* xn, unsigned char* xq, float* xs, int xq_fp8, int use_pdl,
+                              cudaStream_t stream) {
+  if (H % 4 || H > 8192 || (xq != nullptr && H % 128)) return cudaErrorInvalidValue;
   cudaLaunchConfig_t cfg = {};
   cudaLaunchAttribute attr[1];
   pdl_cfg(cfg, attr, dim3(1), dim3(256), use_pdl, stream);
-  return cudaLaunchKernelEx(&cfg, embed_norm_kernel, embed, embed_is_bf16, token, H, gamma, eps, resid, xn);
+  return cudaLaunchKernelEx(&cfg, embed_norm_kernel, embed, embed_is_bf16, token, H, gamma, eps, resid, xn, xq, xs, xq_fp8);
 }
 
 extern "C" int ihb_qk_norm_rope_kv(float* qkv, int nq, int nkv, const float* q_gamma, const float* k_gamma,
@@ -314,7 +349,8 @@ extern "C" size_t ihb_flash_decode_scratch_floats(int nq, int nsplit) {
 
 extern "C" int ihb_flash_decode(const float* q, const void* k_cache, const void* v_cache, int nq, int nkv,
                                 int max_seq, const int* pos, int nsplit, float* scratch, unsigned* counters,
-                                float* out, int use_pdl, cudaStream_t stream) {
+                                float* out, unsigned char* out_q, float* out_s, int out_fp8, int use_pdl,
+                                cudaStream_t stream) {
   if (nq % nkv || nsplit < 1) return cudaErrorInvalidValue;
   const int q_per_kv = nq / nkv;
   int gq = q_per_kv >= 8 ? 8 : q_per_kv;
@@ -325,9 +361,9 @@ extern "C" int ihb_flash_decode(const float* q, const void* k_cache, const void*
   const __nv_bfloat16* kc = reinterpret_cast<const __nv_bfloat16*>(k_cache);
   const __nv_bfloat16* vc = reinterpret_cast<const __nv_bfloat16*>(v_cache);
   switch (gq) {
-    case 8: return cudaLaunchKernelEx(&cfg, flash_decode_kernel<8>, q, kc, vc, nq, nkv, max_seq, pos, nsplit, scratch, counters, out);
-    case 4: return cudaLaunchKernelEx(&cfg, flash_decode_kernel<4>, q, kc, vc, nq, nkv, max_seq, pos, nsplit, scratch, counters, out);
-    case 2: return cudaLaunchKernelEx(&cfg, flash_decode_kernel<2>, q, kc, vc, nq, nkv, max_seq, pos, nsplit, scratch, counters, out);
-    default: return cudaLaunchKernelEx(&cfg, flash_decode_kernel<1>, q, kc, vc, nq, nkv, max_seq, pos, nsplit, scratch, counters, out);
+    case 8: return cudaLaunchKernelEx(&cfg, flash_decode_kernel<8>, q, kc, vc, nq, nkv, max_seq, pos, nsplit, scratch, counters, out, out_q, out_s, out_fp8);
+    case 4: return cudaLaunchKernelEx(&cfg, flash_decode_kernel<4>, q, kc, vc, nq, nkv, max_seq, pos, nsplit, scratch, counters, out, out_q, out_s, out_fp8);
+    case 2: return cudaLaunchKernelEx(&cfg, flash_decode_kernel<2>, q, kc, vc, nq, nkv, max_seq, pos, nsplit, scratch, counters, out, out_q, out_s, out_fp8);
+    default: return cudaLaunchKernelEx(&cfg, flash_decode_kernel<1>, q, kc, vc, nq, nkv, max_seq, pos, nsplit, scratch, counters, out, out_q, out_s, out_fp8);
   }
 }

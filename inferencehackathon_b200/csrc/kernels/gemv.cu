@@ -80,53 +80,6 @@ __device__ void tail_router(const IhbGemvArgs& a, int lane) {
   }
 }
 
-__device__ void tail_argmax(const IhbGemvArgs& a, int tid, unsigned long long* red_smem, int nblocks) {
-  unsigned long long best = 0ull;
-  for (int i = tid; i < nblocks; i += CONSUMER_THREADS) {
-    const unsigned long long p = ld_cg_u64(a.argmax_partial + i);
-    best = p > best ? p : best;
-  }
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    const unsigned long long q = __shfl_xor_sync(0xffffffffu, best, o);
-    best = q > best ? q : best;
-  }
-  if ((tid & 31) == 0) red_smem[tid >> 5] = best;
-  named_bar_sync(1, CONSUMER_THREADS);
-  if (tid == 0) {
-#pragma unroll
-    for (int w = 0; w < NCW; ++w) best = red_smem[w] > best ? red_smem[w] : best;
-    const IhbComm& cm = a.comm;
-    // local winner carries the GLOBAL token id so that ties across ranks resolve to the lowest id
-    unsigned long long mine = (best & 0xffffffff00000000ull) |
-                              (0xffffffffu - (unpack_idx(best) + static_cast<unsigned>(a.vocab0)));
-    if (cm.nranks > 1) {
-      const unsigned epoch = *cm.epoch;
-      const int parity = epoch & 1u;
-      unsigned long long* slot_local = cm.arg_slots_local + parity * cm.nranks;
-      if (cm.arg_slots_mc != nullptr) {
-        multimem_st_u64(cm.arg_slots_mc + parity * cm.nranks + cm.rank, mine);
-      } else {
-        for (int r = 0; r < cm.nranks; ++r)
-          st_relaxed_sys_u64(cm.arg_slots_peer[r] + parity * cm.nranks + cm.rank, mine);
-      }
-      peer_barrier(cm, (epoch + 1u) * static_cast<unsigned>(cm.nranks), a.err);
-      for (int r = 0; r < cm.nranks; ++r) {
-        const unsigned long long p = ld_cg_u64(slot_local + r);
-        mine = p > mine ? p : mine;
-      }
-      *cm.epoch = epoch + 1u;
-    }
-    const int tok = static_cast<int>(unpack_idx(mine));
-    const int pos = *a.pos;
-    int next = tok;
-    if (a.forced != nullptr && pos + 1 < *a.n_forced) next = a.forced[pos + 1];
-    *a.cur_token = next;
-    if (a.token_ring != nullptr) a.token_ring[pos % a.token_ring_size] = tok;
-    *a.pos = pos + 1;
-  }
-}
-
 // ---- the kernel ----------------------------------------------------------------------------------------------------
 
 template <int WT, int NI, int EPI>
@@ -265,7 +218,11 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) gemv_kernel(const IhbGemvAr
     tail_ar_norm<CONSUMER_THREADS, 1>(t, tid, red_f);
   }
   if (EPI == IHB_EPI_ROUTER) { if (warp == 0) tail_router(a, lane); }
-  if (EPI == IHB_EPI_ARGMAX) tail_argmax(a, tid, red_u, gridDim.x);
+  if (EPI == IHB_EPI_ARGMAX) {
+    ArgmaxTail t{a.comm, a.argmax_partial, static_cast<int>(gridDim.x), a.vocab0, a.cur_token, a.pos, a.token_ring,
+                 a.token_ring_size, a.forced, a.n_forced, a.err};
+    tail_argmax<CONSUMER_THREADS, 1>(t, tid, red_u);
+  }
 }
 
 template <int WT, int NI>

@@ -123,6 +123,72 @@ __device__ __forceinline__ void tail_ar_norm(const ArNormTail& a, int tid, float
 }
 
 
+struct ArgmaxTail {
+  IhbComm comm;
+  unsigned long long* argmax_partial;   // one packed (value, local row) per CTA
+  int nblocks;
+  int vocab0;
+  int* cur_token;
+  int* pos;
+  int* token_ring;
+  int token_ring_size;
+  const int* forced;
+  const int* n_forced;
+  unsigned* err;
+};
+
+// Last CTA: global argmax over the per-CTA maxima (and over the ranks of a vocabulary-sharded head), next token
+// and position counter update.
+template <int NTHR, int BAR>
+__device__ __forceinline__ void tail_argmax(const ArgmaxTail& a, int tid, unsigned long long* red_smem) {
+  const int nblocks = a.nblocks;
+  unsigned long long best = 0ull;
+  for (int i = tid; i < nblocks; i += NTHR) {
+    const unsigned long long p = ld_cg_u64(a.argmax_partial + i);
+    best = p > best ? p : best;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const unsigned long long q = __shfl_xor_sync(0xffffffffu, best, o);
+    best = q > best ? q : best;
+  }
+  if ((tid & 31) == 0) red_smem[tid >> 5] = best;
+  named_bar_sync(BAR, NTHR);
+  if (tid == 0) {
+#pragma unroll
+    for (int w = 0; w < NTHR / 32; ++w) best = red_smem[w] > best ? red_smem[w] : best;
+    const IhbComm& cm = a.comm;
+    // local winner carries the GLOBAL token id so that ties across ranks resolve to the lowest id
+    unsigned long long mine = (best & 0xffffffff00000000ull) |
+                              (0xffffffffu - (unpack_idx(best) + static_cast<unsigned>(a.vocab0)));
+    if (cm.nranks > 1) {
+      const unsigned epoch = *cm.epoch;
+      const int parity = epoch & 1u;
+      unsigned long long* slot_local = cm.arg_slots_local + parity * cm.nranks;
+      if (cm.arg_slots_mc != nullptr) {
+        multimem_st_u64(cm.arg_slots_mc + parity * cm.nranks + cm.rank, mine);
+      } else {
+        for (int r = 0; r < cm.nranks; ++r)
+          st_relaxed_sys_u64(cm.arg_slots_peer[r] + parity * cm.nranks + cm.rank, mine);
+      }
+      peer_barrier(cm, (epoch + 1u) * static_cast<unsigned>(cm.nranks), a.err);
+      for (int r = 0; r < cm.nranks; ++r) {
+        const unsigned long long p = ld_cg_u64(slot_local + r);
+        mine = p > mine ? p : mine;
+      }
+      *cm.epoch = epoch + 1u;
+    }
+    const int tok = static_cast<int>(unpack_idx(mine));
+    const int pos = *a.pos;
+    int next = tok;
+    if (a.forced != nullptr && pos + 1 < *a.n_forced) next = a.forced[pos + 1];
+    *a.cur_token = next;
+    if (a.token_ring != nullptr) a.token_ring[pos % a.token_ring_size] = tok;
+    *a.pos = pos + 1;
+  }
+}
+
+
 // Push one partial output value into slot `slot` of every GPU's buffer (or the local one).
 __device__ __forceinline__ void push_partial(const IhbComm& cm, size_t off, float y) {
   if (cm.nranks == 1) {

@@ -78,6 +78,14 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* d) {
   for (int i = 0; i < 16; ++i) d[i] = __uint_as_float(r[i]);
 }
 
+// One column of this thread's TMEM lane (issue several, then tmem_ld_wait()).
+__device__ __forceinline__ float tmem_ld1(uint32_t taddr) {
+  uint32_t r;
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(r) : "r"(taddr) : "memory");
+  return __uint_as_float(r);
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
 // Shared-memory matrix descriptor of a K-major tile with 128-byte rows and the 128-byte swizzle: 8-row groups
 // 1024 bytes apart (stride byte offset), descriptor version 1, layout type 2.
 __device__ __forceinline__ uint64_t smem_desc_sw128(const void* tile, uint32_t group_stride_bytes = 1024) {

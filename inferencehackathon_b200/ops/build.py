@@ -53,7 +53,7 @@ def _run(cmd: List[str]) -> None:
 
 def build_kernels(force: bool = False, verbose: bool = False) -> str:
     srcs = _sources("kernels", (".cu",))
-    deps = srcs + _sources("kernels", (".cuh", ".h"))
+    deps = srcs + _sources("kernels", (".cuh", ".h", ".inc"))
     digest = _digest(deps, " ".join(NVCC_FLAGS))
     if not force and not _stale(KERNEL_LIB, digest):
         return KERNEL_LIB

@@ -71,6 +71,24 @@ class IhbTcArgs(C.Structure):
                 ("tiled", C.c_int), ("x_rows1", C.c_int)]
 
 
+DEC_STORE, DEC_AR_NORM, DEC_ARGMAX, DEC_ACT = 0, 1, 2, 3
+
+
+class IhbTcDecArgs(C.Structure):
+    _fields_ = [("W", _vp), ("wscale", _vp), ("wtype", C.c_int), ("rows", C.c_int), ("K", C.c_int),
+                ("rb", C.c_int), ("nrb", C.c_int), ("nkb_stride", C.c_int),
+                ("n_experts", C.c_int), ("expert0", C.c_int), ("top_k", C.c_int),
+                ("X", _vp), ("xscale", _vp), ("mode", C.c_int), ("epi", C.c_int),
+                ("sel_idx", _vp), ("sel_w", _vp), ("out", _vp), ("act_q", _vp), ("act_s", _vp),
+                ("partial", _vp), ("tile_counters", _vp),
+                ("ks", C.c_int), ("S", C.c_int), ("grid", C.c_int), ("n_units", C.c_int),
+                ("counter", _vp), ("err", _vp),
+                ("argmax_partial", _vp), ("vocab0", C.c_int), ("cur_token", _vp), ("pos", _vp),
+                ("token_ring", _vp), ("token_ring_size", C.c_int), ("forced", _vp), ("n_forced", _vp),
+                ("resid", _vp), ("gamma", _vp), ("xn_out", _vp), ("eps", C.c_float), ("xq", _vp), ("xs", _vp),
+                ("comm", IhbComm)]
+
+
 _lib: Optional[C.CDLL] = None
 
 
@@ -92,17 +110,21 @@ def load(build_if_missing: bool = True) -> C.CDLL:
     lib.ihb_gemv.argtypes = [C.POINTER(IhbGemvArgs), C.c_int, _vp]
     lib.ihb_moe_gateup.argtypes = [C.POINTER(IhbMoeArgs), C.c_int, _vp]
     lib.ihb_moe_down.argtypes = [C.POINTER(IhbMoeArgs), C.c_int, _vp]
-    lib.ihb_embed_norm.argtypes = [_vp, C.c_int, _vp, C.c_int, _vp, C.c_float, _vp, _vp, C.c_int, _vp]
+    lib.ihb_embed_norm.argtypes = [_vp, C.c_int, _vp, C.c_int, _vp, C.c_float, _vp, _vp, _vp, _vp, C.c_int, C.c_int, _vp]
     lib.ihb_qk_norm_rope_kv.argtypes = [_vp, C.c_int, C.c_int, _vp, _vp, C.c_float, _vp, _vp, _vp, _vp, _vp,
                                         C.c_int, C.c_int, _vp]
     lib.ihb_flash_decode.argtypes = [_vp, _vp, _vp, C.c_int, C.c_int, C.c_int, _vp, C.c_int, _vp, _vp, _vp,
-                                     C.c_int, _vp]
+                                     _vp, _vp, C.c_int, C.c_int, _vp]
     lib.ihb_flash_decode_scratch_floats.argtypes = [C.c_int, C.c_int]
     lib.ihb_flash_decode_scratch_floats.restype = C.c_size_t
     lib.ihb_tc_gemm.argtypes = [C.POINTER(IhbTcArgs), C.c_int, _vp]
     lib.ihb_tc_gemm.restype = C.c_int
     lib.ihb_tc_partial_floats.argtypes = [C.POINTER(IhbTcArgs)]
     lib.ihb_tc_partial_floats.restype = C.c_size_t
+    lib.ihb_tc_decode.argtypes = [C.POINTER(IhbTcDecArgs), C.c_int, _vp]
+    lib.ihb_tc_decode.restype = C.c_int
+    lib.ihb_tc_dec_partial_floats.argtypes = [C.POINTER(IhbTcDecArgs)]
+    lib.ihb_tc_dec_partial_floats.restype = C.c_size_t
     for name in ("ihb_gemv", "ihb_moe_gateup", "ihb_moe_down", "ihb_embed_norm", "ihb_qk_norm_rope_kv",
                  "ihb_flash_decode"):
         getattr(lib, name).restype = C.c_int
@@ -189,10 +211,11 @@ def moe_down(args: IhbMoeArgs, use_pdl: bool = False) -> None:
 
 
 def embed_norm(embed: torch.Tensor, token: torch.Tensor, gamma: torch.Tensor, eps: float, resid: torch.Tensor,
-               xn: torch.Tensor, use_pdl: bool = False) -> None:
+               xn: torch.Tensor, use_pdl: bool = False, xq: Optional[torch.Tensor] = None,
+               xs: Optional[torch.Tensor] = None, xq_fp8: bool = True) -> None:
     check(load().ihb_embed_norm(embed.data_ptr(), int(embed.dtype == torch.bfloat16), token.data_ptr(),
                                 embed.shape[1], gamma.data_ptr(), eps, resid.data_ptr(), xn.data_ptr(),
-                                int(use_pdl), stream_ptr()), "ihb_embed_norm")
+                                ptr(xq), ptr(xs), int(xq_fp8), int(use_pdl), stream_ptr()), "ihb_embed_norm")
 
 
 def qk_norm_rope_kv(qkv: torch.Tensor, nq: int, nkv: int, q_gamma, k_gamma, eps: float, cos_t, sin_t, pos,
@@ -208,10 +231,12 @@ def flash_decode_scratch_floats(nq: int, nsplit: int) -> int:
 
 
 def flash_decode(q, k_cache, v_cache, nq: int, nkv: int, max_seq: int, pos, nsplit: int, scratch, counters, out,
-                 use_pdl: bool = False) -> None:
+                 use_pdl: bool = False, out_q: Optional[torch.Tensor] = None, out_s: Optional[torch.Tensor] = None,
+                 out_fp8: bool = True) -> None:
     check(load().ihb_flash_decode(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), nq, nkv, max_seq,
                                   pos.data_ptr(), nsplit, scratch.data_ptr(), counters.data_ptr(), out.data_ptr(),
-                                  int(use_pdl), stream_ptr()), "ihb_flash_decode")
+                                  ptr(out_q), ptr(out_s), int(out_fp8), int(use_pdl), stream_ptr()),
+          "ihb_flash_decode")
 
 
 def tc_gemm(args: IhbTcArgs, use_pdl: bool = False) -> None:
@@ -258,3 +283,55 @@ def tile_weight(data: torch.Tensor) -> torch.Tensor:
     v = torch.gather(v, -2, idx.expand(v.shape))
     out = v.permute(*range(len(lead)), len(lead) + 2, len(lead), len(lead) + 1, len(lead) + 3, len(lead) + 4)
     return out.contiguous().reshape(*lead, nkb, rows_p8, 128)
+
+
+def tile_weight_v2(data: torch.Tensor) -> torch.Tensor:
+    """Decode-path HBM layout: per matrix ``[row tile][k block][rows of the tile, padded to 8][128 B]`` (swizzled
+    as in :func:`tile_weight`), flattened to ``[..., bytes]``. All K blocks of one 128-row tile are contiguous, so
+    a stage of several K blocks is a single bulk copy."""
+    v1 = tile_weight(data)                                   # [..., nkb, rows_p8, 128]
+    rows_p8 = v1.shape[-2]
+    lead = v1.shape[:-3]
+    parts = []
+    for r0 in range(0, rows_p8, 128):
+        rt = min(128, rows_p8 - r0)
+        parts.append(v1[..., :, r0:r0 + rt, :].reshape(*lead, -1))
+    return torch.cat(parts, dim=-1).contiguous()
+
+
+def act_row(x: torch.Tensor, fp8: bool):
+    """Activation vector(s) ``x[..., K]`` (fp32) in the decode kernels' input format: plain rows padded to a
+    multiple of 128 bytes, e4m3 with one scale per 128 channels (returns ``(bytes, scales)``) or bf16
+    (``(bytes, None)``)."""
+    K = x.shape[-1]
+    if not fp8:
+        raw = x.to(torch.bfloat16).contiguous().view(torch.uint8).reshape(*x.shape[:-1], -1)
+        return torch.nn.functional.pad(raw, (0, (-raw.shape[-1]) % 128)).contiguous(), None
+    Kp = (K + 127) // 128 * 128
+    xp = torch.nn.functional.pad(x.float(), (0, Kp - K)).reshape(*x.shape[:-1], Kp // 128, 128)
+    s = xp.abs().amax(dim=-1).clamp_min(1e-12) / 448.0
+    q = (xp / s[..., None]).clamp(-448, 448).to(torch.float8_e4m3fn).reshape(*x.shape[:-1], Kp)
+    return q.view(torch.uint8).contiguous(), s.contiguous()
+
+
+def tc_dec_fill_weight(args: IhbTcDecArgs, qw, tiled: torch.Tensor, rows: Optional[int] = None) -> None:
+    """Weight fields of a decode block: ``qw`` gives shapes and scales, ``tiled`` is ``tile_weight_v2`` of its data
+    (gate/up: of ``data.reshape(E, 2, I, K)`` with ``rows = I``)."""
+    args.W = tiled.data_ptr()
+    args.wtype = wtype_of(qw.data)
+    args.rows, args.K = (rows if rows is not None else qw.data.shape[-2]), qw.data.shape[-1]
+    args.n_experts = qw.data.shape[0] if qw.data.dim() == 3 else 1
+    if qw.scale is not None:
+        if qw.kb != 128:
+            raise ValueError("the tensor-core path needs 128-wide K scale blocks")
+        ks = kernel_scale(qw)
+        args.wscale = ks.data_ptr()
+        args.rb, args.nrb, args.nkb_stride = qw.rb, ks.shape[-2], ks.shape[-1]
+
+
+def tc_decode(args: IhbTcDecArgs, use_pdl: bool = False) -> None:
+    check(load().ihb_tc_decode(C.byref(args), int(use_pdl), stream_ptr()), "ihb_tc_decode")
+
+
+def tc_dec_partial_floats(args: IhbTcDecArgs) -> int:
+    return int(load().ihb_tc_dec_partial_floats(C.byref(args)))

@@ -208,8 +208,10 @@ def test_rope_kv_and_flash_decode(nq, nkv, ctx):
     scratch = torch.zeros(lib.flash_decode_scratch_floats(nq, nsplit), device=d)
     ctrs = torch.zeros(nq, dtype=torch.int32, device=d)
     out = torch.zeros(nq * 128, device=d)
+    out_q = torch.zeros(nq * 128, dtype=torch.uint8, device=d)
+    out_s = torch.zeros(nq, device=d)
     for _ in range(2):
-        lib.flash_decode(qkv, kc, vc, nq, nkv, max_seq, pos, nsplit, scratch, ctrs, out, False)
+        lib.flash_decode(qkv, kc, vc, nq, nkv, max_seq, pos, nsplit, scratch, ctrs, out, False, out_q, out_s, True)
     torch.cuda.synchronize()
     # reference
     q = raw[: nq * 128].reshape(1, nq, 128)
@@ -228,3 +230,29 @@ def test_rope_kv_and_flash_decode(nq, nkv, ctx):
     ref = torch.einsum("kgs,ksd->kgd", torch.softmax(sc, -1), vf).reshape(-1)
     assert float((out - ref).abs().max()) < 2e-3
     assert int(ctrs.sum().item()) == 0
+    deq = (out_q.view(torch.float8_e4m3fn).float().reshape(nq, 128) * out_s[:, None]).reshape(-1)
+    assert float((deq - out).abs().max()) <= 0.07 * float(out.abs().max()) + 1e-6
+
+
+def test_embed_norm_quantised_copy():
+    lib = _K()
+    d = _dev()
+    H, V = 2048, 1000
+    g = torch.Generator(device=d).manual_seed(5)
+    emb = (torch.randn(V, H, device=d, generator=g)).to(torch.bfloat16)
+    gamma = 1.0 + 0.1 * torch.randn(H, device=d, generator=g)
+    tok = torch.tensor([123], dtype=torch.int32, device=d)
+    resid, xn = torch.zeros(H, device=d), torch.zeros(H, device=d)
+    xq, xs = torch.zeros(H, dtype=torch.uint8, device=d), torch.zeros(H // 128, device=d)
+    lib.embed_norm(emb, tok, gamma, 1e-6, resid, xn, False, xq, xs, True)
+    xb = torch.zeros(2 * H, dtype=torch.uint8, device=d)
+    lib.embed_norm(emb, tok, gamma, 1e-6, resid, xn, False, xb, None, False)
+    torch.cuda.synchronize()
+    ref = rmsnorm(emb[123].float(), gamma, 1e-6)
+    assert torch.equal(resid, emb[123].float())
+    assert float((xn - ref).abs().max()) < 1e-4
+    q2, s2 = lib.act_row(xn, True)
+    assert float((xs - s2).abs().max()) < 1e-6
+    deq = (xq.view(torch.float8_e4m3fn).float().reshape(-1, 128) * xs[:, None]).reshape(-1)
+    assert float((deq - xn).abs().max()) <= 0.07 * float(xn.abs().max())
+    assert torch.equal(xb.view(torch.bfloat16), xn.to(torch.bfloat16))
