@@ -43,6 +43,21 @@ def apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.T
     return torch.cat([x1 * c - x2 * s, x2 * c + x1 * s], dim=-1)
 
 
+def fake_quant_act(x: torch.Tensor, mode) -> torch.Tensor:
+    """Round activations the way the tensor-core kernels store them: ``"fp8"`` = e4m3 with one scale per token
+    per 128 channels, ``"bf16"``; ``None`` leaves them alone."""
+    if mode is None:
+        return x
+    if mode == "bf16":
+        return x.to(torch.bfloat16).float()
+    K = x.shape[-1]
+    Kp = (K + 127) // 128 * 128
+    xp = torch.nn.functional.pad(x.float(), (0, Kp - K)).reshape(*x.shape[:-1], Kp // 128, 128)
+    s = xp.abs().amax(dim=-1, keepdim=True).clamp_min(1e-12) / 448.0
+    q = (xp / s).clamp(-448, 448).to(torch.float8_e4m3fn).float() * s
+    return q.reshape(*x.shape[:-1], Kp)[..., :K]
+
+
 def route(h: torch.Tensor, router_w: torch.Tensor, top_k: int, renorm: bool = True):
     """Router: fp32 softmax over all experts, top-k, optional renormalisation. Returns ``(idx, w, logits)``."""
     logits = h.float() @ router_w.float().t()
@@ -97,17 +112,17 @@ def _attention(q: torch.Tensor, kc: torch.Tensor, vc: torch.Tensor, positions: t
 
 
 def _experts_local(h: torch.Tensor, lw: LayerWeights, idx: torch.Tensor, w: torch.Tensor, expert0: int,
-                   n_local: int) -> torch.Tensor:
+                   n_local: int, act_mode=None) -> torch.Tensor:
     """Sum over the (token, slot) pairs whose expert is held locally; ``idx`` holds global expert ids."""
     out = torch.zeros(h.shape[0], lw.w_d.data.shape[-2], dtype=torch.float32, device=h.device)
     local = idx - expert0
     for e in torch.unique(local[(local >= 0) & (local < n_local)]).tolist():
         tok, slot = torch.nonzero(local == e, as_tuple=True)
-        x = h[tok].float()
+        x = fake_quant_act(h[tok].float(), act_mode)
         wgu = lw.w_gu.select(e).dequant()
         I = wgu.shape[0] // 2
         gu = x @ wgu.t()
-        a = torch.nn.functional.silu(gu[:, :I]) * gu[:, I:]
+        a = fake_quant_act(torch.nn.functional.silu(gu[:, :I]) * gu[:, I:], act_mode)
         y = a @ lw.w_d.select(e).dequant().t()
         out.index_add_(0, tok, y * w[tok, slot].float()[:, None])
     return out
@@ -125,6 +140,7 @@ class Qwen3MoE:
         self.compute_dtype = compute_dtype
         self.last_routes: List[RouteRecord] = []
         self.aux_taps: dict = {}
+        self.act_mode = None       # "fp8" / "bf16": round activations before every linear layer like the CUDA path
 
     def new_cache(self, max_seq: int, dtype=torch.float32, device=None) -> TorchKV:
         device = device if device is not None else self.w.embed.device
@@ -137,7 +153,7 @@ class Qwen3MoE:
             idx, w, _ = route(h, lw.router, cfg.top_k, cfg.norm_topk_prob)
             if record:
                 self.last_routes.append(RouteRecord(L, idx[-1].tolist(), w[-1].tolist()))
-            y = _experts_local(h, lw, idx, w, 0, cfg.n_experts)
+            y = _experts_local(h, lw, idx, w, 0, cfg.n_experts, self.act_mode)
             return self.comm.all_reduce_tp(y)
         # expert parallel: home rank of token m is m % world -----------------------------------------------
         world, rank = par.world, par.rank
@@ -158,7 +174,7 @@ class Qwen3MoE:
         rh, ridx, rw = recv[:, :-2], recv[:, -2].long(), recv[:, -1]
         yo = torch.zeros(rh.shape[0], cfg.hidden, dtype=torch.float32, device=h.device)
         if rh.shape[0]:
-            yo = _experts_local(rh, lw, ridx[:, None], rw[:, None], geom.expert0, n_el)
+            yo = _experts_local(rh, lw, ridx[:, None], rw[:, None], geom.expert0, n_el, self.act_mode)
         # combine: rows go back to their home rank in the order they came
         back, _ = self.comm.all_to_all_rows(yo, recv_counts)
         y_mine = torch.zeros(mine.shape[0], cfg.hidden, dtype=torch.float32, device=h.device)
@@ -198,7 +214,7 @@ class Qwen3MoE:
         hd = cfg.head_dim
         for L, lw in enumerate(self.w.layers):
             h = rmsnorm(x, lw.in_ln, cfg.rms_eps)
-            qkv = h @ lw.wqkv.dequant().t()
+            qkv = fake_quant_act(h, self.act_mode) @ lw.wqkv.dequant().t()
             nq, nkv = geom.nq_local, geom.nkv_local
             q = qkv[:, : nq * hd].reshape(T, nq, hd)
             k = qkv[:, nq * hd: (nq + nkv) * hd].reshape(T, nkv, hd)
@@ -208,7 +224,7 @@ class Qwen3MoE:
             cache.k[L, :, start:start + T] = k.permute(1, 0, 2).to(cache.k.dtype)
             cache.v[L, :, start:start + T] = v.permute(1, 0, 2).to(cache.v.dtype)
             attn = _attention(q, cache.k[L, :, : start + T], cache.v[L, :, : start + T], positions, tree_mask)
-            o = attn @ lw.wo.dequant().t()
+            o = fake_quant_act(attn, self.act_mode) @ lw.wo.dequant().t()
             x = x + self.comm.all_reduce_tp(o)
             h2 = rmsnorm(x, lw.post_ln, cfg.rms_eps)
             x = x + self._moe(L, h2, lw, record_routes)
@@ -220,11 +236,11 @@ class Qwen3MoE:
 
     def logits(self, hidden: torch.Tensor) -> torch.Tensor:
         """Full-vocabulary logits ``[T, V]`` (gathered from the vocabulary shards)."""
-        local = hidden.float() @ self.w.lm_head.dequant().t()
+        local = fake_quant_act(hidden.float(), self.act_mode) @ self.w.lm_head.dequant().t()
         return self.comm.gather_logits(local, self.cfg.vocab, self.geom.vocab_chunk)
 
     def greedy(self, hidden: torch.Tensor) -> torch.Tensor:
-        local = hidden.float() @ self.w.lm_head.dequant().t()
+        local = fake_quant_act(hidden.float(), self.act_mode) @ self.w.lm_head.dequant().t()
         return self.comm.argmax_sharded(local, self.geom.vocab0)[1]
 
     def forward(self, tokens: torch.Tensor, cache: TorchKV, **kw) -> torch.Tensor:

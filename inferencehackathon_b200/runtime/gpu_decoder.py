@@ -43,6 +43,8 @@ class GpuDecoder:
         self.H, self.nq, self.nkv, self.I = m.hidden, g.nq_local, g.nkv_local, g.inter_local
         self.max_seq = cfg.max_seq
         self.use_pdl = bool(env_flag("IHB_PDL", 1))
+        self.use_tc = bool(env_flag("IHB_TC", 1))          # tensor-core linears (0: SIMT streaming GEMVs)
+        self.fp8 = weights.quant.weights == "fp8_block"
         self.use_graph = cfg.use_graph and bool(env_flag("IHB_GRAPH", 1))
         self.comm_ref = comm
         self.n_launches_per_step = 0
@@ -82,7 +84,10 @@ class GpuDecoder:
         celems = 16 if weights.quant.weights == "fp8_block" else 8
         self.ks_o = _pick_ks(self.nq * 128, celems)
         self._setup_comm()
-        self._build_args()
+        if self.use_tc:
+            self._build_tc()
+        else:
+            self._build_args()
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self._ev0 = torch.cuda.Event(enable_timing=True)
         self._ev1 = torch.cuda.Event(enable_timing=True)
@@ -160,8 +165,111 @@ class GpuDecoder:
                                     n_forced=self.n_forced)
         self.head.comm = self._comm()
 
+    # tensor-core path -------------------------------------------------------------------------------------------
+    def _tc_args(self, qw, tiled, x, xscale, mode, epi, rows=None, **kw) -> K.IhbTcDecArgs:
+        a = K.IhbTcDecArgs()
+        K.tc_dec_fill_weight(a, qw, tiled, rows)
+        a.X, a.mode, a.epi, a.err = x.data_ptr(), mode, epi, self.err.data_ptr()
+        if self.fp8:
+            a.xscale = xscale.data_ptr()
+        for k, v in kw.items():
+            setattr(a, k, v.data_ptr() if isinstance(v, torch.Tensor) else v)
+        return a
+
+    def _build_tc(self) -> None:
+        """Re-tile every weight for the tensor-core decode kernels (the plain copies are released) and build the
+        per-layer argument blocks."""
+        m, w, dev = self.cfg.model, self.w, self.device
+        from ..models.quant import QWeight
+        es = 1 if self.fp8 else 2
+        u8 = dict(dtype=torch.uint8, device=dev)
+        f32 = dict(dtype=torch.float32, device=dev)
+        H, I, k = self.H, self.I, m.top_k
+        nkb_i = (I * es + 127) // 128
+        self.xq, self.xs = torch.zeros(H * es, **u8), torch.zeros(H // 128, **f32)
+        self.attn_q, self.attn_s = torch.zeros(self.nq * 128 * es, **u8), torch.zeros(self.nq, **f32)
+        self.act_q, self.act_s = torch.zeros(k * nkb_i * 128, **u8), torch.zeros(k * nkb_i, **f32)
+        self.tile_ctr = torch.zeros(5, 4096, dtype=torch.int32, device=dev)
+        tiled_of = {}
+
+        def tiled(qw, reshape=None):
+            key = id(qw)
+            if key not in tiled_of:
+                data = qw.data if reshape is None else qw.data.reshape(*reshape)
+                shape = tuple(qw.data.shape)
+                tiled_of[key] = K.tile_weight_v2(data)
+                if qw.scale is not None:
+                    K.kernel_scale(qw)
+                # release the plain copy; keep a meta tensor for the shape/dtype queries of the argument builders
+                qw.data = torch.empty(shape, dtype=qw.data.dtype, device="meta")
+            return tiled_of[key]
+
+        self.layer_args = []
+        ctr = self.counters
+        parts = 1
+        for L, lw in enumerate(w.layers):
+            nxt_gamma = w.layers[L + 1].in_ln if L + 1 < len(w.layers) else w.final_norm
+            E_l = lw.w_gu.data.shape[0]
+            t_qkv, t_o = tiled(lw.wqkv), tiled(lw.wo)
+            t_gu, t_d = tiled(lw.w_gu, (E_l, 2, I, H)), tiled(lw.w_d)
+            qkv = self._tc_args(lw.wqkv, t_qkv, self.xq, self.xs, K.TC_LINEAR, K.DEC_STORE, out=self.qkv,
+                                tile_counters=self.tile_ctr[0])
+            oproj = self._tc_args(lw.wo, t_o, self.attn_q, self.attn_s, K.TC_LINEAR, K.DEC_AR_NORM,
+                                  tile_counters=self.tile_ctr[1], counter=ctr[0:1], resid=self.resid, gamma=lw.post_ln,
+                                  xn_out=self.xn, eps=m.rms_eps, xq=self.xq, xs=self.xs)
+            oproj.comm = self._comm()
+            router = self._gemv_args(QWeight(lw.router), self.xn, K.EPI_ROUTER, counter=ctr[1:2],
+                                     out=self.router_logits[L], top_k=m.top_k, renorm=int(m.norm_topk_prob),
+                                     sel_idx=self.sel_idx[L], sel_w=self.sel_w[L])
+            gu = self._tc_args(lw.w_gu, t_gu, self.xq, self.xs, K.TC_GATEUP, K.DEC_ACT, rows=I,
+                               tile_counters=self.tile_ctr[2], expert0=w.geom.expert0, top_k=k,
+                               sel_idx=self.sel_idx[L], sel_w=self.sel_w[L], act_q=self.act_q, act_s=self.act_s)
+            gu.n_experts = E_l
+            dn = self._tc_args(lw.w_d, t_d, self.act_q, self.act_s, K.TC_DOWN, K.DEC_AR_NORM,
+                               tile_counters=self.tile_ctr[3], counter=ctr[2:3], expert0=w.geom.expert0, top_k=k,
+                               sel_idx=self.sel_idx[L], sel_w=self.sel_w[L], resid=self.resid, gamma=nxt_gamma,
+                               xn_out=self.xn, eps=m.rms_eps, xq=self.xq, xs=self.xs)
+            dn.comm = self._comm()
+            for a in (qkv, oproj, gu, dn):
+                parts = max(parts, K.tc_dec_partial_floats(a))
+            self.layer_args.append((qkv, oproj, router, gu, dn, lw))
+        t_head = tiled(w.lm_head)
+        self.head = self._tc_args(w.lm_head, t_head, self.xq, self.xs, K.TC_LINEAR, K.DEC_ARGMAX, out=self.logits,
+                                  tile_counters=self.tile_ctr[4], counter=ctr[3:4], argmax_partial=self.argmax_partial,
+                                  vocab0=w.geom.vocab0, cur_token=self.cur_token, pos=self.pos,
+                                  token_ring=self.token_ring, token_ring_size=self.token_ring.numel(),
+                                  forced=self.forced, n_forced=self.n_forced)
+        self.head.comm = self._comm()
+        parts = max(parts, K.tc_dec_partial_floats(self.head))
+        self.tc_partial = torch.zeros(parts, **f32)
+        for (qkv, oproj, router, gu, dn, lw) in self.layer_args:
+            for a in (qkv, oproj, gu, dn):
+                a.partial = self.tc_partial.data_ptr()
+        self.head.partial = self.tc_partial.data_ptr()
+        self._tiled = tiled_of
+
+    def _enqueue_step_tc(self) -> None:
+        m, w, pdl = self.cfg.model, self.w, self.use_pdl
+        K.embed_norm(w.embed, self.cur_token, w.layers[0].in_ln, m.rms_eps, self.resid, self.xn, False,
+                     self.xq, self.xs, self.fp8)
+        fd_ctr = self.counters[8:]
+        for L, (qkv, oproj, router, gu, dn, lw) in enumerate(self.layer_args):
+            K.tc_decode(qkv, pdl)
+            K.qk_norm_rope_kv(self.qkv, self.nq, self.nkv, lw.q_norm, lw.k_norm, m.rms_eps, self.cos, self.sin,
+                              self.pos, self.k_cache[L], self.v_cache[L], self.max_seq, pdl)
+            K.flash_decode(self.qkv, self.k_cache[L], self.v_cache[L], self.nq, self.nkv, self.max_seq, self.pos,
+                           self.nsplit, self.fd_scratch, fd_ctr, self.attn, pdl, self.attn_q, self.attn_s, self.fp8)
+            K.tc_decode(oproj, pdl)
+            K.gemv(router, pdl)
+            K.tc_decode(gu, pdl)
+            K.tc_decode(dn, pdl)
+        K.tc_decode(self.head, pdl)
+        self.n_launches_per_step = 2 + 7 * len(self.layer_args)
+
     # one token -------------------------------------------------------------------------------------------------
     def _enqueue_step(self) -> None:
+        if self.use_tc:
+            return self._enqueue_step_tc()
         m, w, pdl = self.cfg.model, self.w, self.use_pdl
         n = 0
         K.embed_norm(w.embed, self.cur_token, w.layers[0].in_ln, m.rms_eps, self.resid, self.xn, False)
