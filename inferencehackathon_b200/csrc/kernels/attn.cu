@@ -367,3 +367,70 @@ extern "C" int ihb_flash_decode(const float* q, const void* k_cache, const void*
     default: return cudaLaunchKernelEx(&cfg, flash_decode_kernel<1>, q, kc, vc, nq, nkv, max_seq, pos, nsplit, scratch, counters, out, out_q, out_s, out_fp8);
   }
 }
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Flash decode for callers that cannot allocate (declared in noalloc.h): the scratch lives in the library image.
+// ---------------------------------------------------------------------------------------------------------------------
+#include "noalloc.h"
+#include <mutex>
+#include <stdio.h>
+
+namespace {
+
+constexpr size_t kStaticCounterBytes = 256;   // IHB_FD_STATIC_MAX_HEADS unsigned counters
+constexpr size_t kStaticPartialBytes = static_cast<size_t>(IHB_FD_STATIC_MAX_PARTIALS) * ihb::FD_REC * sizeof(float);
+
+// [counters | partials]. In host code this name is only a handle for cudaGetSymbolAddress, never a pointer.
+static __device__ __align__(256) unsigned char ihb_fd_static_scratch[kStaticCounterBytes + kStaticPartialBytes];
+
+constexpr int kMaxDevices = 64;
+unsigned char* g_static_ptr[kMaxDevices] = {};
+std::mutex g_static_mutex;
+thread_local char g_static_msg[160] = "";
+
+cudaError_t static_scratch_for_current_device(unsigned char** out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+  std::lock_guard<std::mutex> lock(g_static_mutex);
+  if (g_static_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, ihb_fd_static_scratch);      // address of this device's copy of the array
+    if (e != cudaSuccess) return e;
+    g_static_ptr[dev] = static_cast<unsigned char*>(p);
+  }
+  *out = g_static_ptr[dev];
+  return cudaSuccess;
+}
+
+}  // namespace
+
+extern "C" size_t ihb_flash_decode_static_bytes(void) { return kStaticCounterBytes + kStaticPartialBytes; }
+
+extern "C" const char* ihb_flash_decode_static_error(void) { return g_static_msg; }
+
+extern "C" int ihb_flash_decode_static(const float* q, const void* k_cache, const void* v_cache, int nq, int nkv,
+                                       int max_seq, const int* pos, int nsplit, float* out, cudaStream_t stream) {
+  g_static_msg[0] = '\0';
+  if (nq < 1 || nkv < 1 || nsplit < 1 || nq > IHB_FD_STATIC_MAX_HEADS ||
+      static_cast<long long>(nq) * nsplit > IHB_FD_STATIC_MAX_PARTIALS) {
+    snprintf(g_static_msg, sizeof(g_static_msg),
+             "ihb_flash_decode_static: nq=%d, nsplit=%d exceed the built-in scratch (nq <= %d, nq * nsplit <= %d)", nq,
+             nsplit, IHB_FD_STATIC_MAX_HEADS, IHB_FD_STATIC_MAX_PARTIALS);
+    return cudaErrorInvalidValue;
+  }
+  unsigned char* base = nullptr;
+  cudaError_t e = static_scratch_for_current_device(&base);
+  if (e != cudaSuccess) {
+    snprintf(g_static_msg, sizeof(g_static_msg), "ihb_flash_decode_static: no device address for the scratch: %s",
+             cudaGetErrorString(e));
+    return e;
+  }
+  // the partials are overwritten before they are read; only the arrival counters have to start at zero
+  e = cudaMemsetAsync(base, 0, kStaticCounterBytes, stream);
+  if (e != cudaSuccess) return e;
+  return ihb_flash_decode(q, k_cache, v_cache, nq, nkv, max_seq, pos, nsplit,
+                          reinterpret_cast<float*>(base + kStaticCounterBytes), reinterpret_cast<unsigned*>(base), out,
+                          nullptr, nullptr, 0, 0, stream);
+}
