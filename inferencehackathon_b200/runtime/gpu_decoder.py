@@ -295,20 +295,21 @@ class GpuDecoder:
             return
         if self.graph is None:
             # warm up on a side stream (lazy module loading, attribute calls) and restore the state it advanced
-            state = (self.pos.clone(), self.cur_token.clone(), self.epoch.clone())
+            # (the collective epoch is NOT restored: the peers' arrival counters advanced with it)
+            state = (self.pos.clone(), self.cur_token.clone())
             s = torch.cuda.Stream(device=self.device)
             s.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(s):
                 self._enqueue_step()
             torch.cuda.current_stream().wait_stream(s)
             torch.cuda.synchronize()
-            self.pos.copy_(state[0]); self.cur_token.copy_(state[1]); self.epoch.copy_(state[2])
+            self.pos.copy_(state[0]); self.cur_token.copy_(state[1])
             if self.symm is not None:
                 self.symm.barrier_host()
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g):
                 self._enqueue_step()
-            self.pos.copy_(state[0]); self.cur_token.copy_(state[1]); self.epoch.copy_(state[2])
+            self.pos.copy_(state[0]); self.cur_token.copy_(state[1])
             self.graph = g
         self.graph.replay()
 
