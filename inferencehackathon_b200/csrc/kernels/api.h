@@ -51,6 +51,7 @@ typedef struct {
   int top_k, renorm;
   int* sel_idx;            // [top_k]
   float* sel_w;            // [top_k]
+  float* router_partial;   // ROUTER with ks > 1: [ks][rows] partial logits, summed in order by the tail
   // ARGMAX
   unsigned long long* argmax_partial;   // [grid]
   int vocab0;

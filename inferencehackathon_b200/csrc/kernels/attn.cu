@@ -268,39 +268,50 @@ __global__ void __launch_bounds__(FD_WARPS * 32) flash_decode_kernel(
   }
   __syncthreads();
   if (!s_last) return;
-  // merge of the split partials by the last CTA of this (kv head, group)
-  for (int i = tid; i < GQ * HD; i += FD_WARPS * 32) {
-    const int g = i / HD, d = i % HD;
+  // merge of the split partials by the last CTA of this (kv head, group). All loads of a phase are independent
+  // (the loops over heads are unrolled), so the merge costs two memory round trips, not two per head.
+  const int d = tid;                                   // 128 threads = 128 channels
+  float* ml_s = &acc_s[0][0][0];                       // reuse: [GQ][nsplit] m, then [GQ][nsplit] l (nsplit <= 256)
+  const int nml = GQ * nsplit;
+  for (int i = tid; i < nml; i += FD_WARPS * 32) {
+    const float* rec = scratch + (static_cast<size_t>(head0 + i / nsplit) * nsplit + (i % nsplit)) * FD_REC;
+    ml_s[i] = ld_cg_f(rec + HD);
+    ml_s[nml + i] = ld_cg_f(rec + HD + 1);
+  }
+  __syncthreads();
+  float o[GQ];
+#pragma unroll
+  for (int g = 0; g < GQ; ++g) {
     const float* recs = scratch + static_cast<size_t>(head0 + g) * nsplit * FD_REC;
     float M = -INFINITY;
-#pragma unroll 8
-    for (int sp = 0; sp < nsplit; ++sp) M = fmaxf(M, ld_cg_f(recs + sp * FD_REC + HD));
+    for (int sp = 0; sp < nsplit; ++sp) M = fmaxf(M, ml_s[g * nsplit + sp]);
     float a = 0.f, L = 0.f;
-#pragma unroll 8
+#pragma unroll 4
     for (int sp = 0; sp < nsplit; ++sp) {
-      const float ms = ld_cg_f(recs + sp * FD_REC + HD);
-      if (ms > -INFINITY) {
-        const float f = exp2f(ms - M);
-        a += ld_cg_f(recs + sp * FD_REC + d) * f;
-        L += ld_cg_f(recs + sp * FD_REC + HD + 1) * f;
-      }
+      const float ms = ml_s[g * nsplit + sp];
+      const float f = (ms > -INFINITY) ? exp2f(ms - M) : 0.f;
+      a = fmaf(ld_cg_f(recs + sp * FD_REC + d), f, a);     // empty splits wrote zeros
+      L = fmaf(ml_s[nml + g * nsplit + sp], f, L);
     }
-    const float o = a / L;
-    out[static_cast<size_t>(head0 + g) * HD + d] = o;
+    o[g] = a / L;
+  }
+#pragma unroll
+  for (int g = 0; g < GQ; ++g) {
+    out[static_cast<size_t>(head0 + g) * HD + d] = o[g];
     if (out_q != nullptr) {
-      // one iteration of this loop is one head = one group of 128 channels of the o_proj input row
+      // a head is one group of 128 channels of the o_proj input row
       if (out_fp8) {
-        const float mx = warp_max(fabsf(o));
+        const float mx = warp_max(fabsf(o[g]));
+        __syncthreads();
         if (lane == 0) red_m[warp] = mx;
         __syncthreads();
         const float amax = fmaxf(fmaxf(red_m[0], red_m[1]), fmaxf(red_m[2], red_m[3]));
         const float sc = fmaxf(amax, 1e-12f) * (1.f / 448.f);
         out_q[static_cast<size_t>(head0 + g) * HD + d] =
-            static_cast<uint8_t>(__nv_cvt_float_to_fp8(o / sc, __NV_SATFINITE, __NV_E4M3));
+            static_cast<uint8_t>(__nv_cvt_float_to_fp8(o[g] / sc, __NV_SATFINITE, __NV_E4M3));
         if (tid == 0) out_s[head0 + g] = sc;
-        __syncthreads();
       } else {
-        reinterpret_cast<__nv_bfloat16*>(out_q)[static_cast<size_t>(head0 + g) * HD + d] = __float2bfloat16(o);
+        reinterpret_cast<__nv_bfloat16*>(out_q)[static_cast<size_t>(head0 + g) * HD + d] = __float2bfloat16(o[g]);
       }
     }
   }
@@ -351,7 +362,7 @@ extern "C" int ihb_flash_decode(const float* q, const void* k_cache, const void*
                                 int max_seq, const int* pos, int nsplit, float* scratch, unsigned* counters,
                                 float* out, unsigned char* out_q, float* out_s, int out_fp8, int use_pdl,
                                 cudaStream_t stream) {
-  if (nq % nkv || nsplit < 1) return cudaErrorInvalidValue;
+  if (nq % nkv || nsplit < 1 || nsplit > 256) return cudaErrorInvalidValue;
   const int q_per_kv = nq / nkv;
   int gq = q_per_kv >= 8 ? 8 : q_per_kv;
   if (q_per_kv % gq || (gq != 8 && gq != 4 && gq != 2 && gq != 1)) return cudaErrorInvalidValue;

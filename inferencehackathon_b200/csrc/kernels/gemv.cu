@@ -37,7 +37,17 @@ __device__ void tail_router(const IhbGemvArgs& a, int lane) {
 #pragma unroll
   for (int j = 0; j < MAXPER; ++j) {
     const int e = lane + 32 * j;
-    v[j] = (e < E) ? ld_cg_f(a.out + e) : -INFINITY;
+    v[j] = -INFINITY;
+    if (e < E) {
+      if (a.ks > 1) {           // K-split partial logits, added in slice order (identical on every rank)
+        float s = 0.f;
+        for (int h = 0; h < a.ks; ++h) s += ld_cg_f(a.router_partial + h * E + e);
+        v[j] = s;
+        a.out[e] = s;
+      } else {
+        v[j] = ld_cg_f(a.out + e);
+      }
+    }
     m = fmaxf(m, v[j]);
   }
   m = warp_max(m);
@@ -169,7 +179,9 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) gemv_kernel(const IhbGemvAr
       }
       const int row = row0 + r;
       if (lane == 0) {
-        if (EPI == IHB_EPI_STORE || EPI == IHB_EPI_ROUTER) {
+        if (EPI == IHB_EPI_ROUTER && a.ks > 1) {
+          a.router_partial[h * a.rows + row] = y;
+        } else if (EPI == IHB_EPI_STORE || EPI == IHB_EPI_ROUTER) {
           a.out[row] = y;
         } else if (EPI == IHB_EPI_ARGMAX) {
           const unsigned long long p = pack_max(y, static_cast<unsigned>(row));
@@ -261,7 +273,7 @@ extern "C" int ihb_gemv(IhbGemvArgs* args, int use_pdl, cudaStream_t stream) {
   const int celems = a.wtype == IHB_W_FP8 ? 16 : 8;
   if (a.ks < 1) a.ks = 1;
   if (a.K % (celems * a.ks) != 0 || (NCW % a.ks) != 0 || a.rows <= 0) return cudaErrorInvalidValue;
-  if (a.ks > 1 && a.epi != IHB_EPI_AR_NORM) return cudaErrorInvalidValue;
+  if (a.ks > 1 && a.epi != IHB_EPI_AR_NORM && !(a.epi == IHB_EPI_ROUTER && a.router_partial != nullptr)) return cudaErrorInvalidValue;
   const int nchunks = a.K / a.ks / celems;
   const int ni = (nchunks + 31) / 32;
   if (ni > 16) return cudaErrorInvalidValue;

@@ -38,7 +38,7 @@ class IhbGemvArgs(C.Structure):
                 ("x", _vp),
                 ("R", C.c_int), ("S", C.c_int), ("grid", C.c_int), ("ks", C.c_int), ("epi", C.c_int),
                 ("out", _vp), ("counter", _vp), ("err", _vp),
-                ("top_k", C.c_int), ("renorm", C.c_int), ("sel_idx", _vp), ("sel_w", _vp),
+                ("top_k", C.c_int), ("renorm", C.c_int), ("sel_idx", _vp), ("sel_w", _vp), ("router_partial", _vp),
                 ("argmax_partial", _vp), ("vocab0", C.c_int), ("cur_token", _vp), ("pos", _vp),
                 ("token_ring", _vp), ("token_ring_size", C.c_int), ("forced", _vp), ("n_forced", _vp),
                 ("resid", _vp), ("gamma", _vp), ("xn_out", _vp), ("eps", C.c_float),

@@ -170,6 +170,7 @@ class GpuDecoder:
         a = K.IhbTcDecArgs()
         K.tc_dec_fill_weight(a, qw, tiled, rows)
         a.X, a.mode, a.epi, a.err = x.data_ptr(), mode, epi, self.err.data_ptr()
+        a.S = env_flag("IHB_TD_S", 0)
         if self.fp8:
             a.xscale = xscale.data_ptr()
         for k, v in kw.items():
@@ -190,6 +191,9 @@ class GpuDecoder:
         self.attn_q, self.attn_s = torch.zeros(self.nq * 128 * es, **u8), torch.zeros(self.nq, **f32)
         self.act_q, self.act_s = torch.zeros(k * nkb_i * 128, **u8), torch.zeros(k * nkb_i, **f32)
         self.tile_ctr = torch.zeros(5, 4096, dtype=torch.int32, device=dev)
+        # router GEMV: all eight warps of a CTA share one expert row (K split 8) when K allows
+        self.router_ks = 8 if (H // 8) % 8 == 0 and H >= 1024 else 1
+        self.router_partial = torch.zeros(8 * m.n_experts, **f32)
         tiled_of = {}
 
         def tiled(qw, reshape=None):
@@ -218,9 +222,10 @@ class GpuDecoder:
                                   tile_counters=self.tile_ctr[1], counter=ctr[0:1], resid=self.resid, gamma=lw.post_ln,
                                   xn_out=self.xn, eps=m.rms_eps, xq=self.xq, xs=self.xs)
             oproj.comm = self._comm()
-            router = self._gemv_args(QWeight(lw.router), self.xn, K.EPI_ROUTER, counter=ctr[1:2],
+            router = self._gemv_args(QWeight(lw.router), self.xn, K.EPI_ROUTER, counter=ctr[1:2], ks=self.router_ks,
                                      out=self.router_logits[L], top_k=m.top_k, renorm=int(m.norm_topk_prob),
-                                     sel_idx=self.sel_idx[L], sel_w=self.sel_w[L])
+                                     sel_idx=self.sel_idx[L], sel_w=self.sel_w[L],
+                                     router_partial=self.router_partial)
             gu = self._tc_args(lw.w_gu, t_gu, self.xq, self.xs, K.TC_GATEUP, K.DEC_ACT, rows=I,
                                tile_counters=self.tile_ctr[2], expert0=w.geom.expert0, top_k=k,
                                sel_idx=self.sel_idx[L], sel_w=self.sel_w[L], act_q=self.act_q, act_s=self.act_s)

@@ -1,0 +1,159 @@
+"""Analytical model and benchmark harness (CPU only). Mirrors the reference's unit-test strategy: model accounting,
+MockEngine == analytical floor, statistics, store/export round trips, gates, levers, sweeps, optimiser, CLI."""
+import json
+import os
+
+import pytest
+
+import inferutil as iu
+from inferutil import bench as B
+from inferutil.bench.cli import main as bench_main
+from inferutil.optimize import MEASURED_BASELINE, apply_spec, optimize, plain_decode_ceiling, sensitivity_grid
+
+H100 = iu.Cluster(iu.H100_SXM, 8)
+CFG = iu.QWEN3_235B
+
+
+def test_param_accounting():
+    assert 234e9 < CFG.total_params < 236e9 and 21e9 < CFG.active_params < 23e9
+    assert CFG.kv_bytes_per_token(2) == 2 * 94 * 512 * 2
+    assert 30e9 < iu.QWEN3_30B.total_params < 31e9
+
+
+def test_emax_and_latency_plans():
+    assert iu.expected_max_experts_per_gpu(8, 1) == 8.0
+    assert abs(iu.expected_max_experts_per_gpu(8, 8) - 2.597) < 1e-3
+    floor = iu.decode_latency(CFG, H100, plan="floor", dtype_bytes=1, seq_len=2048)
+    tp = iu.decode_latency(CFG, H100, plan="tp", dtype_bytes=1, seq_len=2048)
+    ep = iu.decode_latency(CFG, H100, plan="ep", dtype_bytes=1, seq_len=2048)
+    ideal = iu.decode_latency(CFG, H100, plan="ep", dtype_bytes=1, seq_len=2048, ideal_routing=True)
+    assert floor.total_s < tp.total_s < ep.total_s and ideal.total_s < ep.total_s and ep.imbalance > 2.5
+    assert tp.comms_s == pytest.approx(188 * 5e-6)
+    b200 = iu.decode_latency(CFG, iu.Cluster(iu.B200_SXM, 8), plan="tp", dtype_bytes=1, seq_len=2048)
+    assert b200.tokens_per_s > tp.tokens_per_s
+    with pytest.raises(ValueError):
+        iu.decode_latency(CFG, H100, plan="nope")
+
+
+def test_mock_engine_reproduces_the_floor():
+    cfgb = B.BenchConfig("t", "hybrid", 1, 2, 2, 8, prompt_tokens=64, decode_tokens=16, repeats=2, warmup_steps=2)
+    eng = B.MockEngine(CFG, H100)
+    assert isinstance(eng, B.Engine)
+    res = B.run_benchmark(eng, cfgb, CFG, H100, telemetry=B.FakeTelemetrySource([
+        B.GpuSample(g, 0.0, 60.0, 50.0 + g, 40.0, 300.0, 1500.0, 2000.0, 1 << 30) for g in range(2)]))
+    assert res.pct_of_floor == pytest.approx(1.0, rel=1e-9)
+    assert res.telemetry.available and res.telemetry.n_gpus == 2 and res.telemetry.power_w_mean == pytest.approx(600.0)
+    slow = B.run_benchmark(B.MockEngine(CFG, H100, efficiency=0.5, jitter=0.1, seed=3, expose_routes=True), cfgb, CFG, H100)
+    assert 0.4 < slow.pct_of_floor < 0.6 and slow.tpot_p95_s >= slow.tpot_p50_s
+    step = B.MockEngine(CFG, H100, expose_routes=True)
+    step.reset(plan="tp", dtype_bytes=1, kv_dtype_bytes=2, tp=8, ep=1, seq_len=128)
+    s = step.decode_step()
+    assert len(s.routes) == 8 and all(0 <= r.gpu < 8 for r in s.routes)
+    with pytest.raises(ValueError):
+        B.run_benchmark(eng, B.BenchConfig("x", "tp", 1, 2, 8, 1, decode_tokens=1), CFG, H100)
+
+
+def test_stats_and_quality():
+    s = B.summarize([1.0, 2.0, 3.0, 4.0])
+    assert s.mean == 2.5 and s.ci95_lo < 2.5 < s.ci95_hi and s.p50 == 2.5
+    assert B.summarize([]).n == 0 and B.summarize([5]).std is None
+    a, b = B.summarize([10, 10.1, 9.9]), B.summarize([20, 20.1, 19.9])
+    assert B.means_differ(a, b) and not B.means_differ(a, a)
+    q = B.match_rate([1, 2, 3, 4], [1, 2, 9, 4])
+    assert q.match_rate == 0.75 and q.first_divergence == 2
+
+
+def test_store_roundtrip_exports_and_gates(tmp_path):
+    cfgb = B.BenchConfig("rt", "tp", 2, 2, 8, 1, prompt_tokens=32, decode_tokens=8, repeats=3, warmup_steps=1)
+    res = B.run_benchmark(B.MockEngine(CFG, H100, jitter=0.05, seed=1), cfgb, CFG, H100, reference_ids=[0] * 7)
+    rec = B.RunRecord("r1", cfgb, {"gpu": "H100-SXM-80GB", "n_gpus": 8}, res)
+    path = B.write_run(rec, str(tmp_path))
+    back = B.load_run(path)
+    assert back.result.decode_tok_per_s == res.decode_tok_per_s and back.config == cfgb
+    assert B.load_latest("rt", str(tmp_path)).runid == "r1"
+    row = B.record_row(back)
+    assert row["energy_j_per_token"] is None and row["regime_decode"] == "memory-bound"
+    for fn, ext in ((B.export_csv, "csv"), (B.export_jsonl, "jsonl"), (B.export_markdown, "md")):
+        assert os.path.getsize(fn([back], str(tmp_path / f"o.{ext}"))) > 0
+    assert set(B.result_to_x_summary(back)) == {"ttft_ms", "decode_tok_per_s", "prefill_tokens", "completion_tokens"}
+    assert B.evaluate(res, B.Thresholds(min_decode_tok_per_s=1.0)).passed
+    assert not B.evaluate(res, B.Thresholds(min_decode_tok_per_s=1e9, min_quality_match=0.99)).passed
+    slow = B.run_benchmark(B.MockEngine(CFG, H100, efficiency=0.5, jitter=0.01, seed=2), cfgb, CFG, H100)
+    assert not B.regression_gate(res, slow).passed and B.regression_gate(slow, res).passed
+    man = B.build_manifest(CFG, H100, cfgb, runid="r1")
+    assert man["bench"]["config_id"] == B.config_id(cfgb) and len(B.model_hash(CFG)) == 12
+
+
+def test_diagnose_levers_sweeps_and_spec_model():
+    cfgb = B.BenchConfig("d", "hybrid", 1, 2, 2, 8, prompt_tokens=512, decode_tokens=16, repeats=1, warmup_steps=0)
+    res = B.run_benchmark(B.MockEngine(CFG, H100, efficiency=0.4), cfgb, CFG, H100)
+    b = B.diagnose(res)
+    assert b.dominant_term == "kernel_gap" and 0.5 <= b.confidence <= 1.0
+    levers = B.recommend(CFG, H100, cfgb, bottleneck=b)
+    assert levers and all(lv.speedup >= 1.02 for lv in levers) and levers == sorted(levers, key=lambda l: -l.speedup)
+    pts = B.depth_sweep(CFG, H100, cfgb, [1024, 32768])
+    assert pts[0].decode_tok_s > pts[1].decode_tok_s and pts[1].kv_byte_share > pts[0].kv_byte_share
+    assert len(B.layout_grid(cfgb, 8)) == 16 and len(B.quant_grid(cfgb)) == 6 and len(B.full_grid(cfgb, 8)) == 96
+    ranked = B.config_sweep(CFG, H100, B.layout_grid(cfgb, 8))
+    assert ranked[0].decode_tok_s >= ranked[-1].decode_tok_s
+    e, floor = B.realized_efficiency(CFG, H100, cfgb, 80.0)
+    assert 0 < e < 1 and floor > 80
+    assert B.expected_emitted(0.7, 4) == pytest.approx((1 - 0.7 ** 5) / 0.3)
+    assert B.verify_cost(4, 1, 1.0) == pytest.approx(1.0) and B.verify_cost(8, 4, 0.0) > B.verify_cost(2, 1, 0.0)
+    rows = B.spec_sweep(0.7, 0.86)
+    assert rows[0].speedup == max(r.speedup for r in rows)
+    assert B.prefill_latency(CFG, H100, dtype_bytes=1, kv_dtype_bytes=2, prompt_tokens=2048) > \
+        B.prefill_latency(CFG, H100, dtype_bytes=1, kv_dtype_bytes=2, prompt_tokens=128)
+    assert B.rental_usd_per_mtok(100.0, 8) == pytest.approx(8 * 3.0 / 3600 / 100 * 1e6)
+    assert B.energy_metrics(None, None)["joules_per_token"] is None
+
+
+def test_optimiser_is_monotone():
+    final, steps = optimize()
+    assert final.tok_s > MEASURED_BASELINE.tok_s and all(s.after_tok_s >= s.before_tok_s for s in steps if s.kept)
+    assert all(s.status != "MISSING" or "UNMEASURED" in s.note for s in steps)
+    lossy, _ = optimize(allow_lossy=True)
+    assert lossy.tok_s >= final.tok_s
+    sp = apply_spec(final)
+    assert sp.spec_tok_s > sp.plain_tok_s and 0 <= sp.floor_fraction <= 1
+    c = plain_decode_ceiling()
+    assert c["hard_floor_fp8_weight"] > c["optimistic_overlap"] > c["conservative_nvls2us"]
+    assert sensitivity_grid()[0]["min_overlap_for_1000"] is not None
+
+
+def test_routing_graph_and_speculative_math():
+    g = iu.CoActGraph(n_experts=16, n_layers=2)
+    iu.ingest_telemetry(g, [{"token_index": 0, "experts": [{"layer": 0, "expert_id": e, "gpu": 0} for e in (0, 1, 2, 3)]
+                             + [{"layer": 1, "expert_id": e, "gpu": 0} for e in (4, 5)]}] * 5)
+    assert g.total_edge_weight() == 5 * (6 + 1 + 8)
+    gp = iu.greedy_partition(g, n_gpus=4, n_experts=16, n_layers=2)
+    rr = iu.round_robin_placement(4, 16, 2)
+    assert iu.placement_stats(g, gp)["cross_gpu_weight"] <= iu.placement_stats(g, rr)["cross_gpu_weight"]
+    assert sorted(list(gp.values()).count(x) for x in range(4)) == [8, 8, 8, 8]
+    dag = iu.TokenDAG()
+    dag.add_layer(0, [0, 1]); dag.add_layer(1, [4, 5])
+    plan = dag.prefetch_schedule(gp, 16)
+    assert plan[0]["prefetch_layer"] == 1 and len(plan[0]["prefetch_experts"]) == 2
+    assert iu.expected_accepted_multi(0.7, 4, 2) > iu.expected_accepted_multi(0.7, 4, 1)
+    assert iu.expected_accepted_single(1.0, 4) == 4.0 and iu.memory_feasibility()["max_drafters"] > 0
+
+
+def test_cli_smoke(tmp_path, capsys):
+    d = str(tmp_path)
+    bench_main(["--results-dir", d, "run", "--name", "c", "--repeats", "2", "--decode", "8", "--prompt", "16"])
+    bench_main(["--results-dir", d, "run", "--name", "c", "--repeats", "2", "--decode", "8", "--prompt", "16", "--json"])
+    bench_main(["--results-dir", d, "report", "--name", "c"])
+    bench_main(["--results-dir", d, "gate", "--name", "c", "--min-pct-floor", "0.9"])
+    bench_main(["--results-dir", d, "diagnose", "--name", "c"])
+    runs = sorted(f[:-5] for f in os.listdir(os.path.join(d, "c")) if f.endswith(".json") and "manifest" not in f)
+    assert len(runs) == 2
+    bench_main(["--results-dir", d, "compare", "--name", "c", runs[0], runs[1]])
+    bench_main(["--results-dir", d, "export", "--name", "c", "--format", "csv", "--out", os.path.join(d, "o.csv")])
+    for cmd in (["plan"], ["sweep"], ["sweep", "--layout"], ["spec"], ["calibrate", "--measured-tok-s", "90"]):
+        bench_main(cmd)
+    with pytest.raises(SystemExit):
+        bench_main(["--results-dir", d, "gate", "--name", "c", "--min-tok-s", "1e9"])
+    from inferutil.cli import main as top
+    top(["--gpu", "B200-SXM-180GB", "--n-gpus", "8"])
+    out = capsys.readouterr().out
+    assert "GATE PASS" in out and "takeaways" in out and not B.NvmlTelemetry().available in (None,)

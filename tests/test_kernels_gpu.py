@@ -84,8 +84,9 @@ def test_gemv_residual_norm_tail(fp8, K, ks):
     assert int(st["err"].item()) == 0
 
 
+@pytest.mark.parametrize("ks", [1, 8])
 @pytest.mark.parametrize("E,k", [(128, 8), (16, 4)])
-def test_router_tail(E, k):
+def test_router_tail(E, k, ks):
     lib = _K()
     H = 2048
     g = torch.Generator(device=_dev()).manual_seed(E)
@@ -97,7 +98,9 @@ def test_router_tail(E, k):
     st = _state()
     a = lib.IhbGemvArgs()
     lib.fill_weight(a, QWeight(wr))
-    a.x, a.out, a.epi, a.ks = x.data_ptr(), logits.data_ptr(), lib.EPI_ROUTER, 1
+    a.x, a.out, a.epi, a.ks = x.data_ptr(), logits.data_ptr(), lib.EPI_ROUTER, ks
+    part = torch.zeros(ks * E, device=_dev())
+    a.router_partial = part.data_ptr()
     a.counter, a.err = st["counter"].data_ptr(), st["err"].data_ptr()
     a.top_k, a.renorm, a.sel_idx, a.sel_w = k, 1, sel_idx.data_ptr(), sel_w.data_ptr()
     lib.gemv(a, False)
