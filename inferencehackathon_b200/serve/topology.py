@@ -1,0 +1,59 @@
+"""``GET /v1/topology``: live GPU stats (``nvidia-smi`` read-only query, static fallback) and the expert -> GPU
+placement (optimised placement JSON when present, else ``expert % n_gpus``)
+(reference: server/topology.py:8-79)."""
+from __future__ import annotations
+
+import json
+import os
+import subprocess
+from pathlib import Path
+from typing import List, Optional
+
+OPTIMIZED_PLACEMENT_PATH = Path(os.environ.get("OPTIMIZED_PLACEMENT", "/alloc/data/optimized_placement.json"))
+_QUERY = "index,name,memory.total,memory.used,utilization.gpu,temperature.gpu"
+
+
+def _static_gpus(n: int = 8, name: str = "B200") -> List[dict]:
+    return [{"id": i, "name": f"{name}-{i}", "mem_total_mb": 183359, "mem_used_mb": 0, "utilization_pct": 0,
+             "temp_c": 0} for i in range(n)]
+
+
+def _query_gpus() -> List[dict]:
+    try:
+        text = subprocess.check_output(["nvidia-smi", f"--query-gpu={_QUERY}", "--format=csv,noheader,nounits"],
+                                       timeout=5).decode()
+        gpus = []
+        for line in text.strip().splitlines():
+            idx, name, total, used, util, temp = (x.strip() for x in line.split(","))
+            gpus.append({"id": int(idx), "name": name, "mem_total_mb": int(total), "mem_used_mb": int(used),
+                         "utilization_pct": int(util), "temp_c": int(temp)})
+        return gpus or _static_gpus()
+    except Exception:
+        return _static_gpus()
+
+
+def _load_placement(num_layers: int, experts_per_layer: int, num_gpus: int, path: Optional[Path] = None) -> dict:
+    path = path or OPTIMIZED_PLACEMENT_PATH
+    table = {}
+    try:
+        if path.exists():
+            with open(path) as f:
+                table = json.load(f)["placement"]
+    except Exception:
+        table = {}
+    return {str(L): {str(e): int(table.get(str(L), {}).get(str(e), e % num_gpus)) for e in range(experts_per_layer)}
+            for L in range(num_layers)}
+
+
+def build_topology(num_layers: int = 94, experts_per_layer: int = 128, placement_fn=None) -> dict:
+    """``placement_fn(expert_id) -> gpu`` (from a live engine) overrides file / round-robin placement."""
+    gpus = _query_gpus()
+    n = len(gpus)
+    if placement_fn is not None:
+        placement = {str(L): {str(e): int(placement_fn(e)) for e in range(experts_per_layer)} for L in range(num_layers)}
+        source = "engine"
+    else:
+        placement = _load_placement(num_layers, experts_per_layer, n)
+        source = "optimized" if OPTIMIZED_PLACEMENT_PATH.exists() else "round-robin"
+    return {"gpus": gpus, "num_layers": num_layers, "experts_per_layer": experts_per_layer, "placement": placement,
+            "placement_source": source}

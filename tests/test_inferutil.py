@@ -157,3 +157,17 @@ def test_cli_smoke(tmp_path, capsys):
     top(["--gpu", "B200-SXM-180GB", "--n-gpus", "8"])
     out = capsys.readouterr().out
     assert "GATE PASS" in out and "takeaways" in out and not B.NvmlTelemetry().available in (None,)
+
+
+def test_real_engine_through_the_seam(tmp_path):
+    from inferencehackathon_b200.runtime.bench_adapter import B200Engine
+    from inferencehackathon_b200.runtime.engine import InferenceEngine
+    eng = B200Engine(InferenceEngine.build("tiny", weights="fp32", max_seq=128))
+    assert isinstance(eng, B.Engine)
+    cfgb = B.BenchConfig("real", "tp", 4, 4, 1, 1, prompt_tokens=16, decode_tokens=6, repeats=2, warmup_steps=1)
+    res = B.run_benchmark(eng, cfgb, eng.cfg, eng.cluster, collect_ids=True)
+    assert res.decode_tok_per_s > 0 and res.measured_breakdown is not None and len(res.generated_token_ids) == 5
+    again = B.run_benchmark(eng, cfgb, eng.cfg, eng.cluster, reference_ids=res.generated_token_ids)
+    assert again.quality.match_rate == 1.0
+    bench_main(["--results-dir", str(tmp_path), "run", "--name", "real", "--engine", "b200", "--repeats", "1",
+                "--prompt", "8", "--decode", "4", "--dtype", "2"])

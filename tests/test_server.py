@@ -1,0 +1,141 @@
+"""HTTP contract of the serving layer (CPU): health / models / topology, SSE framing with x_telemetry and x_summary,
+backend selection, the vLLM proxy against a fake HTTP response, Prometheus spec counters, and the real engine
+streaming real router selections."""
+import io
+import json
+
+import pytest
+from fastapi.testclient import TestClient
+
+from inferencehackathon_b200.serve import backends as bk
+from inferencehackathon_b200.serve.app import create_app
+from inferencehackathon_b200.serve.mock_engine import ENGINE_PROFILES, mock_stream
+from inferencehackathon_b200.serve.optimization_telemetry import B200X8, floor_breakdown, summary_fields
+from inferencehackathon_b200.serve.schemas import ChatMessage, ChatRequest, sse, sse_done
+from inferencehackathon_b200.serve.spec_metrics import accept_stats, cumulative_accept, parse_spec_counters
+from inferencehackathon_b200.serve.topology import build_topology
+
+
+def _frames(text):
+    return [f[6:] for f in text.split("\n\n") if f.startswith("data: ")]
+
+
+def test_health_models_topology():
+    c = TestClient(create_app(bk.MockBackend()))
+    assert c.get("/health").json()["status"] == "ok"
+    assert c.get("/v1/models").json()["data"][0]["id"] == "qwen3-235b-a22b"
+    t = c.get("/v1/topology").json()
+    assert len(t["gpus"]) == 8 and t["num_layers"] == 94 and t["experts_per_layer"] == 128
+    assert t["placement"]["3"]["17"] == 17 % 8 and t["placement_source"] in ("round-robin", "optimized")
+    assert set(t["gpus"][0]) == {"id", "name", "mem_total_mb", "mem_used_mb", "utilization_pct", "temp_c"}
+
+
+def test_sse_contract_with_mock_backend():
+    c = TestClient(create_app(bk.MockBackend()))
+    body = {"messages": [{"role": "user", "content": "hello there"}], "max_tokens": 6, "stream": True}
+    r = c.post("/v1/chat/completions", json=body)
+    assert r.headers["content-type"].startswith("text/event-stream")
+    frames = _frames(r.text)
+    assert frames[-1] == "[DONE]"
+    summary = json.loads(frames[-2])["x_summary"]
+    chunks = [json.loads(f) for f in frames[:-2]]
+    assert len(chunks) == 6 and all(ch["object"] == "chat.completion.chunk" for ch in chunks)
+    for i, ch in enumerate(chunks):
+        tel = ch["x_telemetry"]
+        assert tel["token_index"] == i and len(tel["experts"]) == 8
+        assert all(0 <= e["gpu"] < 8 and e["layer"] == i % 94 for e in tel["experts"])
+        assert tel["spec"]["accepted"] <= tel["spec"]["proposed"]
+    for key in ("ttft_ms", "decode_tok_per_s", "prefill_tokens", "completion_tokens", "spec_accept_rate", "engine",
+                "spec_enabled", "floor_breakdown_ms", "regime", "next_lever", "pct_of_ceiling", "pct_of_roofline"):
+        assert key in summary
+    assert summary["prefill_tokens"] == 2 and summary["completion_tokens"] == 6
+    r2 = c.post("/v1/chat/completions", json={**body, "stream": False, "engine": "vllm"})
+    assert r2.json()["object"] == "chat.completion" and r2.json()["choices"][0]["message"]["content"]
+
+
+def test_mock_is_deterministic_and_profiles_differ():
+    req = ChatRequest(messages=[ChatMessage(role="user", content="x")], max_tokens=5)
+    topo = build_topology()
+    assert list(mock_stream(req, topo)) == list(mock_stream(req, topo))
+    v = list(mock_stream(ChatRequest(messages=req.messages, max_tokens=5, engine="vllm"), topo))[-1]["x_summary"]
+    a = list(mock_stream(req, topo))[-1]["x_summary"]
+    assert a["decode_tok_per_s"] > v["decode_tok_per_s"] and a["spec_enabled"] and not v["spec_enabled"]
+    assert set(ENGINE_PROFILES) == {"conifer", "vllm"}
+    assert sse({"a": 1}) == 'data: {"a": 1}\n\n' and sse_done() == "data: [DONE]\n\n"
+
+
+def test_optimization_telemetry_blocks():
+    bd = floor_breakdown(11.7, "bf16", "bf16", 17.0, 512)
+    assert bd["weight"] == pytest.approx(1.61, abs=0.01) and bd["comms"] == pytest.approx(3.196, abs=1e-3)
+    assert bd["overhead"] == pytest.approx(11.7 - bd["weight"] - bd["comms"] - bd["kv"], abs=2e-3)
+    s = summary_fields(11.7, 85.7, "bf16")
+    assert s["regime"] == "floor-bound" and 0 < s["pct_of_roofline"] < 100
+    w = summary_fields(0.9, 1100.0, "fp8", collective_us=0.1)
+    assert w["regime"] == "weight-bound"
+    assert summary_fields(2.0, 500.0, "fp8", profile=B200X8)["floor_breakdown_ms"]["weight"] < bd["weight"] / 2
+
+
+def test_backend_selection(monkeypatch):
+    monkeypatch.setenv("BACKEND", "mock")
+    assert isinstance(bk.get_backend(), bk.MockBackend)
+    monkeypatch.delenv("BACKEND")
+    monkeypatch.setattr(bk, "_vllm_healthy", lambda url=None: True)
+    assert isinstance(bk.get_backend(), bk.VLLMBackend)
+    monkeypatch.setattr(bk, "_vllm_healthy", lambda url=None: False)
+    assert isinstance(bk.get_backend(), bk.MockBackend)
+
+
+class _FakeResponse(io.BytesIO):
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        return False
+
+
+def test_vllm_proxy_reframes_and_summarises(monkeypatch):
+    words = ["Hi", " there", " friend"]
+    payload = b"".join(b"data: " + json.dumps({"choices": [{"delta": {"content": w}}]}).encode() + b"\n\n" for w in words)
+    payload += b"data: [DONE]\n\n"
+    monkeypatch.setattr(bk.urllib.request, "urlopen", lambda *a, **k: _FakeResponse(payload))
+    out = list(bk.VLLMBackend(scrape_spec=False).stream(
+        ChatRequest(messages=[ChatMessage(role="user", content="one two three")], max_tokens=8), build_topology()))
+    assert [c["choices"][0]["delta"]["content"] for c in out[:-1]] == words
+    assert all(len(c["x_telemetry"]["experts"]) == 8 for c in out[:-1])
+    assert out[-1]["x_summary"]["completion_tokens"] == 3 and out[-1]["x_summary"]["prefill_tokens"] == 3
+
+
+def test_spec_metrics_parsing():
+    before = '# HELP x\nvllm:spec_decode_num_accepted_tokens_total{model="m"} 100\nvllm:spec_decode_num_drafts_total{model="m"} 50\n'
+    after = 'vllm:spec_decode_num_accepted_tokens_total{model="m"} 160\nvllm:spec_decode_num_drafts_total{model="m"} 90\n'
+    assert parse_spec_counters(before) == {"accepted": 100.0, "drafts": 50.0}
+    st = accept_stats(before, after)
+    assert st["accepted"] == 60 and st["drafts"] == 40 and st["tau"] == pytest.approx(2.5) and st["accept_rate"] == 1.0
+    assert accept_stats(after, after)["tau"] == 1.0
+    assert cumulative_accept("")["accept_rate"] == 0.0
+
+
+def test_engine_backend_streams_real_routes():
+    from inferencehackathon_b200 import TINY
+    from inferencehackathon_b200.runtime.engine import InferenceEngine
+    eng = InferenceEngine.build("tiny", weights="fp32", max_seq=128)
+    backend = bk.EngineBackend(eng)
+    c = TestClient(create_app(backend))
+    t = c.get("/v1/topology").json()
+    assert t["num_layers"] == TINY.n_layers and t["experts_per_layer"] == TINY.n_experts and t["placement_source"] == "engine"
+    body = {"messages": [{"role": "user", "content": "route me"}], "max_tokens": 5, "temperature": 0.0}
+    frames = _frames(c.post("/v1/chat/completions", json=body).text)
+    chunks = [json.loads(f) for f in frames[:-2]]
+    assert frames[-1] == "[DONE]" and len(chunks) == 5
+    for i, ch in enumerate(chunks):
+        ex = ch["x_telemetry"]["experts"]
+        assert len(ex) == TINY.top_k and len({e["expert_id"] for e in ex}) == TINY.top_k
+        assert all(e["layer"] == i % TINY.n_layers and 0 <= e["expert_id"] < TINY.n_experts for e in ex)
+        assert ch["x_telemetry"]["t_ms"] > 0
+    again = [json.loads(f) for f in _frames(c.post("/v1/chat/completions", json=body).text)[:-2]]
+    assert [a["choices"][0]["delta"]["content"] for a in again] == [b["choices"][0]["delta"]["content"] for b in chunks]
+    summ = json.loads(frames[-2])["x_summary"]
+    assert summ["completion_tokens"] == 5 and summ["prefill_tokens"] == len("route me") and summ["decode_tok_per_s"] > 0
+    assert "qwen3" in c.get("/v1/models").json()["data"][0]["id"]
+    from server.main import app as shim_app     # the reference's import path
+    assert shim_app.title == "multi-gpu-inference-console"
