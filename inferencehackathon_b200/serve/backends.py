@@ -137,6 +137,8 @@ class EngineBackend(Backend):
             try:
                 pre = self.engine.prefill(prompt)
                 tokens = [pre.next_token]
+                if self.spec is not None and hasattr(self.spec, "begin"):
+                    self.spec.begin(prompt)
                 routes = list(self.engine.model.last_routes) if self.engine.gpu is None else self.engine.gpu.last_routes()
                 yield self._chunk(req, 0, tokens[0], 1e3 * pre.seconds, routes, 1, 1)
                 while len(tokens) < n_new:

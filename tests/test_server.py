@@ -139,3 +139,21 @@ def test_engine_backend_streams_real_routes():
     assert "qwen3" in c.get("/v1/models").json()["data"][0]["id"]
     from server.main import app as shim_app     # the reference's import path
     assert shim_app.title == "multi-gpu-inference-console"
+
+
+def test_engine_backend_with_speculative_driver_streams_same_text():
+    from inferencehackathon_b200.runtime.engine import InferenceEngine
+    from inferencehackathon_b200.spec.driver import SpecDriver
+    from inferencehackathon_b200.spec.ngram import NGramDrafter
+    eng = InferenceEngine.build("tiny", weights="fp32", max_seq=256)
+    body = {"messages": [{"role": "user", "content": "abcabcabcabcabcabc"}], "max_tokens": 12, "temperature": 0.0}
+    plain = [json.loads(f) for f in _frames(TestClient(create_app(bk.EngineBackend(eng))).post(
+        "/v1/chat/completions", json=body).text)[:-2]]
+    spec_backend = bk.EngineBackend(eng, spec_driver=SpecDriver(eng, NGramDrafter(2), depth=4, width=1, floor_fraction=1.0))
+    frames = _frames(TestClient(create_app(spec_backend)).post("/v1/chat/completions", json=body).text)
+    spec = [json.loads(f) for f in frames[:-2]]
+    text = lambda cs: [c["choices"][0]["delta"]["content"] for c in cs]
+    assert text(spec) == text(plain) and len(spec) == 12
+    summ = json.loads(frames[-2])["x_summary"]
+    assert summ["spec_enabled"] is True and 0.0 <= summ["spec_accept_rate"] <= 1.0
+    assert all("spec" in c["x_telemetry"] for c in spec)
