@@ -206,6 +206,70 @@ typedef struct {
 int ihb_tc_decode(IhbTcDecArgs* args, int use_pdl, cudaStream_t stream);
 size_t ihb_tc_dec_partial_floats(const IhbTcDecArgs* args);
 
+// ---- persistent decode megakernel: one cooperative launch runs `steps` whole tokens -------------------------------------
+// One weight matrix (or a stack of per-expert matrices with the same shape): rows contiguous, K-major.
+typedef struct {
+  const uint8_t* W;
+  const float* wscale;     // fp8: [matrices][ceil(rows / rb)][nkb]
+  int rows, K;             // per matrix
+  int rb, kb_shift, nkb;   // scale block: rb rows x (16 << kb_shift) columns; nkb = floats per scale row
+} IhbMat;
+
+typedef struct {
+  IhbMat wqkv;             // [(nq + 2 nkv) * 128, H]
+  IhbMat wo;               // [H, nq * 128]
+  IhbMat wgu;              // per expert [2 I, H] (gate rows then up rows)
+  IhbMat wd;               // per expert [H, I]
+  const void* router;      // bf16 [E, H]
+  const float* in_ln;
+  const float* post_ln;
+  const float* q_norm;
+  const float* k_norm;
+  void* k_cache;           // [nkv, max_seq, 128] bf16
+  void* v_cache;
+  float* router_logits;    // [E] (written every token: telemetry)
+  int* sel_idx;            // [top_k]
+  float* sel_w;            // [top_k]
+} IhbMegaLayer;
+
+typedef struct {
+  const IhbMegaLayer* layers;   // device array
+  int n_layers;
+  int wtype;                    // IHB_W_FP8 | IHB_W_BF16 (all linear layers; the router is always bf16)
+  int H, nq, nkv, I, E, top_k, renorm;
+  int max_seq;
+  const float* cos_t;           // [max_seq, 64]
+  const float* sin_t;
+  float eps;
+  const void* embed;            // [vocab, H] fp32 or bf16
+  int embed_is_bf16;
+  const float* final_norm;
+  IhbMat lm_head;               // [vocab_local, H]
+  int vocab0;
+  float* logits;                // optional [vocab_local]
+  int* cur_token;
+  int* pos;
+  int* token_ring;
+  int token_ring_size;
+  const int* forced;
+  const int* n_forced;
+  float* qkv;                   // [(nq + 2 nkv) * 128]
+  float* attn_part;             // [nq][max_split][130]
+  float* attn;                  // [nq * 128]
+  float* act;                   // [top_k * I]
+  unsigned long long* argmax_partial;   // [grid]
+  unsigned* bar;                // [0] arrivals, [1] releases, [2] arrival base, [3] release base, [8 ...] head counters
+  unsigned* err;
+  unsigned long long* prof;     // optional: CTA 0 stores %globaltimer at kernel start ([0]) and after barrier i ([i])
+  int max_split;                // attention splits available per (kv head, group of 8 query heads)
+  int steps;                    // tokens per launch
+  IhbComm comm;
+} IhbMegaArgs;
+
+// grid = 0: one CTA per SM. Returns cudaErrorCooperativeLaunchTooLarge when the CTAs cannot all be resident.
+int ihb_mega_decode(const IhbMegaArgs* args, int grid, cudaStream_t stream);
+int ihb_mega_max_grid(const IhbMegaArgs* args);
+
 #ifdef __cplusplus
 }
 #endif

@@ -92,6 +92,29 @@ class IhbTcDecArgs(C.Structure):
 _lib: Optional[C.CDLL] = None
 
 
+class IhbMat(C.Structure):
+    _fields_ = [("W", _vp), ("wscale", _vp), ("rows", C.c_int), ("K", C.c_int),
+                ("rb", C.c_int), ("kb_shift", C.c_int), ("nkb", C.c_int)]
+
+
+class IhbMegaLayer(C.Structure):
+    _fields_ = [("wqkv", IhbMat), ("wo", IhbMat), ("wgu", IhbMat), ("wd", IhbMat), ("router", _vp),
+                ("in_ln", _vp), ("post_ln", _vp), ("q_norm", _vp), ("k_norm", _vp),
+                ("k_cache", _vp), ("v_cache", _vp), ("router_logits", _vp), ("sel_idx", _vp), ("sel_w", _vp)]
+
+
+class IhbMegaArgs(C.Structure):
+    _fields_ = [("layers", _vp), ("n_layers", C.c_int), ("wtype", C.c_int),
+                ("H", C.c_int), ("nq", C.c_int), ("nkv", C.c_int), ("I", C.c_int), ("E", C.c_int),
+                ("top_k", C.c_int), ("renorm", C.c_int), ("max_seq", C.c_int),
+                ("cos_t", _vp), ("sin_t", _vp), ("eps", C.c_float),
+                ("embed", _vp), ("embed_is_bf16", C.c_int), ("final_norm", _vp), ("lm_head", IhbMat),
+                ("vocab0", C.c_int), ("logits", _vp), ("cur_token", _vp), ("pos", _vp), ("token_ring", _vp),
+                ("token_ring_size", C.c_int), ("forced", _vp), ("n_forced", _vp),
+                ("qkv", _vp), ("attn_part", _vp), ("attn", _vp), ("act", _vp), ("argmax_partial", _vp),
+                ("bar", _vp), ("err", _vp), ("prof", _vp), ("max_split", C.c_int), ("steps", C.c_int), ("comm", IhbComm)]
+
+
 def load(build_if_missing: bool = True) -> C.CDLL:
     """Load (building first if the sources changed and nvcc is present) the kernel library."""
     global _lib
@@ -125,6 +148,10 @@ def load(build_if_missing: bool = True) -> C.CDLL:
     lib.ihb_tc_decode.restype = C.c_int
     lib.ihb_tc_dec_partial_floats.argtypes = [C.POINTER(IhbTcDecArgs)]
     lib.ihb_tc_dec_partial_floats.restype = C.c_size_t
+    lib.ihb_mega_decode.argtypes = [C.POINTER(IhbMegaArgs), C.c_int, _vp]
+    lib.ihb_mega_decode.restype = C.c_int
+    lib.ihb_mega_max_grid.argtypes = [C.POINTER(IhbMegaArgs)]
+    lib.ihb_mega_max_grid.restype = C.c_int
     for name in ("ihb_gemv", "ihb_moe_gateup", "ihb_moe_down", "ihb_embed_norm", "ihb_qk_norm_rope_kv",
                  "ihb_flash_decode"):
         getattr(lib, name).restype = C.c_int
@@ -335,3 +362,23 @@ def tc_decode(args: IhbTcDecArgs, use_pdl: bool = False) -> None:
 
 def tc_dec_partial_floats(args: IhbTcDecArgs) -> int:
     return int(load().ihb_tc_dec_partial_floats(C.byref(args)))
+
+
+def mat_of(qw) -> IhbMat:
+    """Describes a (stack of) plain row-major weight matrices to the persistent decode kernel."""
+    m = IhbMat()
+    m.W = qw.data.data_ptr()
+    m.rows, m.K = qw.data.shape[-2], qw.data.shape[-1]
+    if qw.scale is not None:
+        ks = kernel_scale(qw)
+        m.wscale = ks.data_ptr()
+        m.rb, m.kb_shift, m.nkb = qw.rb, kb_shift_of(qw.kb) - 4, ks.shape[-1]     # shift counted in 16-element chunks
+    return m
+
+
+def mega_max_grid(args: IhbMegaArgs) -> int:
+    return int(load().ihb_mega_max_grid(C.byref(args)))
+
+
+def mega_decode(args: IhbMegaArgs, grid: int = 0) -> None:
+    check(load().ihb_mega_decode(C.byref(args), grid, stream_ptr()), "ihb_mega_decode")

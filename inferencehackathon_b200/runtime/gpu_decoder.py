@@ -44,6 +44,8 @@ class GpuDecoder:
         self.max_seq = cfg.max_seq
         self.use_pdl = bool(env_flag("IHB_PDL", 1))
         self.use_tc = bool(env_flag("IHB_TC", 1))          # tensor-core linears (0: SIMT streaming GEMVs)
+        # persistent whole-token kernel (tensor parallel only; expert parallel keeps the per-kernel pipeline)
+        self.use_mega = bool(env_flag("IHB_MEGA", 1)) and cfg.parallel.ep <= 1 and m.n_experts <= 256
         self.fp8 = weights.quant.weights == "fp8_block"
         self.use_graph = cfg.use_graph and bool(env_flag("IHB_GRAPH", 1))
         self.comm_ref = comm
@@ -84,7 +86,9 @@ class GpuDecoder:
         celems = 16 if weights.quant.weights == "fp8_block" else 8
         self.ks_o = _pick_ks(self.nq * 128, celems)
         self._setup_comm()
-        if self.use_tc:
+        if self.use_mega:
+            self._build_mega()
+        elif self.use_tc:
             self._build_tc()
         else:
             self._build_args()
@@ -164,6 +168,61 @@ class GpuDecoder:
                                     token_ring_size=self.token_ring.numel(), forced=self.forced,
                                     n_forced=self.n_forced)
         self.head.comm = self._comm()
+
+    # persistent whole-token kernel -------------------------------------------------------------------------------
+    def _build_mega(self) -> None:
+        """One cooperative launch per token: builds the device-side layer table and the argument block."""
+        import ctypes as C
+        from ..models.quant import QWeight
+        m, w, dev = self.cfg.model, self.w, self.device
+        f32 = dict(dtype=torch.float32, device=dev)
+        layers = (K.IhbMegaLayer * len(w.layers))()
+        for L, lw in enumerate(w.layers):
+            e = layers[L]
+            e.wqkv, e.wo, e.wgu, e.wd = K.mat_of(lw.wqkv), K.mat_of(lw.wo), K.mat_of(lw.w_gu), K.mat_of(lw.w_d)
+            e.router = lw.router.data_ptr()
+            e.in_ln, e.post_ln = lw.in_ln.data_ptr(), lw.post_ln.data_ptr()
+            e.q_norm, e.k_norm = lw.q_norm.data_ptr(), lw.k_norm.data_ptr()
+            e.k_cache, e.v_cache = self.k_cache[L].data_ptr(), self.v_cache[L].data_ptr()
+            e.router_logits = self.router_logits[L].data_ptr()
+            e.sel_idx, e.sel_w = self.sel_idx[L].data_ptr(), self.sel_w[L].data_ptr()
+        if w.layers and w.layers[0].router.dtype != torch.bfloat16:
+            raise ValueError("the persistent kernel reads the router matrix as bf16")
+        raw = bytes(layers)
+        self.mega_layers = torch.frombuffer(bytearray(raw), dtype=torch.uint8).to(dev)
+        a = K.IhbMegaArgs()
+        a.layers, a.n_layers = self.mega_layers.data_ptr(), len(w.layers)
+        a.wtype = K.W_FP8 if self.fp8 else K.W_BF16
+        a.H, a.nq, a.nkv, a.I, a.E = self.H, self.nq, self.nkv, self.I, m.n_experts
+        a.top_k, a.renorm, a.max_seq = m.top_k, int(m.norm_topk_prob), self.max_seq
+        a.cos_t, a.sin_t, a.eps = self.cos.data_ptr(), self.sin.data_ptr(), m.rms_eps
+        a.embed, a.embed_is_bf16 = w.embed.data_ptr(), int(w.embed.dtype == torch.bfloat16)
+        a.final_norm, a.lm_head, a.vocab0 = w.final_norm.data_ptr(), K.mat_of(w.lm_head), w.geom.vocab0
+        a.logits = self.logits.data_ptr()
+        a.cur_token, a.pos = self.cur_token.data_ptr(), self.pos.data_ptr()
+        a.token_ring, a.token_ring_size = self.token_ring.data_ptr(), self.token_ring.numel()
+        a.forced, a.n_forced = self.forced.data_ptr(), self.n_forced.data_ptr()
+        ngrp = (self.nq // self.nkv + 7) // 8
+        sms = torch.cuda.get_device_properties(dev).multi_processor_count
+        a.max_split = env_flag("IHB_MEGA_SPLITS", max(1, min(64, sms // (self.nkv * ngrp))))
+        self.mega_attn_part = torch.zeros(self.nq * a.max_split * 130, **f32)
+        self.mega_act = torch.zeros(m.top_k * 2 * self.I, **f32)
+        self.mega_bar = torch.zeros(8 + self.nkv * ngrp, dtype=torch.int32, device=dev)
+        a.qkv, a.attn_part, a.attn, a.act = (self.qkv.data_ptr(), self.mega_attn_part.data_ptr(), self.attn.data_ptr(),
+                                             self.mega_act.data_ptr())
+        a.argmax_partial, a.bar, a.err = self.argmax_partial.data_ptr(), self.mega_bar.data_ptr(), self.err.data_ptr()
+        a.steps = 1
+        a.comm = self._comm()
+        self.mega_prof = None
+        if env_flag("IHB_MEGA_PROF", 0):
+            self.mega_prof = torch.zeros(6 * len(w.layers) + 4 + 4096, dtype=torch.int64, device=dev)
+            a.prof = self.mega_prof.data_ptr()
+        self.mega = a
+        self.mega_grid = min(env_flag("IHB_MEGA_GRID", sms), K.mega_max_grid(a), self.argmax_partial.numel())
+        if self.mega_grid < 1:
+            raise RuntimeError("the persistent decode kernel does not fit on this device")
+        self.use_graph = False                   # one launch per token: nothing to capture
+        self.n_launches_per_step = 1
 
     # tensor-core path -------------------------------------------------------------------------------------------
     def _tc_args(self, qw, tiled, x, xscale, mode, epi, rows=None, **kw) -> K.IhbTcDecArgs:
@@ -295,6 +354,9 @@ class GpuDecoder:
         self.n_launches_per_step = n + 1
 
     def _step(self) -> None:
+        if self.use_mega:
+            K.mega_decode(self.mega, self.mega_grid)
+            return
         if not self.use_graph:
             self._enqueue_step()
             return
@@ -335,6 +397,8 @@ class GpuDecoder:
         code = int(self.err.item())
         if code:
             self.err.zero_()
+            if self.use_mega:
+                self.mega_bar.zero_()          # the grid barrier counters are out of step after an abandoned wait
             raise RuntimeError(f"device-side wait gave up: {K.ERR_NAMES.get(code, code)}")
 
     def prefill(self, toks: torch.Tensor, sampler, return_logits: bool):
@@ -389,6 +453,22 @@ class GpuDecoder:
     def last_routes(self) -> List[RouteRecord]:
         idx, w = self.sel_idx.cpu(), self.sel_w.cpu()
         return [RouteRecord(L, idx[L].tolist(), w[L].tolist()) for L in range(idx.shape[0])]
+
+    def mega_phase_us(self) -> dict:
+        """Per-phase device times (microseconds, from CTA 0's barrier timestamps) of the last token; needs
+        ``IHB_MEGA_PROF=1``. Phases per layer: qkv, attention, o_proj (+ all-reduce), norm + router, gate/up,
+        down (+ all-reduce); then head and token update."""
+        if self.mega_prof is None:
+            raise RuntimeError("set IHB_MEGA_PROF=1 before building the engine")
+        t = self.mega_prof.cpu().numpy().astype("float64")
+        d = (t[1:] - t[:-1]) / 1e3
+        L = len(self.w.layers)
+        names = ["qkv", "attention", "o_proj_ar", "norm_router", "gate_up", "down_ar"]
+        out = {n: float(d[i:6 * L:6].mean()) for i, n in enumerate(names)} if L else {}
+        out["head"] = float(d[6 * L])
+        out["token_update"] = float(d[6 * L + 1])
+        out["total"] = float((t[6 * L + 2] - t[0]) / 1e3)
+        return out
 
     def run_steps(self, n: int) -> None:
         """Enqueue ``n`` decode steps without any host synchronisation (benchmark loop)."""

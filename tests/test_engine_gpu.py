@@ -13,12 +13,17 @@ def _prompt(n=24):
 
 
 @pytest.mark.parametrize("weights", ["bf16", "fp8_block"])
-@pytest.mark.parametrize("graph", [False, True])
-def test_cuda_decode_matches_torch_reference(weights, graph):
+@pytest.mark.parametrize("pipeline,graph", [("mega", False), ("tc", False), ("tc", True), ("simt", True)])
+def test_cuda_decode_matches_torch_reference(weights, pipeline, graph, monkeypatch):
+    """``mega``: the persistent whole-token kernel; ``tc``: tensor-core linears, one kernel per op; ``simt``: the
+    streaming GEMV kernels."""
+    monkeypatch.setenv("IHB_MEGA", "1" if pipeline == "mega" else "0")
+    monkeypatch.setenv("IHB_TC", "0" if pipeline == "simt" else "1")
     dev = "cuda:0"
     ref = InferenceEngine.build("small", weights=weights, device=dev, backend="torch", max_seq=256)
     eng = InferenceEngine.build("small", weights=weights, device=dev, backend="cuda", max_seq=256, use_graph=graph)
-    if eng.gpu.use_tc:      # the oracle rounds activations the way the tensor-core kernels store them
+    assert eng.gpu.use_mega == (pipeline == "mega")
+    if eng.gpu.use_tc and not eng.gpu.use_mega:      # the oracle rounds activations the way the tensor-core kernels store them
         ref.model.act_mode = "fp8" if weights == "fp8_block" else "bf16"
     pr = ref.prefill(_prompt(), return_logits=True)
     pe = eng.prefill(_prompt(), return_logits=True)
@@ -45,7 +50,9 @@ def test_cuda_decode_matches_torch_reference(weights, graph):
     eng.gpu.check_error()
 
 
-def test_graph_replay_is_deterministic():
+@pytest.mark.parametrize("mega", ["0", "1"])
+def test_graph_replay_is_deterministic(mega, monkeypatch):
+    monkeypatch.setenv("IHB_MEGA", mega)
     eng = InferenceEngine.build("small", weights="fp8_block", device="cuda:0", backend="cuda", max_seq=256)
     a = eng.generate(_prompt(), 16).tokens
     b = eng.generate(_prompt(), 16).tokens
