@@ -39,15 +39,15 @@ struct MgCtx {
   unsigned base, rel_base, n_bar, n_rel, epoch;
   // shared memory carve-up
   float* resid;          // [H]
-  float* xf;             // fp32 activation vector (router input; every GEMV input for bf16 weights)
-  __half* xh;            // fp16 pre-scaled activation vector (fp8 weights)
+  float* xf;             // [H] fp32 normed hidden state (router input)
+  float* xv;             // bf16 weights: fp32 activation vector of the running GEMV
+  __half* xh;            // fp8 weights: the activation vector as fp16, pre-scaled by a power of two
+  float unscale;         // undoes that pre-scale
   float* red;            // [32] block reductions
   int* sel_e;            // [top_k]
   float* sel_w;          // [top_k]
   int* flags;            // [0] dead, [1] last-arriver flag of the attention merge
   MgAttnSmem* attn;
-  uint8_t* ring;         // [warps][MG_STAGES][4 KB] weight stream
-  float unscale;         // undoes the power-of-two pre-scale of xh
 };
 
 __device__ __forceinline__ unsigned ld_acquire_gpu_u32(const unsigned* p) {
@@ -131,44 +131,37 @@ __device__ __forceinline__ float block_max(float v, float* red) {
   return t;
 }
 
-// xf[0..n) (fp32, shared) -> xh (fp16, shared) scaled by a power of two so that max|x| <= 8 (bounds the fp16
-// accumulation chains of dot16_e4m3); c.unscale undoes it.
-__device__ __forceinline__ void mg_stage_half(MgCtx& c, const float* src, int n) {
-  float m = 0.f;
-  for (int i = threadIdx.x; i < n; i += MG_THREADS) m = fmaxf(m, fabsf(src[i]));
-  m = block_max(m, c.red);
-  int e = 0;
-  if (m > 8.f) e = static_cast<int>(ceilf(log2f(m * 0.125f)));
-  const float s = exp2f(static_cast<float>(-e));
-  c.unscale = exp2f(static_cast<float>(e));
-  for (int i = threadIdx.x; i < n; i += MG_THREADS) c.xh[i] = __float2half_rn(src[i] * s);
-  __syncthreads();
-}
-
-// n values produced by f(i) (one global read each) -> xh: stored as fp16 at once, the maximum is found on the way and
-// the vector is re-scaled in shared memory only when it exceeds 8 (a power-of-two factor: no second rounding).
-template <typename F>
-__device__ __forceinline__ void mg_stage_half_from(MgCtx& c, int n, F f) {
-  float m = 0.f;
-  for (int i = threadIdx.x; i < n; i += MG_THREADS) {
-    const float v = f(i);
-    m = fmaxf(m, fabsf(v));
-    c.xh[i] = __float2half_rn(v);
-  }
-  m = block_max(m, c.red);
-  c.unscale = 1.f;
-  if (m > 8.f) {
-    const int e = static_cast<int>(ceilf(log2f(m * 0.125f)));
-    const __half s = __float2half_rn(exp2f(static_cast<float>(-e)));
-    c.unscale = exp2f(static_cast<float>(e));
-    for (int i = threadIdx.x; i < n; i += MG_THREADS) c.xh[i] = __hmul(c.xh[i], s);
+// Stages the n values f(i) (one global read each at most) as the activation vector of the next GEMV. fp8 weights:
+// fp16 in shared memory, scaled by a power of two so that max|x| <= 8, which bounds the fp16 accumulation chains of
+// dot16_e4m3 (the values are stored at once and re-scaled in place only when needed: a power-of-two factor, so no
+// second rounding); bf16 weights: fp32.
+template <bool FP8, typename F>
+__device__ __forceinline__ void mg_stage(MgCtx& c, int n, F f) {
+  if (FP8) {
+    float m = 0.f;
+    for (int i = threadIdx.x; i < n; i += MG_THREADS) {
+      const float v = f(i);
+      m = fmaxf(m, fabsf(v));
+      c.xh[i] = __float2half_rn(v);
+    }
+    m = block_max(m, c.red);
+    c.unscale = 1.f;
+    if (m > 8.f) {
+      const int e = static_cast<int>(ceilf(log2f(m * 0.125f)));
+      const __half hs = __float2half_rn(exp2f(static_cast<float>(-e)));
+      c.unscale = exp2f(static_cast<float>(e));
+      for (int i = threadIdx.x; i < n; i += MG_THREADS) c.xh[i] = __hmul(c.xh[i], hs);
+    }
+  } else {
+    for (int i = threadIdx.x; i < n; i += MG_THREADS) c.xv[i] = f(i);
   }
   __syncthreads();
 }
 
-// resid (+= the all-reduce slots of `parity`, in rank order) -> RMSNorm(gamma) -> xf (fp32) [+ xh].
+// resid (+= the all-reduce slots of `parity`, in rank order) -> RMSNorm(gamma) -> xf (fp32) and the staged GEMV input.
+template <bool FP8>
 __device__ __forceinline__ void mg_residual_norm(const IhbMegaArgs& a, MgCtx& c, bool add_slots, int parity,
-                                                 const float* gamma, bool want_half) {
+                                                 const float* gamma) {
   const int H = a.H;
   const int nr = a.comm.nranks;
   float ss = 0.f;
@@ -192,191 +185,136 @@ __device__ __forceinline__ void mg_residual_norm(const IhbMegaArgs& a, MgCtx& c,
     *reinterpret_cast<float4*>(c.xf + i) = make_float4(v.x * rinv * g.x, v.y * rinv * g.y, v.z * rinv * g.z, v.w * rinv * g.w);
   }
   __syncthreads();
-  if (want_half) mg_stage_half(c, c.xf, H);
+  const float* xf = c.xf;
+  mg_stage<FP8>(c, H, [xf](int i) { return xf[i]; });
 }
 
-// ---- streaming GEMV building block --------------------------------------------------------------------------------------------
-// Every warp owns a private ring of MG_STAGES x 4 KB in shared memory that its lanes fill with 16-byte asynchronous
-// copies (cp.async: the bytes in flight live in shared memory, not in registers - up to 128 KB per SM, enough to
-// cover HBM latency at full bandwidth; bulk TMA copies of this size are bound by their issue rate instead). Work is dealt in groups of R consecutive output rows; a group is streamed as P contiguous pieces of
-// at most 4 KB (R whole short rows, or one slice of a long row, or - for the down projection - R rows of one
-// routed expert). Chunk = 16 bytes of weights = EPC activation elements (16 for e4m3, 8 for bf16).
-constexpr int MG_STAGES = 3;
-constexpr int MG_STAGE_BYTES = 4096;
+// ---- GEMV building block ----------------------------------------------------------------------------------------------------
+// A "virtual row" is a list of 16-byte weight chunks; chunk c multiplies activation elements [EPC c, EPC c + EPC)
+// (EPC = 16 for e4m3, 8 for bf16). A warp takes groups of R consecutive rows and keeps R x U independent 16-byte loads
+// in flight per lane. ONE plan type covers the three matrix layouts and one sink type the three result uses, so the
+// loop is instantiated once per (R, U) and not inlined: the whole kernel has to stay small for the instruction cache.
+//   PLAIN  rows x rowbytes
+//   EXPERT gate/up of the routed experts: virtual row v = slot * rpe + jj (rpe = 2 I rows per expert)
+//   DOWN   output rows over all routing slots: chunk c -> (expert of slot c / nch1, chunk c % nch1 of its row)
+//          through a table of offsets in shared memory (the same for every row, built once per layer)
+enum { MG_PLAIN = 0, MG_EXPERT = 1, MG_DOWN = 2 };
+struct MgPlan {
+  int kind;
+  const uint8_t* W; const float* sc;
+  int rows, nch, rowbytes, rb, kbs, nkb, rpe, nrb;
+  const int* sel_e;
+  const uint2* tab;
+};
+struct RowBase { const uint8_t* w; const float* s; };
 
-struct Piece {
-  const uint8_t* src;    // first byte (16-byte aligned)
-  unsigned bytes;        // nr * seg
-  int seg;               // bytes of one row inside the piece
-  int nr;                // rows in the piece (<= R)
-  int xchunk0;           // first activation chunk this piece multiplies
-  int kc0;               // chunk offset inside the (expert's) row, for the block-scale column
-  const float* srow;     // scale row of the piece's rows (all R rows share a row block)
-  int out0;              // output index of row 0
-};
+__device__ __forceinline__ RowBase mg_row(const MgPlan& pl, int v) {
+  if (pl.kind == MG_EXPERT) {
+    const int slot = v / pl.rpe, jj = v - slot * pl.rpe;
+    const size_t e = static_cast<size_t>(pl.sel_e[slot]);
+    return RowBase{pl.W + (e * pl.rpe + jj) * pl.rowbytes, pl.sc + (e * pl.nrb + jj / pl.rb) * pl.nkb};
+  }
+  return RowBase{pl.W + static_cast<size_t>(v) * pl.rowbytes, pl.sc + static_cast<size_t>(v / pl.rb) * pl.nkb};
+}
 
-struct PlainPlan {
-  const uint8_t* W; const float* sc; int rows, rowbytes, rb, kbs, nkb, R, P, seg;
-  __device__ __forceinline__ Piece piece(int g, int p) const {
-    Piece pc;
-    const int r0 = g * R;
-    pc.nr = min(R, rows - r0);
-    pc.seg = seg;
-    pc.src = W + static_cast<size_t>(r0) * rowbytes + static_cast<size_t>(p) * seg;
-    pc.bytes = static_cast<unsigned>(pc.nr) * seg;
-    pc.xchunk0 = pc.kc0 = (p * seg) >> 4;
-    pc.srow = sc + static_cast<size_t>(r0 / rb) * nkb;
-    pc.out0 = r0;
-    return pc;
-  }
-};
-// gate / up: virtual row v = slot * rpe + jj (rpe = 2 I rows per expert)
-struct ExpertPlan {
-  const uint8_t* W; const float* sc; int rowbytes, rb, kbs, nkb, R, P, seg, rpe, nrb; const int* sel_e;
-  __device__ __forceinline__ Piece piece(int g, int p) const {
-    Piece pc;
-    const int v0 = g * R;
-    const int slot = v0 / rpe, jj0 = v0 - slot * rpe;
-    const size_t e = static_cast<size_t>(sel_e[slot]);
-    pc.nr = R;
-    pc.seg = seg;
-    pc.src = W + (e * rpe + jj0) * rowbytes + static_cast<size_t>(p) * seg;
-    pc.bytes = static_cast<unsigned>(R) * seg;
-    pc.xchunk0 = pc.kc0 = (p * seg) >> 4;
-    pc.srow = sc + (e * nrb + jj0 / rb) * nkb;
-    pc.out0 = v0;
-    return pc;
-  }
-};
-// down: group = R consecutive output rows, piece p = routing slot p (R rows of that expert, contiguous)
-struct DownPlan {
-  const uint8_t* W; const float* sc; int rowbytes, rb, kbs, nkb, R, nch1, H, nrb; const int* sel_e;
-  __device__ __forceinline__ Piece piece(int g, int p) const {
-    Piece pc;
-    const int r0 = g * R;
-    const size_t e = static_cast<size_t>(sel_e[p]);
-    pc.nr = min(R, H - r0);
-    pc.seg = rowbytes;
-    pc.src = W + (e * H + r0) * rowbytes;
-    pc.bytes = static_cast<unsigned>(pc.nr) * rowbytes;
-    pc.xchunk0 = p * nch1;
-    pc.kc0 = 0;
-    pc.srow = sc + (e * nrb + r0 / rb) * nkb;
-    pc.out0 = r0;
-    return pc;
-  }
+enum { MG_STORE = 0, MG_PUSH = 1, MG_ARGMAX = 2 };
+struct MgSink {
+  int kind;
+  float* out;                    // STORE: out[i]; ARGMAX: optional logits
+  size_t off;                    // PUSH: slot offset of this rank
+  unsigned long long best;       // ARGMAX: packed running maximum (lane 0 of each warp)
 };
 
 template <bool FP8>
-__device__ __forceinline__ float mg_chunk_dot(uint4 w, const MgCtx& c, int cch) {
+__device__ __forceinline__ float mg_chunk_dot(uint4 w, const __half* xh, const float* xv, int cch) {
   if (FP8) {
-    const uint4* x = reinterpret_cast<const uint4*>(c.xh + 16 * cch);
+    const uint4* x = reinterpret_cast<const uint4*>(xh + 16 * cch);
     return dot16_e4m3(w, x[0], x[1]);
   } else {
-    const float4* x = reinterpret_cast<const float4*>(c.xf + 8 * cch);
+    const float4* x = reinterpret_cast<const float4*>(xv + 8 * cch);
     return dot8_bf16(w, x[0], x[1]);
   }
 }
 
-__device__ __forceinline__ void cp_async16(void* dst_smem, const void* src) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst_smem)), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
-
-// sink(output index, value) is called by one lane per finished row.
-template <bool FP8, int R, typename Plan, typename Sink>
-__device__ __forceinline__ void mg_stream(const IhbMegaArgs& a, MgCtx& c, const Plan& plan, int ngroups, int P, int kbs,
-                                          Sink sink) {
-  if (c.flags[0] != 0) return;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int gw = warp * gridDim.x + blockIdx.x;      // consecutive groups go to different SMs
-  const int W = gridDim.x * MG_WARPS;
-  const int mine = ngroups > gw ? (ngroups - gw + W - 1) / W : 0;
-  const int total = mine * P;
-  uint8_t* ring = c.ring + warp * (MG_STAGES * MG_STAGE_BYTES);
-  // every lane copies its 16-byte chunks of the piece (asynchronous, no registers held); one commit group per piece,
-  // committed even when empty so that "at most MG_STAGES - 1 groups pending" always means "piece t has landed"
-  auto issue = [&](int t) {
-    if (t < total) {
-      const Piece pc = plan.piece(gw + (t / P) * W, t % P);
-      uint8_t* dst = ring + (t % MG_STAGES) * MG_STAGE_BYTES;
-      const int nch = static_cast<int>(pc.bytes >> 4);
-#pragma unroll 4
-      for (int cc = lane; cc < nch; cc += 32) cp_async16(dst + 16 * cc, pc.src + 16 * cc);
-    }
-    cp_async_commit();
-  };
-#pragma unroll
-  for (int t = 0; t < MG_STAGES - 1; ++t) issue(t);
-  float acc[R];
-  for (int t = 0; t < total; ++t) {
-    issue(t + MG_STAGES - 1);                      // its stage was consumed in iteration t - 1
-    const int p = t % P;
-    const Piece pc = plan.piece(gw + (t / P) * W, p);
-    if (p == 0) {
-#pragma unroll
-      for (int j = 0; j < R; ++j) acc[j] = 0.f;
-    }
-    cp_async_wait<MG_STAGES - 1>();
-    __syncwarp();                                  // the other lanes' chunks of piece t are visible too
-    const uint8_t* sm = ring + (t % MG_STAGES) * MG_STAGE_BYTES;
-    const int segch = pc.seg >> 4;
+template <bool FP8, int R, int U>
+__device__ __forceinline__ void mg_gemv(const IhbMegaArgs& a, const MgCtx& c, const MgPlan& plan, MgSink& sink) {
+  const int lane = threadIdx.x & 31;
+  const int first = blockIdx.x * MG_WARPS + (threadIdx.x >> 5);     // the warps of a CTA read one contiguous run
+  const int stride = gridDim.x * MG_WARPS;
+  const int n = plan.rows, nch = plan.nch, kbs = plan.kbs;
+  const __half* xh = c.xh;
+  const float* xv = c.xv;
+  const float unscale = FP8 ? c.unscale : 1.f;
+  const bool down = plan.kind == MG_DOWN;
+  for (int i0 = first * R; i0 < n; i0 += stride * R) {
+    RowBase b[R];
+    float acc[R];
 #pragma unroll
     for (int j = 0; j < R; ++j) {
-      if (j < pc.nr) {
-        const uint8_t* row = sm + j * pc.seg;
-#pragma unroll 4
-        for (int cc = lane; cc < segch; cc += 32) {
-          const uint4 w = *reinterpret_cast<const uint4*>(row + 16 * cc);
-          const float s = FP8 ? __ldg(pc.srow + ((pc.kc0 + cc) >> kbs)) : 1.f;
-          acc[j] = fmaf(s, mg_chunk_dot<FP8>(w, c, pc.xchunk0 + cc), acc[j]);
+      b[j] = mg_row(plan, min(i0 + j, n - 1));
+      acc[j] = 0.f;
+    }
+    for (int cb = 0; cb < nch; cb += 32 * U) {
+      uint4 w[R][U];
+      float s[R][U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int cch = cb + lane + 32 * u;
+        const bool valid = cch < nch;
+        unsigned wo = 0, so = 0;
+        if (valid) {
+          if (down) { const uint2 t = plan.tab[cch]; wo = t.x; so = t.y; }
+          else { wo = 16u * cch; so = cch >> kbs; }
+        }
+#pragma unroll
+        for (int j = 0; j < R; ++j) {
+          w[j][u] = valid ? ldg_stream(b[j].w + wo) : make_uint4(0u, 0u, 0u, 0u);
+          s[j][u] = (FP8 && valid) ? __ldg(b[j].s + so) : (valid ? 1.f : 0.f);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int cch = min(cb + lane + 32 * u, nch - 1);
+#pragma unroll
+        for (int j = 0; j < R; ++j) acc[j] = fmaf(s[j][u], mg_chunk_dot<FP8>(w[j][u], xh, xv, cch), acc[j]);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < R; ++j) {
+      const float v = warp_sum(acc[j]) * unscale;
+      const int i = i0 + j;
+      if (lane == 0 && i < n) {
+        if (sink.kind == MG_STORE) {
+          sink.out[i] = v;
+        } else if (sink.kind == MG_PUSH) {
+          push_partial(a.comm, sink.off + i, v);
+        } else {
+          const unsigned long long pk = pack_max(v, static_cast<unsigned>(i));
+          sink.best = pk > sink.best ? pk : sink.best;
+          if (sink.out != nullptr) sink.out[i] = v;
         }
       }
     }
-    __syncwarp();                                  // all lanes are done with this stage before it is refilled
-    if (p == P - 1) {
-#pragma unroll
-      for (int j = 0; j < R; ++j) {
-        const float v = warp_sum(acc[j]) * (FP8 ? c.unscale : 1.f);
-        if (lane == (j & 31) && j < pc.nr) sink(pc.out0 + j, v);
-      }
-    }
   }
-  cp_async_wait<0>();
 }
 
-template <bool FP8, typename Plan, typename Sink>
-__device__ __forceinline__ void mg_stream_auto(const IhbMegaArgs& a, MgCtx& c, const Plan& plan, int R, int ngroups, int P,
-                                               int kbs, Sink sink) {
-  if (R == 1) mg_stream<FP8, 1>(a, c, plan, ngroups, P, kbs, sink);
-  else if (R == 2) mg_stream<FP8, 2>(a, c, plan, ngroups, P, kbs, sink);
-  else if (R == 4) mg_stream<FP8, 4>(a, c, plan, ngroups, P, kbs, sink);
-  else mg_stream<FP8, 16>(a, c, plan, ngroups, P, kbs, sink);
-}
-
-// Rows per group for rows of `rowbytes` bytes: as many whole rows as fit a 4 KB stage (1, 2, 4 or 16), but no more
-// than keeps every warp of the grid busy (short serial chains matter more than long copies when a matrix is small),
-// and never straddling a scale row block (`rb`) or `align` rows.
-__device__ __forceinline__ int mg_rows_per_group(int rowbytes, int rb, int align, int rows) {
-  int R = 1;
-  const int fit = MG_STAGE_BYTES / rowbytes;
+// Picks the (rows, rounds) shape by the number of chunk rounds a row needs and by how many rows a warp gets.
+template <bool FP8>
+__device__ __forceinline__ void mg_gemv_auto(const IhbMegaArgs& a, const MgCtx& c, const MgPlan& plan, MgSink& sink) {
   const int W = gridDim.x * MG_WARPS;
-  if (fit >= 16) R = 16; else if (fit >= 4) R = 4; else if (fit >= 2) R = 2;
-  while (R > 1 && ((rb % R) != 0 || (align % R) != 0 || rows / R < W)) R = (R == 16) ? 4 : R / 2;
-  return R;
+  if (plan.nch > 128 && plan.rows >= 2 * W) mg_gemv<FP8, 2, 8>(a, c, plan, sink);
+  else if (plan.nch > 128) mg_gemv<FP8, 1, 8>(a, c, plan, sink);
+  else if (plan.nch > 64) mg_gemv<FP8, 2, 4>(a, c, plan, sink);
+  else mg_gemv<FP8, 4, 2>(a, c, plan, sink);
 }
 
-__device__ __forceinline__ PlainPlan plain_plan(const IhbMat& m, bool fp8) {
-  PlainPlan pl;
-  pl.W = m.W; pl.sc = m.wscale; pl.rows = m.rows; pl.rowbytes = fp8 ? m.K : 2 * m.K;
+__device__ __forceinline__ MgPlan mg_plan(int kind, const IhbMat& m, int rows, int nch, int rowbytes, const int* sel_e,
+                                          int rpe, const uint2* tab) {
+  MgPlan pl;
+  pl.kind = kind; pl.W = m.W; pl.sc = m.wscale; pl.rows = rows; pl.nch = nch; pl.rowbytes = rowbytes;
   pl.rb = m.rb > 0 ? m.rb : (1 << 30); pl.kbs = m.kb_shift; pl.nkb = m.nkb;
-  if (pl.rowbytes > MG_STAGE_BYTES) {
-    pl.R = 1; pl.seg = MG_STAGE_BYTES; pl.P = pl.rowbytes / MG_STAGE_BYTES;     // rows are multiples of 4 KB (checked on the host)
-  } else {
-    pl.R = mg_rows_per_group(pl.rowbytes, pl.rb == (1 << 30) ? 16 : pl.rb, 16, pl.rows); pl.seg = pl.rowbytes; pl.P = 1;
-  }
+  pl.rpe = rpe; pl.sel_e = sel_e; pl.tab = tab;
+  pl.nrb = m.rb > 0 ? ((kind == MG_EXPERT ? rpe : rows) + m.rb - 1) / m.rb : 0;
   return pl;
 }
 
