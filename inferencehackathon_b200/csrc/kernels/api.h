@@ -151,6 +151,12 @@ typedef struct {
   unsigned* err;
   int tiled;               // 1: W is pre-tiled [matrix][k block][rows padded to 8][128 B] in swizzled order
   int x_rows1;             // 1 (needs tiled, T == 1): X is [slots][K padded to 128 B], one plain row per slot
+  // Grouped mode (GATEUP / DOWN over tokens sorted by expert; top_k = 1, ks = 1): group g multiplies rows
+  // [tok0, tok0 + ntok) of X (ntok <= the token tile) by local expert e. The table and its length live on the device,
+  // so routing results never pass through the host. out rows are indexed by the sorted token position.
+  const int* groups;       // [max_groups][4] = {e, tok0, ntok, 0}; NULL = not grouped
+  const int* n_groups;     // device scalar
+  int max_groups;
 } IhbTcArgs;
 
 int ihb_tc_gemm(IhbTcArgs* args, int use_pdl, cudaStream_t stream);
@@ -205,6 +211,30 @@ typedef struct {
 
 int ihb_tc_decode(IhbTcDecArgs* args, int use_pdl, cudaStream_t stream);
 size_t ihb_tc_dec_partial_floats(const IhbTcDecArgs* args);
+
+// ---- multi-token ("window") kernels: prompt chunks and speculative-verify windows -------------------------------------
+// Row-wise RMSNorm (gamma != NULL) + activation quantisation: x [T][K] fp32 -> xn [T][K] fp32 (optional),
+// xq [T][K] e4m3 (fp8 = 1, K % 128 == 0) or bf16, xs [K / 128][T] (fp8 only): the layout ihb_tc_gemm reads.
+int ihb_norm_quant_rows(const float* x, const float* gamma, float eps, int K, int T, float* xn, unsigned char* xq,
+                        float* xs, int fp8, cudaStream_t stream);
+// qkv [T][(nq + 2 nkv) * 128] fp32: per-head RMSNorm + NeoX RoPE at positions[t]; q rows are rewritten in place, K / V
+// rows go to cache row slots[t] (bf16).
+int ihb_qk_norm_rope_rows(float* qkv, int nq, int nkv, const float* q_gamma, const float* k_gamma, float eps,
+                          const float* cos_t, const float* sin_t, const int* positions, const int* slots, void* k_cache,
+                          void* v_cache, int max_seq, int T, cudaStream_t stream);
+// Query t (row t of qkv, qkv_stride floats apart) attends to cache rows [0, base) and to window row base + j when
+// mask[t][j] != 0 (mask == NULL: causal, j <= t). out [T][nq * 128] fp32.
+int ihb_window_attention(const float* qkv, int qkv_stride, const void* k_cache, const void* v_cache, int nq, int nkv,
+                         int max_seq, int base, int T, const unsigned char* mask, float* out, cudaStream_t stream);
+
+// ---- stand-alone fused all-reduce (+ residual + RMSNorm) over symmetric memory -----------------------------------------
+// x [T, H] fp32 partial of this rank -> out = sum over ranks (+ resid); out_norm = RMSNorm(out) * gamma (gamma != NULL).
+// algo 0 = by size, 1 = one-shot (push + one barrier, every rank adds), 2 = two-shot (row owners reduce with
+// multimem.ld_reduce or peer loads and broadcast). Slot region (floats): one-shot 2 * nranks * T * H, two-shot
+// 2 * T * H. counter: 8 unsigned words, zero before the first launch. One cooperative launch.
+int ihb_allreduce_norm(const IhbComm* comm, const float* x, const float* resid, const float* gamma, float eps, int T,
+                       int H, float* out, float* out_norm, unsigned* counter, unsigned* err, int algo, int grid,
+                       cudaStream_t stream);
 
 // ---- persistent decode megakernel: one cooperative launch runs `steps` whole tokens -------------------------------------
 // One weight matrix (or a stack of per-expert matrices with the same shape): rows contiguous, K-major.

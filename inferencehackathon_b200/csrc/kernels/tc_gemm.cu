@@ -46,10 +46,20 @@ struct Unit {
   int row0;      // first weight row of the tile (mode 1: j0 inside the expert's gate block)
   int slot;      // routing slot (modes 1, 2) else 0
   int kb0, kb1;  // K blocks [kb0, kb1)
+  int e, tok0, ntok;   // grouped mode: local expert, first row of X, valid rows
 };
 
 __device__ __forceinline__ Unit decode_unit(const IhbTcArgs& a, int u, int nkb_total) {
   Unit un;
+  un.e = 0; un.tok0 = a.tok0; un.ntok = a.T;
+  if (a.groups != nullptr) {
+    const int rtiles = (a.rows + TC_BM - 1) / TC_BM;
+    const int g = u / rtiles, tile = u - g * rtiles;
+    const int4 gr = *reinterpret_cast<const int4*>(a.groups + 4 * g);
+    un.e = gr.x; un.tok0 = gr.y; un.ntok = gr.z;
+    un.tile = u; un.member = 0; un.row0 = tile * TC_BM; un.slot = 0; un.kb0 = 0; un.kb1 = nkb_total;
+    return un;
+  }
   const int s = u % a.ks;
   int rest = u / a.ks;
   const int base = nkb_total / a.ks, rem = nkb_total % a.ks;
@@ -118,7 +128,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   // Everything below reads outputs of earlier kernels (activations, expert ids).
   pdl_wait();
   pdl_launch_dependents();
-  if (a.mode != IHB_TC_LINEAR && tid < a.top_k) {
+  if (a.mode != IHB_TC_LINEAR && a.groups == nullptr && tid < a.top_k) {
     int e = ld_cg_i(a.sel_idx + tid) - a.expert0;
     const bool here = (e >= 0 && e < a.n_experts);
     sh.sel_e[tid] = here ? e : 0;
@@ -132,7 +142,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     }
     fence_proxy_async_smem();
   }
-  if (KIND == 0 && warp >= 4) {
+  if (KIND == 0 && warp >= 4 && a.groups == nullptr) {
     // activation scales for every K block: global layout [slot][kb][T], padded here to NT columns
     const int n = nslot_x * nkb_total * NT;
     for (int i = tid - 128; i < n; i += 128) {
@@ -142,7 +152,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   }
   __syncthreads();
 
-  const int total_units = a.n_units;
+  const int total_units = a.groups != nullptr ? ld_cg_i(a.n_groups) * ((a.rows + TC_BM - 1) / TC_BM) : a.n_units;
   const uint32_t idesc = (1u << 4) | (KIND == 1 ? ((1u << 7) | (1u << 10)) : 0u) |
                          (static_cast<uint32_t>(NT >> 3) << 17) | (static_cast<uint32_t>(TC_BM >> 4) << 24);
   const int kx = TC_BKB / esize;     // K elements per block (tensor-map coordinate units)
@@ -155,7 +165,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       bool ok = true;
       for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
         const Unit un = decode_unit(a, u, nkb_total);
-        const int e = (a.mode == IHB_TC_LINEAR) ? 0 : sh.sel_e[un.slot];
+        const int e = (a.mode == IHB_TC_LINEAR) ? 0 : (a.groups != nullptr ? un.e : sh.sel_e[un.slot]);
         for (int kb = un.kb0; kb < un.kb1; ++kb, ++g) {
           if (g % TC_PRODUCERS != warp) continue;
           const int st = g % S;
@@ -182,22 +192,22 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                                   (static_cast<size_t>(a.mode == IHB_TC_DOWN ? un.slot : 0) * nkb_total + kb) * TC_BKB;
               bulk_g2s(sB, xs, TC_BKB, &sh.full[st]);
             } else if (a.mode == IHB_TC_DOWN) {
-              tma_load_3d(sB, &tmB, kb * kx, a.tok0, un.slot, &sh.full[st]);
+              tma_load_3d(sB, &tmB, kb * kx, un.tok0, un.slot, &sh.full[st]);
             } else {
-              tma_load_2d(sB, &tmB, kb * kx, a.tok0, &sh.full[st]);
+              tma_load_2d(sB, &tmB, kb * kx, un.tok0, &sh.full[st]);
             }
           } else {
             mbar_arrive_expect_tx(&sh.full[st], STAGE_BYTES);
             if (a.mode == IHB_TC_LINEAR) {
               tma_load_2d(sA, &tmA, kb * kx, un.row0, &sh.full[st]);
-              tma_load_2d(sB, &tmB, kb * kx, a.tok0, &sh.full[st]);
+              tma_load_2d(sB, &tmB, kb * kx, un.tok0, &sh.full[st]);
             } else if (a.mode == IHB_TC_GATEUP) {
               tma_load_4d(sA, &tmA, kb * kx, un.row0, 0, e, &sh.full[st]);
               if (NA == 2) tma_load_4d(sA + TC_A_BYTES, &tmA, kb * kx, un.row0, 1, e, &sh.full[st]);
-              tma_load_2d(sB, &tmB, kb * kx, a.tok0, &sh.full[st]);
+              tma_load_2d(sB, &tmB, kb * kx, un.tok0, &sh.full[st]);
             } else {
               tma_load_3d(sA, &tmA, kb * kx, un.row0, e, &sh.full[st]);
-              tma_load_3d(sB, &tmB, kb * kx, a.tok0, un.slot, &sh.full[st]);
+              tma_load_3d(sB, &tmB, kb * kx, un.tok0, un.slot, &sh.full[st]);
             }
           }
         }
@@ -249,7 +259,16 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     bool ok = true;
     for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x, ++ui) {
       const Unit un = decode_unit(a, u, nkb_total);
-      const int e = (a.mode == IHB_TC_LINEAR) ? 0 : sh.sel_e[un.slot];
+      const int e = (a.mode == IHB_TC_LINEAR) ? 0 : (a.groups != nullptr ? un.e : sh.sel_e[un.slot]);
+      if (KIND == 0 && a.groups != nullptr) {
+        // grouped mode: the activation scales of this unit's tokens (the previous unit's readers are done: barrier)
+        named_bar_sync(2, 128);
+        for (int i = etid; i < nkb_total * NT; i += 128) {
+          const int col = i % NT, r = i / NT;
+          xs_s[i] = (col < un.ntok) ? ld_cg_f(a.xscale + static_cast<size_t>(r) * a.T_total + un.tok0 + col) : 0.f;
+        }
+        named_bar_sync(2, 128);
+      }
       float acc[NA][NT];
 #pragma unroll
       for (int ai = 0; ai < NA; ++ai)
@@ -329,8 +348,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       if (!ok) break;
 
       // ---- combine the units that feed this output tile -------------------------------------------------------------------
-      const int members = (a.mode == IHB_TC_DOWN) ? a.top_k * a.ks : a.ks;
-      const float wslot = (a.mode == IHB_TC_DOWN) ? sh.sel_w[un.slot] : 1.f;
+      const int members = a.groups != nullptr ? 1 : ((a.mode == IHB_TC_DOWN) ? a.top_k * a.ks : a.ks);
+      const float wslot = (a.mode == IHB_TC_DOWN && a.groups == nullptr) ? sh.sel_w[un.slot] : 1.f;
       bool finisher = true;
       if (members > 1) {
         float* part = a.partial + (static_cast<size_t>(un.tile) * members + un.member) * (NA * a.T * TC_BM);
@@ -377,13 +396,16 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (row < a.rows) {
 #pragma unroll
           for (int n = 0; n < NT; ++n)
-            if (n < a.T) a.out[(static_cast<size_t>(un.slot) * a.T + n) * a.rows + row] = silu(acc[0][n]) * acc[NA - 1][n];
+            if (n < un.ntok) {
+              const size_t orow = a.groups != nullptr ? static_cast<size_t>(un.tok0 + n) : static_cast<size_t>(un.slot) * a.T + n;
+              a.out[orow * a.rows + row] = silu(acc[0][n]) * acc[NA - 1][n];
+            }
         }
       } else {
         if (row < a.rows) {
 #pragma unroll
           for (int n = 0; n < NT; ++n)
-            if (n < a.T) a.out[static_cast<size_t>(n) * a.out_stride + row] = acc[0][n];
+            if (n < un.ntok) a.out[static_cast<size_t>(a.groups != nullptr ? un.tok0 + n : n) * a.out_stride + row] = acc[0][n];
         }
       }
     }
@@ -444,6 +466,9 @@ extern "C" int ihb_tc_gemm(IhbTcArgs* args, int use_pdl, cudaStream_t stream) {
   IhbTcArgs a = *args;
   const int is_fp8 = a.wtype == IHB_W_FP8;
   const int esize = is_fp8 ? 1 : 2;
+  const int grouped = a.groups != nullptr;
+  if (grouped && (a.mode == IHB_TC_LINEAR || a.n_groups == nullptr || a.max_groups < 1 || a.tiled || a.x_rows1)) return cudaErrorInvalidValue;
+  if (grouped) { a.top_k = 1; a.ks = 1; a.tok0 = 0; }
   if (a.T < 1 || a.T > 128 || a.rows < 1 || a.K < 1 || (a.K * esize) % 16) return cudaErrorInvalidValue;
   if (is_fp8 && (a.rb < 1 || a.wscale == nullptr || a.xscale == nullptr)) return cudaErrorInvalidValue;
   if (a.mode != IHB_TC_LINEAR && (a.top_k < 1 || a.top_k > IHB_MAX_TOPK)) return cudaErrorInvalidValue;
@@ -467,7 +492,7 @@ extern "C" int ihb_tc_gemm(IhbTcArgs* args, int use_pdl, cudaStream_t stream) {
     a.ks = ks;
   }
   if (a.ks > nkb_total) a.ks = nkb_total;
-  a.n_units = base_units * a.ks;
+  a.n_units = grouped ? a.max_groups * tiles_rows : base_units * a.ks;
   const int members = a.mode == IHB_TC_DOWN ? a.top_k * a.ks : a.ks;
   if (members > 1 && (a.partial == nullptr || a.tile_counters == nullptr)) return cudaErrorInvalidValue;
 

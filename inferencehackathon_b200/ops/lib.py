@@ -68,7 +68,8 @@ class IhbTcArgs(C.Structure):
                 ("mode", C.c_int), ("sel_idx", _vp), ("sel_w", _vp),
                 ("out", _vp), ("out_stride", C.c_int), ("partial", _vp), ("tile_counters", _vp),
                 ("ks", C.c_int), ("S", C.c_int), ("grid", C.c_int), ("n_units", C.c_int), ("err", _vp),
-                ("tiled", C.c_int), ("x_rows1", C.c_int)]
+                ("tiled", C.c_int), ("x_rows1", C.c_int),
+                ("groups", _vp), ("n_groups", _vp), ("max_groups", C.c_int)]
 
 
 DEC_STORE, DEC_AR_NORM, DEC_ARGMAX, DEC_ACT = 0, 1, 2, 3
@@ -148,6 +149,16 @@ def load(build_if_missing: bool = True) -> C.CDLL:
     lib.ihb_tc_decode.restype = C.c_int
     lib.ihb_tc_dec_partial_floats.argtypes = [C.POINTER(IhbTcDecArgs)]
     lib.ihb_tc_dec_partial_floats.restype = C.c_size_t
+    lib.ihb_norm_quant_rows.argtypes = [_vp, _vp, C.c_float, C.c_int, C.c_int, _vp, _vp, _vp, C.c_int, _vp]
+    lib.ihb_norm_quant_rows.restype = C.c_int
+    lib.ihb_qk_norm_rope_rows.argtypes = [_vp, C.c_int, C.c_int, _vp, _vp, C.c_float, _vp, _vp, _vp, _vp, _vp, _vp,
+                                          C.c_int, C.c_int, _vp]
+    lib.ihb_qk_norm_rope_rows.restype = C.c_int
+    lib.ihb_window_attention.argtypes = [_vp, C.c_int, _vp, _vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _vp, _vp, _vp]
+    lib.ihb_window_attention.restype = C.c_int
+    lib.ihb_allreduce_norm.argtypes = [C.POINTER(IhbComm), _vp, _vp, _vp, C.c_float, C.c_int, C.c_int, _vp, _vp, _vp, _vp,
+                                       C.c_int, C.c_int, _vp]
+    lib.ihb_allreduce_norm.restype = C.c_int
     lib.ihb_mega_decode.argtypes = [C.POINTER(IhbMegaArgs), C.c_int, _vp]
     lib.ihb_mega_decode.restype = C.c_int
     lib.ihb_mega_max_grid.argtypes = [C.POINTER(IhbMegaArgs)]
@@ -382,3 +393,36 @@ def mega_max_grid(args: IhbMegaArgs) -> int:
 
 def mega_decode(args: IhbMegaArgs, grid: int = 0) -> None:
     check(load().ihb_mega_decode(C.byref(args), grid, stream_ptr()), "ihb_mega_decode")
+
+
+def norm_quant_rows(x: torch.Tensor, gamma: Optional[torch.Tensor], eps: float, xq: torch.Tensor,
+                    xs: Optional[torch.Tensor], fp8: bool, xn: Optional[torch.Tensor] = None) -> None:
+    """x ``[T, K]`` fp32 -> (optional RMSNorm) -> ``xq`` ``[T, K]`` e4m3 / bf16 and ``xs`` ``[K / 128, T]``."""
+    T, Kd = x.shape
+    check(load().ihb_norm_quant_rows(x.data_ptr(), ptr(gamma), eps, Kd, T, ptr(xn), xq.data_ptr(), ptr(xs), int(fp8),
+                                     stream_ptr()), "ihb_norm_quant_rows")
+
+
+def qk_norm_rope_rows(qkv: torch.Tensor, nq: int, nkv: int, q_gamma, k_gamma, eps: float, cos_t, sin_t, positions,
+                      slots, k_cache, v_cache, max_seq: int) -> None:
+    check(load().ihb_qk_norm_rope_rows(qkv.data_ptr(), nq, nkv, q_gamma.data_ptr(), k_gamma.data_ptr(), eps,
+                                       cos_t.data_ptr(), sin_t.data_ptr(), positions.data_ptr(), slots.data_ptr(),
+                                       k_cache.data_ptr(), v_cache.data_ptr(), max_seq, qkv.shape[0], stream_ptr()),
+          "ihb_qk_norm_rope_rows")
+
+
+def window_attention(qkv: torch.Tensor, k_cache, v_cache, nq: int, nkv: int, max_seq: int, base: int,
+                     mask: Optional[torch.Tensor], out: torch.Tensor) -> None:
+    check(load().ihb_window_attention(qkv.data_ptr(), qkv.shape[1], k_cache.data_ptr(), v_cache.data_ptr(), nq, nkv,
+                                      max_seq, base, qkv.shape[0], ptr(mask), out.data_ptr(), stream_ptr()),
+          "ihb_window_attention")
+
+
+def allreduce_norm(comm: IhbComm, x: torch.Tensor, out: torch.Tensor, counter: torch.Tensor, err: torch.Tensor,
+                   resid: Optional[torch.Tensor] = None, gamma: Optional[torch.Tensor] = None, eps: float = 1e-6,
+                   out_norm: Optional[torch.Tensor] = None, algo: int = 0, grid: int = 0) -> None:
+    """Fused all-reduce (+ residual + RMSNorm) of ``x [T, H]`` fp32 over the symmetric buffer described by ``comm``."""
+    T, H = x.shape
+    check(load().ihb_allreduce_norm(C.byref(comm), x.data_ptr(), ptr(resid), ptr(gamma), eps, T, H, out.data_ptr(),
+                                    ptr(out_norm), counter.data_ptr(), err.data_ptr(), algo, grid, stream_ptr()),
+          "ihb_allreduce_norm")

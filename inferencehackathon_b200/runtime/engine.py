@@ -180,9 +180,12 @@ class InferenceEngine:
 
     def logits_for(self, tokens: Sequence[int], commit: bool = True, tree_mask=None, positions=None,
                    aux_layers=()) -> torch.Tensor:
-        """Logits ``[T, V]`` of a window of new tokens (speculative verify); PyTorch path."""
+        """Logits ``[T, V]`` of a window of new tokens (speculative verify, chains and token trees)."""
         if self.gpu is not None:
-            return self.gpu.logits_for(tokens, commit=commit, tree_mask=tree_mask, positions=positions)
+            logits = self.gpu.logits_for(tokens, commit=commit, tree_mask=tree_mask, positions=positions,
+                                         aux_layers=tuple(aux_layers))
+            self.model.aux_taps = getattr(self.gpu.window(), "aux_taps", {})
+            return logits
         t = torch.as_tensor(list(tokens), dtype=torch.long, device=self.device)
         hidden = self.model.forward_hidden(t, self.cache, positions=positions, tree_mask=tree_mask,
                                            commit=commit, aux_layers=tuple(aux_layers))

@@ -93,6 +93,7 @@ class GpuDecoder:
         else:
             self._build_args()
         self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self._window = None
         self._ev0 = torch.cuda.Event(enable_timing=True)
         self._ev1 = torch.cuda.Event(enable_timing=True)
         # pinned staging for the per-step host<->device traffic of the public decode_step API
@@ -407,6 +408,13 @@ class GpuDecoder:
         T = toks.shape[0]
         if self.seq_len + T > self.max_seq:
             raise ValueError("KV cache overflow")
+        if T >= 2 and self.has_window() and env_flag("IHB_WINDOW_PREFILL", 1):
+            # batched prompt processing on the tensor cores
+            logits = self.window().forward(toks, commit=True, last_only=True)
+            nxt = int(torch.argmax(logits[0])) if sampler.params.greedy else int(sampler.sample(logits[0]))
+            self.cur_token.fill_(nxt)
+            self.n_forced.zero_()
+            return nxt, (logits if return_logits else None)
         start = self.seq_len
         self.forced[start:start + T] = toks.to(torch.int32)
         self.n_forced.fill_(start + T)
@@ -475,5 +483,20 @@ class GpuDecoder:
         for _ in range(n):
             self._step()
 
-    def logits_for(self, tokens, commit=True, tree_mask=None, positions=None):
-        raise NotImplementedError("window logits on the CUDA path come from the speculative verifier")
+    def window(self):
+        """Multi-token forward (prompt chunks, verify windows); needs the plain row-major weights, i.e. the
+        persistent or the streaming pipeline, and tensor parallelism only."""
+        if self._window is None:
+            from .gpu_window import GpuWindow
+            self._window = GpuWindow(self)
+        return self._window
+
+    def has_window(self) -> bool:
+        return (self.use_mega or not self.use_tc) and self.cfg.parallel.ep <= 1 and bool(env_flag("IHB_WINDOW", 1))
+
+    def logits_for(self, tokens, commit=True, tree_mask=None, positions=None, aux_layers=()):
+        """Logits ``[T, V]`` of a window of new tokens: one batched forward on the tensor cores."""
+        if not self.has_window():
+            raise NotImplementedError("window logits need the persistent or streaming pipeline (plain weight layout)")
+        return self.window().forward(tokens, commit=commit, tree_mask=tree_mask, positions=positions,
+                                     aux_layers=aux_layers)

@@ -1,0 +1,206 @@
+"""Multi-token forward on the GPU: prompt chunks (TTFT) and speculative-verify windows (chains and token trees).
+
+Per layer: row RMSNorm + per-token activation quantisation -> tcgen05 GEMM (QKV) -> QK-norm / RoPE / KV append at
+explicit positions -> window attention (causal or tree mask) -> tcgen05 GEMM (o_proj) -> all-reduce -> router ->
+tokens sorted by expert -> GROUPED tcgen05 GEMMs (gate/up + SwiGLU, down) driven by a device-side group table (the
+routing result never visits the host) -> weighted combine -> all-reduce. Windows are processed in chunks of up to
+128 tokens (the GEMM's token tile).
+
+The contractions and the attention are this package's kernels (``ihb_tc_gemm``, ``ihb_window_attention``,
+``ihb_norm_quant_rows``, ``ihb_qk_norm_rope_rows``); index bookkeeping (sort by expert, top-k, gathers) uses
+PyTorch tensor ops on the device. Reference counterparts: kernels/prefill_attn.cu, kernels/prefill_moe.cu,
+kernels/prefill_wgmma.cu (prefill) and kernels/spec_verify_forward_gemm.cu, engine/native/tc_verify_attn.cuh
+(verify).
+"""
+from __future__ import annotations
+
+from typing import List, Optional
+
+import torch
+
+from ..ops import lib as K
+
+CHUNK = 128
+
+
+class GpuWindow:
+    def __init__(self, dec):
+        self.d = dec
+        m, w = dec.cfg.model, dec.w
+        if dec.cfg.parallel.ep > 1:
+            raise NotImplementedError("the window path is tensor-parallel only")
+        if w.layers and w.layers[0].wqkv.data.device.type == "meta":
+            raise RuntimeError("the window path needs the plain row-major weights (persistent or streaming pipeline)")
+        self.fp8 = dec.fp8
+        self.es = 1 if self.fp8 else 2
+        dev = dec.device
+        self.sms = torch.cuda.get_device_properties(dev).multi_processor_count
+        self.err = dec.err
+        self._ws = {}
+        self.n_gemm_launches = 0
+
+    # ---- small helpers ---------------------------------------------------------------------------------------------
+    def _buf(self, name: str, shape, dtype) -> torch.Tensor:
+        t = self._ws.get(name)
+        n = 1
+        for s in shape:
+            n *= s
+        if t is None or t.numel() < n or t.dtype != dtype:
+            t = torch.zeros(max(n, 1), dtype=dtype, device=self.d.device)
+            self._ws[name] = t
+        return t[:n].view(*shape)
+
+    def _quant(self, x: torch.Tensor, gamma: Optional[torch.Tensor], tag: str, want_norm: bool = False):
+        """x [T, K] fp32 -> (xq [T, K] e4m3|bf16 bytes, xs [ceil(K / 128), T] or None, xn or None)."""
+        T, Kd = x.shape
+        xq = self._buf("q_" + tag, (T, Kd * self.es), torch.uint8)
+        xs = self._buf("s_" + tag, ((Kd + 127) // 128, T), torch.float32) if self.fp8 else None
+        xn = self._buf("n_" + tag, (T, Kd), torch.float32) if want_norm else None
+        K.norm_quant_rows(x.contiguous(), gamma, self.d.cfg.model.rms_eps, xq, xs, self.fp8, xn)
+        return xq, xs, xn
+
+    def _linear(self, qw, xq, xs, T: int, tag: str) -> torch.Tensor:
+        """[T, K] x W[rows, K]^T on the tensor cores."""
+        a = K.IhbTcArgs()
+        K.tc_fill_weight(a, qw)
+        rows = a.rows
+        out = self._buf("o_" + tag, (T, rows), torch.float32)
+        a.X, a.mode, a.out, a.out_stride = xq.data_ptr(), K.TC_LINEAR, out.data_ptr(), rows
+        if xs is not None:
+            a.xscale = xs.data_ptr()
+        a.T, a.T_total, a.tok0, a.err = T, T, 0, self.err.data_ptr()
+        tiles = (rows + 127) // 128
+        nkb = (a.K * self.es + 127) // 128
+        a.ks = max(1, min(nkb, 16, -(-2 * self.sms // tiles)))
+        part = self._buf("part", (max(1, K.tc_partial_floats(a)),), torch.float32)
+        ctr = self._buf("ctr", (max(tiles, 1),), torch.int32)
+        a.partial, a.tile_counters = part.data_ptr(), ctr.data_ptr()
+        K.tc_gemm(a, False)
+        self.n_gemm_launches += 1
+        return out
+
+    def _grouped(self, qw, mode, rows: int, xq, xs, groups, n_groups, max_groups: int, nt: int, n_pairs: int, tag: str):
+        a = K.IhbTcArgs()
+        K.tc_fill_weight(a, qw)
+        a.rows = rows
+        out = self._buf("g_" + tag, (n_pairs, rows), torch.float32)
+        a.X, a.mode, a.out, a.out_stride = xq.data_ptr(), mode, out.data_ptr(), rows
+        if xs is not None:
+            a.xscale = xs.data_ptr()
+        a.T, a.T_total, a.tok0, a.err = nt, n_pairs, 0, self.err.data_ptr()
+        a.top_k, a.ks = 1, 1
+        a.groups, a.n_groups, a.max_groups = groups.data_ptr(), n_groups.data_ptr(), max_groups
+        K.tc_gemm(a, False)
+        self.n_gemm_launches += 1
+        return out
+
+    @staticmethod
+    def _group_table(flat_e: torch.Tensor, n_experts: int, nt: int):
+        """Tokens sorted by expert -> (order, groups [G, 4] int32 = {expert, first row, rows, 0}, n_groups [1], G).
+        Everything stays on the device; G is an upper bound that depends only on shapes."""
+        pairs = flat_e.numel()
+        order = torch.argsort(flat_e, stable=True)
+        cnt = torch.bincount(flat_e, minlength=n_experts)
+        offs = torch.cumsum(cnt, 0) - cnt
+        ng = (cnt + nt - 1) // nt
+        cum = torch.cumsum(ng, 0)
+        gmax = n_experts + pairs // nt + 1
+        j = torch.arange(gmax, device=flat_e.device)
+        e_of = torch.searchsorted(cum, j, right=True).clamp_(max=n_experts - 1)
+        k_in = j - (cum[e_of] - ng[e_of])
+        valid = j < cum[-1]
+        tok0 = torch.where(valid, offs[e_of] + k_in * nt, torch.zeros_like(j))
+        ntok = torch.where(valid, (cnt[e_of] - k_in * nt).clamp(0, nt), torch.zeros_like(j))
+        groups = torch.stack([e_of, tok0, ntok, torch.zeros_like(j)], 1).to(torch.int32).contiguous()
+        return order, groups, cum[-1:].to(torch.int32).contiguous(), gmax
+
+    # ---- one chunk of up to 128 tokens ----------------------------------------------------------------------------------
+    def _chunk(self, tokens: torch.Tensor, base: int, positions: torch.Tensor, mask: Optional[torch.Tensor],
+               aux_layers=()) -> torch.Tensor:
+        d = self.d
+        m, w = d.cfg.model, d.w
+        T = tokens.shape[0]
+        dev = d.device
+        slots = (base + torch.arange(T, device=dev)).to(torch.int32)
+        pos32 = positions.to(torch.int32).contiguous()
+        x = w.embed[tokens].float().contiguous()
+        nq, nkv, H, I, k = d.nq, d.nkv, d.H, d.I, m.top_k
+        mask_u8 = mask.to(torch.uint8).contiguous() if mask is not None else None
+        self.aux_taps = {}
+        for L, lw in enumerate(w.layers):
+            xq, xs, _ = self._quant(x, lw.in_ln, "x")
+            qkv = self._linear(lw.wqkv, xq, xs, T, "qkv")
+            K.qk_norm_rope_rows(qkv, nq, nkv, lw.q_norm, lw.k_norm, m.rms_eps, d.cos, d.sin, pos32, slots,
+                                d.k_cache[L], d.v_cache[L], d.max_seq)
+            attn = self._buf("attn", (T, nq * 128), torch.float32)
+            K.window_attention(qkv, d.k_cache[L], d.v_cache[L], nq, nkv, d.max_seq, base, mask_u8, attn)
+            aq, asc, _ = self._quant(attn, None, "a")
+            o = self._linear(lw.wo, aq, asc, T, "wo")
+            x = x + d.comm_ref.all_reduce_tp(o.clone() if d.cfg.parallel.tp > 1 else o)
+            hq, hs, h2 = self._quant(x, lw.post_ln, "h", want_norm=True)
+            # router (tiny GEMM) + top-k, on the device
+            logits = h2 @ lw.router.float().t()
+            p = torch.softmax(logits, -1)
+            tw, ti = torch.topk(p, k, dim=-1)
+            if m.norm_topk_prob:
+                tw = tw / tw.sum(-1, keepdim=True)
+            d.sel_idx[L].copy_(ti[-1].to(torch.int32))          # routing telemetry of the window's last token
+            d.sel_w[L].copy_(tw[-1])
+            # grouped expert GEMMs over (token, slot) pairs sorted by expert
+            flat_e = ti.reshape(-1)
+            pairs = T * k
+            E_l = lw.w_gu.data.shape[0]
+            per = max(1, pairs // E_l)
+            nt = 16 if per <= 12 else 32 if per <= 28 else 64
+            order, groups, n_groups, gmax = self._group_table(flat_e, E_l, nt)
+            tok_of = order // k
+            gq = hq[tok_of].contiguous()
+            gs = hs[:, tok_of].contiguous() if hs is not None else None
+            act = self._grouped(lw.w_gu, K.TC_GATEUP, I, gq, gs, groups, n_groups, gmax, nt, pairs, "act")
+            cq, cs, _ = self._quant(act, None, "c")
+            yg = self._grouped(lw.w_d, K.TC_DOWN, H, cq, cs, groups, n_groups, gmax, nt, pairs, "y")
+            inv = torch.empty_like(order)
+            inv[order] = torch.arange(pairs, device=dev)
+            y = (yg[inv].reshape(T, k, H) * tw[..., None]).sum(1)       # slot order: deterministic
+            x = x + d.comm_ref.all_reduce_tp(y)
+            if L in aux_layers:
+                self.aux_taps[L] = x.clone()
+        return x
+
+    def _head(self, x: torch.Tensor) -> torch.Tensor:
+        d = self.d
+        w = d.w
+        xq, xs, _ = self._quant(x, w.final_norm, "f")
+        local = self._linear(w.lm_head, xq, xs, x.shape[0], "head")
+        if d.cfg.parallel.world == 1:
+            return local.clone()
+        return d.comm_ref.gather_logits(local.clone(), d.cfg.model.vocab, w.geom.vocab_chunk)
+
+    # ---- public -----------------------------------------------------------------------------------------------------------
+    @torch.no_grad()
+    def forward(self, tokens, commit: bool = True, tree_mask=None, positions=None, last_only: bool = False,
+                aux_layers=()) -> torch.Tensor:
+        """Logits ``[T, V]`` (``last_only``: ``[1, V]``) of ``tokens`` appended after the cached context. Rows are
+        written to the KV cache at ``seq_len ...``; ``commit=False`` leaves the sequence length unchanged."""
+        d = self.d
+        dev = d.device
+        toks = torch.as_tensor(list(tokens) if not isinstance(tokens, torch.Tensor) else tokens, dtype=torch.long, device=dev)
+        T = toks.shape[0]
+        base = d.seq_len
+        if base + T > d.max_seq:
+            raise ValueError("KV cache overflow")
+        if tree_mask is not None and T > CHUNK:
+            raise ValueError(f"a masked window holds at most {CHUNK} tokens")
+        pos = positions.to(dev) if positions is not None else base + torch.arange(T, device=dev)
+        outs: List[torch.Tensor] = []
+        for c0 in range(0, T, CHUNK):
+            c1 = min(T, c0 + CHUNK)
+            x = self._chunk(toks[c0:c1], base + c0, pos[c0:c1], tree_mask, aux_layers)
+            if not last_only:
+                outs.append(self._head(x))
+            elif c1 == T:
+                outs.append(self._head(x[-1:].contiguous()))
+        if commit:
+            d.pos.fill_(base + T)
+        d.check_error()
+        return torch.cat(outs, 0)

@@ -171,3 +171,35 @@ def test_real_engine_through_the_seam(tmp_path):
     assert again.quality.match_rate == 1.0
     bench_main(["--results-dir", str(tmp_path), "run", "--name", "real", "--engine", "b200", "--repeats", "1",
                 "--prompt", "8", "--decode", "4", "--dtype", "2"])
+
+
+def test_client_tools_measure_and_roofline_against_the_mock_server():
+    """Stand-alone SSE client: TTFT / TPOT distributions from the wall clock; roofline attribution."""
+    import threading
+    import uvicorn
+    from inferutil.bench import client_tools as ct
+    from inferencehackathon_b200.serve.app import create_app
+    from inferencehackathon_b200.serve.backends import MockBackend
+    import socket
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
+    server = uvicorn.Server(uvicorn.Config(create_app(MockBackend()), host="127.0.0.1", port=port, log_level="error"))
+    th = threading.Thread(target=server.run, daemon=True)
+    th.start()
+    import time
+    for _ in range(100):
+        if server.started:
+            break
+        time.sleep(0.05)
+    try:
+        m = ct.measure(f"http://127.0.0.1:{port}", ctx=8, decode=6, repeats=2, warmup=0, engine="conifer")
+        assert m["tokens"] >= 2 and m["ttft_ms"]["n"] == 2 and m["tpot_ms"]["mean"] > 0
+        assert m["server_summary"] and "decode_tok_per_s" in m["server_summary"]
+    finally:
+        server.should_exit = True
+        th.join(timeout=5)
+    a = ct.analyze(4096, 3.0, 1.0, 2.0, "b200", 8)
+    assert a["regime"] == "memory-bound" and a["dominant_term"] == "kernel_gap" and 0 < a["mbu"] < 1
+    assert ct.analyze(4096, a["ideal_TPOT_ms"], 1.0, 2.0)["dominant_term"] == "weight_bw"
+    s5 = ct.summarize([1.0, 2.0, 3.0, 4.0, 5.0])
+    assert s5["p50"] == 3.0 and s5["ci95_lo"] < 3.0 < s5["ci95_hi"] and ct.t95(4) == 2.776
+    assert ct.main(["roofline", "--ctx", "1024", "--tpot-ms", "2.5"]) == 0

@@ -1,0 +1,137 @@
+"""Multi-token GPU path (prompt chunks, verify windows, token trees) against the PyTorch reference model (B200)."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from inferencehackathon_b200 import SMALL
+from inferencehackathon_b200.runtime.engine import InferenceEngine
+
+
+def _prompt(n, seed=3):
+    return torch.randint(0, SMALL.vocab, (n,), generator=torch.Generator().manual_seed(seed)).tolist()
+
+
+def _pair(weights, max_seq=512):
+    dev = "cuda:0"
+    ref = InferenceEngine.build("small", weights=weights, device=dev, backend="torch", max_seq=max_seq)
+    eng = InferenceEngine.build("small", weights=weights, device=dev, backend="cuda", max_seq=max_seq)
+    ref.model.act_mode = "fp8" if weights == "fp8_block" else "bf16"     # the window GEMMs quantise activations per token
+    return ref, eng
+
+
+def test_grouped_gemm_matches_per_expert_reference():
+    """Device-side group table + grouped tcgen05 GEMM == per-expert matmuls."""
+    from inferencehackathon_b200.models.quant import quant_block, quant_act_per_token
+    from inferencehackathon_b200.ops import lib as K
+    from inferencehackathon_b200.runtime.gpu_window import GpuWindow
+    K.load()
+    d = torch.device("cuda", 0)
+    g = torch.Generator(device=d).manual_seed(0)
+    E, rows, Kd, pairs, nt = 8, 384, 512, 50, 16
+    w = quant_block(torch.randn(E, rows, Kd, device=d, generator=g) * 0.05, 128, 128)
+    flat_e = torch.randint(0, E, (pairs,), device=d, generator=g)
+    flat_e[:20] = 3                                              # one expert needs two groups
+    order, groups, n_groups, gmax = GpuWindow._group_table(flat_e, E, nt)
+    x = torch.randn(pairs, Kd, device=d, generator=g)
+    xs_sorted = x[order]
+    q, s = quant_act_per_token(xs_sorted, 128)
+    deq = (q.float().reshape(pairs, Kd // 128, 128) * s[..., None]).reshape(pairs, Kd)
+    sT = s.t().contiguous()
+    out = torch.full((pairs, rows), float("nan"), device=d)
+    err = torch.zeros(1, dtype=torch.int32, device=d)
+    a = K.IhbTcArgs()
+    K.tc_fill_weight(a, w)
+    a.X, a.xscale, a.mode, a.out, a.out_stride = q.contiguous().data_ptr(), sT.data_ptr(), K.TC_DOWN, out.data_ptr(), rows
+    a.T, a.T_total, a.tok0, a.err, a.top_k, a.ks = nt, pairs, 0, err.data_ptr(), 1, 1
+    a.groups, a.n_groups, a.max_groups = groups.data_ptr(), n_groups.data_ptr(), gmax
+    K.tc_gemm(a, False)
+    torch.cuda.synchronize()
+    assert int(err.item()) == 0
+    es = flat_e[order]
+    ref = torch.stack([deq[i] @ w.select(int(es[i])).dequant().t() for i in range(pairs)])
+    assert float((out - ref).abs().max()) < 2e-3 * float(ref.abs().max()) + 1e-3
+    assert int(n_groups.item()) == int(((torch.bincount(flat_e, minlength=E) + nt - 1) // nt).sum())
+
+
+@pytest.mark.parametrize("weights", ["bf16", "fp8_block"])
+def test_window_logits_match_reference_chain_and_chunks(weights):
+    ref, eng = _pair(weights)
+    toks = _prompt(150)                                          # two chunks: 128 + 22
+    a = ref.logits_for(toks[:150], commit=True)
+    b = eng.logits_for(toks[:150], commit=True)
+    assert b.shape == a.shape and eng.seq_len == 150
+    scale = float(a.abs().max())
+    assert float((a - b).abs().max()) < 0.03 * scale
+    assert float((a.argmax(-1) == b.argmax(-1)).float().mean()) > 0.9
+    # a second window on top of the cached context
+    more = _prompt(9, seed=5)
+    a2 = ref.logits_for(more)
+    b2 = eng.logits_for(more)
+    assert float((a2 - b2).abs().max()) < 0.03 * float(a2.abs().max())
+    eng.gpu.check_error()
+
+
+@pytest.mark.parametrize("weights", ["bf16", "fp8_block"])
+def test_window_tree_mask_and_rollback(weights):
+    ref, eng = _pair(weights)
+    ctx = _prompt(40)
+    ref.logits_for(ctx); eng.logits_for(ctx)
+    # root + 5 nodes: 0 -> {1, 2}, 1 -> {3, 4}, 2 -> {5}
+    parent = [0, 0, 0, 1, 1, 2]
+    n = len(parent)
+    depth = [0, 1, 1, 2, 2, 2]
+    mask = torch.zeros(n, n, dtype=torch.bool, device="cuda:0")
+    for i in range(n):
+        j = i
+        while True:
+            mask[i, j] = True
+            if j == 0:
+                break
+            j = parent[j]
+    toks = _prompt(n, seed=9)
+    pos = torch.tensor([40 + dpt for dpt in depth], device="cuda:0")
+    a = ref.logits_for(toks, commit=False, tree_mask=mask, positions=pos)
+    b = eng.logits_for(toks, commit=False, tree_mask=mask, positions=pos)
+    assert eng.seq_len == 40 and ref.seq_len == 40
+    assert float((a - b).abs().max()) < 0.03 * float(a.abs().max())
+    # node 3's row must equal a plain chain root -> 1 -> 3
+    chain = [toks[0], toks[1], toks[3]]
+    c = eng.logits_for(chain, commit=False)
+    assert float((c[2] - b[3]).abs().max()) < 0.02 * float(b.abs().max())
+
+
+def test_window_prefill_then_persistent_decode_matches_reference():
+    ref, eng = _pair("fp8_block")
+    ref.model.act_mode = None if eng.gpu.use_mega else ref.model.act_mode
+    prompt = _prompt(64)
+    want = ref.generate(prompt, 12)
+    pe = eng.prefill(prompt)
+    got = [pe.next_token]
+    for t in want.tokens[:-1]:                                   # teacher forcing
+        got.append(eng.decode_step(t).token_id)
+    agree = sum(int(x == y) for x, y in zip(want.tokens, got))
+    assert agree >= 9, (want.tokens, got)
+    eng.gpu.check_error()
+
+
+def test_speculative_driver_on_gpu_engine_equals_its_own_greedy():
+    """n-gram speculative decoding through the batched verify window emits what the same engine's plain greedy
+    window decoding emits."""
+    from inferencehackathon_b200.spec.driver import DecodeStop, EngineRunner, Rng, SpecConfig, SpecEngine, ChainDrafterPool
+    from inferencehackathon_b200.spec.ngram import NGramDrafter
+    eng = InferenceEngine.build("small", weights="bf16", device="cuda:0", backend="cuda", max_seq=512)
+    block = _prompt(12, seed=11)
+    prompt = block * 3
+    r = EngineRunner(eng)
+    plain = []
+    ctx = list(prompt)
+    for _ in range(16):
+        row = r.forward_single(ctx[:-1], ctx[-1])
+        t = int(row.argmax())
+        plain.append(t); ctx.append(t)
+    r2 = EngineRunner(eng)
+    se = SpecEngine(r2, ChainDrafterPool([NGramDrafter(2)]), SpecConfig(4, SMALL.vocab, 0.0))
+    out, tel = se.decode(prompt, DecodeStop(16), Rng(0))
+    assert out == plain
+    assert r2.forwards <= 16
