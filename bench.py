@@ -149,7 +149,11 @@ def main() -> None:
             dist.barrier()
             torch.cuda.synchronize()
 
-    # TTFT: prompt processing + first token, device-timed
+    # TTFT: prompt processing + first token, device-timed. The first pass pays one-time costs (workspace
+    # allocation, lazy module loading); it is reported separately and the second pass is the TTFT.
+    sync_all()
+    cold = eng.prefill(prompt).seconds
+    eng.reset()
     sync_all()
     pre = eng.prefill(prompt)
     ttft = pre.seconds
@@ -208,7 +212,10 @@ def main() -> None:
                           "l2": "inputs larger than L2 (per-token weight stream >> 126 MB)",
                           "weights": args.weights, "kv": "bf16", "init_s": round(t_init, 1)},
                "tpot_ms_p50": p50, "tpot_ms_p95": p95, "ttft_ms": ttft * 1e3,
-               "ttft_note": "prompt processed token by token with the decode pipeline",
+               "ttft_cold_ms": cold * 1e3,
+               "ttft_note": ("batched prompt pass on the tensor cores (tcgen05 GEMMs, grouped experts, window attention)"
+                             if gpu.has_window() else "prompt processed token by token with the decode pipeline"),
+               "pipeline": "persistent" if gpu.use_mega else ("tcgen05 per-op" if gpu.use_tc else "simt per-op"),
                "clocks": clocks, "e2e": e2e, "gpu_launches": gpu.n_launches_per_step * args.steps,
                "impl": "ours"}
         print(json.dumps(out))

@@ -267,6 +267,9 @@ typedef struct {
   int n_layers;
   int wtype;                    // IHB_W_FP8 | IHB_W_BF16 (all linear layers; the router is always bf16)
   int H, nq, nkv, I, E, top_k, renorm;
+  int expert0, E_local;         // experts held by this rank (expert parallel: a slice; tensor parallel: all, with I split)
+  float attn_ar_scale;          // weight of the summed attention partials: tp / world (hybrid and pure expert
+                                // parallel layouts compute the same attention shard on world / tp ranks)
   int max_seq;
   const float* cos_t;           // [max_seq, 64]
   const float* sin_t;

@@ -49,7 +49,7 @@ struct MgCtx {
   float* red;            // [32] block reductions
   int* sel_e;            // [top_k]
   float* sel_w;          // [top_k]
-  int* flags;            // [0] dead, [1] last-arriver flag of the attention merge
+  int* flags;            // [0] dead, [1] last-arriver flag of the attention merge, [2] routed experts held by this rank
   MgAttnSmem* attn;
 };
 
@@ -164,7 +164,7 @@ __device__ __forceinline__ void mg_stage(MgCtx& c, int n, F f) {
 // resid (+= the all-reduce slots of `parity`, in rank order) -> RMSNorm(gamma) -> xf (fp32) and the staged GEMV input.
 template <bool FP8>
 __device__ __forceinline__ void mg_residual_norm(const IhbMegaArgs& a, MgCtx& c, bool add_slots, int parity,
-                                                 const float* gamma) {
+                                                 const float* gamma, float scale = 1.f) {
   const int H = a.H;
   const int nr = a.comm.nranks;
   float ss = 0.f;
@@ -172,10 +172,12 @@ __device__ __forceinline__ void mg_residual_norm(const IhbMegaArgs& a, MgCtx& c,
     float4 v = *reinterpret_cast<float4*>(c.resid + i);
     if (add_slots) {
       const float* sl = a.comm.slots_local + static_cast<size_t>(parity) * nr * H + i;
+      float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
       for (int r = 0; r < nr; ++r) {
         const float4 p = ld_cg_f4(reinterpret_cast<const float4*>(sl + static_cast<size_t>(r) * H));
-        v.x += p.x; v.y += p.y; v.z += p.z; v.w += p.w;
+        sum.x += p.x; sum.y += p.y; sum.z += p.z; sum.w += p.w;
       }
+      v.x = fmaf(sum.x, scale, v.x); v.y = fmaf(sum.y, scale, v.y); v.z = fmaf(sum.z, scale, v.z); v.w = fmaf(sum.w, scale, v.w);
       *reinterpret_cast<float4*>(c.resid + i) = v;
     }
     ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;

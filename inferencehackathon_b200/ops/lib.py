@@ -107,7 +107,8 @@ class IhbMegaLayer(C.Structure):
 class IhbMegaArgs(C.Structure):
     _fields_ = [("layers", _vp), ("n_layers", C.c_int), ("wtype", C.c_int),
                 ("H", C.c_int), ("nq", C.c_int), ("nkv", C.c_int), ("I", C.c_int), ("E", C.c_int),
-                ("top_k", C.c_int), ("renorm", C.c_int), ("max_seq", C.c_int),
+                ("top_k", C.c_int), ("renorm", C.c_int), ("expert0", C.c_int), ("E_local", C.c_int),
+                ("attn_ar_scale", C.c_float), ("max_seq", C.c_int),
                 ("cos_t", _vp), ("sin_t", _vp), ("eps", C.c_float),
                 ("embed", _vp), ("embed_is_bf16", C.c_int), ("final_norm", _vp), ("lm_head", IhbMat),
                 ("vocab0", C.c_int), ("logits", _vp), ("cur_token", _vp), ("pos", _vp), ("token_ring", _vp),

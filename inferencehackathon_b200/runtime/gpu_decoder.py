@@ -45,7 +45,7 @@ class GpuDecoder:
         self.use_pdl = bool(env_flag("IHB_PDL", 1))
         self.use_tc = bool(env_flag("IHB_TC", 1))          # tensor-core linears (0: SIMT streaming GEMVs)
         # persistent whole-token kernel (tensor parallel only; expert parallel keeps the per-kernel pipeline)
-        self.use_mega = bool(env_flag("IHB_MEGA", 1)) and cfg.parallel.ep <= 1 and m.n_experts <= 256
+        self.use_mega = bool(env_flag("IHB_MEGA", 1)) and m.n_experts <= 256
         self.fp8 = weights.quant.weights == "fp8_block"
         self.use_graph = cfg.use_graph and bool(env_flag("IHB_GRAPH", 1))
         self.comm_ref = comm
@@ -105,7 +105,7 @@ class GpuDecoder:
     # communication block -------------------------------------------------------------------------------------
     def _setup_comm(self) -> None:
         par = self.cfg.parallel
-        nslots = 2 * max(par.tp, 1) * max(self.ks_o, 1) * self.H
+        nslots = 2 * max(par.world, par.tp, 1) * max(self.ks_o, 1) * self.H
         if par.world == 1:
             self.slots = torch.zeros(nslots, dtype=torch.float32, device=self.device)
             self.symm = None
@@ -196,6 +196,10 @@ class GpuDecoder:
         a.wtype = K.W_FP8 if self.fp8 else K.W_BF16
         a.H, a.nq, a.nkv, a.I, a.E = self.H, self.nq, self.nkv, self.I, m.n_experts
         a.top_k, a.renorm, a.max_seq = m.top_k, int(m.norm_topk_prob), self.max_seq
+        par = self.cfg.parallel
+        a.expert0, a.E_local = w.geom.expert0, w.geom.n_experts_local
+        # the attention shard is computed identically on world / tp ranks: the sum over all ranks counts it that often
+        a.attn_ar_scale = float(par.tp) / float(max(par.world, 1))
         a.cos_t, a.sin_t, a.eps = self.cos.data_ptr(), self.sin.data_ptr(), m.rms_eps
         a.embed, a.embed_is_bf16 = w.embed.data_ptr(), int(w.embed.dtype == torch.bfloat16)
         a.final_norm, a.lm_head, a.vocab0 = w.final_norm.data_ptr(), K.mat_of(w.lm_head), w.geom.vocab0

@@ -3,8 +3,8 @@
 Per layer: row RMSNorm + per-token activation quantisation -> tcgen05 GEMM (QKV) -> QK-norm / RoPE / KV append at
 explicit positions -> window attention (causal or tree mask) -> tcgen05 GEMM (o_proj) -> all-reduce -> router ->
 tokens sorted by expert -> GROUPED tcgen05 GEMMs (gate/up + SwiGLU, down) driven by a device-side group table (the
-routing result never visits the host) -> weighted combine -> all-reduce. Windows are processed in chunks of up to
-128 tokens (the GEMM's token tile).
+routing result never visits the host) -> weighted combine -> all-reduce. Windows are processed in passes of up to
+1024 tokens; dense GEMMs run one launch per 128-token tile, the grouped expert GEMMs one launch per pass.
 
 The contractions and the attention are this package's kernels (``ihb_tc_gemm``, ``ihb_window_attention``,
 ``ihb_norm_quant_rows``, ``ihb_qk_norm_rope_rows``); index bookkeeping (sort by expert, top-k, gathers) uses
@@ -20,7 +20,8 @@ import torch
 
 from ..ops import lib as K
 
-CHUNK = 128
+CHUNK = 1024          # tokens per pass (the expert weights are read about once per pass)
+TILE = 128            # token tile of one dense GEMM launch
 
 
 class GpuWindow:
@@ -65,18 +66,22 @@ class GpuWindow:
         K.tc_fill_weight(a, qw)
         rows = a.rows
         out = self._buf("o_" + tag, (T, rows), torch.float32)
-        a.X, a.mode, a.out, a.out_stride = xq.data_ptr(), K.TC_LINEAR, out.data_ptr(), rows
+        a.X, a.mode, a.out_stride = xq.data_ptr(), K.TC_LINEAR, rows
         if xs is not None:
             a.xscale = xs.data_ptr()
-        a.T, a.T_total, a.tok0, a.err = T, T, 0, self.err.data_ptr()
+        a.T_total, a.err = T, self.err.data_ptr()
         tiles = (rows + 127) // 128
         nkb = (a.K * self.es + 127) // 128
         a.ks = max(1, min(nkb, 16, -(-2 * self.sms // tiles)))
+        a.T = min(T, TILE)
         part = self._buf("part", (max(1, K.tc_partial_floats(a)),), torch.float32)
         ctr = self._buf("ctr", (max(tiles, 1),), torch.int32)
         a.partial, a.tile_counters = part.data_ptr(), ctr.data_ptr()
-        K.tc_gemm(a, False)
-        self.n_gemm_launches += 1
+        for t0 in range(0, T, TILE):                      # token tiles of one launch each
+            a.T, a.tok0 = min(TILE, T - t0), t0
+            a.out = out[t0:].data_ptr()
+            K.tc_gemm(a, False)
+            self.n_gemm_launches += 1
         return out
 
     def _grouped(self, qw, mode, rows: int, xq, xs, groups, n_groups, max_groups: int, nt: int, n_pairs: int, tag: str):
@@ -189,8 +194,8 @@ class GpuWindow:
         base = d.seq_len
         if base + T > d.max_seq:
             raise ValueError("KV cache overflow")
-        if tree_mask is not None and T > CHUNK:
-            raise ValueError(f"a masked window holds at most {CHUNK} tokens")
+        if tree_mask is not None and T > TILE:
+            raise ValueError(f"a masked window holds at most {TILE} tokens")
         pos = positions.to(dev) if positions is not None else base + torch.arange(T, device=dev)
         outs: List[torch.Tensor] = []
         for c0 in range(0, T, CHUNK):

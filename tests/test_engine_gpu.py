@@ -23,13 +23,17 @@ def test_cuda_decode_matches_torch_reference(weights, pipeline, graph, monkeypat
     ref = InferenceEngine.build("small", weights=weights, device=dev, backend="torch", max_seq=256)
     eng = InferenceEngine.build("small", weights=weights, device=dev, backend="cuda", max_seq=256, use_graph=graph)
     assert eng.gpu.use_mega == (pipeline == "mega")
-    if eng.gpu.use_tc and not eng.gpu.use_mega:      # the oracle rounds activations the way the tensor-core kernels store them
-        ref.model.act_mode = "fp8" if weights == "fp8_block" else "bf16"
+    tc_mode = "fp8" if weights == "fp8_block" else "bf16"
+    # the oracle rounds activations the way the kernels store them: per-token fp8 / bf16 in the tensor-core GEMMs
+    # (per-op pipeline, and the batched prompt pass of the other pipelines), fp16 in the CUDA-core GEMVs
+    decode_mode = tc_mode if (eng.gpu.use_tc and not eng.gpu.use_mega) else None
+    ref.model.act_mode = tc_mode if eng.gpu.has_window() else decode_mode
     pr = ref.prefill(_prompt(), return_logits=True)
     pe = eng.prefill(_prompt(), return_logits=True)
     scale = float(pr.logits.abs().max())
     assert float((pr.logits[0] - pe.logits[0]).abs().max()) < 0.02 * scale
     ref.reset(); eng.reset()
+    ref.model.act_mode = decode_mode
     a = ref.generate(_prompt(), 24)
     # teacher forcing: the CUDA engine is fed the reference's tokens, so one near-tie cannot derail the comparison
     pe = eng.prefill(_prompt())

@@ -21,7 +21,9 @@ rank, world, local = init_distributed()
 dev = torch.device("cuda", local)
 weights = os.environ.get("IHB_TEST_WEIGHTS", "bf16")
 prompt = torch.randint(0, 4096, (20,), generator=torch.Generator().manual_seed(3)).tolist()
-eng = InferenceEngine.build("small", tp=world, rank=rank, world=world, weights=weights, device=dev, backend="cuda", max_seq=128)
+plan = os.environ.get("IHB_TEST_PLAN", "tp")
+tp, ep = {"tp": (world, 1), "ep": (1, world), "hybrid": (world, world)}[plan]
+eng = InferenceEngine.build("small", tp=tp, ep=ep, rank=rank, world=world, weights=weights, device=dev, backend="cuda", max_seq=128)
 res = eng.generate(prompt, 12)
 eng.gpu.check_error()
 ref_tokens = None
@@ -37,8 +39,8 @@ dist.destroy_process_group()
 """
 
 
-def _run(n, mode, weights):
-    env = dict(os.environ, IHB_ROOT=ROOT, IHB_COMM_MODE=mode, IHB_TEST_WEIGHTS=weights)
+def _run(n, mode, weights, plan="tp"):
+    env = dict(os.environ, IHB_ROOT=ROOT, IHB_COMM_MODE=mode, IHB_TEST_WEIGHTS=weights, IHB_TEST_PLAN=plan)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
            "--master-addr", "127.0.0.1", "--master-port", "29533", "-c", WORKER]
     # torchrun has no -c: write the worker to a temp file instead
@@ -65,3 +67,15 @@ def test_tp2_decode_matches_single_gpu(mode, weights):
     agree = sum(int(a == b) for a, b in zip(out["tokens"][0], out["ref"]))
     # TP changes the summation order (and, for fp8, the quantisation blocks of the shards)
     assert agree >= (9 if weights == "bf16" else 4), out
+
+
+@pytest.mark.parametrize("plan", ["ep", "hybrid"])
+def test_expert_parallel_decode_in_the_persistent_kernel(plan):
+    """Experts owned by ranks (full intermediate size), attention replicated (ep) or tensor-parallel (hybrid): the
+    owners push their weighted expert outputs into every GPU's slot buffer, the same in-kernel combine as TP."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    out = _run(2, "auto", "bf16", plan)
+    assert out["tokens"][0] == out["tokens"][1], out
+    agree = sum(int(a == b) for a, b in zip(out["tokens"][0], out["ref"]))
+    assert agree >= 9, out
