@@ -291,7 +291,7 @@ typedef struct {
   float* attn;                  // [nq * 128]
   float* act;                   // [top_k * I]
   unsigned long long* argmax_partial;   // [grid]
-  unsigned* bar;                // [0] arrivals, [1] releases, [2] arrival base, [3] release base, [8 ...] head counters
+  unsigned* bar;                // [0] grid-barrier arrivals, [2] their base for the next launch, [8 ...] attention merge counters
   unsigned* err;
   unsigned long long* prof;     // optional: CTA 0 stores %globaltimer at kernel start ([0]) and after barrier i ([i])
   int max_split;                // attention splits available per (kv head, group of 8 query heads)

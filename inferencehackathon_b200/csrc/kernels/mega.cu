@@ -29,17 +29,20 @@ constexpr int MG_GQ = 8;                 // query heads per attention work item
 #endif
 constexpr int MG_REC = MG_HD + 2;        // attention partial record: acc[128], m, l
 
+constexpr int MG_HW = 4;                 // query heads per warp: a warp pair shares a block of 32 positions
+constexpr int MG_ABLK = (MG_WARPS / 2) * 32;   // positions per CTA round
+
 struct MgAttnSmem {
   float q[MG_GQ][MG_HD];
-  float p[MG_WARPS][MG_GQ][32];
-  float m[MG_WARPS][MG_GQ], l[MG_WARPS][MG_GQ];
-  float acc[MG_WARPS][MG_GQ][MG_HD];
+  float p[MG_WARPS][MG_HW][32];
+  float m[MG_WARPS][MG_HW], l[MG_WARPS][MG_HW];
+  float acc[MG_WARPS][MG_HW][MG_HD];
   __nv_bfloat16 knew[MG_HD], vnew[MG_HD];
 };
 
 struct MgCtx {
   // barrier state: the counters are meaningful in thread 0; epoch (cross-GPU rounds so far) in every thread
-  unsigned base, rel_base, n_bar, n_rel, epoch;
+  unsigned base, n_bar, n_prof, epoch;
   // shared memory carve-up
   float* resid;          // [H]
   float* xf;             // [H] fp32 normed hidden state (router input)
@@ -82,32 +85,47 @@ __device__ __forceinline__ void red_release_gpu_add_u32(unsigned* p, unsigned v)
   asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
-// Grid-wide barrier: one fire-and-forget release-add per CTA, then a spin on the same counter. cross = true:
-// CTA 0, once every CTA of this GPU has arrived (all partials pushed), also runs the cross-GPU arrive/wait and
-// then opens a second counter on which the other CTAs wait.
+// Bounded spin on this GPU's cross-GPU arrival counter (system-scope acquire).
+__device__ __forceinline__ bool mg_wait_sys(const unsigned* flag, unsigned target, unsigned* err) {
+  const unsigned long long t0 = globaltimer_ns();
+  unsigned spins = 0;
+  while (static_cast<int>(ld_acquire_sys_u32(flag) - target) < 0) {
+    if ((++spins & 63u) == 0u) {
+      if (ld_cg_u(err) != 0u) return false;
+      if (globaltimer_ns() - t0 > IHB_PEER_WAIT_NS) { set_error(err, ERR_PEER_BARRIER_TIMEOUT); return false; }
+    }
+  }
+  return true;
+}
+
+// `count` arrivals of this rank on every GPU's counter (one multicast reduction, or one per peer).
+__device__ __forceinline__ void mg_arrive_all(const IhbComm& cm, unsigned count) {
+  if (cm.flag_mc != nullptr) {
+    multimem_red_release_sys_add_u32(cm.flag_mc, count);
+  } else {
+    for (int r = 0; r < cm.nranks; ++r) red_release_sys_add_u32(cm.flag_peer[r], count);
+  }
+}
+
+// Grid-wide barrier: one fire-and-forget release-add per CTA, then a spin on the same counter.
+// cross = true (several GPUs): every CTA of every rank arrives directly on every GPU's counter - its partials were
+// pushed before, the release orders them - and waits until all ranks x CTAs of this round are in: one NVLink round
+// trip, no local hop before or after it. The counter advances by nranks * gridDim.x per cross-GPU round.
 __device__ __forceinline__ void mg_barrier(const IhbMegaArgs& a, MgCtx& c, bool cross) {
   __syncthreads();
   if (threadIdx.x == 0 && c.flags[0] == 0) {
-    c.n_bar++;
-    const unsigned target = c.base + c.n_bar * gridDim.x;
     bool ok = true;
     if (cross && a.comm.nranks > 1) {
       __threadfence_system();
-      red_release_gpu_add_u32(a.bar + 0, 1u);
-      c.n_rel++;
-      if (blockIdx.x == 0) {
-        ok = mg_wait(a.bar + 0, target, a.err);
-        ok = ok && peer_barrier(a.comm, (c.epoch + 1u) * static_cast<unsigned>(a.comm.nranks), a.err);
-        red_release_gpu_add_u32(a.bar + 1, 1u);
-      } else {
-        ok = mg_wait(a.bar + 1, c.rel_base + c.n_rel, a.err);
-      }
+      mg_arrive_all(a.comm, 1u);
+      ok = mg_wait_sys(a.comm.flag_local, (c.epoch + 1u) * static_cast<unsigned>(a.comm.nranks) * gridDim.x, a.err);
     } else {
+      c.n_bar++;
       red_release_gpu_add_u32(a.bar + 0, 1u);
-      ok = mg_wait(a.bar + 0, target, a.err);
+      ok = mg_wait(a.bar + 0, c.base + c.n_bar * gridDim.x, a.err);
     }
     if (!ok) c.flags[0] = 1;
-    if (a.prof != nullptr && blockIdx.x == 0) a.prof[c.n_bar] = globaltimer_ns();
+    if (a.prof != nullptr && blockIdx.x == 0) a.prof[++c.n_prof] = globaltimer_ns();
   }
   if (cross) c.epoch++;          // every thread keeps the count of cross-GPU rounds (it selects the slot parity)
   __syncthreads();

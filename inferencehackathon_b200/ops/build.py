@@ -29,12 +29,34 @@ def _sources(sub: str, exts) -> List[str]:
 
 
 def _digest(paths: List[str], extra: str) -> str:
+    """Content hash of the sources (names relative to the source tree, so that a copy of the tree elsewhere with
+    its built libraries is not rebuilt)."""
     h = hashlib.sha256(extra.encode())
     for p in paths:
         with open(p, "rb") as f:
-            h.update(p.encode())
+            h.update(os.path.relpath(p, CSRC).encode())
             h.update(f.read())
     return h.hexdigest()
+
+
+class _BuildLock:
+    """Inter-process lock: the ranks of a multi-GPU job import the package at the same time and only one of them
+    may (re)build; the others wait and then find the library up to date."""
+
+    def __init__(self, name: str):
+        self.path = os.path.join(HERE, name)
+        self.f = None
+
+    def __enter__(self):
+        import fcntl
+        self.f = open(self.path, "w")
+        fcntl.flock(self.f, fcntl.LOCK_EX)
+        return self
+
+    def __exit__(self, *exc):
+        import fcntl
+        fcntl.flock(self.f, fcntl.LOCK_UN)
+        self.f.close()
 
 
 def _stale(lib: str, digest: str) -> bool:
@@ -57,6 +79,13 @@ def build_kernels(force: bool = False, verbose: bool = False) -> str:
     digest = _digest(deps, " ".join(NVCC_FLAGS))
     if not force and not _stale(KERNEL_LIB, digest):
         return KERNEL_LIB
+    with _BuildLock(".build_kernels.lock"):
+        if not force and not _stale(KERNEL_LIB, digest):      # another process built it while this one waited
+            return KERNEL_LIB
+        return _build_kernels_locked(srcs, digest, verbose)
+
+
+def _build_kernels_locked(srcs: List[str], digest: str, verbose: bool) -> str:
     nvcc = os.environ.get("NVCC", "nvcc")
     objs = []
     objdir = os.path.join(HERE, "build")
@@ -73,7 +102,9 @@ def build_kernels(force: bool = False, verbose: bool = False) -> str:
             print(out)
         if p.returncode != 0:
             raise RuntimeError("build failed: " + " ".join(cmd) + "\n" + out)
-    _run([nvcc, "-shared", "-o", KERNEL_LIB] + objs + ["-lcuda"])
+    tmp = KERNEL_LIB + ".tmp"
+    _run([nvcc, "-shared", "-o", tmp] + objs + ["-lcuda"])
+    os.replace(tmp, KERNEL_LIB)                               # readers never see a half-written library
     with open(KERNEL_LIB + ".stamp", "w") as f:
         f.write(digest)
     return KERNEL_LIB
@@ -88,9 +119,14 @@ def build_ctrl(force: bool = False) -> str:
     digest = _digest(deps, " ".join(flags))
     if not force and not _stale(CTRL_LIB, digest):
         return CTRL_LIB
-    _run([os.environ.get("CXX", "g++")] + flags + srcs + ["-o", CTRL_LIB])
-    with open(CTRL_LIB + ".stamp", "w") as f:
-        f.write(digest)
+    with _BuildLock(".build_ctrl.lock"):
+        if not force and not _stale(CTRL_LIB, digest):
+            return CTRL_LIB
+        tmp = CTRL_LIB + ".tmp"
+        _run([os.environ.get("CXX", "g++")] + flags + srcs + ["-o", tmp])
+        os.replace(tmp, CTRL_LIB)
+        with open(CTRL_LIB + ".stamp", "w") as f:
+            f.write(digest)
     return CTRL_LIB
 
 
