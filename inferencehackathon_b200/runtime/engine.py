@@ -89,6 +89,11 @@ class InferenceEngine:
         self._last_token: Optional[int] = None
         self._index = 0
         self._timer = StepTimer(self.device)
+        # failure handling: tokens fed so far (to rebuild the cache on the fallback path) and the health record
+        self._history: List[int] = []
+        self.healthy = True
+        self.fallback_enabled = True
+        self.failures: List[str] = []
 
     # construction ------------------------------------------------------------------------------------------
     @classmethod
@@ -127,6 +132,7 @@ class InferenceEngine:
             self.cache.reset()
         self._last_token = None
         self._index = 0
+        self._history = []
 
     def set_sampling(self, params: SamplingParams) -> None:
         self.sampler = Sampler(params)
@@ -135,9 +141,14 @@ class InferenceEngine:
     def prefill(self, token_ids: Sequence[int], return_logits: bool = False) -> PrefillOutput:
         """Process the prompt, fill the KV cache, return the first generated token (device-timed)."""
         toks = torch.as_tensor(list(token_ids), dtype=torch.long, device=self.device)
+        self._history += [int(t) for t in token_ids]
         self._timer.start()
         if self.gpu is not None:
-            nxt, logits = self.gpu.prefill(toks, self.sampler, return_logits)
+            try:
+                nxt, logits = self.gpu.prefill(toks, self.sampler, return_logits)
+            except RuntimeError as e:
+                self._fall_back(e, drop=len(toks))
+                return self.prefill_torch(toks, return_logits)
         else:
             hidden = self.model.forward_hidden(toks, self.cache)
             nxt, logits = self._pick(hidden[-1:], return_logits)
@@ -145,6 +156,36 @@ class InferenceEngine:
         self._last_token = int(nxt)
         self._index = 0
         return PrefillOutput(len(toks), seconds, int(nxt), logits)
+
+    def prefill_torch(self, toks: torch.Tensor, return_logits: bool) -> PrefillOutput:
+        self._timer.start()
+        hidden = self.model.forward_hidden(toks, self.cache)
+        nxt, logits = self._pick(hidden[-1:], return_logits)
+        seconds = self._timer.stop()
+        self._last_token = int(nxt)
+        self._index = 0
+        return PrefillOutput(len(toks), seconds, int(nxt), logits)
+
+    # failure handling --------------------------------------------------------------------------------------------
+    def _fall_back(self, err: Exception, drop: int = 0) -> None:
+        """A device-side wait gave up (a peer stopped answering, a poisoned error word, ...): the fused pipeline is
+        abandoned, the engine is marked unhealthy and continues on the PyTorch + NCCL reference path. The KV cache of
+        that path is rebuilt from the tokens fed so far (``drop`` = tokens of the failed call, which the caller
+        re-runs)."""
+        self.failures.append(f"{type(err).__name__}: {err}")
+        self.healthy = False
+        if not self.fallback_enabled or self.gpu is None:
+            raise err
+        if self.weights.layers and self.weights.layers[0].wqkv.data.device.type == "meta":
+            raise RuntimeError("no fallback: the plain weight copies were released for the tiled layout") from err
+        kv_dtype = {"fp32": torch.float32, "bf16": torch.bfloat16}[self.cfg.quant.kv]
+        max_seq = self.gpu.max_seq
+        self.gpu = None
+        self.backend = "torch"
+        self.cache = self.model.new_cache(max_seq, kv_dtype, self.device)
+        done = self._history[: len(self._history) - drop]
+        if done:
+            self.model.forward_hidden(torch.as_tensor(done, dtype=torch.long, device=self.device), self.cache)
 
     def _pick(self, hidden_last: torch.Tensor, return_logits: bool):
         if self.sampler.params.greedy and not return_logits:
@@ -164,9 +205,13 @@ class InferenceEngine:
         tok = self._last_token if token is None else token
         if tok is None:
             raise RuntimeError("decode_step before prefill")
+        self._history.append(int(tok))
         if self.gpu is not None:
-            out_tok, seconds, routes = self.gpu.decode_step(tok, self.sampler, want_routes=want_routes)
-        else:
+            try:
+                out_tok, seconds, routes = self.gpu.decode_step(tok, self.sampler, want_routes=want_routes)
+            except RuntimeError as e:
+                self._fall_back(e, drop=1)
+        if self.gpu is None:
             t = torch.tensor([tok], dtype=torch.long, device=self.device)
             self._timer.start()
             hidden = self.model.forward_hidden(t, self.cache)

@@ -62,13 +62,15 @@ class GpuDecoder:
         self.router_logits = torch.zeros(L, m.n_experts, **f32)
         self.sel_idx = torch.zeros(L, m.top_k, **i32)
         self.sel_w = torch.zeros(L, m.top_k, **f32)
-        self.cur_token = torch.zeros(1, **i32)
+        # next token and device error word side by side: one device->host copy per step returns both
+        self._tok_err = torch.zeros(2, **i32)
+        self.cur_token = self._tok_err[0:1]
         self.pos = torch.zeros(1, **i32)
         self.n_forced = torch.zeros(1, **i32)
         self.forced = torch.zeros(self.max_seq + 1, **i32)
         self.token_ring = torch.zeros(self.max_seq + 1, **i32)
         self.counters = torch.zeros(8 + self.nq, dtype=torch.int32, device=dev)
-        self.err = torch.zeros(1, **i32)
+        self.err = self._tok_err[1:2]
         self.epoch = torch.zeros(1, **i32)
         self.argmax_partial = torch.zeros(1024, dtype=torch.int64, device=dev)
         self.logits = torch.zeros(max(g.vocab_local, 1), **f32)
@@ -98,7 +100,7 @@ class GpuDecoder:
         self._ev1 = torch.cuda.Event(enable_timing=True)
         # pinned staging for the per-step host<->device traffic of the public decode_step API
         self._tok_in = torch.zeros(1, dtype=torch.int32).pin_memory()
-        self._tok_out = torch.zeros(1, dtype=torch.int32).pin_memory()
+        self._tok_out = torch.zeros(2, dtype=torch.int32).pin_memory()
         self.h2d_bytes_per_step = self._tok_in.numel() * 4
         self.d2h_bytes_per_step = self._tok_out.numel() * 4
 
@@ -448,11 +450,13 @@ class GpuDecoder:
         self._ev0.record()
         self.cur_token.copy_(self._tok_in, non_blocking=True)
         self._step()
-        self._tok_out.copy_(self.cur_token, non_blocking=True)
+        self._tok_out.copy_(self._tok_err, non_blocking=True)
         self._ev1.record()
         self._ev1.synchronize()
         seconds = self._ev0.elapsed_time(self._ev1) * 1e-3
         out = int(self._tok_out[0])
+        if int(self._tok_out[1]):
+            self.check_error()                       # a device-side wait gave up during this step: raises
         if not sampler.params.greedy:
             out = int(sampler.sample(self._full_logits()))
             self.cur_token.fill_(out)

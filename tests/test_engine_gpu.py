@@ -61,3 +61,23 @@ def test_graph_replay_is_deterministic(mega, monkeypatch):
     a = eng.generate(_prompt(), 16).tokens
     b = eng.generate(_prompt(), 16).tokens
     assert a == b
+
+
+def test_poisoned_error_word_ends_the_waits_and_the_engine_falls_back():
+    """A nonzero device error word makes every bounded wait of the persistent kernel give up at once (no hang, no
+    fault); the step reports it, the engine continues on the reference path with the same tokens."""
+    dev = "cuda:0"
+    ref = InferenceEngine.build("small", weights="bf16", device=dev, backend="torch", max_seq=256)
+    eng = InferenceEngine.build("small", weights="bf16", device=dev, backend="cuda", max_seq=256)
+    ref.model.act_mode = "bf16"
+    prompt = _prompt(20)
+    want = ref.generate(prompt, 10).tokens
+    pe = eng.prefill(prompt)
+    got = [pe.next_token]
+    for i in range(9):
+        if i == 3:
+            eng.gpu.err.fill_(7)                   # host-set poison: the kernel's barriers check this word
+        got.append(eng.decode_step().token_id)
+    assert eng.healthy is False and eng.gpu is None and len(eng.failures) == 1
+    agree = sum(int(a == b) for a, b in zip(want, got))
+    assert agree >= 8, (want, got)

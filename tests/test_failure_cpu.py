@@ -1,0 +1,192 @@
+"""Failure handling without a GPU: (a) a device-side wait that gives up surfaces as an exception of the decode
+pipeline; the engine marks itself unhealthy, rebuilds the cache on the PyTorch + collectives reference path from
+the tokens fed so far and keeps generating the same tokens; the serving layer turns an unrecoverable error into an
+in-stream error chunk. (b) A host-side model of the cross-GPU slot / arrival-counter protocol of the fused
+all-reduce (double-buffered slots by round parity, monotonic counter, bounded waits) is run under random
+interleavings and never reads a slot of the wrong round; a rank that stops arriving ends the others' waits with an
+error status instead of a hang."""
+import json
+import random
+
+import pytest
+import torch
+
+from inferencehackathon_b200.runtime.engine import InferenceEngine
+
+
+class _FailingDecoder:
+    """Stands in for the CUDA decoder: works for ``ok_steps`` decode steps, then reports a timed-out device wait."""
+
+    def __init__(self, inner: InferenceEngine, ok_steps: int, prefill_fails: bool = False):
+        self.inner, self.ok_steps, self.prefill_fails = inner, ok_steps, prefill_fails
+        self.max_seq = inner.cache.max_seq
+        self.steps = 0
+
+    def reset(self):
+        self.inner.reset()
+
+    @property
+    def seq_len(self):
+        return self.inner.seq_len
+
+    def prefill(self, toks, sampler, return_logits):
+        if self.prefill_fails:
+            raise RuntimeError("device-side wait gave up: peer barrier time-out")
+        out = self.inner.prefill(toks.tolist(), return_logits)
+        return out.next_token, out.logits
+
+    def decode_step(self, tok, sampler, want_routes=True):
+        if self.steps >= self.ok_steps:
+            raise RuntimeError("device-side wait gave up: peer barrier time-out")
+        self.steps += 1
+        st = self.inner.decode_step(tok)
+        return st.token_id, st.seconds, st.routes
+
+    def last_routes(self):
+        return list(self.inner.model.last_routes)
+
+    def check_error(self):
+        pass
+
+
+def _engines():
+    eng = InferenceEngine.build("tiny", weights="fp32", max_seq=128)
+    shadow = InferenceEngine.build("tiny", weights="fp32", max_seq=128)
+    return eng, shadow
+
+
+@pytest.mark.parametrize("ok_steps,prefill_fails", [(3, False), (0, False), (0, True)])
+def test_engine_falls_back_to_reference_path_and_keeps_its_tokens(ok_steps, prefill_fails):
+    prompt = torch.randint(0, 2048, (12,), generator=torch.Generator().manual_seed(1)).tolist()
+    want = InferenceEngine.build("tiny", weights="fp32", max_seq=128).generate(prompt, 10).tokens
+    eng, shadow = _engines()
+    eng.gpu = _FailingDecoder(shadow, ok_steps, prefill_fails)
+    got = eng.generate(prompt, 10).tokens
+    assert got == want
+    assert eng.healthy is False and eng.gpu is None and eng.backend == "torch"
+    assert len(eng.failures) == 1 and "time-out" in eng.failures[0]
+    # the next request runs on the fallback path from the start
+    assert eng.generate(prompt, 6).tokens == want[:6]
+
+
+def test_fallback_can_be_disabled_and_server_reports_in_stream():
+    from fastapi.testclient import TestClient
+    from inferencehackathon_b200.serve import backends as bk
+    from inferencehackathon_b200.serve.app import create_app
+    eng, shadow = _engines()
+    eng.gpu = _FailingDecoder(shadow, 2)
+    eng.fallback_enabled = False
+    backend = bk.EngineBackend(eng)
+    c = TestClient(create_app(backend))
+    body = {"messages": [{"role": "user", "content": "hello"}], "max_tokens": 8, "temperature": 0.0}
+    frames = [f[6:] for f in c.post("/v1/chat/completions", json=body).text.split("\n\n") if f.startswith("data: ")]
+    objs = [json.loads(f) for f in frames if f != "[DONE]"]
+    assert any("error" in o and o["error"]["type"] == "engine_error" for o in objs)
+    assert backend.healthy is False and frames[-1] == "[DONE]"
+
+
+# ---- protocol model ---------------------------------------------------------------------------------------------------------
+class _Rank:
+    def __init__(self, r, n):
+        self.r, self.n = r, n
+        self.epoch = 0
+        self.pc = "push"
+        self.out = []
+        self.err = None
+        self.spins = 0
+
+
+def _run_protocol(n_ranks, rounds, seed, dead_rank=None, dead_after=None, spin_limit=200):
+    """Slots [parity][rank] and one arrival counter per GPU. Each rank: push value(round) into slot[parity][self] of
+    every GPU, arrive on every GPU's counter, wait until the own counter reaches (epoch + 1) * n, read all slots of
+    the parity, next round. The scheduler picks which rank advances one step."""
+    rng = random.Random(seed)
+    slots = [[[None] * n_ranks for _ in range(2)] for _ in range(n_ranks)]
+    counter = [0] * n_ranks
+    ranks = [_Rank(r, n_ranks) for r in range(n_ranks)]
+    live = list(range(n_ranks))
+    while live:
+        r = rng.choice(live)
+        k = ranks[r]
+        if dead_rank == r and k.epoch >= dead_after and k.pc == "push":
+            live.remove(r)                       # stops between rounds, nothing in flight
+            continue
+        par = k.epoch & 1
+        if k.pc == "push":
+            for g in range(n_ranks):
+                slots[g][par][r] = (k.epoch, r)
+            k.pc = "arrive"
+        elif k.pc == "arrive":
+            for g in range(n_ranks):
+                counter[g] += 1
+            k.pc = "wait"
+        elif k.pc == "wait":
+            if counter[r] >= (k.epoch + 1) * n_ranks:
+                k.pc = "read"
+                k.spins = 0
+            else:
+                k.spins += 1
+                if k.spins > spin_limit:         # bounded wait: status, not a hang
+                    k.err = "peer barrier time-out"
+                    live.remove(r)
+        else:
+            got = list(slots[r][par])
+            assert all(v is not None and v[0] == k.epoch for v in got), (r, k.epoch, got)
+            k.out.append(sum(v[1] for v in got))
+            k.epoch += 1
+            k.pc = "push"
+            if k.epoch == rounds:
+                live.remove(r)
+    return ranks
+
+
+@pytest.mark.parametrize("n_ranks", [2, 4, 8])
+def test_slot_protocol_never_reads_a_stale_or_future_round(n_ranks):
+    for seed in range(20):
+        ranks = _run_protocol(n_ranks, rounds=12, seed=seed)
+        want = [sum(range(n_ranks))] * 12
+        assert all(k.out == want and k.err is None for k in ranks)
+
+
+def test_slot_protocol_with_single_buffer_would_break():
+    """The same schedule with ONE slot set (parity ignored) lets a fast rank overwrite a slot a slow rank has not
+    read yet: the double buffer is what makes one barrier per round enough."""
+    def run(seed):
+        rng = random.Random(seed)
+        n = 2
+        slots = [[None] * n for _ in range(n)]
+        counter = [0] * n
+        st = [dict(epoch=0, pc="push") for _ in range(n)]
+        for _ in range(400):
+            r = rng.randrange(n)
+            k = st[r]
+            if k["epoch"] >= 6:
+                continue
+            if k["pc"] == "push":
+                for g in range(n):
+                    slots[g][r] = k["epoch"]
+                k["pc"] = "arrive"
+            elif k["pc"] == "arrive":
+                for g in range(n):
+                    counter[g] += 1
+                k["pc"] = "wait"
+            elif k["pc"] == "wait":
+                if counter[r] >= (k["epoch"] + 1) * n:
+                    k["pc"] = "read"
+            else:
+                if any(v != k["epoch"] for v in slots[r]):
+                    return True
+                k["epoch"] += 1
+                k["pc"] = "push"
+        return False
+    assert any(run(seed) for seed in range(200))
+
+
+def test_rank_that_stops_arriving_gives_the_others_a_status_not_a_hang():
+    ranks = _run_protocol(4, rounds=10, seed=3, dead_rank=2, dead_after=4)
+    for k in ranks:
+        if k.r == 2:
+            assert k.epoch == 4 and k.err is None
+        else:
+            assert k.err == "peer barrier time-out" and 4 <= k.epoch <= 5
+            assert k.out == [6] * k.epoch
