@@ -287,7 +287,7 @@ typedef struct {
   const int* forced;
   const int* n_forced;
   float* qkv;                   // [(nq + 2 nkv) * 128]
-  float* attn_part;             // [nq][max_split][130]
+  float* attn_part;             // [nq][max_split][132]
   float* attn;                  // [nq * 128]
   float* act;                   // [top_k * I]
   unsigned long long* argmax_partial;   // [grid]

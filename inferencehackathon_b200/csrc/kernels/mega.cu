@@ -27,7 +27,7 @@ constexpr int MG_GQ = 8;                 // query heads per attention work item
 #ifndef MG_INT_CVT
 #define MG_INT_CVT 0
 #endif
-constexpr int MG_REC = MG_HD + 2;        // attention partial record: acc[128], m, l
+constexpr int MG_REC = MG_HD + 4;        // attention partial record: acc[128], m, l, 2 pad (16-byte multiple)
 
 constexpr int MG_HW = 4;                 // query heads per warp: a warp pair shares a block of 32 positions
 constexpr int MG_ABLK = (MG_WARPS / 2) * 32;   // positions per CTA round
@@ -38,6 +38,9 @@ struct MgAttnSmem {
   float m[MG_WARPS][MG_HW], l[MG_WARPS][MG_HW];
   float acc[MG_WARPS][MG_HW][MG_HD];
   __nv_bfloat16 knew[MG_HD], vnew[MG_HD];
+  // K rows of the block a warp pair works on: loaded row-contiguous (coalesced), read one row per lane; the 16-byte
+  // pad per row spreads the rows of a quarter warp over all banks
+  __align__(16) __nv_bfloat16 kst[MG_WARPS / 2][32][MG_HD + 8];
 };
 
 struct MgCtx {

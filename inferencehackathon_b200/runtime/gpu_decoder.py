@@ -212,7 +212,7 @@ class GpuDecoder:
         ngrp = (self.nq // self.nkv + 7) // 8
         sms = torch.cuda.get_device_properties(dev).multi_processor_count
         a.max_split = env_flag("IHB_MEGA_SPLITS", max(1, min(64, sms // (self.nkv * ngrp))))
-        self.mega_attn_part = torch.zeros(self.nq * a.max_split * 130, **f32)
+        self.mega_attn_part = torch.zeros(self.nq * a.max_split * 132, **f32)
         self.mega_act = torch.zeros(m.top_k * 2 * self.I, **f32)
         self.mega_bar = torch.zeros(8 + self.nkv * ngrp, dtype=torch.int32, device=dev)
         a.qkv, a.attn_part, a.attn, a.act = (self.qkv.data_ptr(), self.mega_attn_part.data_ptr(), self.attn.data_ptr(),
