@@ -20,8 +20,8 @@
 
 namespace ihb {
 
-constexpr int MG_THREADS = 256;
-constexpr int MG_WARPS = 8;
+constexpr int MG_THREADS = 512;
+constexpr int MG_WARPS = 16;
 constexpr int MG_HD = 128;
 constexpr int MG_GQ = 8;                 // query heads per attention work item
 #ifndef MG_INT_CVT
@@ -29,8 +29,10 @@ constexpr int MG_GQ = 8;                 // query heads per attention work item
 #endif
 constexpr int MG_REC = MG_HD + 4;        // attention partial record: acc[128], m, l, 2 pad (16-byte multiple)
 
-constexpr int MG_HW = 4;                 // query heads per warp: a warp pair shares a block of 32 positions
-constexpr int MG_ABLK = (MG_WARPS / 2) * 32;   // positions per CTA round
+constexpr int MG_NPB = 4;                // blocks of 32 positions per CTA round
+constexpr int MG_WPB = MG_WARPS / MG_NPB;      // warps sharing a block; each takes MG_HW of the 8 query heads
+constexpr int MG_HW = MG_GQ / MG_WPB;
+constexpr int MG_ABLK = MG_NPB * 32;           // positions per CTA round
 
 struct MgAttnSmem {
   float q[MG_GQ][MG_HD];
@@ -40,7 +42,7 @@ struct MgAttnSmem {
   __nv_bfloat16 knew[MG_HD], vnew[MG_HD];
   // K rows of the block a warp pair works on: loaded row-contiguous (coalesced), read one row per lane; the 16-byte
   // pad per row spreads the rows of a quarter warp over all banks
-  __align__(16) __nv_bfloat16 kst[MG_WARPS / 2][32][MG_HD + 8];
+  __align__(16) __nv_bfloat16 kst[MG_NPB][32][MG_HD + 8];
 };
 
 struct MgCtx {
