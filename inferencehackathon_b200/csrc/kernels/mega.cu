@@ -24,9 +24,6 @@ constexpr int MG_THREADS = 512;
 constexpr int MG_WARPS = 16;
 constexpr int MG_HD = 128;
 constexpr int MG_GQ = 8;                 // query heads per attention work item
-#ifndef MG_INT_CVT
-#define MG_INT_CVT 0
-#endif
 constexpr int MG_REC = MG_HD + 4;        // attention partial record: acc[128], m, l, 2 pad (16-byte multiple)
 
 constexpr int MG_NPB = 4;                // blocks of 32 positions per CTA round
@@ -121,7 +118,10 @@ __device__ __forceinline__ void mg_barrier(const IhbMegaArgs& a, MgCtx& c, bool 
   if (threadIdx.x == 0 && c.flags[0] == 0) {
     bool ok = true;
     if (cross && a.comm.nranks > 1) {
-      __threadfence_system();
+      // release at system scope: the CTA's pushes (ordered before thread 0 by the barrier above) become visible to
+      // whoever acquires the counter; an acq_rel fence is enough here and cheaper than the sequentially consistent
+      // one __threadfence_system() issues
+      asm volatile("fence.acq_rel.sys;" ::: "memory");
       mg_arrive_all(a.comm, 1u);
       ok = mg_wait_sys(a.comm.flag_local, (c.epoch + 1u) * static_cast<unsigned>(a.comm.nranks) * gridDim.x, a.err);
     } else {
@@ -134,6 +134,15 @@ __device__ __forceinline__ void mg_barrier(const IhbMegaArgs& a, MgCtx& c, bool 
   }
   if (cross) c.epoch++;          // every thread keeps the count of cross-GPU rounds (it selects the slot parity)
   __syncthreads();
+}
+
+// Ask L2 for `bytes` at `p` (all CTAs together, one 128-byte line per thread and round): issued right before a
+// cross-GPU barrier, so that the wait for the other GPUs brings the next phase's weights on chip.
+__device__ __forceinline__ void mg_prefetch_l2(const void* p, size_t bytes) {
+  const char* base = reinterpret_cast<const char*>(p);
+  const size_t step = static_cast<size_t>(gridDim.x) * MG_THREADS * 128;
+  for (size_t off = (static_cast<size_t>(blockIdx.x) * MG_THREADS + threadIdx.x) * 128; off < bytes; off += step)
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(base + off));
 }
 
 __device__ __forceinline__ float block_sum(float v, float* red) {
@@ -253,36 +262,11 @@ struct MgSink {
   unsigned long long best;       // ARGMAX: packed running maximum (lane 0 of each warp)
 };
 
-// e4m3 -> fp16 without the conversion pipe: a byte s eeee mmm placed at bits 15..8 of a half and shifted so that its
-// exponent and mantissa land in the fp16 fields reads as the same number times 2^-8 (normals and subnormals alike,
-// exactly). Two bytes per 32-bit register: one byte permute, two logic ops and a shift on the integer pipe, next to
-// the fp16 FMAs.
-__device__ __forceinline__ __half2 e4m3x2_scaled(uint32_t hi_bytes) {
-  const uint32_t t = ((hi_bytes & 0x7f007f00u) >> 1) | (hi_bytes & 0x80008000u);
-  return *reinterpret_cast<const __half2*>(&t);
-}
-// 16 e4m3 weights x 16 fp16 activations; the result is 2^-8 times the true sum (folded into MgCtx::unscale).
-__device__ __forceinline__ float dot16_e4m3_int(uint4 w, uint4 xlo, uint4 xhi) {
-  const __half2* xl = reinterpret_cast<const __half2*>(&xlo);
-  const __half2* xh = reinterpret_cast<const __half2*>(&xhi);
-  __half2 a = __float2half2_rn(0.f), b = a;
-  a = __hfma2(e4m3x2_scaled(__byte_perm(w.x, 0u, 0x1404)), xl[0], a);
-  b = __hfma2(e4m3x2_scaled(__byte_perm(w.x, 0u, 0x3424)), xl[1], b);
-  a = __hfma2(e4m3x2_scaled(__byte_perm(w.y, 0u, 0x1404)), xl[2], a);
-  b = __hfma2(e4m3x2_scaled(__byte_perm(w.y, 0u, 0x3424)), xl[3], b);
-  a = __hfma2(e4m3x2_scaled(__byte_perm(w.z, 0u, 0x1404)), xh[0], a);
-  b = __hfma2(e4m3x2_scaled(__byte_perm(w.z, 0u, 0x3424)), xh[1], b);
-  a = __hfma2(e4m3x2_scaled(__byte_perm(w.w, 0u, 0x1404)), xh[2], a);
-  b = __hfma2(e4m3x2_scaled(__byte_perm(w.w, 0u, 0x3424)), xh[3], b);
-  const float2 fa = __half22float2(a), fb = __half22float2(b);
-  return (fa.x + fa.y) + (fb.x + fb.y);
-}
-
 template <bool FP8>
 __device__ __forceinline__ float mg_chunk_dot(uint4 w, const __half* xh, const float* xv, int cch) {
   if (FP8) {
     const uint4* x = reinterpret_cast<const uint4*>(xh + 16 * cch);
-    return (MG_INT_CVT ? dot16_e4m3_int(w, x[0], x[1]) : dot16_e4m3(w, x[0], x[1]));
+    return dot16_e4m3(w, x[0], x[1]);
   } else {
     const float4* x = reinterpret_cast<const float4*>(xv + 8 * cch);
     return dot8_bf16(w, x[0], x[1]);
@@ -297,7 +281,7 @@ __device__ __forceinline__ void mg_gemv(const IhbMegaArgs& a, const MgCtx& c, co
   const int n = plan.rows, nch = plan.nch, kbs = plan.kbs;
   const __half* xh = c.xh;
   const float* xv = c.xv;
-  const float unscale = FP8 ? c.unscale * (MG_INT_CVT ? 256.f : 1.f) : 1.f;
+  const float unscale = FP8 ? c.unscale : 1.f;
   const bool down = plan.kind == MG_DOWN;
   for (int i0 = first * R; i0 < n; i0 += stride * R) {
     RowBase b[R];
