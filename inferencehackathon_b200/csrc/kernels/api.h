@@ -21,6 +21,7 @@ typedef struct {
   int nranks;
   int rank;
   float* slots_local;                        // [2][nranks * ks][H] fp32 partials, double buffered by epoch parity
+                                             // (persistent kernel: [2][nranks][H] 8-byte {value, round tag} pairs)
   float* slots_mc;
   float* slots_peer[IHB_MAX_RANKS];
   unsigned* flag_local;                      // monotonic arrival counter
@@ -29,7 +30,8 @@ typedef struct {
   unsigned long long* arg_slots_local;       // [2][nranks] packed (value, token) for the sharded head
   unsigned long long* arg_slots_mc;
   unsigned long long* arg_slots_peer[IHB_MAX_RANKS];
-  unsigned* epoch;                           // local: number of collectives completed so far
+  unsigned* epoch;                           // local, 4 words: [0] collectives completed so far, [1] rounds of the
+                                             // arrival counter made by the persistent kernel
 } IhbComm;
 
 typedef struct {

@@ -43,8 +43,9 @@ struct MgAttnSmem {
 };
 
 struct MgCtx {
-  // barrier state: the counters are meaningful in thread 0; epoch (cross-GPU rounds so far) in every thread
-  unsigned base, n_bar, n_prof, epoch;
+  // barrier state: the counters are meaningful in thread 0; epoch (all-reduce rounds so far: slot parity and tag) in
+  // every thread; xr counts the rounds on the cross-GPU arrival counter (one per token: the arg-max exchange)
+  unsigned base, n_bar, n_prof, epoch, xr;
   // shared memory carve-up
   float* resid;          // [H]
   float* xf;             // [H] fp32 normed hidden state (router input)
@@ -54,7 +55,8 @@ struct MgCtx {
   float* red;            // [32] block reductions
   int* sel_e;            // [top_k]
   float* sel_w;          // [top_k]
-  int* flags;            // [0] dead, [1] last-arriver flag of the attention merge, [2] routed experts held by this rank
+  int* flags;            // [0] dead, [1] last-arriver flag of the attention merge, [2] routed experts held by this rank,
+                         // [3] tag of the all-reduce round being pushed
   MgAttnSmem* attn;
 };
 
@@ -110,30 +112,58 @@ __device__ __forceinline__ void mg_arrive_all(const IhbComm& cm, unsigned count)
 }
 
 // Grid-wide barrier: one fire-and-forget release-add per CTA, then a spin on the same counter.
-// cross = true (several GPUs): every CTA of every rank arrives directly on every GPU's counter - its partials were
-// pushed before, the release orders them - and waits until all ranks x CTAs of this round are in: one NVLink round
-// trip, no local hop before or after it. The counter advances by nranks * gridDim.x per cross-GPU round.
-__device__ __forceinline__ void mg_barrier(const IhbMegaArgs& a, MgCtx& c, bool cross) {
+__device__ __forceinline__ void mg_barrier(const IhbMegaArgs& a, MgCtx& c) {
   __syncthreads();
   if (threadIdx.x == 0 && c.flags[0] == 0) {
-    bool ok = true;
-    if (cross && a.comm.nranks > 1) {
-      // release at system scope: the CTA's pushes (ordered before thread 0 by the barrier above) become visible to
-      // whoever acquires the counter; an acq_rel fence is enough here and cheaper than the sequentially consistent
-      // one __threadfence_system() issues
-      asm volatile("fence.acq_rel.sys;" ::: "memory");
-      mg_arrive_all(a.comm, 1u);
-      ok = mg_wait_sys(a.comm.flag_local, (c.epoch + 1u) * static_cast<unsigned>(a.comm.nranks) * gridDim.x, a.err);
-    } else {
-      c.n_bar++;
-      red_release_gpu_add_u32(a.bar + 0, 1u);
-      ok = mg_wait(a.bar + 0, c.base + c.n_bar * gridDim.x, a.err);
-    }
-    if (!ok) c.flags[0] = 1;
+    c.n_bar++;
+    red_release_gpu_add_u32(a.bar + 0, 1u);
+    if (!mg_wait(a.bar + 0, c.base + c.n_bar * gridDim.x, a.err)) c.flags[0] = 1;
     if (a.prof != nullptr && blockIdx.x == 0) a.prof[++c.n_prof] = globaltimer_ns();
   }
-  if (cross) c.epoch++;          // every thread keeps the count of cross-GPU rounds (it selects the slot parity)
   __syncthreads();
+}
+
+// ---- all-reduce without a barrier: tagged slots ----------------------------------------------------------------------------------
+// A partial sum travels as ONE 8-byte store {fp32 value, round tag}: a store of 8 aligned bytes arrives whole, so a
+// reader that sees the tag of the round it waits for has the value too, and no fence, arrival counter or barrier is
+// needed: the all-reduce costs one one-way trip through NVSwitch. Slots are [parity][rank][H] pairs; the round
+// number (never 0, never reused while a slot of that parity can still hold it) is the tag. A slot of round n can be
+// overwritten (round n + 2) only by a CTA that has read ALL of round n + 1, which every CTA of every rank pushed
+// after it had read round n, so two parities are enough.
+__device__ __forceinline__ ulonglong2 ld_relaxed_sys_v2_u64(const unsigned long long* p) {
+  ulonglong2 v;
+  asm volatile("ld.relaxed.sys.global.v2.u64 {%0,%1}, [%2];" : "=l"(v.x), "=l"(v.y) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void mg_push(const IhbComm& cm, size_t off, float y, unsigned tag) {
+  const unsigned long long v = (static_cast<unsigned long long>(tag) << 32) | __float_as_uint(y);
+  unsigned long long* local = reinterpret_cast<unsigned long long*>(cm.slots_local) + off;
+  if (cm.nranks == 1) {
+    st_relaxed_sys_u64(local, v);
+  } else if (cm.slots_mc != nullptr) {
+    multimem_st_u64(reinterpret_cast<unsigned long long*>(cm.slots_mc) + off, v);
+  } else {
+    for (int p = 0; p < cm.nranks; ++p) st_relaxed_sys_u64(reinterpret_cast<unsigned long long*>(cm.slots_peer[p]) + off, v);
+  }
+}
+__device__ __forceinline__ bool mg_tagged(const ulonglong2 (&p)[2], unsigned tag) {
+  return static_cast<unsigned>(p[0].x >> 32) == tag && static_cast<unsigned>(p[0].y >> 32) == tag &&
+         static_cast<unsigned>(p[1].x >> 32) == tag && static_cast<unsigned>(p[1].y >> 32) == tag;
+}
+// Re-reads four slots until all carry `tag` (bounded; a set error word ends the wait).
+__device__ __forceinline__ bool mg_settle(const unsigned long long* q, ulonglong2 (&p)[2], unsigned tag, unsigned* err) {
+  if (mg_tagged(p, tag)) return true;
+  const unsigned long long t0 = globaltimer_ns();
+  unsigned spins = 0;
+  for (;;) {
+    p[0] = ld_relaxed_sys_v2_u64(q);
+    p[1] = ld_relaxed_sys_v2_u64(q + 2);
+    if (mg_tagged(p, tag)) return true;
+    if ((++spins & 63u) == 0u) {
+      if (ld_cg_u(err) != 0u) return false;
+      if (globaltimer_ns() - t0 > IHB_PEER_WAIT_NS) { set_error(err, ERR_PEER_BARRIER_TIMEOUT); return false; }
+    }
+  }
 }
 
 // Ask L2 for `bytes` at `p` (all CTAs together, one 128-byte line per thread and round): issued right before a
@@ -193,28 +223,82 @@ __device__ __forceinline__ void mg_stage(MgCtx& c, int n, F f) {
   __syncthreads();
 }
 
-// resid (+= the all-reduce slots of `parity`, in rank order) -> RMSNorm(gamma) -> xf (fp32) and the staged GEMV input.
-template <bool FP8>
-__device__ __forceinline__ void mg_residual_norm(const IhbMegaArgs& a, MgCtx& c, bool add_slots, int parity,
-                                                 const float* gamma, float scale = 1.f) {
-  const int H = a.H;
-  const int nr = a.comm.nranks;
-  float ss = 0.f;
-  for (int i = threadIdx.x * 4; i < H; i += MG_THREADS * 4) {
-    float4 v = *reinterpret_cast<float4*>(c.resid + i);
-    if (add_slots) {
-      const float* sl = a.comm.slots_local + static_cast<size_t>(parity) * nr * H + i;
-      float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
-      for (int r = 0; r < nr; ++r) {
-        const float4 p = ld_cg_f4(reinterpret_cast<const float4*>(sl + static_cast<size_t>(r) * H));
-        sum.x += p.x; sum.y += p.y; sum.z += p.z; sum.w += p.w;
+// resid += scale * (the all-reduce round `tag`, summed in rank order so that every rank gets the same bits); returns
+// this thread's share of sum(resid^2). ONE thread first polls a sentinel per rank (the slot of the last row, which a
+// rank's GEMV writes in its last wave) while the others sleep at a barrier: 75 000 threads polling L2 would slow the
+// CTAs that are still streaming weights. Then every thread reads its slots (the loads of up to MG_LLB ranks in
+// flight together) and spins only on those that have not landed yet. Kept out of line (scalar arguments only) so
+// that its registers do not weigh on the GEMV loops.
+constexpr int MG_LLB = 4;
+__device__ __noinline__ float mg_reduce_slots(const unsigned long long* base, float* resid, int H, int nr, unsigned tag,
+                                              float scale, unsigned* err, bool live) {
+  if (threadIdx.x == 0 && live) {
+    const unsigned long long t0 = globaltimer_ns();
+    unsigned spins = 0;
+    bool give_up = false;
+    for (int r = 0; r < nr && !give_up; ++r) {
+      const unsigned long long* q = base + static_cast<size_t>(r) * H + (H - 2);
+      while (static_cast<unsigned>(ld_relaxed_sys_v2_u64(q).y >> 32) != tag) {
+        if ((++spins & 63u) == 0u) {
+          if (ld_cg_u(err) != 0u) { give_up = true; break; }
+          if (globaltimer_ns() - t0 > IHB_PEER_WAIT_NS) { set_error(err, ERR_PEER_BARRIER_TIMEOUT); give_up = true; break; }
+        }
       }
-      v.x = fmaf(sum.x, scale, v.x); v.y = fmaf(sum.y, scale, v.y); v.z = fmaf(sum.z, scale, v.z); v.w = fmaf(sum.w, scale, v.w);
-      *reinterpret_cast<float4*>(c.resid + i) = v;
     }
+  }
+  __syncthreads();
+  float ss = 0.f;
+  bool ok = live;
+  for (int i = threadIdx.x * 4; i < H; i += MG_THREADS * 4) {
+    float4 v = *reinterpret_cast<float4*>(resid + i);
+    float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int r0 = 0; r0 < nr; r0 += MG_LLB) {
+      ulonglong2 p[MG_LLB][2];
+#pragma unroll
+      for (int j = 0; j < MG_LLB; ++j) {
+        if (r0 + j < nr) {
+          const unsigned long long* q = base + static_cast<size_t>(r0 + j) * H + i;
+          p[j][0] = ld_relaxed_sys_v2_u64(q);
+          p[j][1] = ld_relaxed_sys_v2_u64(q + 2);
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < MG_LLB; ++j) {
+        if (r0 + j < nr) {
+          if (ok) ok = mg_settle(base + static_cast<size_t>(r0 + j) * H + i, p[j], tag, err);
+          sum.x += __uint_as_float(static_cast<unsigned>(p[j][0].x));
+          sum.y += __uint_as_float(static_cast<unsigned>(p[j][0].y));
+          sum.z += __uint_as_float(static_cast<unsigned>(p[j][1].x));
+          sum.w += __uint_as_float(static_cast<unsigned>(p[j][1].y));
+        }
+      }
+    }
+    v.x = fmaf(sum.x, scale, v.x); v.y = fmaf(sum.y, scale, v.y); v.z = fmaf(sum.z, scale, v.z); v.w = fmaf(sum.w, scale, v.w);
+    *reinterpret_cast<float4*>(resid + i) = v;
     ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
   }
+  return ss;
+}
+
+// resid (+= the all-reduce round pushed last) -> RMSNorm(gamma) -> xf (fp32) and the staged GEMV input.
+template <bool FP8>
+__device__ __forceinline__ void mg_residual_norm(const IhbMegaArgs& a, MgCtx& c, bool add_slots, const float* gamma,
+                                                 float scale = 1.f) {
+  const int H = a.H;
+  float ss = 0.f;
+  if (add_slots) {
+    const unsigned long long* base = reinterpret_cast<const unsigned long long*>(a.comm.slots_local) +
+                                     static_cast<size_t>((c.epoch + 1u) & 1u) * a.comm.nranks * H;
+    // c.epoch: the round that ended with the last push
+    ss = mg_reduce_slots(base, c.resid, H, a.comm.nranks, c.epoch, scale, a.err, c.flags[0] == 0);
+  } else {
+    for (int i = threadIdx.x * 4; i < H; i += MG_THREADS * 4) {
+      const float4 v = *reinterpret_cast<float4*>(c.resid + i);
+      ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+  }
   const float tot = block_sum(ss, c.red);
+  if (add_slots && a.prof != nullptr && blockIdx.x == 0 && threadIdx.x == 0) a.prof[++c.n_prof] = globaltimer_ns();
   const float rinv = rsqrtf(tot / static_cast<float>(H) + a.eps);
   for (int i = threadIdx.x * 4; i < H; i += MG_THREADS * 4) {
     const float4 v = *reinterpret_cast<float4*>(c.resid + i);
@@ -258,7 +342,7 @@ enum { MG_STORE = 0, MG_PUSH = 1, MG_ARGMAX = 2 };
 struct MgSink {
   int kind;
   float* out;                    // STORE: out[i]; ARGMAX: optional logits
-  size_t off;                    // PUSH: slot offset of this rank
+  size_t off;                    // PUSH: slot offset of this rank (the round's tag waits in c.flags[3])
   unsigned long long best;       // ARGMAX: packed running maximum (lane 0 of each warp)
 };
 
@@ -324,7 +408,7 @@ __device__ __forceinline__ void mg_gemv(const IhbMegaArgs& a, const MgCtx& c, co
         if (sink.kind == MG_STORE) {
           sink.out[i] = v;
         } else if (sink.kind == MG_PUSH) {
-          push_partial(a.comm, sink.off + i, v);
+          mg_push(a.comm, sink.off + i, v, static_cast<unsigned>(*reinterpret_cast<volatile int*>(c.flags + 3)));
         } else {
           const unsigned long long pk = pack_max(v, static_cast<unsigned>(i));
           sink.best = pk > sink.best ? pk : sink.best;

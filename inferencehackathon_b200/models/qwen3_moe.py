@@ -141,6 +141,15 @@ class Qwen3MoE:
         self.last_routes: List[RouteRecord] = []
         self.aux_taps: dict = {}
         self.act_mode = None       # "fp8" / "bf16": round activations before every linear layer like the CUDA path
+        # optional replacement of the router: (layer, h, router_w, top_k, renorm) -> (idx, w, logits); a dropped
+        # expert keeps its slot with weight 0 (experiments: confidence-adaptive top-k)
+        self.route_fn = None
+
+    def _route(self, L: int, h: torch.Tensor, lw: LayerWeights):
+        cfg = self.cfg
+        if self.route_fn is not None:
+            return self.route_fn(L, h, lw.router, cfg.top_k, cfg.norm_topk_prob)
+        return route(h, lw.router, cfg.top_k, cfg.norm_topk_prob)
 
     def new_cache(self, max_seq: int, dtype=torch.float32, device=None) -> TorchKV:
         device = device if device is not None else self.w.embed.device
@@ -150,7 +159,7 @@ class Qwen3MoE:
     def _moe(self, L: int, h: torch.Tensor, lw: LayerWeights, record: bool) -> torch.Tensor:
         cfg, par, geom = self.cfg, self.par, self.geom
         if par.ep == 1:
-            idx, w, _ = route(h, lw.router, cfg.top_k, cfg.norm_topk_prob)
+            idx, w, _ = self._route(L, h, lw)
             if record:
                 self.last_routes.append(RouteRecord(L, idx[-1].tolist(), w[-1].tolist()))
             y = _experts_local(h, lw, idx, w, 0, cfg.n_experts, self.act_mode)
@@ -160,7 +169,7 @@ class Qwen3MoE:
         T = h.shape[0]
         home = torch.arange(T, device=h.device) % world
         mine = torch.nonzero(home == rank, as_tuple=True)[0]
-        idx, w, _ = route(h[mine], lw.router, cfg.top_k, cfg.norm_topk_prob)
+        idx, w, _ = self._route(L, h[mine], lw)
         n_el = geom.n_experts_local
         owner = idx // n_el                                                     # [Tm, k]
         flat_tok = mine[:, None].expand_as(idx).reshape(-1)

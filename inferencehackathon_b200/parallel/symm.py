@@ -85,6 +85,6 @@ class SymmetricComm:
     def reset(self, epoch: torch.Tensor) -> None:
         """Bring all ranks back to the initial state (arrival counter and epoch zero); collective."""
         self.barrier_host()
-        self.buf[self.slot_bytes: self.extra_off].zero_()
+        self.buf[: self.extra_off].zero_()          # slots too: tagged slots must not survive an epoch restart
         epoch.zero_()
         self.barrier_host()

@@ -71,7 +71,7 @@ class GpuDecoder:
         self.token_ring = torch.zeros(self.max_seq + 1, **i32)
         self.counters = torch.zeros(8 + self.nq, dtype=torch.int32, device=dev)
         self.err = self._tok_err[1:2]
-        self.epoch = torch.zeros(1, **i32)
+        self.epoch = torch.zeros(4, **i32)          # [0] all-reduce rounds, [1] arrival-counter rounds (persistent kernel)
         self.argmax_partial = torch.zeros(1024, dtype=torch.int64, device=dev)
         self.logits = torch.zeros(max(g.vocab_local, 1), **f32)
         kv_shape = (L, self.nkv, self.max_seq, 128)
@@ -107,7 +107,8 @@ class GpuDecoder:
     # communication block -------------------------------------------------------------------------------------
     def _setup_comm(self) -> None:
         par = self.cfg.parallel
-        nslots = 2 * max(par.world, par.tp, 1) * max(self.ks_o, 1) * self.H
+        # the persistent kernel keeps {value, tag} pairs: two floats per slot
+        nslots = 2 * max(par.world, par.tp, 1) * max(self.ks_o, 2) * self.H
         if par.world == 1:
             self.slots = torch.zeros(nslots, dtype=torch.float32, device=self.device)
             self.symm = None
