@@ -259,7 +259,7 @@ typedef struct {
   const float* k_norm;
   void* k_cache;           // [nkv, max_seq, 128] bf16
   void* v_cache;
-  float* router_logits;    // [E] (written every token: telemetry)
+  float* router_logits;    // [E] {fp32 value, tag} pairs (8 bytes each; zero-initialised)
   int* sel_idx;            // [top_k]
   float* sel_w;            // [top_k]
 } IhbMegaLayer;
@@ -288,14 +288,15 @@ typedef struct {
   int token_ring_size;
   const int* forced;
   const int* n_forced;
-  float* qkv;                   // [(nq + 2 nkv) * 128]
+  float* qkv;                   // [(nq + 2 nkv) * 128] {fp32 value, tag} pairs (8 bytes each; zero-initialised)
   float* attn_part;             // [nq][max_split][132]
-  float* attn;                  // [nq * 128]
-  float* act;                   // [top_k * I]
+  float* attn;                  // [nq * 128] {value, tag} pairs
+  float* act;                   // [top_k * 2 I] {value, tag} pairs
   unsigned long long* argmax_partial;   // [grid]
   unsigned* bar;                // [0] grid-barrier arrivals, [2] their base for the next launch, [8 ...] attention merge counters
   unsigned* err;
-  unsigned long long* prof;     // optional: CTA 0 stores %globaltimer at kernel start ([0]) and after barrier i ([i])
+  unsigned long long* prof;     // optional: CTA 0 stores %globaltimer at kernel start ([0]) and at the end of phase i ([i]);
+                                // from [6 n_layers + 4]: per layer, start of the expert phase, selection done, gate/up done, activations seen
   int max_split;                // attention splits available per (kv head, group of 8 query heads)
   int steps;                    // tokens per launch
   IhbComm comm;

@@ -56,7 +56,7 @@ struct MgCtx {
   int* sel_e;            // [top_k]
   float* sel_w;          // [top_k]
   int* flags;            // [0] dead, [1] last-arriver flag of the attention merge, [2] routed experts held by this rank,
-                         // [3] tag of the all-reduce round being pushed
+                         // [3] tag of the vector being produced (GEMV stores and all-reduce pushes)
   MgAttnSmem* attn;
 };
 
@@ -223,6 +223,81 @@ __device__ __forceinline__ void mg_stage(MgCtx& c, int n, F f) {
   __syncthreads();
 }
 
+// ---- tagged hand-over between phases on one GPU -----------------------------------------------------------------------------------
+// The vectors that one phase writes and the next one reads (QKV, attention output, router logits, expert
+// activations) are kept as {fp32 value, tag} pairs too: the consumer waits on the data, no grid barrier separates
+// the phases of a layer. Where every CTA consumes, one thread per CTA first polls a sentinel (an element written in
+// the producers' last wave), so that idle CTAs do not flood L2 with polls.
+__device__ __forceinline__ unsigned long long mg_pack(float v, unsigned tag) {
+  return (static_cast<unsigned long long>(tag) << 32) | __float_as_uint(v);
+}
+__device__ __forceinline__ void st_relaxed_gpu_u64(unsigned long long* p, unsigned long long v) {
+  asm volatile("st.relaxed.gpu.global.b64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long ld_relaxed_gpu_u64(const unsigned long long* p) {
+  unsigned long long v;
+  asm volatile("ld.relaxed.gpu.global.b64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+// Bounded wait until *p carries `tag`; returns the value (whatever is there after a time-out or a set error word).
+__device__ __forceinline__ float mg_ldt(const unsigned long long* p, unsigned tag, unsigned* err) {
+  unsigned long long v = ld_relaxed_gpu_u64(p);
+  if (static_cast<unsigned>(v >> 32) != tag) {
+    const unsigned long long t0 = globaltimer_ns();
+    unsigned spins = 0;
+    for (;;) {
+      v = ld_relaxed_gpu_u64(p);
+      if (static_cast<unsigned>(v >> 32) == tag) break;
+      if ((++spins & 63u) == 0u) {
+        if (ld_cg_u(err) != 0u) break;
+        if (globaltimer_ns() - t0 > IHB_LOCAL_WAIT_NS) { set_error(err, ERR_GRID_COUNTER_TIMEOUT); break; }
+      }
+    }
+  }
+  return __uint_as_float(static_cast<unsigned>(v));
+}
+// Second half of a batched tagged read: `raw` was loaded from p earlier (several such loads in flight together); only
+// a value whose tag has not arrived yet falls back to the bounded wait.
+__device__ __forceinline__ float mg_fix(const unsigned long long* p, unsigned long long raw, unsigned tag, unsigned* err) {
+  if (static_cast<unsigned>(raw >> 32) == tag) return __uint_as_float(static_cast<unsigned>(raw));
+  return mg_ldt(p, tag, err);
+}
+// End of a phase inside a CTA: shared memory may be reused, CTA 0 records its time.
+__device__ __forceinline__ void mg_phase_end(const IhbMegaArgs& a, MgCtx& c) {
+  __syncthreads();
+  if (a.prof != nullptr && blockIdx.x == 0 && threadIdx.x == 0) a.prof[++c.n_prof] = globaltimer_ns();
+}
+
+// mg_stage with U values per thread and round: f(i, v) fills v[u] for index i + u * MG_THREADS (anything past n is
+// ignored), so that a source in global memory can have its U loads in flight together.
+template <bool FP8, int U, typename F>
+__device__ __forceinline__ void mg_stage_batched(MgCtx& c, int n, F f) {
+  float m = 0.f;
+  for (int i = threadIdx.x; i < n; i += MG_THREADS * U) {
+    float v[U];
+    f(i, v);
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int idx = i + u * MG_THREADS;
+      if (idx < n) {
+        if (FP8) { m = fmaxf(m, fabsf(v[u])); c.xh[idx] = __float2half_rn(v[u]); }
+        else c.xv[idx] = v[u];
+      }
+    }
+  }
+  if (FP8) {
+    m = block_max(m, c.red);
+    c.unscale = 1.f;
+    if (m > 8.f) {
+      const int e = static_cast<int>(ceilf(log2f(m * 0.125f)));
+      const __half hs = __float2half_rn(exp2f(static_cast<float>(-e)));
+      c.unscale = exp2f(static_cast<float>(e));
+      for (int i = threadIdx.x; i < n; i += MG_THREADS) c.xh[i] = __hmul(c.xh[i], hs);
+    }
+  }
+  __syncthreads();
+}
+
 // resid += scale * (the all-reduce round `tag`, summed in rank order so that every rank gets the same bits); returns
 // this thread's share of sum(resid^2). ONE thread first polls a sentinel per rank (the slot of the last row, which a
 // rank's GEMV writes in its last wave) while the others sleep at a barrier: 75 000 threads polling L2 would slow the
@@ -341,7 +416,7 @@ __device__ __forceinline__ RowBase mg_row(const MgPlan& pl, int v) {
 enum { MG_STORE = 0, MG_PUSH = 1, MG_ARGMAX = 2 };
 struct MgSink {
   int kind;
-  float* out;                    // STORE: out[i]; ARGMAX: optional logits
+  float* out;                    // STORE: {value, tag} pairs (the tag waits in c.flags[3]); ARGMAX: optional logits
   size_t off;                    // PUSH: slot offset of this rank (the round's tag waits in c.flags[3])
   unsigned long long best;       // ARGMAX: packed running maximum (lane 0 of each warp)
 };
@@ -406,7 +481,8 @@ __device__ __forceinline__ void mg_gemv(const IhbMegaArgs& a, const MgCtx& c, co
       const int i = i0 + j;
       if (lane == 0 && i < n) {
         if (sink.kind == MG_STORE) {
-          sink.out[i] = v;
+          st_relaxed_gpu_u64(reinterpret_cast<unsigned long long*>(sink.out) + i,
+                             mg_pack(v, static_cast<unsigned>(*reinterpret_cast<volatile int*>(c.flags + 3))));
         } else if (sink.kind == MG_PUSH) {
           mg_push(a.comm, sink.off + i, v, static_cast<unsigned>(*reinterpret_cast<volatile int*>(c.flags + 3)));
         } else {

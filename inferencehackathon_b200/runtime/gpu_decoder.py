@@ -181,6 +181,10 @@ class GpuDecoder:
         m, w, dev = self.cfg.model, self.w, self.device
         f32 = dict(dtype=torch.float32, device=dev)
         layers = (K.IhbMegaLayer * len(w.layers))()
+        # vectors handed from one phase to the next are {fp32 value, tag} pairs: two floats per element, zero = no tag
+        self.mega_logits = torch.zeros(max(1, len(w.layers)), 2 * m.n_experts, **f32)
+        self.mega_qkv = torch.zeros(2 * (self.nq + 2 * self.nkv) * 128, **f32)
+        self.mega_attn = torch.zeros(2 * self.nq * 128, **f32)
         for L, lw in enumerate(w.layers):
             e = layers[L]
             e.wqkv, e.wo, e.wgu, e.wd = K.mat_of(lw.wqkv), K.mat_of(lw.wo), K.mat_of(lw.w_gu), K.mat_of(lw.w_d)
@@ -188,7 +192,7 @@ class GpuDecoder:
             e.in_ln, e.post_ln = lw.in_ln.data_ptr(), lw.post_ln.data_ptr()
             e.q_norm, e.k_norm = lw.q_norm.data_ptr(), lw.k_norm.data_ptr()
             e.k_cache, e.v_cache = self.k_cache[L].data_ptr(), self.v_cache[L].data_ptr()
-            e.router_logits = self.router_logits[L].data_ptr()
+            e.router_logits = self.mega_logits[L].data_ptr()
             e.sel_idx, e.sel_w = self.sel_idx[L].data_ptr(), self.sel_w[L].data_ptr()
         if w.layers and w.layers[0].router.dtype != torch.bfloat16:
             raise ValueError("the persistent kernel reads the router matrix as bf16")
@@ -214,10 +218,10 @@ class GpuDecoder:
         sms = torch.cuda.get_device_properties(dev).multi_processor_count
         a.max_split = env_flag("IHB_MEGA_SPLITS", max(1, min(64, sms // (self.nkv * ngrp))))
         self.mega_attn_part = torch.zeros(self.nq * a.max_split * 132, **f32)
-        self.mega_act = torch.zeros(m.top_k * 2 * self.I, **f32)
+        self.mega_act = torch.zeros(2 * m.top_k * 2 * self.I, **f32)
         self.mega_bar = torch.zeros(8 + self.nkv * ngrp, dtype=torch.int32, device=dev)
-        a.qkv, a.attn_part, a.attn, a.act = (self.qkv.data_ptr(), self.mega_attn_part.data_ptr(), self.attn.data_ptr(),
-                                             self.mega_act.data_ptr())
+        a.qkv, a.attn_part, a.attn, a.act = (self.mega_qkv.data_ptr(), self.mega_attn_part.data_ptr(),
+                                             self.mega_attn.data_ptr(), self.mega_act.data_ptr())
         a.argmax_partial, a.bar, a.err = self.argmax_partial.data_ptr(), self.mega_bar.data_ptr(), self.err.data_ptr()
         a.steps = 1
         a.comm = self._comm()
@@ -482,6 +486,10 @@ class GpuDecoder:
         L = len(self.w.layers)
         names = ["qkv", "attention", "o_proj_ar", "norm_router", "gate_up", "down_ar"]
         out = {n: float(d[i:6 * L:6].mean()) for i, n in enumerate(names)} if L else {}
+        if L:
+            sub = t[6 * L + 4: 6 * L + 4 + 4 * L].reshape(L, 4)
+            out["expert_select"] = float((sub[:, 1] - sub[:, 0]).mean() / 1e3)
+            out["gate_up_gemv"] = float((sub[:, 2] - sub[:, 1]).mean() / 1e3)
         out["head"] = float(d[6 * L])
         out["token_update"] = float(d[6 * L + 1])
         out["total"] = float((t[6 * L + 2] - t[0]) / 1e3)
