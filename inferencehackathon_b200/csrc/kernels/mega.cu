@@ -262,8 +262,20 @@ __device__ __forceinline__ float mg_fix(const unsigned long long* p, unsigned lo
   if (static_cast<unsigned>(raw >> 32) == tag) return __uint_as_float(static_cast<unsigned>(raw));
   return mg_ldt(p, tag, err);
 }
+// The layer table lives in global memory; its entry for the NEXT layer is copied into shared memory while the current
+// layer runs, so that no phase starts with a dependent load of a weight pointer from L2.
+__device__ __forceinline__ void mg_fetch_layer(IhbMegaLayer* dst, const IhbMegaLayer* src) {
+  static_assert(sizeof(IhbMegaLayer) % 16 == 0, "layer entries are copied in 16-byte pieces");
+  if (threadIdx.x < sizeof(IhbMegaLayer) / 16)
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(reinterpret_cast<char*>(dst) + 16 * threadIdx.x)),
+                 "l"(reinterpret_cast<const char*>(src) + 16 * threadIdx.x) : "memory");
+  asm volatile("cp.async.commit_group;" ::: "memory");
+}
+__device__ __forceinline__ void mg_fetch_wait() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
 // End of a phase inside a CTA: shared memory may be reused, CTA 0 records its time.
 __device__ __forceinline__ void mg_phase_end(const IhbMegaArgs& a, MgCtx& c) {
+  mg_fetch_wait();
   __syncthreads();
   if (a.prof != nullptr && blockIdx.x == 0 && threadIdx.x == 0) a.prof[++c.n_prof] = globaltimer_ns();
 }
