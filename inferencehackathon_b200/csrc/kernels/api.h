@@ -299,6 +299,7 @@ typedef struct {
                                 // from [6 n_layers + 4]: per layer, start of the expert phase, selection done, gate/up done, activations seen
   int max_split;                // attention splits available per (kv head, group of 8 query heads)
   int steps;                    // tokens per launch
+  int use_logit_barrier;        // 1: grid barrier between router logits and expert selection; 0: selection waits on tagged logits
   IhbComm comm;
 } IhbMegaArgs;
 

@@ -224,6 +224,7 @@ class GpuDecoder:
                                              self.mega_attn.data_ptr(), self.mega_act.data_ptr())
         a.argmax_partial, a.bar, a.err = self.argmax_partial.data_ptr(), self.mega_bar.data_ptr(), self.err.data_ptr()
         a.steps = 1
+        a.use_logit_barrier = env_flag("IHB_MEGA_LOGIT_BARRIER", 1)
         a.comm = self._comm()
         self.mega_prof = None
         if env_flag("IHB_MEGA_PROF", 0):
