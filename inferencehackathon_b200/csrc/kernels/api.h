@@ -238,6 +238,27 @@ int ihb_allreduce_norm(const IhbComm* comm, const float* x, const float* resid, 
                        int H, float* out, float* out_norm, unsigned* counter, unsigned* err, int algo, int grid,
                        cudaStream_t stream);
 
+// ---- all-to-all exchange of rows over peer memory (expert-parallel dispatch / combine for multi-token windows) -----
+// Rows for destination d are pairs offsets[d] .. offsets[d + 1] of `send` (through `gather` when given). Receive region
+// of every rank: [2 parities][nranks sources][cap rows][row_floats]; counts: [2][nranks] ints; flag: one arrival
+// counter, zero before round 0. `round` is the number of exchanges made so far on this region (same on all ranks);
+// all ranks pass the same grid. After the kernel, rows [0, counts[parity][s]) from source s are in place.
+typedef struct {
+  int nranks, rank;
+  int row_floats;                            // multiple of 4
+  int cap;
+  unsigned round;
+  const float* send;
+  const int* gather;                         // optional [P]
+  const int* offsets;                        // device, [nranks + 1]
+  float* recv_peer[IHB_MAX_RANKS];
+  int* count_peer[IHB_MAX_RANKS];
+  unsigned* flag_peer[IHB_MAX_RANKS];
+  unsigned* flag_local;
+  unsigned* err;
+} IhbA2AArgs;
+int ihb_a2a_rows(const IhbA2AArgs* args, int grid, cudaStream_t stream);
+
 // ---- persistent decode megakernel: one cooperative launch runs `steps` whole tokens -------------------------------------
 // One weight matrix (or a stack of per-expert matrices with the same shape): rows contiguous, K-major.
 typedef struct {

@@ -32,6 +32,13 @@ class IhbComm(C.Structure):
                 ("epoch", _vp)]
 
 
+class IhbA2AArgs(C.Structure):
+    _fields_ = [("nranks", C.c_int), ("rank", C.c_int), ("row_floats", C.c_int), ("cap", C.c_int), ("round", C.c_uint),
+                ("send", _vp), ("gather", _vp), ("offsets", _vp),
+                ("recv_peer", _vp * MAX_RANKS), ("count_peer", _vp * MAX_RANKS), ("flag_peer", _vp * MAX_RANKS),
+                ("flag_local", _vp), ("err", _vp)]
+
+
 class IhbGemvArgs(C.Structure):
     _fields_ = [("W", _vp), ("wscale", _vp), ("wtype", C.c_int), ("rows", C.c_int), ("K", C.c_int),
                 ("rb", C.c_int), ("kb_shift", C.c_int), ("nkb", C.c_int),
@@ -158,6 +165,8 @@ def load(build_if_missing: bool = True) -> C.CDLL:
     lib.ihb_qk_norm_rope_rows.restype = C.c_int
     lib.ihb_window_attention.argtypes = [_vp, C.c_int, _vp, _vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _vp, _vp, _vp]
     lib.ihb_window_attention.restype = C.c_int
+    lib.ihb_a2a_rows.argtypes = [C.POINTER(IhbA2AArgs), C.c_int, _vp]
+    lib.ihb_a2a_rows.restype = C.c_int
     lib.ihb_allreduce_norm.argtypes = [C.POINTER(IhbComm), _vp, _vp, _vp, C.c_float, C.c_int, C.c_int, _vp, _vp, _vp, _vp,
                                        C.c_int, C.c_int, _vp]
     lib.ihb_allreduce_norm.restype = C.c_int
@@ -418,6 +427,11 @@ def window_attention(qkv: torch.Tensor, k_cache, v_cache, nq: int, nkv: int, max
     check(load().ihb_window_attention(qkv.data_ptr(), qkv.shape[1], k_cache.data_ptr(), v_cache.data_ptr(), nq, nkv,
                                       max_seq, base, qkv.shape[0], ptr(mask), out.data_ptr(), stream_ptr()),
           "ihb_window_attention")
+
+
+def a2a_rows(args: IhbA2AArgs, grid: int = 32) -> None:
+    """One all-to-all exchange of rows over peer memory (see ``csrc/kernels/a2a.cu``)."""
+    check(load().ihb_a2a_rows(C.byref(args), grid, stream_ptr()), "ihb_a2a_rows")
 
 
 def allreduce_norm(comm: IhbComm, x: torch.Tensor, out: torch.Tensor, counter: torch.Tensor, err: torch.Tensor,

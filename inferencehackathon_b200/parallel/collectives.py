@@ -95,6 +95,17 @@ class Collectives:
         world = self.par.world
         if world == 1:
             return rows, list(send_counts)
+        fast = getattr(self, "fast_a2a", None)
+        if fast is not None and rows.is_cuda and rows.dtype == torch.float32 and rows.dim() == 2 \
+                and rows.shape[1] <= fast.row_floats:
+            # one kernel over peer memory (parallel/a2a.py); narrower rows are padded to the region's row width. The
+            # choice depends only on properties that are the same on every rank (a count above the capacity raises).
+            self.n_collectives += 1
+            width = rows.shape[1]
+            if width < fast.row_floats:
+                rows = torch.nn.functional.pad(rows, (0, fast.row_floats - width))
+            out, counts = fast.exchange(rows, send_counts)
+            return (out[:, :width].contiguous() if width < fast.row_floats else out), counts
         self.n_collectives += 2
         sc = torch.tensor(send_counts, dtype=torch.int64, device=rows.device)
         rc = torch.empty(world, dtype=torch.int64, device=rows.device)
