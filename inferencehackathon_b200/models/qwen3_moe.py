@@ -179,13 +179,16 @@ class Qwen3MoE:
         # dispatch: hidden row, expert id and weight travel together (2 extra fp32 columns)
         payload = torch.cat([h[flat_tok[order]].float(), flat_idx[order, None].float(),
                              flat_w[order, None].float()], dim=1)
-        recv, recv_counts = self.comm.all_to_all_rows(payload, send_counts)
+        # the peer-memory exchange holds at most `cap` rows per (source, destination): decided from T, which every rank knows
+        fast = getattr(self.comm, "fast_a2a", None)
+        allow = fast is not None and -(-T // world) * cfg.top_k <= fast.cap
+        recv, recv_counts = self.comm.all_to_all_rows(payload, send_counts, allow)
         rh, ridx, rw = recv[:, :-2], recv[:, -2].long(), recv[:, -1]
         yo = torch.zeros(rh.shape[0], cfg.hidden, dtype=torch.float32, device=h.device)
         if rh.shape[0]:
             yo = _experts_local(rh, lw, ridx[:, None], rw[:, None], geom.expert0, n_el, self.act_mode)
         # combine: rows go back to their home rank in the order they came
-        back, _ = self.comm.all_to_all_rows(yo, recv_counts)
+        back, _ = self.comm.all_to_all_rows(yo, recv_counts, allow)
         y_mine = torch.zeros(mine.shape[0], cfg.hidden, dtype=torch.float32, device=h.device)
         if back.shape[0]:
             slot_of = torch.arange(mine.shape[0], device=h.device)[:, None].expand_as(idx).reshape(-1)[order]

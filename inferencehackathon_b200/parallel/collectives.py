@@ -89,14 +89,15 @@ class Collectives:
         return best, cand.min(dim=0).values.long()
 
     # expert parallel ---------------------------------------------------------------------------------------
-    def all_to_all_rows(self, rows: torch.Tensor, send_counts: List[int]) -> Tuple[torch.Tensor, List[int]]:
+    def all_to_all_rows(self, rows: torch.Tensor, send_counts: List[int], allow_fast: bool = True) -> Tuple[torch.Tensor, List[int]]:
         """Variable-size row exchange: ``rows`` is ordered by destination rank with ``send_counts[d]`` rows for
-        rank ``d``. Returns the received rows ordered by source rank and the per-source counts."""
+        rank ``d``. Returns the received rows ordered by source rank and the per-source counts. ``allow_fast`` must be
+        the same on every rank (it selects the peer-memory kernel when one is installed)."""
         world = self.par.world
         if world == 1:
             return rows, list(send_counts)
         fast = getattr(self, "fast_a2a", None)
-        if fast is not None and rows.is_cuda and rows.dtype == torch.float32 and rows.dim() == 2 \
+        if fast is not None and allow_fast and rows.is_cuda and rows.dtype == torch.float32 and rows.dim() == 2 \
                 and rows.shape[1] <= fast.row_floats:
             # one kernel over peer memory (parallel/a2a.py); narrower rows are padded to the region's row width. The
             # choice depends only on properties that are the same on every rank (a count above the capacity raises).

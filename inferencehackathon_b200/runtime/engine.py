@@ -14,7 +14,7 @@ from typing import Callable, List, Optional, Sequence
 
 import torch
 
-from ..config import EngineConfig, ModelConfig, ParallelConfig, QuantConfig, get_model_config
+from ..config import EngineConfig, ModelConfig, ParallelConfig, QuantConfig, env_flag, get_model_config
 from ..models.qwen3_moe import Qwen3MoE, RouteRecord
 from ..models.weights import ModelWeights, random_sharded_weights, random_state_dict, shard_state_dict
 from ..parallel.collectives import Collectives
@@ -85,6 +85,13 @@ class InferenceEngine:
             self.cache = None
         else:
             self.cache = self.model.new_cache(cfg.max_seq, kv_dtype, self.device)
+        # expert parallel on GPUs: multi-token windows exchange rows through peer memory (one kernel per exchange)
+        par = cfg.parallel
+        if self.device.type == "cuda" and par.ep > 1 and par.world > 1 and env_flag("IHB_A2A", 1):
+            from ..parallel.a2a import PeerRowExchange
+            window = min(cfg.max_seq, 1024)
+            self.comm.fast_a2a = PeerRowExchange(self.device, (cfg.model.hidden + 2 + 3) // 4 * 4,
+                                                 -(-window // par.world) * cfg.model.top_k)
         self.sampler = Sampler()
         self._last_token: Optional[int] = None
         self._index = 0

@@ -68,7 +68,7 @@ dist.destroy_process_group()
 def test_peer_row_exchange_matches_nccl_all_to_all():
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
-    env = dict(os.environ, IHB_ROOT=ROOT, NCCL_NVLS_ENABLE="0")
+    env = dict(os.environ, IHB_ROOT=ROOT, NCCL_NVLS_ENABLE="0", IHB_A2A="0")      # the test installs the exchange itself
     with tempfile.NamedTemporaryFile("w", suffix=".py", delete=False) as f:
         f.write(WORKER)
         path = f.name
