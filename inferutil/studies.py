@@ -129,12 +129,14 @@ class Terms:
         return 1000.0 / self.tpot_ms
 
 
-B200_MEASURED_START = Terms(overhead=4.3, comms=1.9, weight=0.42, kv=0.02)   # 6.64 ms: 8 GPUs, persistent kernel
+B200_MEASURED_START = Terms(overhead=3.77, comms=1.22, weight=0.42, kv=0.02)   # 5.43 ms: 8 GPUs, persistent kernel
+# (comms: 94 layers x 13 us that the two all-reduces cost beyond the same phases on one GPU; weight: bytes at the
+# measured copy bandwidth; overhead: the rest, i.e. phase latencies)
 
 DEFAULT_RUNGS: List[Tuple[str, Dict[str, float]]] = [
-    ("tagged-slot all-reduce (one one-way trip per collective)", {"comms": 0.55}),
-    ("data-driven phase hand-over instead of grid barriers", {"overhead": 3.2}),
-    ("two layers' dense weights staged in L2 ahead of use", {"overhead": 2.4}),
+    ("attention merge and logits handed over as tagged values too (no barrier, no atomics)", {"overhead": 3.3}),
+    ("skew between GPUs absorbed by prefetching two phases ahead", {"comms": 0.8}),
+    ("dense weights of the next layer staged in L2 during the expert phase", {"overhead": 2.6}),
     ("fp4 expert weights", {"weight": 0.27}),
     ("speculative decoding, tau 2.5 at verify cost 1.25", {"spec": 2.0}),
 ]
@@ -197,7 +199,7 @@ def predict_matrix(efficiency: float = 0.46, gpu: str = "B200-SXM-180GB", collec
 
 # ---- speculative decoding: unified predictor and tree-shape search ------------------------------------------------------------------
 def spec_predict(floor: float, alpha: float, width: int, depth: int, layout: str = "tp", n_ranks: int = 8,
-                 draft_ms_per_step: float = 0.0, decode_step_ms: float = 6.6, temperature: float = 0.0,
+                 draft_ms_per_step: float = 0.0, decode_step_ms: float = 5.43, temperature: float = 0.0,
                  overlap: float = 0.0, n_experts: int = 128, top_k: int = 8) -> dict:
     """speedup = E[emitted] / (verify cost + draft cost). Sampling lowers acceptance (about 0.8x at temperature
     0.7); on expert parallelism the busiest-rank factor of the expert term falls toward 1 as the union fills."""
@@ -349,7 +351,7 @@ def main(argv=None) -> int:
     s = sub.add_parser("floor", help="back the floor share out of (k, tau, S) triples")
     s.add_argument("triples", nargs="+", help="k:tau:S")
     s = sub.add_parser("reconcile", help="which per-collective latency fits the measured step time")
-    s.add_argument("--tpot-ms", type=float, default=6.64)
+    s.add_argument("--tpot-ms", type=float, default=5.43)
     s.add_argument("--collectives", type=int, default=188)
     s.add_argument("--weight-floor-ms", type=float, default=0.42)
     s.add_argument("--efficiency", type=float, default=0.45)

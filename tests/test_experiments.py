@@ -170,7 +170,7 @@ def test_union_reconcile_ladder_and_tree():
     rows = studies.comms_reconcile(11.67, 188, 1.56, 0.19, [5, 16, 35, 60])
     assert [r["consistent"] for r in rows] == [True, True, False, False]
     lad = studies.ladder()
-    assert lad[0]["tok_s"] == pytest.approx(1000.0 / 6.64) and all(b["tok_s"] > a["tok_s"] for a, b in zip(lad, lad[1:]))
+    assert lad[0]["tok_s"] == pytest.approx(1000.0 / 5.43) and all(b["tok_s"] > a["tok_s"] for a, b in zip(lad, lad[1:]))
     hi = studies.tree_optimizer(0.9, 0.7)[0]
     lo = studies.tree_optimizer(0.0, 0.7)[0]
     assert hi["positions"] > lo["positions"]                       # a floor-bound step favours large trees

@@ -190,3 +190,87 @@ def test_rank_that_stops_arriving_gives_the_others_a_status_not_a_hang():
         else:
             assert k.err == "peer barrier time-out" and 4 <= k.epoch <= 5
             assert k.out == [6] * k.epoch
+
+
+# ---- tagged-slot protocol (the persistent kernel's all-reduce and phase hand-over) ----------------------------------------------
+def _run_tagged(n_ranks, n_ctas, rounds, seed, n_parities=2, dead=None, spin_limit=400):
+    """Every (rank, CTA) is an agent. Round n (tag n + 1): the agent pushes ITS element of its rank's partial sum as
+    one {value, tag} store to every GPU - the stores to different GPUs land one at a time, in any order, at any later
+    step - then reads all ranks x CTAs elements of the round from its own GPU, retrying an element until it carries
+    the tag. No counter, no barrier. Returns (agents, violations): a violation is a read that accepted a value of
+    another round."""
+    rng = random.Random(seed)
+    E = n_ctas                                              # elements per rank: one per CTA
+    mem = [[[[(0, None)] * E for _ in range(n_ranks)] for _ in range(n_parities)] for _ in range(n_ranks)]
+    inflight = []                                           # (gpu, parity, rank, elem, tag, value)
+    agents = [dict(r=r, c=c, rnd=0, pc="push", todo=None, acc=0, out=[], err=None, spins=0)
+              for r in range(n_ranks) for c in range(n_ctas)]
+    live = list(range(len(agents)))
+    violations = 0
+    while live or inflight:
+        if inflight and (not live or rng.random() < 0.5):
+            g, p, r, e, tag, val = inflight.pop(rng.randrange(len(inflight)))
+            mem[g][p][r][e] = (tag, val)
+            continue
+        i = rng.choice(live)
+        a = agents[i]
+        if dead is not None and (a["r"], a["c"]) == dead[0] and a["rnd"] >= dead[1] and a["pc"] == "push":
+            live.remove(i)                                   # leaves between rounds with nothing in flight
+            continue
+        tag, par = a["rnd"] + 1, a["rnd"] % n_parities
+        if a["pc"] == "push":
+            for g in range(n_ranks):
+                inflight.append((g, par, a["r"], a["c"], tag, (a["rnd"], a["r"], a["c"])))
+            a["pc"], a["todo"], a["acc"] = "read", [(r, e) for r in range(n_ranks) for e in range(E)], 0
+        else:
+            r, e = a["todo"][0]
+            t, val = mem[a["r"]][par][r][e]
+            if t == tag:
+                if val != (a["rnd"], r, e):
+                    violations += 1
+                a["acc"] += 1
+                a["todo"].pop(0)
+                a["spins"] = 0
+                if not a["todo"]:
+                    a["out"].append(a["acc"])
+                    a["rnd"] += 1
+                    a["pc"] = "push"
+                    if a["rnd"] == rounds:
+                        live.remove(i)
+            else:
+                a["spins"] += 1
+                if a["spins"] > spin_limit:                  # bounded wait: status, not a hang
+                    a["err"] = "tag time-out"
+                    live.remove(i)
+    return agents, violations
+
+
+@pytest.mark.parametrize("n_ranks,n_ctas", [(1, 4), (2, 3), (4, 2), (8, 2)])
+def test_tagged_slots_need_no_barrier_and_two_parities_suffice(n_ranks, n_ctas):
+    for seed in range(10):
+        agents, bad = _run_tagged(n_ranks, n_ctas, rounds=8, seed=seed)
+        assert bad == 0
+        assert all(a["err"] is None and a["out"] == [n_ranks * n_ctas] * 8 for a in agents)
+
+
+def test_tagged_slots_with_one_parity_can_lose_a_round():
+    """With a single slot set a fast agent's store of round n + 1 may land before a slow reader has taken round n:
+    the reader then never sees tag n (a time-out in the model, a wrong wait in the kernel). Two parities exclude it,
+    because a store of round n + 2 needs its author to have read ALL of round n + 1, which every agent pushed only
+    after reading round n."""
+    lost = 0
+    for seed in range(60):
+        agents, bad = _run_tagged(2, 2, rounds=6, seed=seed, n_parities=1, spin_limit=150)
+        assert bad == 0                                      # a tag never validates another round's value
+        lost += any(a["err"] for a in agents)
+    assert lost > 0
+
+
+def test_tagged_slots_dead_agent_gives_status_not_hang():
+    agents, bad = _run_tagged(2, 2, rounds=6, seed=1, dead=((1, 0), 3), spin_limit=120)
+    assert bad == 0
+    for a in agents:
+        if (a["r"], a["c"]) == (1, 0):
+            assert a["rnd"] == 3 and a["err"] is None
+        else:
+            assert a["err"] == "tag time-out" and 3 <= a["rnd"] <= 4
