@@ -103,7 +103,7 @@ def _build_kernels_locked(srcs: List[str], digest: str, verbose: bool) -> str:
         if p.returncode != 0:
             raise RuntimeError("build failed: " + " ".join(cmd) + "\n" + out)
     tmp = KERNEL_LIB + ".tmp"
-    _run([nvcc, "-shared", "-o", tmp] + objs + ["-lcuda"])
+    _run([nvcc, "-shared", "-o", tmp] + objs)          # no driver library: see tc_gemm.cu::encode_tiled_fn
     os.replace(tmp, KERNEL_LIB)                               # readers never see a half-written library
     with open(KERNEL_LIB + ".stamp", "w") as f:
         f.write(digest)
