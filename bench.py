@@ -54,13 +54,9 @@ def reference_arm(args) -> None:
     path = os.path.join(ROOT, "baseline", "_ref", "bin", binary) if binary else None
     if binary is None:
         out["unavailable"] = "the reference engine exists only as a single-GPU and an 8-GPU (TP8) driver"
-        if getattr(gpu, "mega_prof", None) is not None:
-            out["phase_us"] = {k: round(v, 2) for k, v in gpu.mega_phase_us().items()}
         print(json.dumps(out)); return
     if not os.path.exists(path):
         out["unavailable"] = f"baseline/_ref/bin/{binary} not built (run baseline/build_reference.py)"
-        if getattr(gpu, "mega_prof", None) is not None:
-            out["phase_us"] = {k: round(v, 2) for k, v in gpu.mega_phase_us().items()}
         print(json.dumps(out)); return
     env = dict(os.environ)
     try:
@@ -101,8 +97,6 @@ def reference_arm(args) -> None:
             tok_s = max(cands)
     if tok_s is None or r is None or r.returncode != 0:
         out["unavailable"] = "reference driver failed: " + (text.strip().splitlines()[-1][:200] if text.strip() else "no output")
-        if getattr(gpu, "mega_prof", None) is not None:
-            out["phase_us"] = {k: round(v, 2) for k, v in gpu.mega_phase_us().items()}
         print(json.dumps(out)); return
     out.update({"metric": "decode_tok_per_s", "value": tok_s, "unit": "tok/s", "steps": args.steps, "warmup": args.warmup,
                 "ms_per_step": 1000.0 / tok_s, "higher_is_better": True, "scaling": "strong",
