@@ -40,6 +40,10 @@ def parse_args():
     p.add_argument("--distinct-layers", type=int, default=-1, help="-1: as many as fit")
     p.add_argument("--max-seq", type=int, default=0)
     p.add_argument("--no-e2e", action="store_true")
+    p.add_argument("--plan", default="tp", choices=["tp", "ep", "hybrid"],
+                   help="tp: tensor parallel over all GPUs (the headline); ep: experts owned by ranks, attention replicated; "
+                        "hybrid: experts owned by ranks, attention tensor-parallel inside groups of --tp ranks")
+    p.add_argument("--tp", type=int, default=2, help="attention tensor-parallel degree of the hybrid plan")
     return p.parse_args()
 
 
@@ -136,7 +140,11 @@ def main() -> None:
         fit = int(free // per_layer)
         distinct = 0 if fit >= mcfg.n_layers else max(1, fit)
     t0 = time.time()
-    eng = InferenceEngine.build(args.model, tp=world, rank=rank, world=world, weights=args.weights, device=dev,
+    tp, ep = {"tp": (world, 1), "ep": (1, world), "hybrid": (min(args.tp, world), world)}[args.plan]
+    if world == 1:
+        tp, ep = 1, 1
+    par_name = f"tp{world}" if ep == 1 else (f"ep{ep}" if tp == 1 else f"tp{tp}xep{ep}")
+    eng = InferenceEngine.build(args.model, tp=tp, ep=ep, rank=rank, world=world, weights=args.weights, device=dev,
                                 backend="cuda", max_seq=max_seq, n_layers=args.layers, distinct_layers=distinct)
     torch.cuda.synchronize()
     t_init = time.time() - t0
@@ -207,7 +215,7 @@ def main() -> None:
                "scaling": "strong", "vs_baseline": (value / PUBLISHED[world]) if world in PUBLISHED else None,
                "dtype": "fp8" if args.weights == "fp8_block" else "bf16", "data": "synthetic",
                "config": {"model": mcfg.name, "global_batch": 1, "seq_len": args.prompt, "decode_tokens": args.steps,
-                          "parallelism": f"tp{world}", "layers": mcfg.n_layers,
+                          "parallelism": par_name, "layers": mcfg.n_layers,
                           "distinct_layer_weight_sets": distinct or mcfg.n_layers,
                           "l2": "inputs larger than L2 (per-token weight stream >> 126 MB)",
                           "weights": args.weights, "kv": "bf16", "init_s": round(t_init, 1)},
