@@ -297,14 +297,14 @@ class Eagle3Engine:
         emitted, nacc = N.accept_chain(rows, toks, lps, rng.uniforms(depth + 1), cfg.temperature)
         return AcceptedRun(emitted[:-1], emitted[-1], 0), Eagle3RoundStats(nacc, n_drafted, depth, union)
 
-    def step_tree(self, context: Sequence[int], depth: int, branch: int, rng: Rng):
+    def step_tree(self, context: Sequence[int], depth: int, branch: int, rng: Rng, max_nodes: Optional[int] = None):
         ctx = list(context)
         root = ctx[-1] if ctx else 0
 
         def source(prefix, b):
             return [(c.token, c.draft_logprob) for c in self.drafter.source.candidates(ctx, prefix[len(ctx):], b)]
 
-        tree = SpecTree.build_from_source(source, ctx, root, depth, branch)
+        tree = SpecTree.build_from_source(source, ctx, root, depth, branch, max_nodes)
         n_drafted = tree.n_nodes - 1
         if n_drafted == 0:
             return AcceptedRun([], self._fallback(ctx)), Eagle3RoundStats(0, 0, 0, 0)
@@ -471,7 +471,8 @@ class SpecRound:
 class SpecDriver:
     """Stateful speculative decoding on one engine, the hook the serving backend calls once per round:
     ``begin(prompt_tokens)`` after the prompt was prefilled, then ``step(last_token)`` returns the tokens of one
-    round. ``mode``: ``"chain"`` (adaptive depth) or ``"tree"`` (``tree=(depth, branch)``)."""
+    round. ``mode``: ``"chain"`` (adaptive depth) or ``"tree"`` (``tree=(depth, branch)`` or
+    ``(depth, branch, max_candidates)``)."""
 
     def __init__(self, engine, source, *, depth: int = 5, width: int = 4, lam: float = 0.0,
                  floor_fraction: float = 0.86, tree: Optional[Tuple[int, int]] = None, seed: int = 0,
@@ -503,7 +504,8 @@ class SpecDriver:
             self.context.append(int(token))
         ctx = self.context
         if self.tree:
-            run, st = self.eagle.step_tree(ctx, self.tree[0], self.tree[1], self.rng)
+            run, st = self.eagle.step_tree(ctx, self.tree[0], self.tree[1], self.rng,
+                                           self.tree[2] if len(self.tree) > 2 else None)
         else:
             run, st = self.eagle.step(ctx, self.rng)
         toks = run.all_tokens() if (st.n_drafted > 0 or self.tree) else [self.eagle._fallback(ctx)]

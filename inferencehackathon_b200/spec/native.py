@@ -179,17 +179,23 @@ class SpecTree:
         return t
 
     @classmethod
-    def build_from_source(cls, source, ctx: Sequence[int], root_token: int, depth: int, branch: int) -> "SpecTree":
+    def build_from_source(cls, source, ctx: Sequence[int], root_token: int, depth: int, branch: int,
+                          max_nodes: Optional[int] = None) -> "SpecTree":
         """Breadth-first expansion: ``source(prefix_tokens, branch)`` returns ``[(token, logprob), ...]`` for the
-        continuation of ``ctx + path``."""
+        continuation of ``ctx + path``. With ``max_nodes`` the tree is a beam: every level keeps only its
+        ``max_nodes // depth`` best children by cumulative log-probability (e.g. 4 levels x 4 = 16 candidates)."""
         t = cls.root(root_token)
-        frontier = [0]
+        frontier = [(0, 0.0)]
+        keep = max(1, max_nodes // max(1, depth)) if max_nodes else None
         for _ in range(depth):
-            nxt = []
-            for node in frontier:
+            cand = []
+            for node, cum in frontier:
                 for tok, lp in source(list(ctx) + t.path(node), branch):
-                    nxt.append(t.add(node, tok, lp))
-            frontier = nxt
+                    cand.append((cum + float(lp), node, tok, lp))
+            if keep is not None and len(cand) > keep:
+                cand = sorted(cand, key=lambda c: -c[0])[:keep]
+                cand.sort(key=lambda c: c[1])                      # children of one parent stay together
+            frontier = [(t.add(node, tok, lp), cum) for cum, node, tok, lp in cand]
             if not frontier:
                 break
         return t

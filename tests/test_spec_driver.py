@@ -203,3 +203,26 @@ def test_spec_driver_generate_and_serving_hook(tiny):
     assert drv.telemetry.rounds >= 1
     tree = D.SpecDriver(eng, ngram.NGramDrafter(2), tree=(3, 1))
     assert tree.generate(prompt, 24) == plain
+
+
+def test_tree_beam_budget_and_spec_bench_cli(capsys):
+    from inferencehackathon_b200.spec.native import SpecTree
+    import json as _json
+
+    def source(prefix, b):                       # child i of any node: token 10 * depth + i, log-prob -i
+        d = len(prefix) - 3
+        return [(10 * (d + 1) + i, -float(i)) for i in range(b)]
+
+    full = SpecTree.build_from_source(source, [1, 2, 3], 3, 3, 3)
+    assert full.n_nodes - 1 == 3 + 9 + 27
+    beam = SpecTree.build_from_source(source, [1, 2, 3], 3, 4, 4, max_nodes=16)
+    assert beam.n_nodes - 1 == 16                                    # four levels of four
+    assert max(beam.depth(i) for i in range(beam.n_nodes)) == 4
+    # the best path (always child 0) survives at every level
+    assert [beam.tokens[i] for i in range(beam.n_nodes) if beam.depth(i) == 4][0] == 40
+    from inferencehackathon_b200.spec import bench as sb
+    assert sb.main(["--model", "tiny", "--block", "8", "--repeats", "4", "--new-tokens", "12", "--max-candidates", "8",
+                    "--tree", "2x2"]) == 0
+    line = _json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert line["ngram"]["lossless"] and line["eagle_tree"]["lossless"]
+    assert line["ngram"]["forwards_per_token"] <= 1.0 + 1e-9
