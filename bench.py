@@ -44,6 +44,8 @@ def parse_args():
                    help="tp: tensor parallel over all GPUs (the headline); ep: experts owned by ranks, attention replicated; "
                         "hybrid: experts owned by ranks, attention tensor-parallel inside groups of --tp ranks")
     p.add_argument("--tp", type=int, default=2, help="attention tensor-parallel degree of the hybrid plan")
+    p.add_argument("--hot-experts", type=int, default=0, help="skewed routing: scale the router rows of the first N experts")
+    p.add_argument("--hot-scale", type=float, default=4.0)
     return p.parse_args()
 
 
@@ -146,6 +148,13 @@ def main() -> None:
     par_name = f"tp{world}" if ep == 1 else (f"ep{ep}" if tp == 1 else f"tp{tp}xep{ep}")
     eng = InferenceEngine.build(args.model, tp=tp, ep=ep, rank=rank, world=world, weights=args.weights, device=dev,
                                 backend="cuda", max_seq=max_seq, n_layers=args.layers, distinct_layers=distinct)
+    if args.hot_experts > 0:
+        # imbalance run: the same change on every rank (the router is replicated); shared layer sets are scaled once
+        seen = set()
+        for lw in eng.weights.layers:
+            if lw.router.data_ptr() not in seen:
+                seen.add(lw.router.data_ptr())
+                lw.router[: args.hot_experts] *= args.hot_scale
     torch.cuda.synchronize()
     t_init = time.time() - t0
     g = torch.Generator().manual_seed(0)
@@ -218,7 +227,8 @@ def main() -> None:
                           "parallelism": par_name, "layers": mcfg.n_layers,
                           "distinct_layer_weight_sets": distinct or mcfg.n_layers,
                           "l2": "inputs larger than L2 (per-token weight stream >> 126 MB)",
-                          "weights": args.weights, "kv": "bf16", "init_s": round(t_init, 1)},
+                          "weights": args.weights, "kv": "bf16", "init_s": round(t_init, 1),
+                          "router_skew": ({"hot_experts": args.hot_experts, "scale": args.hot_scale} if args.hot_experts else None)},
                "tpot_ms_p50": p50, "tpot_ms_p95": p95, "ttft_ms": ttft * 1e3,
                "ttft_cold_ms": cold * 1e3,
                "ttft_note": ("batched prompt pass on the tensor cores (tcgen05 GEMMs, grouped experts, window attention)"
