@@ -77,16 +77,41 @@ class RouteRecord:
 
 
 class TorchKV:
-    """Contiguous KV cache ``[layers, kv_heads_local, max_seq, hd]`` for the PyTorch path."""
+    """Contiguous KV cache ``[layers, kv_heads_local, max_seq, hd]`` for the PyTorch path. With
+    ``dtype=torch.float8_e4m3fn`` rows are stored as e4m3 with one fp32 scale per (layer, head, position) (amax / 448)
+    and dequantised on read; the reference stores e4m3 with static per-channel scales
+    (kernels/k1_attn_prologue.cu:524-604, kernels/k2_flash_decode.cu:71-83)."""
 
     def __init__(self, n_layers: int, n_kv: int, max_seq: int, hd: int, dtype, device):
         self.k = torch.zeros(n_layers, n_kv, max_seq, hd, dtype=dtype, device=device)
         self.v = torch.zeros_like(self.k)
+        self.fp8 = dtype == torch.float8_e4m3fn
+        if self.fp8:
+            self.k_scale = torch.ones(n_layers, n_kv, max_seq, 1, dtype=torch.float32, device=device)
+            self.v_scale = torch.ones_like(self.k_scale)
         self.len = 0
         self.max_seq = max_seq
 
     def reset(self) -> None:
         self.len = 0
+
+    def write(self, L: int, start: int, k: torch.Tensor, v: torch.Tensor) -> None:
+        """k, v ``[nkv, T, hd]`` -> rows ``start .. start + T`` of layer ``L``."""
+        T = k.shape[1]
+        if not self.fp8:
+            self.k[L, :, start:start + T] = k.to(self.k.dtype)
+            self.v[L, :, start:start + T] = v.to(self.v.dtype)
+            return
+        for buf, sc, x in ((self.k, self.k_scale, k), (self.v, self.v_scale, v)):
+            s = x.float().abs().amax(dim=-1, keepdim=True).clamp_min(1e-12) / 448.0
+            buf[L, :, start:start + T] = (x.float() / s).clamp(-448, 448).to(torch.float8_e4m3fn)
+            sc[L, :, start:start + T] = s
+
+    def read(self, L: int, n: int):
+        """Rows ``0 .. n`` of layer ``L`` as (k, v) in a float type."""
+        if not self.fp8:
+            return self.k[L, :, :n], self.v[L, :, :n]
+        return self.k[L, :, :n].float() * self.k_scale[L, :, :n], self.v[L, :, :n].float() * self.v_scale[L, :, :n]
 
 
 def _attention(q: torch.Tensor, kc: torch.Tensor, vc: torch.Tensor, positions: torch.Tensor,
@@ -233,9 +258,9 @@ class Qwen3MoE:
             v = qkv[:, (nq + nkv) * hd:].reshape(T, nkv, hd)
             q = apply_rope(rmsnorm(q, lw.q_norm, cfg.rms_eps), cos, sin)
             k = apply_rope(rmsnorm(k, lw.k_norm, cfg.rms_eps), cos, sin)
-            cache.k[L, :, start:start + T] = k.permute(1, 0, 2).to(cache.k.dtype)
-            cache.v[L, :, start:start + T] = v.permute(1, 0, 2).to(cache.v.dtype)
-            attn = _attention(q, cache.k[L, :, : start + T], cache.v[L, :, : start + T], positions, tree_mask)
+            cache.write(L, start, k.permute(1, 0, 2), v.permute(1, 0, 2))
+            kc, vc = cache.read(L, start + T)
+            attn = _attention(q, kc, vc, positions, tree_mask)
             o = fake_quant_act(attn, self.act_mode) @ lw.wo.dequant().t()
             x = x + self.comm.all_reduce_tp(o)
             h2 = rmsnorm(x, lw.post_ln, cfg.rms_eps)

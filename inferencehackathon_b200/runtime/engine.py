@@ -77,8 +77,10 @@ class InferenceEngine:
             backend = "cuda" if self.device.type == "cuda" else "torch"
         self.backend = backend
         self.model = Qwen3MoE(weights, self.comm)
-        kv_dtype = {"fp32": torch.float32, "bf16": torch.bfloat16}[cfg.quant.kv]
+        kv_dtype = {"fp32": torch.float32, "bf16": torch.bfloat16, "fp8": torch.float8_e4m3fn}[cfg.quant.kv]
         self.gpu = None
+        if backend == "cuda" and cfg.quant.kv == "fp8":
+            raise NotImplementedError("the CUDA pipelines keep the KV cache in bf16; kv='fp8' exists on the PyTorch path only")
         if backend == "cuda":
             from .gpu_decoder import GpuDecoder            # imports the compiled kernels; fails loudly if absent
             self.gpu = GpuDecoder(cfg, weights, self.comm, self.device)
@@ -185,7 +187,7 @@ class InferenceEngine:
             raise err
         if self.weights.layers and self.weights.layers[0].wqkv.data.device.type == "meta":
             raise RuntimeError("no fallback: the plain weight copies were released for the tiled layout") from err
-        kv_dtype = {"fp32": torch.float32, "bf16": torch.bfloat16}[self.cfg.quant.kv]
+        kv_dtype = {"fp32": torch.float32, "bf16": torch.bfloat16, "fp8": torch.float8_e4m3fn}[self.cfg.quant.kv]
         max_seq = self.gpu.max_seq
         self.gpu = None
         self.backend = "torch"

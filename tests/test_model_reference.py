@@ -55,3 +55,19 @@ def test_fp8_block_weights_close_to_fp32():
     m32, m8 = Qwen3MoE(w32), Qwen3MoE(w8)
     l32, l8 = m32.forward(toks, m32.new_cache(16)), m8.forward(toks, m8.new_cache(16))
     assert torch.nn.functional.cosine_similarity(l32.flatten(), l8.flatten(), dim=0) > 0.98
+
+
+def test_fp8_kv_cache_on_the_pytorch_path_tracks_the_fp32_cache():
+    import torch
+    from inferencehackathon_b200.runtime.engine import InferenceEngine
+    prompt = torch.randint(0, 2048, (24,), generator=torch.Generator().manual_seed(2)).tolist()
+    ref = InferenceEngine.build("tiny", device="cpu", backend="torch", max_seq=64, kv="fp32")
+    q8 = InferenceEngine.build("tiny", device="cpu", backend="torch", max_seq=64, kv="fp8")
+    assert q8.cache.fp8 and q8.cache.k.dtype == torch.float8_e4m3fn
+    la = ref.prefill(prompt, return_logits=True).logits.float()
+    lb = q8.prefill(prompt, return_logits=True).logits.float()
+    scale = float(la.abs().max())
+    assert float((la - lb).abs().max()) < 0.05 * scale            # e4m3 rows: ~2^-4 relative steps, averaged by the softmax
+    a = ref.generate(prompt, 8).tokens
+    b = q8.generate(prompt, 8).tokens
+    assert sum(int(x == y) for x, y in zip(a, b)) >= 6
