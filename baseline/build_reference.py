@@ -24,7 +24,10 @@ def nccl_dirs():
     return os.path.join(base, "include"), os.path.join(base, "lib")
 
 
-def build(reference_root: str = "/root/reference") -> None:
+def build(reference_root: str = "") -> None:
+    reference_root = reference_root or os.environ.get("REFERENCE_ROOT", "")
+    if not os.path.isdir(os.path.join(reference_root, "kernels")) and not os.path.isdir(os.path.join(REF, "kernels")):
+        raise SystemExit("usage: python baseline/build_reference.py <path of the reference checkout> (or REFERENCE_ROOT)")
     os.makedirs(os.path.join(REF, "bin"), exist_ok=True)
     kdir = os.path.join(REF, "kernels")
     if not os.path.isdir(kdir):

@@ -23,7 +23,7 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-# published reference numbers (8xH100 / 1xH100, BASELINE.md): TP8 engine best graphed forward, single-GPU graph step
+# published reference numbers (8xH100 / 1xH100): TP8 engine best graphed forward, single-GPU graph step
 PUBLISHED = {8: 116.1, 1: 30.7}
 
 
