@@ -203,3 +203,12 @@ def test_client_tools_measure_and_roofline_against_the_mock_server():
     s5 = ct.summarize([1.0, 2.0, 3.0, 4.0, 5.0])
     assert s5["p50"] == 3.0 and s5["ci95_lo"] < 3.0 < s5["ci95_hi"] and ct.t95(4) == 2.776
     assert ct.main(["roofline", "--ctx", "1024", "--tpot-ms", "2.5"]) == 0
+
+
+def test_b200_measured_baseline_is_consistent():
+    from inferutil import optimize as O
+    b = O.B200_MEASURED
+    total = b.overhead_ms + b.comms_ms + b.weight_ms + b.kv_ms
+    assert abs(1000.0 / total - O.B200_MEASURED_TOK_S) < 1.0
+    final, steps = O.optimize(b)
+    assert (final.overhead_ms + final.comms_ms + final.weight_ms + final.kv_ms) <= total
