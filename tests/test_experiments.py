@@ -199,3 +199,23 @@ def test_layout_studies_and_monte_carlo():
     a = studies.spec_analyze(100, 180, 300, 200, 5, floor_hint=0.8)
     assert a["tau"] == 2.5 and a["V"] == pytest.approx(2.5 / 1.8) and a["implied_union"] > 8
     assert len(studies.predict_matrix()) == 2 * 3 * 4 and studies.main(["verify-cost"]) == 0
+
+
+def test_window_group_table_covers_every_pair_once():
+    """Host-free bookkeeping of the grouped expert GEMM (pure tensor ops, so it can be checked on the CPU)."""
+    from inferencehackathon_b200.runtime.gpu_window import GpuWindow
+    g = torch.Generator().manual_seed(4)
+    for n_experts, pairs, nt in ((16, 96, 16), (8, 40, 32), (128, 1024, 64), (4, 3, 16)):
+        flat_e = torch.randint(0, n_experts, (pairs,), generator=g)
+        order, groups, n_groups, gmax = GpuWindow._group_table(flat_e, n_experts, nt)
+        ng = int(n_groups[0])
+        assert ng <= gmax and groups.shape == (gmax, 4)
+        covered = torch.zeros(pairs, dtype=torch.int32)
+        sorted_e = flat_e[order]
+        for e, tok0, ntok, _ in groups[:ng].tolist():
+            assert 0 < ntok <= nt
+            assert torch.all(sorted_e[tok0: tok0 + ntok] == e)       # a group holds rows of ONE expert
+            covered[tok0: tok0 + ntok] += 1
+        assert torch.all(covered == 1)                                # every (token, slot) pair exactly once
+        assert torch.all(groups[ng:, 2] == 0)                         # unused entries are empty
+        assert torch.equal(torch.sort(order).values, torch.arange(pairs))
