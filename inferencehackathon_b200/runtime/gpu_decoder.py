@@ -496,6 +496,47 @@ class GpuDecoder:
         out["total"] = float((t[6 * L + 2] - t[0]) / 1e3)
         return out
 
+    def op_table(self, reps: int = 20) -> list:
+        """Per-kernel device times of the per-op pipelines (``IHB_MEGA=0``): every launch of one decode step is
+        bracketed by CUDA events (so launches do not overlap), repeated ``reps`` times. Rows: kernel, launches per
+        token, microseconds per launch, microseconds per token, share. The persistent kernel reports its phases
+        through ``mega_phase_us`` instead. Reference: the in-binary profiler table of
+        kernels/decode_step_tp8.cu:2631-2789. All ranks of a parallel run call this together."""
+        if self.use_mega:
+            raise RuntimeError("one launch per token: use mega_phase_us() (IHB_MEGA_PROF=1)")
+        names = ["embed_norm", "gemv", "tc_decode", "qk_norm_rope_kv", "flash_decode", "moe_gateup", "moe_down"]
+        orig = {n: getattr(K, n) for n in names if hasattr(K, n)}
+        spans = []
+
+        def wrap(name):
+            def f(*a, **kw):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                orig[name](*a, **kw)
+                e1.record()
+                spans.append((name, e0, e1))
+            return f
+
+        state = (self.pos.clone(), self.cur_token.clone())
+        try:
+            for n in orig:
+                setattr(K, n, wrap(n))
+            for _ in range(reps):
+                self._enqueue_step()
+            torch.cuda.synchronize(self.device)
+        finally:
+            for n, fn in orig.items():
+                setattr(K, n, fn)
+            self.pos.copy_(state[0]); self.cur_token.copy_(state[1])
+        agg = {}
+        for name, e0, e1 in spans:
+            t, c = agg.get(name, (0.0, 0))
+            agg[name] = (t + e0.elapsed_time(e1) * 1e3, c + 1)
+        total = sum(t for t, _ in agg.values()) / reps
+        rows = [{"kernel": n, "launches_per_token": c // reps, "us_per_launch": t / c, "us_per_token": t / reps,
+                 "share": (t / reps) / total if total else 0.0} for n, (t, c) in agg.items()]
+        return sorted(rows, key=lambda r: -r["us_per_token"])
+
     def run_steps(self, n: int) -> None:
         """Enqueue ``n`` decode steps without any host synchronisation (benchmark loop)."""
         for _ in range(n):
