@@ -81,3 +81,18 @@ def test_poisoned_error_word_ends_the_waits_and_the_engine_falls_back():
     assert eng.healthy is False and eng.gpu is None and len(eng.failures) == 1
     agree = sum(int(a == b) for a, b in zip(want, got))
     assert agree >= 8, (want, got)
+
+
+@pytest.mark.parametrize("tc", ["1", "0"])
+def test_per_kernel_table_of_the_per_op_pipelines(tc, monkeypatch):
+    """Every launch of a step is timed on the device; the table leaves the decode state untouched."""
+    monkeypatch.setenv("IHB_MEGA", "0")
+    monkeypatch.setenv("IHB_TC", tc)
+    eng = InferenceEngine.build("small", weights="fp8_block", device="cuda:0", backend="cuda", max_seq=128)
+    prompt = _prompt(16)
+    first = eng.generate(prompt, 4).tokens
+    rows = eng.gpu.op_table(3)
+    per_token = sum(r["launches_per_token"] for r in rows)
+    assert per_token == eng.gpu.n_launches_per_step
+    assert all(r["us_per_launch"] > 0 for r in rows) and abs(sum(r["share"] for r in rows) - 1.0) < 1e-6
+    assert eng.generate(prompt, 4).tokens == first
