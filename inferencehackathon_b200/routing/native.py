@@ -6,6 +6,7 @@ Reference counterparts: engine/src/routing/{optimizer,predictor,scheduler,stats,
 from __future__ import annotations
 
 import ctypes as C
+import os
 from dataclasses import dataclass, field
 from typing import Callable, Dict, List, Optional, Sequence, Tuple
 

@@ -7,6 +7,7 @@ sdpa_tree_ref.h and engine/src/spec/{accept,tree,tree_shape,adaptive_verify,proj
 from __future__ import annotations
 
 import ctypes as C
+import os
 from dataclasses import dataclass
 from typing import List, Optional, Sequence, Tuple
 
@@ -21,7 +22,7 @@ def lib() -> C.CDLL:
     """Loads (building if stale) the control-plane library."""
     global _lib
     if _lib is None:
-        path = _build.build_ctrl()
+        path = os.environ.get("IHB_CTRL_LIB") or _build.build_ctrl()      # override: a sanitizer build of the library
         _lib = C.CDLL(path)
         _declare(_lib)
     return _lib
