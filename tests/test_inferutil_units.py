@@ -174,3 +174,92 @@ def test_gpu_registry_and_cluster_aggregates():
     cl = Cluster(B200_SXM, 8)
     assert cl.total_hbm == 8 * B200_SXM.hbm_bytes and cl.aggregate_hbm_bw == pytest.approx(8 * 7.7e12)
     assert H100_SXM.collective_latency_s == pytest.approx(5e-6)
+
+
+# ---- gate ------------------------------------------------------------------------------------------------------------------------------
+class _R:
+    def __init__(self, tok=100.0, ttft=0.5, pct=0.4, quality=None, latency=None):
+        self.decode_tok_per_s, self.ttft_s, self.pct_of_floor, self.quality, self.latency = tok, ttft, pct, quality, latency
+
+
+class _Q:
+    def __init__(self, m):
+        self.match_rate = m
+
+
+def test_threshold_gate_lists_every_failure():
+    ok = gate.evaluate(_R(), gate.Thresholds(min_decode_tok_per_s=90.0, max_ttft_s=1.0, min_pct_of_floor=0.3))
+    assert ok.passed and ok.failures == ()
+    bad = gate.evaluate(_R(), gate.Thresholds(min_decode_tok_per_s=150.0, max_ttft_s=0.1, min_pct_of_floor=0.9))
+    assert not bad.passed and len(bad.failures) == 3
+    assert gate.evaluate(_R(), gate.Thresholds()).passed                      # no thresholds: nothing to fail
+
+
+def test_quality_gate_needs_a_reference():
+    t = gate.Thresholds(min_quality_match=0.95)
+    assert not gate.evaluate(_R(quality=None), t).passed                      # not measured is a failure, not a pass
+    assert gate.evaluate(_R(quality=_Q(0.99)), t).passed and not gate.evaluate(_R(quality=_Q(0.5)), t).passed
+
+
+def test_regression_gate_uses_confidence_intervals_when_present():
+    def lat(vals):
+        return {"throughput_tok_s": S.stat_to_dict(S.summarize(vals))}
+    base = _R(tok=100.0, latency=lat([100.0, 100.5, 99.5, 100.2]))
+    same = _R(tok=99.8, latency=lat([99.8, 100.4, 99.3, 100.1]))
+    worse = _R(tok=90.0, latency=lat([90.0, 90.4, 89.6, 90.1]))
+    assert gate.regression_gate(base, same).passed                            # lower mean but overlapping intervals
+    assert not gate.regression_gate(base, worse).passed
+    assert gate.regression_gate(worse, base).passed                           # an improvement never fails
+    # without intervals (single repeat) the point estimates decide
+    assert not gate.regression_gate(_R(tok=100.0), _R(tok=99.0)).passed and gate.regression_gate(_R(tok=100.0), _R(tok=101.0)).passed
+
+
+# ---- telemetry ---------------------------------------------------------------------------------------------------------------------------
+def test_telemetry_summary_sums_power_over_gpus_and_reports_imbalance():
+    from inferutil.bench.metrics import aggregate_breakdown, summarize_telemetry
+    from inferutil.bench.telemetry import FakeTelemetrySource, GpuSample, NullTelemetry
+    from inferutil.bench.engine import StepBreakdown
+    samples = [GpuSample(0, 0.0, 60.0, 80.0, 40.0, 500.0, 1900.0, 3900.0, 10 ** 9),
+               GpuSample(0, 0.1, 62.0, 90.0, 50.0, 520.0, 1900.0, 3900.0, 10 ** 9),
+               GpuSample(1, 0.0, 70.0, 40.0, 20.0, 300.0, 1900.0, 3900.0, 10 ** 9)]
+    src = FakeTelemetrySource(samples)
+    src.start()
+    t = summarize_telemetry(src.stop(), n_decode_tokens=100, decode_window_s=2.0)
+    assert t.available and t.n_gpus == 2 and t.temp_c_max == 70.0
+    assert t.power_w_mean == pytest.approx(510.0 + 300.0)                      # per-GPU means, then summed
+    assert t.energy_j_per_token == pytest.approx(810.0 * 2.0 / 100)
+    assert t.per_gpu_mean_util == (85.0, 40.0) and t.util_imbalance == pytest.approx(85.0 / 62.5)
+    assert NullTelemetry().stop() == [] and not summarize_telemetry([], 10, 1.0).available
+    b = aggregate_breakdown([StepBreakdown(1.0, 2.0, 3.0, 4.0), None, StepBreakdown(3.0, 2.0, 1.0, 0.0)])
+    assert (b.weight_s, b.kv_s, b.comms_s, b.compute_s) == (2.0, 2.0, 2.0, 2.0) and aggregate_breakdown([None]) is None
+
+
+# ---- mock engine ---------------------------------------------------------------------------------------------------------------------------
+def test_mock_engine_is_seeded_and_scales_with_efficiency():
+    from inferutil.bench.engine import Engine, MockEngine
+    cl = Cluster(H100_SXM, 8)
+    kw = dict(plan="tp", dtype_bytes=1, kv_dtype_bytes=2, tp=8, ep=1, seq_len=640)
+    a, b = MockEngine(QWEN3_235B, cl, jitter=0.1, seed=3), MockEngine(QWEN3_235B, cl, jitter=0.1, seed=3)
+    a.reset(**kw); b.reset(**kw)
+    assert [a.decode_step().seconds for _ in range(5)] == [b.decode_step().seconds for _ in range(5)]
+    half = MockEngine(QWEN3_235B, cl, efficiency=0.5)
+    full = MockEngine(QWEN3_235B, cl)
+    half.reset(**kw); full.reset(**kw)
+    assert half.decode_step().seconds == pytest.approx(2 * full.decode_step().seconds)
+    assert isinstance(full, Engine)                                            # runtime-checkable protocol
+    routed = MockEngine(QWEN3_235B, cl, expose_routes=True)
+    routed.reset(**kw)
+    step = routed.decode_step()
+    assert len(step.routes) == QWEN3_235B.top_k and all(0 <= r.gpu < 8 for r in step.routes)
+    bd = step.breakdown
+    assert bd.weight_s + bd.kv_s + bd.comms_s + bd.compute_s == pytest.approx(step.seconds)
+
+
+def test_manifest_names_commit_model_and_host():
+    from inferutil.bench.manifest import build_manifest, model_hash
+    m = build_manifest(QWEN3_235B, Cluster(B200_SXM, 8), _cfg())
+    text = json.dumps(m)
+    assert model_hash(QWEN3_235B) in text and len(model_hash(QWEN3_235B)) >= 8
+    assert model_hash(QWEN3_235B) != model_hash(dataclasses.replace(QWEN3_235B, n_layers=93))
+    assert {"schema", "runid", "host", "code", "model", "hardware", "bench"} <= set(m)
+    assert "commit" in json.dumps(m["code"]) and m["hardware"] and m["bench"]
