@@ -157,3 +157,27 @@ def test_engine_backend_with_speculative_driver_streams_same_text():
     summ = json.loads(frames[-2])["x_summary"]
     assert summ["spec_enabled"] is True and 0.0 <= summ["spec_accept_rate"] <= 1.0
     assert all("spec" in c["x_telemetry"] for c in spec)
+
+
+def test_metrics_endpoint_counts_tokens_and_speculation():
+    from fastapi.testclient import TestClient
+    from inferencehackathon_b200.serve.app import create_app
+    from inferencehackathon_b200.serve import backends as bk
+    from inferencehackathon_b200.serve.spec_metrics import parse_spec_counters
+    c = TestClient(create_app(bk.MockBackend()))
+    before = c.get("/metrics").text
+    assert "ihb:requests_total 0.0" in before and "# TYPE ihb:generation_tokens_total counter" in before
+    body = {"messages": [{"role": "user", "content": "hello"}], "max_tokens": 12, "temperature": 0.0}
+    frames = [f[6:] for f in c.post("/v1/chat/completions", json=body).text.split("\n\n") if f.startswith("data: ")]
+    n_tokens = sum(1 for f in frames if f != "[DONE]" and "x_telemetry" in f)
+    text = c.get("/metrics").text
+    vals = {l.split()[0]: float(l.split()[1]) for l in text.splitlines() if l and not l.startswith("#")}
+    assert vals["ihb:requests_total"] == 1.0 and vals["ihb:generation_tokens_total"] == float(n_tokens) > 0
+    assert vals["ihb:ttft_seconds_count"] == 1.0 and vals["ihb:ttft_seconds_sum"] > 0 and vals["ihb:backend_healthy"] == 1.0
+    # the scraper written for a vLLM server reads the same counters here
+    spec = parse_spec_counters(text)
+    assert spec["accepted"] == vals["ihb:spec_decode_num_accepted_tokens_total"]
+    assert spec["drafts"] == vals["ihb:spec_decode_num_drafts_total"]
+    # non-streaming requests are counted too
+    c.post("/v1/chat/completions", json=dict(body, stream=False))
+    assert "ihb:requests_total 2.0" in c.get("/metrics").text
