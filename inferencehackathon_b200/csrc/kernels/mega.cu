@@ -4,13 +4,13 @@
 // peer stores) with residual + RMSNorm, the final norm, the vocabulary-sharded head and the cross-rank argmax.
 //
 // Why: at one token a tensor-parallel layer moves only a few MB per GPU, so a chain of separate kernels is bound
-// by launch, prologue and tail latencies, not by bytes. Here the phases of a layer are separated by a grid-wide
-// barrier (one atomic arrival per CTA + a spin on one counter); the residual stream lives in every CTA's shared
-// memory (all CTAs add the same partials in the same order, so the copies stay bitwise identical) and the
+// by launch, prologue and tail latencies, not by bytes. Here a phase hands its result to the next one as tagged
+// values the consumer waits on (one grid-wide barrier per layer is left); the residual stream lives in every CTA's
+// shared memory (all CTAs add the same partials in the same order, so the copies stay bitwise identical) and the
 // activation vector of each GEMV is staged once per CTA in shared memory as pre-scaled fp16.
 //
 // All CTAs must be resident (cooperative launch, one per SM). Every wait is bounded: on a time-out the error word is
-// set, all later barriers fall through and the kernel ends normally.
+// set, all later waits fall through and the kernel ends normally.
 //
 // The reference's persistent kernel (kernels/megakernel_decode.cu:575-649) pays ~16 cooperative grid syncs and
 // NVSHMEM barriers per layer and measured 9-11x slower than its multi-kernel path (docs/path-to-1000.md:32-34).
@@ -166,8 +166,8 @@ __device__ __forceinline__ bool mg_settle(const unsigned long long* q, ulonglong
   }
 }
 
-// Ask L2 for `bytes` at `p` (all CTAs together, one 128-byte line per thread and round): issued right before a
-// cross-GPU barrier, so that the wait for the other GPUs brings the next phase's weights on chip.
+// Ask L2 for `bytes` at `p` (all CTAs together, one 128-byte line per thread and round): issued right before the
+// wait for the other GPUs' slots, so that this wait brings the next phase's weights on chip.
 __device__ __forceinline__ void mg_prefetch_l2(const void* p, size_t bytes) {
   const char* base = reinterpret_cast<const char*>(p);
   const size_t step = static_cast<size_t>(gridDim.x) * MG_THREADS * 128;
@@ -401,7 +401,7 @@ __device__ __forceinline__ void mg_residual_norm(const IhbMegaArgs& a, MgCtx& c,
 // A "virtual row" is a list of 16-byte weight chunks; chunk c multiplies activation elements [EPC c, EPC c + EPC)
 // (EPC = 16 for e4m3, 8 for bf16). A warp takes groups of R consecutive rows and keeps R x U independent 16-byte loads
 // in flight per lane. ONE plan type covers the three matrix layouts and one sink type the three result uses, so the
-// loop is instantiated once per (R, U) and not inlined: the whole kernel has to stay small for the instruction cache.
+// loop is instantiated once per (R, U), force-inlined: the whole kernel has to stay small for the instruction cache.
 //   PLAIN  rows x rowbytes
 //   EXPERT gate/up of the routed experts: virtual row v = slot * rpe + jj (rpe = 2 I rows per expert)
 //   DOWN   output rows over all routing slots: chunk c -> (expert of slot c / nch1, chunk c % nch1 of its row)
