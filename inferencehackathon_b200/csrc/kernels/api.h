@@ -21,7 +21,8 @@ typedef struct {
   int nranks;
   int rank;
   float* slots_local;                        // [2][nranks * ks][H] fp32 partials, double buffered by epoch parity
-                                             // (persistent kernel: [2][nranks][H] 8-byte {value, round tag} pairs)
+                                             // (persistent kernel: [8 round parities][H] 64-bit counted fixed-point
+                                             // sums, zero-initialised)
   float* slots_mc;
   float* slots_peer[IHB_MAX_RANKS];
   unsigned* flag_local;                      // monotonic arrival counter
@@ -310,21 +311,28 @@ typedef struct {
   const int* forced;
   const int* n_forced;
   float* qkv;                   // [(nq + 2 nkv) * 128] {fp32 value, tag} pairs (8 bytes each; zero-initialised)
-  float* attn_part;             // [nq][max_split][132]
-  float* attn;                  // [nq * 128] {value, tag} pairs
+  float* attn_part;             // [nq][max_split][132]: partial records of the long-context attention mode
+  float* attn;                  // [nq * 128] {value, tag} pairs: merged output of the long-context attention mode
+  unsigned long long* attn_rec; // [nq][16][66] 8-byte words: per (head, block of 128 positions) 64 {half2, tag} pairs of the
+                                // normalised partial output, {m, tag}, {l, tag}; merged by the CTAs that stage the
+                                // o_proj input while nq * blocks <= 256 (NULL: always use the long-context mode)
   float* act;                   // [top_k * 2 I] {value, tag} pairs
   unsigned long long* argmax_partial;   // [grid]
   unsigned* bar;                // [0] grid-barrier arrivals, [2] their base for the next launch, [8 ...] attention merge counters
   unsigned* err;
-  unsigned long long* prof;     // optional: CTA 0 stores %globaltimer at kernel start ([0]) and at the end of phase i ([i]);
-                                // from [6 n_layers + 4]: per layer, start of the expert phase, selection done, gate/up done, activations seen
-  int max_split;                // attention splits available per (kv head, group of 8 query heads)
+  unsigned long long* prof;     // optional, 2 * prof_n words: CTA 0 stores %globaltimer at kernel start ([0]) and at the end of
+                                // phase i ([i]); from [6 n_layers + 4]: per layer, start of the expert phase, selection done,
+                                // gate/up done, activations seen. [prof_n + i]: the latest stamp of any CTA for phase i
+                                // (atomic maximum: zero this half before a launch)
+  int prof_n;
+  int max_split;                // attention splits available per (kv head, group of 8 query heads) in the long-context mode
   int steps;                    // tokens per launch
-  int use_logit_barrier;        // 1: grid barrier between router logits and expert selection; 0: selection waits on tagged logits
+  int ar_loopback;              // one rank only: k > 1 makes every all-reduce slot receive k adds (the traffic of k ranks)
   IhbComm comm;
 } IhbMegaArgs;
 
-// grid = 0: one CTA per SM. Returns cudaErrorCooperativeLaunchTooLarge when the CTAs cannot all be resident.
+// grid = 0: one CTA per SM, at most H / 4 (every CTA must own rows of every all-reduce round). Returns
+// cudaErrorCooperativeLaunchTooLarge when the CTAs cannot all be resident.
 int ihb_mega_decode(const IhbMegaArgs* args, int grid, cudaStream_t stream);
 int ihb_mega_max_grid(const IhbMegaArgs* args);
 

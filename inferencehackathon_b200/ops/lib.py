@@ -120,9 +120,9 @@ class IhbMegaArgs(C.Structure):
                 ("embed", _vp), ("embed_is_bf16", C.c_int), ("final_norm", _vp), ("lm_head", IhbMat),
                 ("vocab0", C.c_int), ("logits", _vp), ("cur_token", _vp), ("pos", _vp), ("token_ring", _vp),
                 ("token_ring_size", C.c_int), ("forced", _vp), ("n_forced", _vp),
-                ("qkv", _vp), ("attn_part", _vp), ("attn", _vp), ("act", _vp), ("argmax_partial", _vp),
-                ("bar", _vp), ("err", _vp), ("prof", _vp), ("max_split", C.c_int), ("steps", C.c_int), ("use_logit_barrier", C.c_int),
-                ("comm", IhbComm)]
+                ("qkv", _vp), ("attn_part", _vp), ("attn", _vp), ("attn_rec", _vp), ("act", _vp), ("argmax_partial", _vp),
+                ("bar", _vp), ("err", _vp), ("prof", _vp), ("prof_n", C.c_int), ("max_split", C.c_int), ("steps", C.c_int),
+                ("ar_loopback", C.c_int), ("comm", IhbComm)]
 
 
 def load(build_if_missing: bool = True) -> C.CDLL:

@@ -107,8 +107,8 @@ class GpuDecoder:
     # communication block -------------------------------------------------------------------------------------
     def _setup_comm(self) -> None:
         par = self.cfg.parallel
-        # the persistent kernel keeps {value, tag} pairs: two floats per slot
-        nslots = 2 * max(par.world, par.tp, 1) * max(self.ks_o, 2) * self.H
+        # the persistent kernel keeps 8 round parities of 64-bit slots: 16 floats per hidden channel
+        nslots = max(2 * max(par.world, par.tp, 1) * max(self.ks_o, 2), 16) * self.H
         if par.world == 1:
             self.slots = torch.zeros(nslots, dtype=torch.float32, device=self.device)
             self.symm = None
@@ -222,14 +222,21 @@ class GpuDecoder:
         self.mega_bar = torch.zeros(8 + self.nkv * ngrp, dtype=torch.int32, device=dev)
         a.qkv, a.attn_part, a.attn, a.act = (self.mega_qkv.data_ptr(), self.mega_attn_part.data_ptr(),
                                              self.mega_attn.data_ptr(), self.mega_act.data_ptr())
+        # short contexts on few local heads: per-block partial records merged by the o_proj CTAs (IHB_MEGA_MERGE=0:
+        # always the split-and-merge mode of long contexts)
+        self.mega_attn_rec = torch.zeros(self.nq * 16 * 66, dtype=torch.int64, device=dev)
+        if env_flag("IHB_MEGA_MERGE", 1):
+            a.attn_rec = self.mega_attn_rec.data_ptr()
         a.argmax_partial, a.bar, a.err = self.argmax_partial.data_ptr(), self.mega_bar.data_ptr(), self.err.data_ptr()
         a.steps = 1
-        a.use_logit_barrier = env_flag("IHB_MEGA_LOGIT_BARRIER", 1)
+        # profiling aid on one GPU: every all-reduce slot receives k adds, the traffic of k ranks
+        a.ar_loopback = env_flag("IHB_MEGA_LOOPBACK", 0) if par.world == 1 else 0
         a.comm = self._comm()
         self.mega_prof = None
         if env_flag("IHB_MEGA_PROF", 0):
-            self.mega_prof = torch.zeros(6 * len(w.layers) + 4 + 4096, dtype=torch.int64, device=dev)
-            a.prof = self.mega_prof.data_ptr()
+            self.mega_prof_n = 10 * len(w.layers) + 8
+            self.mega_prof = torch.zeros(2 * self.mega_prof_n + 16 * len(w.layers), dtype=torch.int64, device=dev)
+            a.prof, a.prof_n = self.mega_prof.data_ptr(), self.mega_prof_n
         self.mega = a
         self.mega_grid = min(env_flag("IHB_MEGA_GRID", sms), K.mega_max_grid(a), self.argmax_partial.numel())
         if self.mega_grid < 1:
@@ -368,6 +375,8 @@ class GpuDecoder:
 
     def _step(self) -> None:
         if self.use_mega:
+            if self.mega_prof is not None:
+                self.mega_prof[self.mega_prof_n: 2 * self.mega_prof_n].zero_()          # the latest-CTA stamps are atomic maxima
             K.mega_decode(self.mega, self.mega_grid)
             return
         if not self.use_graph:
@@ -412,6 +421,8 @@ class GpuDecoder:
             self.err.zero_()
             if self.use_mega:
                 self.mega_bar.zero_()          # the grid barrier counters are out of step after an abandoned wait
+                if self.symm is None:
+                    self.slots.zero_()         # so are the contribution counts of the all-reduce slots
             raise RuntimeError(f"device-side wait gave up: {K.ERR_NAMES.get(code, code)}")
 
     def prefill(self, toks: torch.Tensor, sampler, return_logits: bool):
@@ -476,18 +487,25 @@ class GpuDecoder:
         idx, w = self.sel_idx.cpu(), self.sel_w.cpu()
         return [RouteRecord(L, idx[L].tolist(), w[L].tolist()) for L in range(idx.shape[0])]
 
-    def mega_phase_us(self) -> dict:
-        """Per-phase device times (microseconds, from CTA 0's barrier timestamps) of the last token; needs
-        ``IHB_MEGA_PROF=1``. Phases per layer: qkv, attention, o_proj (+ all-reduce), norm + router, gate/up,
-        down (+ all-reduce); then head and token update."""
+    def mega_phase_us(self, which: str = "cta0") -> dict:
+        """Per-phase device times (microseconds) of the last token; needs ``IHB_MEGA_PROF=1``. Phases per layer:
+        qkv, attention, o_proj (+ all-reduce), norm + router, gate/up, down (+ all-reduce); then head and token
+        update. ``which="cta0"``: CTA 0's own stamps; ``which="last"``: the latest stamp of any CTA per phase (the
+        difference between the two tables is the spread between CTAs)."""
         if self.mega_prof is None:
             raise RuntimeError("set IHB_MEGA_PROF=1 before building the engine")
         t = self.mega_prof.cpu().numpy().astype("float64")
+        if which == "last":
+            t0 = t[0]
+            t = t[self.mega_prof_n: 2 * self.mega_prof_n].copy()
+            t[0] = t0
+        else:
+            t = t[: self.mega_prof_n]
         d = (t[1:] - t[:-1]) / 1e3
         L = len(self.w.layers)
         names = ["qkv", "attention", "o_proj_ar", "norm_router", "gate_up", "down_ar"]
         out = {n: float(d[i:6 * L:6].mean()) for i, n in enumerate(names)} if L else {}
-        if L:
+        if L and which != "last":
             sub = t[6 * L + 4: 6 * L + 4 + 4 * L].reshape(L, 4)
             out["expert_select"] = float((sub[:, 1] - sub[:, 0]).mean() / 1e3)
             out["gate_up_gemv"] = float((sub[:, 2] - sub[:, 1]).mean() / 1e3)
@@ -495,6 +513,20 @@ class GpuDecoder:
         out["token_update"] = float(d[6 * L + 1])
         out["total"] = float((t[6 * L + 2] - t[0]) / 1e3)
         return out
+
+    def mega_detail_us(self) -> list:
+        """Detail stamps of the last CTA (it runs the first attention work item), microseconds relative to the
+        first stamp of each layer, averaged over layers 1..; needs ``IHB_MEGA_PROF=1``. Points: 0 item entered,
+        1 q / k / v normed, 2 K / V rows in shared memory, 3 scores + softmax, 4 PV done, 5 record stored, 6 merge
+        staging entered, 7 all {m, l} words seen, 8 weights ready, 9 records combined, 10 staged, 11 o_proj rows
+        pushed, 12 all-reduce read + norm done."""
+        if self.mega_prof is None:
+            raise RuntimeError("set IHB_MEGA_PROF=1 before building the engine")
+        L = len(self.w.layers)
+        t = self.mega_prof.cpu().numpy().astype("float64")[2 * self.mega_prof_n:].reshape(L, 16)
+        t = t[1:] if L > 1 else t
+        rel = (t - t[:, :1]) / 1e3
+        return [round(float(x), 2) for x in rel.mean(axis=0)[:13]]
 
     def op_table(self, reps: int = 20) -> list:
         """Per-kernel device times of the per-op pipelines (``IHB_MEGA=0``): every launch of one decode step is

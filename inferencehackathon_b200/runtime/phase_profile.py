@@ -2,13 +2,16 @@
 tensor-parallel group (``tp > 1``: the all-reduce sums only this rank's partial, so the numbers are timings, not
 numerics; the cross-GPU barrier is not part of them).
 
-    python -m inferencehackathon_b200.runtime.phase_profile LAYERS TP CTX [MODEL] [WEIGHTS]
+    python -m inferencehackathon_b200.runtime.phase_profile LAYERS TP CTX [MODEL] [WEIGHTS] [LOOPBACK]
 
-Prints ``MEGA_PHASES {json}``: microseconds per phase averaged over layers (from CTA 0's %globaltimer stamps after
-every grid barrier) and the CUDA-event time per token.
+Prints ``MEGA_PHASES {json}``: microseconds per phase averaged over layers (CTA 0's %globaltimer stamps, and under
+``last`` the latest stamp of any CTA per phase) and the CUDA-event time per token. ``LOOPBACK`` = k > 1 makes every
+all-reduce slot receive k adds, the slot traffic of k ranks on one GPU.
 """
 import os, sys, json, torch
 os.environ["IHB_MEGA_PROF"] = "1"
+if len(sys.argv) > 6:
+    os.environ["IHB_MEGA_LOOPBACK"] = sys.argv[6]
 from inferencehackathon_b200.config import get_model_config, ParallelConfig, QuantConfig, EngineConfig
 from inferencehackathon_b200.models.weights import random_sharded_weights
 from inferencehackathon_b200.runtime.gpu_decoder import GpuDecoder
@@ -34,6 +37,9 @@ for _ in range(20):
 e1.record(); torch.cuda.synchronize()
 dec.check_error()
 ph = dec.mega_phase_us()
+ph["last"] = dec.mega_phase_us("last")
+ph["detail"] = dec.mega_detail_us()
 ph["ms_per_step_events"] = e0.elapsed_time(e1) / 20
-ph["cfg"] = dict(layers=layers, tp=tp, ctx=ctx, model=model, weights=wts, grid=dec.mega_grid)
+ph["cfg"] = dict(layers=layers, tp=tp, ctx=ctx, model=model, weights=wts, grid=dec.mega_grid,
+                 loopback=int(os.environ.get("IHB_MEGA_LOOPBACK", "0")))
 print("MEGA_PHASES " + json.dumps(ph))
