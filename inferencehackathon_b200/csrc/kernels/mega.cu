@@ -201,11 +201,13 @@ __device__ __forceinline__ void mg_stamp(const IhbMegaArgs& a, int idx) {
   }
 }
 
-// Detail stamps (profiling runs only): thread 0 of the LAST CTA, which runs the first attention work item, records up
-// to 16 points per layer at [2 prof_n + 16 layer + k].
+// Detail stamps (builds with -DIHB_MEGA_DETAIL and profiling runs only: they perturb the code layout): thread 0 of the
+// LAST CTA, which runs the first attention work item, records up to 32 points per layer at [2 prof_n + 32 layer + k].
 __device__ __forceinline__ void mg_detail(const IhbMegaArgs& a, const MgCtx& c, int k) {
+#ifdef IHB_MEGA_DETAIL
   if (a.prof != nullptr && threadIdx.x == 0 && blockIdx.x == gridDim.x - 1)
-    a.prof[2 * a.prof_n + 16 * c.layer + k] = globaltimer_ns();
+    a.prof[2 * a.prof_n + 32 * c.layer + k] = globaltimer_ns();
+#endif
 }
 
 // Grid-wide barrier: one fire-and-forget release-add per CTA, then a spin on the same counter. The two halves can be
@@ -256,6 +258,11 @@ __device__ __forceinline__ void red_relaxed_sys_add_u64(unsigned long long* p, u
 }
 __device__ __forceinline__ void multimem_red_add_u64(unsigned long long* mc, unsigned long long v) {
   asm volatile("multimem.red.relaxed.sys.global.add.u64 [%0], %1;" ::"l"(mc), "l"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long ld_relaxed_sys_u64(const unsigned long long* p) {
+  unsigned long long v;
+  asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
 }
 __device__ __forceinline__ ulonglong2 ld_relaxed_sys_v2_u64(const unsigned long long* p) {
   ulonglong2 v;
@@ -458,6 +465,42 @@ __device__ __forceinline__ void mg_read_tagged(const unsigned long long* const (
   }
 }
 
+// Shape of a GEMV: 0 = 2 rows x 8 rounds, 1 = 1 x 8, 2 = 2 x 4, 3 = 2 x 2 (rows per warp x 16-byte loads per lane and
+// row in flight). Long rows take 8 loads per lane; two rows per warp as soon as a CTA's share of the rows exceeds its
+// 16 warps, so that one round of loads covers the share whenever it can.
+__device__ __forceinline__ int mg_gemv_shape(int nch, int rows) {
+#ifdef MG_ONE_SHAPE
+  return 2;
+#else
+  if (nch > 128) return rows > static_cast<int>(gridDim.x) * MG_WARPS ? 0 : 1;
+  return nch > 64 ? 2 : 3;
+#endif
+}
+__device__ __forceinline__ int mg_gemv_rows_per_warp(int nch, int rows) { return mg_gemv_shape(nch, rows) == 1 ? 1 : 2; }
+// Last row of CTA b's contiguous run of a GEMV over `rows` rows (the run may be empty: then the previous run's end).
+__device__ __forceinline__ int mg_run_end(int nch, int rows, int b) {
+  const int R = mg_gemv_rows_per_warp(nch, rows);
+  const unsigned ngroups = static_cast<unsigned>((rows + R - 1) / R);
+  const int g1 = static_cast<int>(ngroups * static_cast<unsigned>(b + 1) / gridDim.x);
+  return max(0, min(rows, g1 * R) - 1);
+}
+// Warp 0 polls (bounded) the element at the end of every CTA's run until all carry the tag: the producers' rows are
+// then very likely all there, and the batched reads that follow find them at the first attempt. Call with the whole
+// CTA; ends with a CTA barrier.
+__device__ __forceinline__ void mg_wait_runs_tagged(const unsigned long long* vec, int nch, int rows, unsigned tag, unsigned* err, bool live) {
+  if (threadIdx.x < 32 && live) {
+    const int nb = static_cast<int>(gridDim.x);
+    for (int b0 = 0; b0 < nb; b0 += 128) {
+      const unsigned long long* ps[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) ps[u] = vec + mg_run_end(nch, rows, min(b0 + static_cast<int>(threadIdx.x) + 32 * u, nb - 1));
+      unsigned bits[4];
+      mg_read_tagged<4>(ps, bits, tag, err);
+    }
+  }
+  __syncthreads();
+}
+
 // The layer table lives in global memory; its entry for the NEXT layer is copied into shared memory while the current
 // layer runs, so that no phase starts with a dependent load of a weight pointer from L2.
 __device__ __forceinline__ void cp_async16(void* dst, const void* src) {
@@ -503,7 +546,7 @@ __device__ __forceinline__ void mg_stage_batched(MgCtx& c, int n, F f) {
 // only on those that are not complete yet.
 template <bool FP8>
 __device__ __noinline__ float mg_residual_norm_fn(const IhbMegaArgs* ap, unsigned epoch, unsigned ar_n, int add_slots,
-                                                 const float* gamma, float scale, int stamp) {
+                                                 const float* gamma, float scale, int stamp, int push_nch) {
   const IhbMegaArgs& a = *ap;
   MgCtx c;
   mg_ctx_pointers<FP8>(a, c);
@@ -518,13 +561,27 @@ __device__ __noinline__ float mg_residual_norm_fn(const IhbMegaArgs* ap, unsigne
   if (add_slots) {
     // c.epoch - 1: the round that ended with the last push
     base = reinterpret_cast<const unsigned long long*>(a.comm.slots_local) + static_cast<size_t>((c.epoch - 1u) & (MG_NPAR - 1)) * H;
-    if (tid == 0 && ok) {
+    if (tid < 32 && ok) {
+      // sentinels: the slot of the last row of every CTA's run of the H-row GEMV that pushed this round (push_nch
+      // tells its shape); complete there means complete nearly everywhere
+      const int nb = static_cast<int>(gridDim.x);
+      const unsigned long long* ps[8];                       // up to 256 CTAs
+#pragma unroll
+      for (int u = 0; u < 8; ++u) ps[u] = base + mg_run_end(push_nch, H, min(tid + 32 * u, nb - 1));
       const unsigned long long t0 = globaltimer_ns();
       unsigned spins = 0;
-      while (static_cast<unsigned>(ld_relaxed_sys_v2_u64(base + H - 2).y >> 56) != n) {
+      for (;;) {
+        unsigned long long w[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) w[u] = (32 * u < nb) ? ld_relaxed_sys_u64(ps[u]) : 0ull;
+        bool all = true;
+#pragma unroll
+        for (int u = 0; u < 8; ++u) all = all && (32 * u >= nb || static_cast<unsigned>(w[u] >> 56) == n);
+        if (__all_sync(0xffffffffu, all)) break;
         if ((++spins & 63u) == 0u) {
-          if (ld_cg_u(a.err) != 0u) break;
-          if (globaltimer_ns() - t0 > IHB_PEER_WAIT_NS) { set_error(a.err, ERR_PEER_BARRIER_TIMEOUT); break; }
+          bool stop = ld_cg_u(a.err) != 0u;
+          if (!stop && globaltimer_ns() - t0 > IHB_PEER_WAIT_NS) { set_error(a.err, ERR_PEER_BARRIER_TIMEOUT); stop = true; }
+          if (__any_sync(0xffffffffu, stop)) break;
         }
       }
     }
@@ -604,8 +661,8 @@ __device__ __noinline__ float mg_residual_norm_fn(const IhbMegaArgs* ap, unsigne
 }
 template <bool FP8>
 __device__ __forceinline__ void mg_residual_norm(const IhbMegaArgs& a, MgCtx& c, bool add_slots, const float* gamma,
-                                                 float scale, int stamp) {
-  c.unscale = mg_residual_norm_fn<FP8>(&a, c.epoch, c.ar_n, add_slots ? 1 : 0, gamma, scale, stamp);
+                                                 float scale, int stamp, int push_nch) {
+  c.unscale = mg_residual_norm_fn<FP8>(&a, c.epoch, c.ar_n, add_slots ? 1 : 0, gamma, scale, stamp, push_nch);
 }
 
 // ---- GEMV building block ----------------------------------------------------------------------------------------------------
@@ -739,11 +796,16 @@ __device__ __noinline__ unsigned long long mg_gemv_run(const IhbMegaArgs* ap, fl
   const __half* xh = c.xh;
   const float* xv = c.xv;
   const int* flags = c.flags;
-  const int W = gridDim.x * MG_WARPS;
-  if (plan.nch > 128 && plan.rows >= 2 * W) return mg_gemv<FP8, 2, 8>(a, plan, sink, xh, xv, unscale, flags);
-  if (plan.nch > 128) return mg_gemv<FP8, 1, 8>(a, plan, sink, xh, xv, unscale, flags);
-  if (plan.nch > 64 || plan.rows >= 4 * W) return mg_gemv<FP8, 2, 4>(a, plan, sink, xh, xv, unscale, flags);
-  return mg_gemv<FP8, 2, 2>(a, plan, sink, xh, xv, unscale, flags);
+#ifdef MG_ONE_SHAPE
+  return mg_gemv<FP8, 2, 4>(a, plan, sink, xh, xv, unscale, flags);
+#else
+  switch (mg_gemv_shape(plan.nch, plan.rows)) {
+    case 0: return mg_gemv<FP8, 2, 8>(a, plan, sink, xh, xv, unscale, flags);
+    case 1: return mg_gemv<FP8, 1, 8>(a, plan, sink, xh, xv, unscale, flags);
+    case 2: return mg_gemv<FP8, 2, 4>(a, plan, sink, xh, xv, unscale, flags);
+    default: return mg_gemv<FP8, 2, 2>(a, plan, sink, xh, xv, unscale, flags);
+  }
+#endif
 }
 // Publishes the arguments of the next GEMV; a CTA barrier must follow before mg_gemv_run.
 __device__ __forceinline__ void mg_gemv_args(const MgPlan& pl, int sink_kind, float* out, size_t off) {

@@ -19,6 +19,8 @@ CTRL_LIB = os.path.join(HERE, "libihb_ctrl.so")
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
               "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]
+# IHB_BUILD_DEFINES="-DIHB_MEGA_DETAIL" adds the detail time stamps of the persistent kernel (profiling builds)
+NVCC_FLAGS += [f for f in os.environ.get("IHB_BUILD_DEFINES", "").split() if f.startswith("-D")]
 
 
 def _sources(sub: str, exts) -> List[str]:

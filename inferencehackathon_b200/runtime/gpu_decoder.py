@@ -235,7 +235,7 @@ class GpuDecoder:
         self.mega_prof = None
         if env_flag("IHB_MEGA_PROF", 0):
             self.mega_prof_n = 10 * len(w.layers) + 8
-            self.mega_prof = torch.zeros(2 * self.mega_prof_n + 16 * len(w.layers), dtype=torch.int64, device=dev)
+            self.mega_prof = torch.zeros(2 * self.mega_prof_n + 32 * len(w.layers), dtype=torch.int64, device=dev)
             a.prof, a.prof_n = self.mega_prof.data_ptr(), self.mega_prof_n
         self.mega = a
         self.mega_grid = min(env_flag("IHB_MEGA_GRID", sms), K.mega_max_grid(a), self.argmax_partial.numel())
@@ -512,21 +512,26 @@ class GpuDecoder:
         out["head"] = float(d[6 * L])
         out["token_update"] = float(d[6 * L + 1])
         out["total"] = float((t[6 * L + 2] - t[0]) / 1e3)
+        if which != "last" and out["total"] > 0:
+            out["sm_mhz"] = float(t[6 * L + 3] / out["total"])          # SM cycles of the launch / its duration
         return out
 
     def mega_detail_us(self) -> list:
         """Detail stamps of the last CTA (it runs the first attention work item), microseconds relative to the
         first stamp of each layer, averaged over layers 1..; needs ``IHB_MEGA_PROF=1``. Points: 0 item entered,
-        1 q / k / v normed, 2 K / V rows in shared memory, 3 scores + softmax, 4 PV done, 5 record stored, 6 merge
-        staging entered, 7 all {m, l} words seen, 8 weights ready, 9 records combined, 10 staged, 11 o_proj rows
-        pushed, 12 all-reduce read + norm done."""
+        1 q / k / v normed, 2 K / V rows in shared memory, 3 scores, 4 softmax + PV, 5 record stored, 6 merge
+        staging entered, 8 {m, l} words seen, 9 records combined, 10 staged, 11 o_proj rows pushed, 12 all-reduce
+        read + norm done, 13 router logit stored, 14 all logits seen, 15 experts selected, 16 / 17 gate-up GEMV
+        starts / ends, 18 phase end, 19 barrier + slot clearing, 20 activations seen, 21 staged, 22 chunk table,
+        23 down rows pushed; 25 previous layer's all-reduce read + norm done, 26 QKV rows stored (both precede
+        point 0 of the same layer)."""
         if self.mega_prof is None:
             raise RuntimeError("set IHB_MEGA_PROF=1 before building the engine")
         L = len(self.w.layers)
-        t = self.mega_prof.cpu().numpy().astype("float64")[2 * self.mega_prof_n:].reshape(L, 16)
+        t = self.mega_prof.cpu().numpy().astype("float64")[2 * self.mega_prof_n:].reshape(L, 32)
         t = t[1:] if L > 1 else t
         rel = (t - t[:, :1]) / 1e3
-        return [round(float(x), 2) for x in rel.mean(axis=0)[:13]]
+        return [round(float(x), 2) for x in rel.mean(axis=0)[:30]]
 
     def op_table(self, reps: int = 20) -> list:
         """Per-kernel device times of the per-op pipelines (``IHB_MEGA=0``): every launch of one decode step is
