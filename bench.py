@@ -25,6 +25,9 @@ sys.path.insert(0, ROOT)
 
 # published reference numbers (8xH100 / 1xH100): TP8 engine best graphed forward, single-GPU graph step
 PUBLISHED = {8: 116.1, 1: 30.7}
+# the reference's own drivers built for sm_100a and run on this pool's B200s (the same-box rows of the baseline table):
+# `vs_baseline` divides by these; `vs_published` by the H100 figures above
+SAME_BOX = {8: 332.4, 1: 24.6}
 
 
 def parse_args():
@@ -46,6 +49,7 @@ def parse_args():
     p.add_argument("--tp", type=int, default=2, help="attention tensor-parallel degree of the hybrid plan")
     p.add_argument("--hot-experts", type=int, default=0, help="skewed routing: scale the router rows of the first N experts")
     p.add_argument("--hot-scale", type=float, default=4.0)
+    p.add_argument("--gate-layers", type=int, default=2, help="layers of the model the distributed correctness gate runs (0: no gate)")
     return p.parse_args()
 
 
@@ -93,25 +97,102 @@ def reference_arm(args) -> None:
     clocks = cs.stop()
     wall = time.time() - t0
     tok_s = None
-    # decode_step prints "captured graph (replay) <us/token> <tok/s> ..."; decode_step_tp8 prints a tok/s table
+    # the whole output is kept beside the number: it says which line the value came from and which comms path ran
+    try:
+        os.makedirs(os.path.join(ROOT, "gpurun_out"), exist_ok=True)
+        with open(os.path.join(ROOT, "gpurun_out", f"ref{args.gpus}.stdout"), "w") as f:
+            f.write(text)
+    except OSError:
+        pass
+    # decode_step prints "captured graph (replay) <us/token> <tok/s> ..."; decode_step_tp8 prints its measured
+    # graph-replay figure as ">>> BEST graphed path: <name> -> <us> us/token = <tok/s> tok/s" (its other tok/s lines
+    # are the eager step and projections tau / T_forward of speculative decoding, not measured decode)
     m = re.search(r"captured graph \(replay\)\s+([0-9.]+)\s+([0-9.]+)", text)
-    if m:
+    m8 = re.search(r">>> BEST graphed path:\s*(.*?)\s*->\s*([0-9.]+)\s*us/token\s*=\s*([0-9.]+)\s*tok/s", text)
+    ref_path = None
+    if args.gpus == 8 and m8:
+        tok_s = float(m8.group(3))
+        ref_path = m8.group(1)
+    elif args.gpus == 1 and m:
         tok_s = float(m.group(2))
+    if "NVLS unavailable" in text:
+        ref_comms = "nccl (NVLS unavailable at run time)"
+    elif "NVLS disabled at build" in text:
+        ref_comms = "nccl (built with USE_NVLS=0)"
     else:
-        cands = [float(x) for x in re.findall(r"([0-9]+\.[0-9]+)\s*tok/s", text)]
-        if cands:
-            tok_s = max(cands)
+        ref_comms = "nvls multimem all-reduce + cuBLASLt GEMM (the source's defaults USE_NVLS=1, USE_GEMM=1)" if args.gpus == 8 else "none (one GPU)"
     if tok_s is None or r is None or r.returncode != 0:
         out["unavailable"] = "reference driver failed: " + (text.strip().splitlines()[-1][:200] if text.strip() else "no output")
         print(json.dumps(out)); return
     out.update({"metric": "decode_tok_per_s", "value": tok_s, "unit": "tok/s", "steps": args.steps, "warmup": args.warmup,
                 "ms_per_step": 1000.0 / tok_s, "higher_is_better": True, "scaling": "strong",
-                "vs_baseline": tok_s / PUBLISHED[args.gpus] if args.gpus in PUBLISHED else None, "dtype": "fp8",
+                "vs_baseline": tok_s / SAME_BOX[args.gpus] if args.gpus in SAME_BOX else None,
+                "vs_published": tok_s / PUBLISHED[args.gpus] if args.gpus in PUBLISHED else None, "dtype": "fp8",
                 "data": "synthetic (the reference replays one layer of dummy weights 94 times)",
                 "config": {"model": "qwen3-235b-a22b", "global_batch": 1, "seq_len": args.prompt,
-                           "parallelism": f"tp{args.gpus}", "driver": binary, "wall_s": round(wall, 1)},
+                           "parallelism": f"tp{args.gpus}", "driver": binary, "wall_s": round(wall, 1),
+                           "graph_path": ref_path, "comms": ref_comms,
+                           "stdout": f"gpurun_out/ref{args.gpus}.stdout"},
                 "clocks": clocks})
     print(json.dumps(out))
+
+
+def correctness_gate(args, rank: int, world: int, dev, tp: int, ep: int) -> dict:
+    """Distributed correctness before any throughput is printed (the reference gates its TP8 layer against a
+    single-GPU run the same way, kernels/decode_step_tp8.cu:2268-2619, and exits non-zero on a mismatch). A
+    layer-truncated model of the benchmarked architecture runs through the same persistent kernel on all ranks:
+    (1) every rank must produce the same tokens; (2) with bf16 weights (no per-shard quantisation blocks, so the
+    sharded and the unsharded model hold the same numbers) the logits after a prompt replayed token by token must
+    agree with a one-GPU run of the same model within 2 % of their range; (3) the block-fp8 run must keep the ranks
+    in lock step too. Raises SystemExit(3) on failure."""
+    import torch
+    import torch.distributed as dist
+    from inferencehackathon_b200.runtime.engine import InferenceEngine
+    os.environ["IHB_WINDOW_PREFILL"] = "0"          # the prompt goes through the decode kernel itself
+    out = {"layers": args.gate_layers, "prompt": 24, "decode": 8}
+    g = torch.Generator().manual_seed(1)
+    from inferencehackathon_b200.config import get_model_config
+    vocab = get_model_config(args.model, args.gate_layers).vocab
+    prompt = torch.randint(0, vocab, (24,), generator=g).tolist()
+    try:
+        for wts in ("bf16", args.weights):
+            eng = InferenceEngine.build(args.model, tp=tp, ep=ep, rank=rank, world=world, weights=wts, device=dev,
+                                        backend="cuda", max_seq=128, n_layers=args.gate_layers)
+            pre = eng.prefill(prompt, return_logits=True)
+            toks = [pre.next_token]
+            for _ in range(7):
+                toks.append(eng.decode_step(want_routes=False).token_id)
+            eng.gpu.check_error()
+            all_toks = [None] * world
+            dist.all_gather_object(all_toks, toks)
+            same = all(t == all_toks[0] for t in all_toks)
+            out[f"ranks_agree_{wts}"] = bool(same)
+            ok = same
+            if wts == "bf16":
+                flag = torch.ones(1, device=dev)
+                if rank == 0:
+                    ref = InferenceEngine.build(args.model, weights="bf16", device=dev, backend="cuda", max_seq=128,
+                                                n_layers=args.gate_layers)
+                    pr = ref.prefill(prompt, return_logits=True)
+                    scale = float(pr.logits.abs().max())
+                    err = float((pr.logits[0].float() - pre.logits[0].float()).abs().max())
+                    out["logits_max_err_over_range"] = err / max(scale, 1e-9)
+                    out["first_token_matches_one_gpu"] = bool(pr.next_token == pre.next_token)
+                    if not (err <= 0.02 * scale):
+                        flag.zero_()
+                    del ref
+                dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+                ok = ok and bool(flag.item() > 0)
+            del eng
+            torch.cuda.empty_cache()
+            if not ok:
+                if rank == 0:
+                    print(json.dumps({"correctness_gate": "FAILED", **out}))
+                raise SystemExit(3)
+    finally:
+        os.environ.pop("IHB_WINDOW_PREFILL", None)
+    out["passed"] = True
+    return out
 
 
 def main() -> None:
@@ -146,6 +227,11 @@ def main() -> None:
     if world == 1:
         tp, ep = 1, 1
     par_name = f"tp{world}" if ep == 1 else (f"ep{ep}" if tp == 1 else f"tp{tp}xep{ep}")
+    gate = None
+    if world > 1 and args.gate_layers > 0:
+        gate = correctness_gate(args, rank, world, dev, tp, ep)
+        if rank == 0:
+            print("correctness gate: " + json.dumps(gate), file=sys.stderr)
     eng = InferenceEngine.build(args.model, tp=tp, ep=ep, rank=rank, world=world, weights=args.weights, device=dev,
                                 backend="cuda", max_seq=max_seq, n_layers=args.layers, distinct_layers=distinct)
     if args.hot_experts > 0:
@@ -221,7 +307,12 @@ def main() -> None:
         value = 1000.0 / ms_per_step
         out = {"metric": "decode_tok_per_s", "value": value, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
                "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
-               "scaling": "strong", "vs_baseline": (value / PUBLISHED[world]) if world in PUBLISHED else None,
+               "scaling": "strong", "vs_baseline": (value / SAME_BOX[world]) if world in SAME_BOX else None,
+               "vs_published": (value / PUBLISHED[world]) if world in PUBLISHED else None,
+               "baseline_note": "vs_baseline: the reference's own driver on this pool's B200s (it replays ONE layer of dummy "
+                                "weights 94 times, L2-resident at 8 GPUs; this engine streams 94 distinct layers from HBM); "
+                                "vs_published: the reference's published 8xH100 / 1xH100 figures",
+               "correctness_gate": gate,
                "dtype": "fp8" if args.weights == "fp8_block" else "bf16", "data": "synthetic",
                "config": {"model": mcfg.name, "global_batch": 1, "seq_len": args.prompt, "decode_tokens": args.steps,
                           "parallelism": par_name, "layers": mcfg.n_layers,

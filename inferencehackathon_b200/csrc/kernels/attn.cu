@@ -431,6 +431,21 @@ extern "C" int ihb_flash_decode_static(const float* q, const void* k_cache, cons
              nsplit, IHB_FD_STATIC_MAX_HEADS, IHB_FD_STATIC_MAX_PARTIALS);
     return cudaErrorInvalidValue;
   }
+  // the limits of the kernel itself, checked here so that a refusal comes with a reason and before anything is enqueued
+  if (nsplit > IHB_FD_STATIC_MAX_SPLITS) {
+    snprintf(g_static_msg, sizeof(g_static_msg), "ihb_flash_decode_static: nsplit=%d exceeds the kernel's limit of %d splits",
+             nsplit, IHB_FD_STATIC_MAX_SPLITS);
+    return cudaErrorInvalidValue;
+  }
+  {
+    const int per_kv = nq % nkv == 0 ? nq / nkv : 0;
+    const bool shape_ok = per_kv > 0 && (per_kv % 8 == 0 || per_kv == 4 || per_kv == 2 || per_kv == 1);
+    if (!shape_ok) {
+      snprintf(g_static_msg, sizeof(g_static_msg),
+               "ihb_flash_decode_static: nq=%d, nkv=%d: query heads per KV head must be 1, 2, 4 or a multiple of 8", nq, nkv);
+      return cudaErrorInvalidValue;
+    }
+  }
   unsigned char* base = nullptr;
   cudaError_t e = static_scratch_for_current_device(&base);
   if (e != cudaSuccess) {
@@ -440,8 +455,16 @@ extern "C" int ihb_flash_decode_static(const float* q, const void* k_cache, cons
   }
   // the partials are overwritten before they are read; only the arrival counters have to start at zero
   e = cudaMemsetAsync(base, 0, kStaticCounterBytes, stream);
-  if (e != cudaSuccess) return e;
-  return ihb_flash_decode(q, k_cache, v_cache, nq, nkv, max_seq, pos, nsplit,
-                          reinterpret_cast<float*>(base + kStaticCounterBytes), reinterpret_cast<unsigned*>(base), out,
-                          nullptr, nullptr, 0, 0, stream);
+  if (e != cudaSuccess) {
+    snprintf(g_static_msg, sizeof(g_static_msg), "ihb_flash_decode_static: clearing the arrival counters failed: %s",
+             cudaGetErrorString(e));
+    return e;
+  }
+  const int rc = ihb_flash_decode(q, k_cache, v_cache, nq, nkv, max_seq, pos, nsplit,
+                                  reinterpret_cast<float*>(base + kStaticCounterBytes), reinterpret_cast<unsigned*>(base), out,
+                                  nullptr, nullptr, 0, 0, stream);
+  if (rc != cudaSuccess)
+    snprintf(g_static_msg, sizeof(g_static_msg), "ihb_flash_decode_static: the launch failed: %s",
+             cudaGetErrorString(static_cast<cudaError_t>(rc)));
+  return rc;
 }

@@ -15,8 +15,11 @@ extern "C" {
 
 // Largest problem the built-in scratch holds: nq * nsplit <= IHB_FD_STATIC_MAX_PARTIALS (and nq <= 64).
 // The array is about 1 MiB; every GPU that loads the library keeps it until the process exits.
+// The kernel's own limits apply as well: at most IHB_FD_STATIC_MAX_SPLITS splits, nkv divides nq, and the number
+// of query heads per KV head is 1, 2, 4 or a multiple of 8.
 #define IHB_FD_STATIC_MAX_PARTIALS 2048
 #define IHB_FD_STATIC_MAX_HEADS 64
+#define IHB_FD_STATIC_MAX_SPLITS 256
 
 // Same computation and argument meaning as ihb_flash_decode (api.h), minus the scratch, counters and quantised
 // output arguments: q [nq, 128] fp32, k_cache / v_cache [nkv, max_seq, 128] bf16, positions 0..*pos, out [nq, 128]
@@ -27,8 +30,8 @@ extern "C" {
 // * Every call uses the same array. It still holds the previous call's partials; the arrival counters are
 //   cleared on the stream at the start of each call. Two calls that overlap on the GPU (different streams, or
 //   two host threads) race on it: serialise them.
-// * Returns a cudaError_t value; cudaErrorInvalidValue when the problem exceeds the limits above, in which case
-//   ihb_flash_decode_static_error() says why.
+// * Returns a cudaError_t value; cudaErrorInvalidValue when the problem exceeds any of the limits above (nothing has
+//   been enqueued then). After every failure ihb_flash_decode_static_error() says why.
 int ihb_flash_decode_static(const float* q, const void* k_cache, const void* v_cache, int nq, int nkv, int max_seq,
                             const int* pos, int nsplit, float* out, cudaStream_t stream);
 

@@ -274,3 +274,102 @@ def test_tagged_slots_dead_agent_gives_status_not_hang():
             assert a["rnd"] == 3 and a["err"] is None
         else:
             assert a["err"] == "tag time-out" and 3 <= a["rnd"] <= 4
+
+
+# ---- counted-accumulation protocol (the persistent kernel's all-reduce) -----------------------------------------------------------
+def _run_counted(n_ranks, n_ctas, layers, seed, n_parities=8, clear_after_barrier=True):
+    """Model of the all-reduce of the persistent decode kernel. Every (rank, CTA) is an agent that owns ONE channel.
+    A round: the agent adds its rank's partial of its channel into the round's slot on every GPU (the adds to different
+    GPUs land one at a time, at any later step, in any order), then reads all channels of the round on its own GPU,
+    waiting on each slot until it has counted n_ranks contributions. Two rounds per layer (attention, experts); after
+    the first read of a layer the agent arrives at its GPU's grid barrier and, once the barrier is complete, clears its
+    own channel in the slots of all rounds it has read since the last clearing; then it pushes the second round. Slots
+    are reused every n_parities rounds. Returns the number of violations: a read that found more contributions than
+    ranks or a sum that mixes rounds, and the agents."""
+    rng = random.Random(seed)
+    rounds = 2 * layers
+    # mem[gpu][parity][channel] = [count, sum]
+    mem = [[[[0, 0] for _ in range(n_ctas)] for _ in range(n_parities)] for _ in range(n_ranks)]
+    inflight = []                                            # (gpu, parity, channel, value)
+    arrivals = [0] * n_ranks
+    agents = [dict(r=r, c=c, rnd=0, pc="push", todo=None, clr_lo=0, waits=0, spins=0, err=None)
+              for r in range(n_ranks) for c in range(n_ctas)]
+    live = list(range(len(agents)))
+    bad = 0
+
+    def value(rnd, rank, chan):                              # distinct per round: a mixed sum cannot look right
+        return (rnd + 1) * 1000 + rank * 10 + chan
+
+    def want(rnd, chan):
+        return sum(value(rnd, r, chan) for r in range(n_ranks))
+
+    while live or inflight:
+        if inflight and (not live or rng.random() < 0.5):
+            g, p, ch, v = inflight.pop(rng.randrange(len(inflight)))
+            mem[g][p][ch][0] += 1
+            mem[g][p][ch][1] += v
+            continue
+        i = rng.choice(live)
+        a = agents[i]
+        r, c, rnd = a["r"], a["c"], a["rnd"]
+        par = rnd % n_parities
+        if a["pc"] == "push":
+            for g in range(n_ranks):
+                inflight.append((g, par, c, value(rnd, r, c)))
+            a["pc"], a["todo"] = "read", list(range(n_ctas))
+        elif a["pc"] == "read":
+            ch = a["todo"][0]
+            cnt, tot = mem[r][par][ch]
+            if cnt > n_ranks:
+                bad += 1
+            if cnt >= n_ranks:
+                if tot != want(rnd, ch):
+                    bad += 1
+                a["todo"].pop(0)
+                a["spins"] = 0
+                if not a["todo"]:
+                    a["rnd"] += 1
+                    if a["rnd"] % 2 == 1:                     # first round of a layer read: arrive, later wait + clear
+                        arrivals[r] += 1
+                        a["waits"] += 1
+                        a["pc"] = "barrier"
+                    elif a["rnd"] == rounds:
+                        live.remove(i)
+                    else:
+                        a["pc"] = "push"
+            else:
+                a["spins"] += 1
+                if a["spins"] > 3000:                         # bounded wait: status, not a hang
+                    a["err"] = "slot time-out"
+                    live.remove(i)
+        else:                                                 # barrier: complete when every CTA of this GPU has arrived
+            if arrivals[r] >= a["waits"] * n_ctas:
+                if clear_after_barrier:
+                    for q in range(a["clr_lo"], a["rnd"]):
+                        mem[r][q % n_parities][c] = [0, 0]
+                    a["clr_lo"] = a["rnd"]
+                a["pc"] = "push"
+    return bad, agents
+
+
+@pytest.mark.parametrize("n_ranks,n_ctas", [(1, 3), (2, 3), (4, 2), (8, 2)])
+def test_counted_slots_are_complete_exact_and_reusable(n_ranks, n_ctas):
+    for seed in range(8):
+        bad, agents = _run_counted(n_ranks, n_ctas, layers=10, seed=seed)
+        assert bad == 0
+        assert all(a["err"] is None and a["rnd"] == 20 for a in agents)
+
+
+def test_counted_slots_with_too_few_parities_lose_or_mix_contributions():
+    """With two parities a fast GPU's add of round n + 2 can land in a slot that a slow CTA of this GPU has not read or
+    cleared yet: the model then sees a mixed sum, a count above the number of ranks, or a wait that never ends."""
+    broken = 0
+    for seed in range(40):
+        bad, agents = _run_counted(2, 3, layers=6, seed=seed, n_parities=2)
+        broken += int(bad > 0 or any(a["err"] for a in agents))
+    assert broken > 0
+
+
+def test_counted_slots_without_clearing_cannot_be_reused():
+    bad, agents = _run_counted(2, 2, layers=6, seed=0, n_parities=4, clear_after_barrier=False)
+    assert bad > 0 or any(a["err"] for a in agents)

@@ -49,3 +49,12 @@ def test_static_scratch_entry_matches_regular_entry():
     # a problem larger than the built-in scratch is refused with a message, nothing is launched
     rc = fn(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), nq, nkv, max_seq, pos.data_ptr(), 4096, out.data_ptr(), stream)
     assert rc != 0 and b"exceed" in raw.ihb_flash_decode_static_error()
+    # so is a split count the kernel does not take although the scratch would hold it, and a head grouping it does not
+    # support: each refusal names its reason
+    rc = fn(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), 4, 2, max_seq, pos.data_ptr(), 512, out.data_ptr(), stream)
+    assert rc != 0 and b"splits" in raw.ihb_flash_decode_static_error()
+    rc = fn(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), 6, 2, max_seq, pos.data_ptr(), 4, out.data_ptr(), stream)
+    assert rc != 0 and b"per KV head" in raw.ihb_flash_decode_static_error()
+    rc = fn(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), 5, 2, max_seq, pos.data_ptr(), 4, out.data_ptr(), stream)
+    assert rc != 0 and b"per KV head" in raw.ihb_flash_decode_static_error()
+    torch.cuda.synchronize()
