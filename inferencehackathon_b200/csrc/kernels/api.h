@@ -160,6 +160,9 @@ typedef struct {
   const int* groups;       // [max_groups][4] = {e, tok0, ntok, 0}; NULL = not grouped
   const int* n_groups;     // device scalar
   int max_groups;
+  // LINEAR over many tokens in ONE launch: tok_tiles > 1 tiles of tok_tile (16 / 32 / 64 / 128) tokens cover T tokens
+  // (T may then exceed 128); every weight tile is then read from HBM once per launch instead of once per token tile
+  int tok_tiles, tok_tile;
 } IhbTcArgs;
 
 int ihb_tc_gemm(IhbTcArgs* args, int use_pdl, cudaStream_t stream);
@@ -229,6 +232,22 @@ int ihb_qk_norm_rope_rows(float* qkv, int nq, int nkv, const float* q_gamma, con
 // mask[t][j] != 0 (mask == NULL: causal, j <= t). out [T][nq * 128] fp32.
 int ihb_window_attention(const float* qkv, int qkv_stride, const void* k_cache, const void* v_cache, int nq, int nkv,
                          int max_seq, int base, int T, const unsigned char* mask, float* out, cudaStream_t stream);
+
+// ---- routing of a window of tokens on the device (moe_rows.cu) --------------------------------------------------------------------
+// Fused router: logits = h W_r^T (h [T][H] fp32, router rows bf16 [E][H]), softmax, top-k with ties to the lowest id,
+// optional renormalisation. logits (optional) [T][E], ti [T][top_k] global expert ids, tw [T][top_k]. E <= 256, top_k <= 8.
+int ihb_router_topk_rows(const float* h, const void* router_bf16, int T, int H, int E, int top_k, int renorm, float* logits,
+                         int* ti, float* tw, cudaStream_t stream);
+// (token, slot) pairs bucketed by expert and cut into groups of at most nt rows: order [pairs] (pair at each sorted row),
+// inv [pairs] (sorted row of each pair, -1 when its expert is not held here), groups [gmax][4] = {local expert, first
+// row, rows, 0}, n_groups [1]. gmax >= E_local + pairs / nt + 1 holds every case.
+int ihb_moe_group_table(const int* ti, int pairs, int expert0, int E_local, int nt, int* order, int* inv, int* groups,
+                        int* n_groups, int gmax, cudaStream_t stream);
+// out[p] = src[order[p] / k]: rows of row_bytes bytes (a multiple of 16) in expert order.
+int ihb_moe_gather_rows(const void* src, const int* order, int k, int row_bytes, int pairs, void* out, cudaStream_t stream);
+// y[t] = (resid ? resid[t] : 0) + sum over slots, in slot order, of tw[t][slot] * yg[inv[t k + slot]]  (rows of H floats).
+int ihb_moe_combine_rows(const float* yg, const int* inv, const float* tw, int k, int H, int T, const float* resid, float* y,
+                         cudaStream_t stream);
 
 // ---- stand-alone fused all-reduce (+ residual + RMSNorm) over symmetric memory -----------------------------------------
 // x [T, H] fp32 partial of this rank -> out = sum over ranks (+ resid); out_norm = RMSNorm(out) * gamma (gamma != NULL).

@@ -46,18 +46,20 @@ struct Unit {
   int row0;      // first weight row of the tile (mode 1: j0 inside the expert's gate block)
   int slot;      // routing slot (modes 1, 2) else 0
   int kb0, kb1;  // K blocks [kb0, kb1)
-  int e, tok0, ntok;   // grouped mode: local expert, first row of X, valid rows
+  int e, tok0, ntok;   // local expert (grouped mode), first row of X, valid rows
+  int orow0;           // first output row of the unit
 };
 
 __device__ __forceinline__ Unit decode_unit(const IhbTcArgs& a, int u, int nkb_total) {
   Unit un;
-  un.e = 0; un.tok0 = a.tok0; un.ntok = a.T;
+  un.e = 0; un.tok0 = a.tok0; un.ntok = a.T; un.orow0 = 0;
   if (a.groups != nullptr) {
     const int rtiles = (a.rows + TC_BM - 1) / TC_BM;
     const int g = u / rtiles, tile = u - g * rtiles;
     const int4 gr = *reinterpret_cast<const int4*>(a.groups + 4 * g);
     un.e = gr.x; un.tok0 = gr.y; un.ntok = gr.z;
     un.tile = u; un.member = 0; un.row0 = tile * TC_BM; un.slot = 0; un.kb0 = 0; un.kb1 = nkb_total;
+    un.orow0 = un.tok0;
     return un;
   }
   const int s = u % a.ks;
@@ -66,7 +68,16 @@ __device__ __forceinline__ Unit decode_unit(const IhbTcArgs& a, int u, int nkb_t
   un.kb0 = s * base + min(s, rem);
   un.kb1 = un.kb0 + base + (s < rem ? 1 : 0);
   if (a.mode == IHB_TC_LINEAR) {
-    un.tile = rest; un.slot = 0; un.member = s; un.row0 = rest * TC_BM;
+    // several token tiles in one launch: a weight tile's units of all token tiles are neighbours, so that the tile is
+    // fetched from HBM once and from L2 afterwards
+    const int tt = a.tok_tiles > 1 ? rest % a.tok_tiles : 0;
+    const int rt = a.tok_tiles > 1 ? rest / a.tok_tiles : rest;
+    un.tile = rest; un.slot = 0; un.member = s; un.row0 = rt * TC_BM;
+    if (a.tok_tiles > 1) {
+      un.orow0 = tt * a.tok_tile;
+      un.tok0 = a.tok0 + un.orow0;
+      un.ntok = min(a.tok_tile, a.T - un.orow0);
+    }
   } else if (a.mode == IHB_TC_GATEUP) {
     const int jtiles = (a.rows + TC_BM - 1) / TC_BM;      // rows = I
     un.slot = rest / jtiles;
@@ -142,7 +153,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     }
     fence_proxy_async_smem();
   }
-  if (KIND == 0 && warp >= 4 && a.groups == nullptr) {
+  if (KIND == 0 && warp >= 4 && a.groups == nullptr && a.tok_tiles <= 1) {
     // activation scales for every K block: global layout [slot][kb][T], padded here to NT columns
     const int n = nslot_x * nkb_total * NT;
     for (int i = tid - 128; i < n; i += 128) {
@@ -260,8 +271,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x, ++ui) {
       const Unit un = decode_unit(a, u, nkb_total);
       const int e = (a.mode == IHB_TC_LINEAR) ? 0 : (a.groups != nullptr ? un.e : sh.sel_e[un.slot]);
-      if (KIND == 0 && a.groups != nullptr) {
-        // grouped mode: the activation scales of this unit's tokens (the previous unit's readers are done: barrier)
+      if (KIND == 0 && (a.groups != nullptr || a.tok_tiles > 1)) {
+        // grouped / token-tiled mode: the activation scales of this unit's tokens (the previous unit's readers are done: barrier)
         named_bar_sync(2, 128);
         for (int i = etid; i < nkb_total * NT; i += 128) {
           const int col = i % NT, r = i / NT;
@@ -352,12 +363,12 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const float wslot = (a.mode == IHB_TC_DOWN && a.groups == nullptr) ? sh.sel_w[un.slot] : 1.f;
       bool finisher = true;
       if (members > 1) {
-        float* part = a.partial + (static_cast<size_t>(un.tile) * members + un.member) * (NA * a.T * TC_BM);
+        float* part = a.partial + (static_cast<size_t>(un.tile) * members + un.member) * (NA * NT * TC_BM);
 #pragma unroll
         for (int ai = 0; ai < NA; ++ai)
 #pragma unroll
           for (int n = 0; n < NT; ++n)
-            if (n < a.T) part[(ai * a.T + n) * TC_BM + r_in_tile] = acc[ai][n] * wslot;
+            if (n < un.ntok) part[(ai * NT + n) * TC_BM + r_in_tile] = acc[ai][n] * wslot;
         __threadfence();
         named_bar_sync(2, 128);
         if (etid == 0) {
@@ -369,15 +380,15 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         named_bar_sync(2, 128);
         finisher = sh.last_flag != 0;
         if (finisher) {
-          const float* p0 = a.partial + static_cast<size_t>(un.tile) * members * (NA * a.T * TC_BM);
+          const float* p0 = a.partial + static_cast<size_t>(un.tile) * members * (NA * NT * TC_BM);
 #pragma unroll
           for (int ai = 0; ai < NA; ++ai)
 #pragma unroll
             for (int n = 0; n < NT; ++n) {
-              if (n < a.T) {
+              if (n < un.ntok) {
                 float s = 0.f;
                 for (int mbr = 0; mbr < members; ++mbr)
-                  s += ld_cg_f(p0 + (static_cast<size_t>(mbr) * NA * a.T + ai * a.T + n) * TC_BM + r_in_tile);
+                  s += ld_cg_f(p0 + (static_cast<size_t>(mbr) * NA * NT + ai * NT + n) * TC_BM + r_in_tile);
                 acc[ai][n] = s;
               }
             }
@@ -397,7 +408,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 #pragma unroll
           for (int n = 0; n < NT; ++n)
             if (n < un.ntok) {
-              const size_t orow = a.groups != nullptr ? static_cast<size_t>(un.tok0 + n) : static_cast<size_t>(un.slot) * a.T + n;
+              const size_t orow = a.groups != nullptr ? static_cast<size_t>(un.orow0 + n) : static_cast<size_t>(un.slot) * a.T + n;
               a.out[orow * a.rows + row] = silu(acc[0][n]) * acc[NA - 1][n];
             }
         }
@@ -405,7 +416,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (row < a.rows) {
 #pragma unroll
           for (int n = 0; n < NT; ++n)
-            if (n < un.ntok) a.out[static_cast<size_t>(a.groups != nullptr ? un.tok0 + n : n) * a.out_stride + row] = acc[0][n];
+            if (n < un.ntok) a.out[static_cast<size_t>(un.orow0 + n) * a.out_stride + row] = acc[0][n];
         }
       }
     }
@@ -473,10 +484,13 @@ using namespace ihb;
 
 extern "C" size_t ihb_tc_partial_floats(const IhbTcArgs* a) {
   const int tiles_rows = (a->rows + TC_BM - 1) / TC_BM;
-  const int tiles = a->mode == IHB_TC_GATEUP ? a->top_k * tiles_rows : tiles_rows;
+  const int tt = (a->mode == IHB_TC_LINEAR && a->tok_tiles > 1) ? a->tok_tiles : 1;
+  const int tiles = (a->mode == IHB_TC_GATEUP ? a->top_k * tiles_rows : tiles_rows) * tt;
   const int members = a->mode == IHB_TC_DOWN ? a->top_k * a->ks : a->ks;
   const int na = a->mode == IHB_TC_GATEUP ? 2 : 1;
-  return members > 1 ? static_cast<size_t>(tiles) * members * na * a->T * TC_BM : 0;
+  const int t1 = tt > 1 ? a->tok_tile : a->T;
+  const int nt = t1 <= 16 ? 16 : t1 <= 32 ? 32 : t1 <= 64 ? 64 : 128;
+  return members > 1 ? static_cast<size_t>(tiles) * members * na * nt * TC_BM : 0;
 }
 
 // Picks the K split so that the grid has about two waves of units, encodes the tensor maps and launches.
@@ -487,10 +501,20 @@ extern "C" int ihb_tc_gemm(IhbTcArgs* args, int use_pdl, cudaStream_t stream) {
   const int grouped = a.groups != nullptr;
   if (grouped && (a.mode == IHB_TC_LINEAR || a.n_groups == nullptr || a.max_groups < 1 || a.tiled || a.x_rows1)) return cudaErrorInvalidValue;
   if (grouped) { a.top_k = 1; a.ks = 1; a.tok0 = 0; }
-  if (a.T < 1 || a.T > 128 || a.rows < 1 || a.K < 1 || (a.K * esize) % 16) return cudaErrorInvalidValue;
+  // LINEAR over more than one token tile: tok_tiles tiles of tok_tile (16, 32, 64 or 128) tokens cover the T tokens
+  if (a.tok_tiles > 1) {
+    if (a.mode != IHB_TC_LINEAR || grouped || a.tiled || a.x_rows1) return cudaErrorInvalidValue;
+    if ((a.tok_tile != 16 && a.tok_tile != 32 && a.tok_tile != 64 && a.tok_tile != 128) || a.T < 1 ||
+        a.T > a.tok_tile * a.tok_tiles || a.T <= a.tok_tile * (a.tok_tiles - 1)) return cudaErrorInvalidValue;
+  } else {
+    a.tok_tiles = 1;
+    if (a.T < 1 || a.T > 128) return cudaErrorInvalidValue;
+  }
+  if (a.rows < 1 || a.K < 1 || (a.K * esize) % 16) return cudaErrorInvalidValue;
   if (is_fp8 && (a.rb < 1 || a.wscale == nullptr || a.xscale == nullptr)) return cudaErrorInvalidValue;
   if (a.mode != IHB_TC_LINEAR && (a.top_k < 1 || a.top_k > IHB_MAX_TOPK)) return cudaErrorInvalidValue;
-  const int nt = a.T <= 16 ? 16 : a.T <= 32 ? 32 : a.T <= 64 ? 64 : 128;
+  const int t_tile = a.tok_tiles > 1 ? a.tok_tile : a.T;
+  const int nt = t_tile <= 16 ? 16 : t_tile <= 32 ? 32 : t_tile <= 64 ? 64 : 128;
   if (a.mode == IHB_TC_GATEUP && nt > 64) return cudaErrorInvalidValue;   // two accumulators per token column
   const int na = a.mode == IHB_TC_GATEUP ? 2 : 1;
   const int nkb_total = (a.K * esize + TC_BKB - 1) / TC_BKB;
@@ -501,7 +525,7 @@ extern "C" int ihb_tc_gemm(IhbTcArgs* args, int use_pdl, cudaStream_t stream) {
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   }
-  const int base_units = a.mode == IHB_TC_LINEAR ? tiles_rows : a.top_k * tiles_rows;
+  const int base_units = a.mode == IHB_TC_LINEAR ? tiles_rows * a.tok_tiles : a.top_k * tiles_rows;
   if (a.ks <= 0) {
     int ks = (2 * sms + base_units - 1) / base_units;
     if (ks > nkb_total) ks = nkb_total;

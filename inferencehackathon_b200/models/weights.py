@@ -441,9 +441,80 @@ def _load(path_base: str, ent: Dict) -> QWeight:
     return QWeight(torch.from_numpy(np.fromfile(path_base + ".f32", dtype=np.float32)).reshape(shape))
 
 
+def _next_pow2(n: int) -> int:
+    p = 16
+    while p < n:
+        p *= 2
+    return p
+
+
+def _load_rowwise(path_base: str, rows: int, K: int) -> QWeight:
+    """A matrix written by the reference's converter: e4m3 bytes ``[rows, K]`` and ONE fp32 scale per row. As a block
+    scale that is a block of 1 row x the whole K range (the K block width is the next power of two, which the kernels'
+    shift arithmetic needs and which changes nothing: there is one block along K)."""
+    q = torch.from_numpy(np.fromfile(path_base + ".fp8", dtype=np.uint8)).view(torch.float8_e4m3fn).reshape(rows, K)
+    s = torch.from_numpy(np.fromfile(path_base + ".scale", dtype=np.float32)).reshape(rows, 1)
+    return QWeight(q, s.contiguous(), 1, _next_pow2(K))
+
+
+def load_reference_layout(rd: str, cfg: ModelConfig, par: ParallelConfig, quant: QuantConfig, device="cpu") -> ModelWeights:
+    """One rank directory written by the reference's own converter (tools/conifer_weight_convert.py:8-19,65-99):
+    no manifest, tensor parallel only, per-ROW fp8 scales, the router as ``wgate.fp8`` + ``.scale``, and a QKV matrix
+    that stacks this rank's query heads on ALL key and value heads (the reference replicates K / V on every rank).
+    Shapes follow from the model and the rank; the K / V heads this rank attends with are cut out of the replicated
+    rows; the router is de-quantised (this engine never multiplies a quantised router)."""
+    if par.ep > 1:
+        raise ValueError("the reference's converted layout is tensor parallel only")
+    geom = shard_geometry(cfg, par)
+    hd, H, tp = cfg.head_dim, cfg.hidden, par.tp
+    nq_l = cfg.n_q_heads // tp
+    I_l = cfg.moe_inter // tp
+    voc_l = cfg.vocab // tp
+    if cfg.vocab % tp or geom.vocab_local != voc_l:
+        raise ValueError("the reference's layout shards the vocabulary evenly")
+
+    def f32(path, n):
+        return torch.from_numpy(np.fromfile(path, dtype=np.float32)).reshape(n)
+
+    def store(qw: QWeight) -> QWeight:
+        return qw if quant.weights == "fp8_block" else store_weight(qw.dequant(), quant.weights)
+
+    epath = os.path.join(rd, "embed.bf16")
+    if not os.path.exists(epath):                                  # the reference writes the table for rank 0 only
+        epath = os.path.join(os.path.dirname(rd), "rank0", "embed.bf16")
+    embed = torch.from_numpy(np.fromfile(epath, dtype=np.int16)).view(torch.bfloat16).reshape(cfg.vocab, H)
+    layers = []
+    for L in range(cfg.n_layers):
+        ld = os.path.join(rd, f"layer{L}")
+        full = _load_rowwise(os.path.join(ld, "wqkv"), (nq_l + 2 * cfg.n_kv_heads) * hd, H)
+        k0 = nq_l * hd + geom.kv_head0 * hd
+        v0 = nq_l * hd + cfg.n_kv_heads * hd + geom.kv_head0 * hd
+        nkv = geom.nkv_local * hd
+        rows = torch.cat([torch.arange(0, nq_l * hd), torch.arange(k0, k0 + nkv), torch.arange(v0, v0 + nkv)])
+        wqkv = QWeight(full.data[rows].contiguous(), full.scale[rows].contiguous(), 1, full.kb)
+        gate = _load_rowwise(os.path.join(ld, "wgate"), cfg.n_experts, H).dequant()
+        gus = [_load_rowwise(os.path.join(ld, f"e{E}_wgu"), 2 * I_l, H) for E in range(cfg.n_experts)]
+        dsl = [_load_rowwise(os.path.join(ld, f"e{E}_wd"), H, I_l) for E in range(cfg.n_experts)]
+        stack = lambda qs: QWeight(torch.stack([q.data for q in qs]), torch.stack([q.scale for q in qs]), qs[0].rb, qs[0].kb)
+        layers.append(LayerWeights(
+            in_ln=f32(os.path.join(ld, "in_ln.f32"), H), post_ln=f32(os.path.join(ld, "post_ln.f32"), H),
+            q_norm=f32(os.path.join(ld, "q_norm.f32"), hd), k_norm=f32(os.path.join(ld, "k_norm.f32"), hd),
+            wqkv=store(wqkv), wo=store(_load_rowwise(os.path.join(ld, "wo"), H, nq_l * hd)),
+            router=gate if quant.weights == "fp32" else gate.to(torch.bfloat16),
+            w_gu=store(stack(gus)), w_d=store(stack(dsl))).to(device))
+    lm = store(_load_rowwise(os.path.join(rd, "lm_head"), voc_l, H))
+    small = torch.float32 if quant.weights == "fp32" else torch.bfloat16
+    return ModelWeights(cfg, par, quant, geom, embed.to(small).to(device), f32(os.path.join(rd, "norm_final.f32"), H).to(device),
+                        lm.to(device), layers)
+
+
 def load_engine_layout(in_dir: str, cfg: ModelConfig, par: ParallelConfig, quant: QuantConfig,
                        device="cpu") -> ModelWeights:
+    """One rank's weights from the converted on-disk layout: this package's (with ``manifest.json``), or, when the rank
+    directory has no manifest, the reference converter's (see :func:`load_reference_layout`)."""
     rd = os.path.join(in_dir, f"rank{par.rank}")
+    if not os.path.exists(os.path.join(rd, "manifest.json")):
+        return load_reference_layout(rd, cfg, par, quant, device)
     with open(os.path.join(rd, "manifest.json")) as f:
         man = json.load(f)
     geom = shard_geometry(cfg, par)

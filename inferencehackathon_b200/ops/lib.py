@@ -76,7 +76,8 @@ class IhbTcArgs(C.Structure):
                 ("out", _vp), ("out_stride", C.c_int), ("partial", _vp), ("tile_counters", _vp),
                 ("ks", C.c_int), ("S", C.c_int), ("grid", C.c_int), ("n_units", C.c_int), ("err", _vp),
                 ("tiled", C.c_int), ("x_rows1", C.c_int),
-                ("groups", _vp), ("n_groups", _vp), ("max_groups", C.c_int)]
+                ("groups", _vp), ("n_groups", _vp), ("max_groups", C.c_int),
+                ("tok_tiles", C.c_int), ("tok_tile", C.c_int)]
 
 
 DEC_STORE, DEC_AR_NORM, DEC_ARGMAX, DEC_ACT = 0, 1, 2, 3
@@ -170,6 +171,14 @@ def load(build_if_missing: bool = True) -> C.CDLL:
     lib.ihb_allreduce_norm.argtypes = [C.POINTER(IhbComm), _vp, _vp, _vp, C.c_float, C.c_int, C.c_int, _vp, _vp, _vp, _vp,
                                        C.c_int, C.c_int, _vp]
     lib.ihb_allreduce_norm.restype = C.c_int
+    lib.ihb_router_topk_rows.argtypes = [_vp, _vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _vp, _vp, _vp, _vp]
+    lib.ihb_router_topk_rows.restype = C.c_int
+    lib.ihb_moe_group_table.argtypes = [_vp, C.c_int, C.c_int, C.c_int, C.c_int, _vp, _vp, _vp, _vp, C.c_int, _vp]
+    lib.ihb_moe_group_table.restype = C.c_int
+    lib.ihb_moe_gather_rows.argtypes = [_vp, _vp, C.c_int, C.c_int, C.c_int, _vp, _vp]
+    lib.ihb_moe_gather_rows.restype = C.c_int
+    lib.ihb_moe_combine_rows.argtypes = [_vp, _vp, _vp, C.c_int, C.c_int, C.c_int, _vp, _vp, _vp]
+    lib.ihb_moe_combine_rows.restype = C.c_int
     lib.ihb_mega_decode.argtypes = [C.POINTER(IhbMegaArgs), C.c_int, _vp]
     lib.ihb_mega_decode.restype = C.c_int
     lib.ihb_mega_max_grid.argtypes = [C.POINTER(IhbMegaArgs)]
@@ -427,6 +436,34 @@ def window_attention(qkv: torch.Tensor, k_cache, v_cache, nq: int, nkv: int, max
     check(load().ihb_window_attention(qkv.data_ptr(), qkv.shape[1], k_cache.data_ptr(), v_cache.data_ptr(), nq, nkv,
                                       max_seq, base, qkv.shape[0], ptr(mask), out.data_ptr(), stream_ptr()),
           "ihb_window_attention")
+
+
+def router_topk_rows(h: torch.Tensor, router: torch.Tensor, top_k: int, renorm: bool, ti: torch.Tensor, tw: torch.Tensor,
+                     logits: Optional[torch.Tensor] = None) -> None:
+    """Fused router of a window: ``h [T, H]`` fp32, ``router [E, H]`` bf16 -> expert ids ``ti [T, k]`` int32 and weights
+    ``tw [T, k]`` fp32 (softmax, top-k, optional renormalisation)."""
+    T, H = h.shape
+    check(load().ihb_router_topk_rows(h.data_ptr(), router.data_ptr(), T, H, router.shape[0], top_k, int(renorm), ptr(logits),
+                                      ti.data_ptr(), tw.data_ptr(), stream_ptr()), "ihb_router_topk_rows")
+
+
+def moe_group_table(ti: torch.Tensor, expert0: int, e_local: int, nt: int, order: torch.Tensor, inv: torch.Tensor,
+                    groups: torch.Tensor, n_groups: torch.Tensor) -> None:
+    check(load().ihb_moe_group_table(ti.data_ptr(), ti.numel(), expert0, e_local, nt, order.data_ptr(), inv.data_ptr(),
+                                     groups.data_ptr(), n_groups.data_ptr(), groups.shape[0], stream_ptr()), "ihb_moe_group_table")
+
+
+def moe_gather_rows(src: torch.Tensor, order: torch.Tensor, k: int, out: torch.Tensor) -> None:
+    """``out[p] = src[order[p] // k]`` for rows of bytes (``src [T, row_bytes]`` uint8)."""
+    check(load().ihb_moe_gather_rows(src.data_ptr(), order.data_ptr(), k, src.shape[1], order.numel(), out.data_ptr(),
+                                     stream_ptr()), "ihb_moe_gather_rows")
+
+
+def moe_combine_rows(yg: torch.Tensor, inv: torch.Tensor, tw: torch.Tensor, k: int, y: torch.Tensor,
+                     resid: Optional[torch.Tensor] = None) -> None:
+    T, H = y.shape
+    check(load().ihb_moe_combine_rows(yg.data_ptr(), inv.data_ptr(), tw.data_ptr(), k, H, T, ptr(resid), y.data_ptr(),
+                                      stream_ptr()), "ihb_moe_combine_rows")
 
 
 def a2a_rows(args: IhbA2AArgs, grid: int = 32) -> None:

@@ -1,10 +1,17 @@
 """Multi-token forward on the GPU: prompt chunks (TTFT) and speculative-verify windows (chains and token trees).
 
-Per layer: row RMSNorm + per-token activation quantisation -> tcgen05 GEMM (QKV) -> QK-norm / RoPE / KV append at
+Per layer: row RMSNorm + activation rows for the tensor cores -> tcgen05 GEMM (QKV) -> QK-norm / RoPE / KV append at
 explicit positions -> window attention (causal or tree mask) -> tcgen05 GEMM (o_proj) -> all-reduce -> router ->
 tokens sorted by expert -> GROUPED tcgen05 GEMMs (gate/up + SwiGLU, down) driven by a device-side group table (the
 routing result never visits the host) -> weighted combine -> all-reduce. Windows are processed in passes of up to
-1024 tokens; dense GEMMs run one launch per 128-token tile, the grouped expert GEMMs one launch per pass.
+1024 tokens; a dense GEMM is ONE launch over all token tiles of the pass, a grouped expert GEMM one launch per pass.
+
+Block-scaled fp8 weights are multiplied as bf16 here (``IHB_WINDOW_BF16=1``, the default): a scale per 128 x 128
+weight block and per token forces the fp8 kernel to fold every 128-deep K block into fp32 registers on the CUDA
+cores, which is ~20x slower than the MMAs it serves; de-quantised bf16 copies of the weights (e4m3 x scale rounds to
+bf16 with 0.2 % relative error, a thirtieth of the e4m3 grid itself) let a whole K range accumulate in tensor memory
+and need no activation quantisation. The copies stay resident when they fit beside the model (they do from two GPUs
+up); otherwise a layer's weights are de-quantised into a scratch buffer right before its GEMMs.
 
 The contractions and the attention are this package's kernels (``ihb_tc_gemm``, ``ihb_window_attention``,
 ``ihb_norm_quant_rows``, ``ihb_qk_norm_rope_rows``); index bookkeeping (sort by expert, top-k, gathers) uses
@@ -18,6 +25,8 @@ from typing import List, Optional
 
 import torch
 
+from ..config import env_flag
+from ..models.quant import QWeight
 from ..ops import lib as K
 
 CHUNK = 1024          # tokens per pass (the expert weights are read about once per pass)
@@ -32,13 +41,31 @@ class GpuWindow:
             raise NotImplementedError("the window path is tensor-parallel only")
         if w.layers and w.layers[0].wqkv.data.device.type == "meta":
             raise RuntimeError("the window path needs the plain row-major weights (persistent or streaming pipeline)")
-        self.fp8 = dec.fp8
+        # GEMM operand type of this path: bf16 for bf16 models and (by default) for block-fp8 models as well
+        self.bf16_copies = dec.fp8 and bool(env_flag("IHB_WINDOW_BF16", 1))
+        self.fp8 = dec.fp8 and not self.bf16_copies
         self.es = 1 if self.fp8 else 2
         dev = dec.device
+        self._bf16 = {}                       # data_ptr of an fp8 weight -> its resident bf16 copy
+        self._resident = False
+        if self.bf16_copies:
+            seen, need = set(), 0
+            for lw in w.layers:
+                for qw in (lw.wqkv, lw.wo, lw.w_gu, lw.w_d):
+                    if qw.data.data_ptr() not in seen:
+                        seen.add(qw.data.data_ptr())
+                        need += qw.data.numel() * 2
+            free = torch.cuda.mem_get_info(dev)[0]
+            self._resident = need + (10 << 30) < free and not env_flag("IHB_WINDOW_BF16_SCRATCH", 0)
         self.sms = torch.cuda.get_device_properties(dev).multi_processor_count
         self.err = dec.err
         self._ws = {}
         self.n_gemm_launches = 0
+
+    @property
+    def act_mode(self) -> str:
+        """How this path rounds activations before a linear layer ("fp8": per token and 128 channels; "bf16")."""
+        return "fp8" if self.fp8 else "bf16"
 
     # ---- small helpers ---------------------------------------------------------------------------------------------
     def _buf(self, name: str, shape, dtype) -> torch.Tensor:
@@ -60,33 +87,55 @@ class GpuWindow:
         K.norm_quant_rows(x.contiguous(), gamma, self.d.cfg.model.rms_eps, xq, xs, self.fp8, xn)
         return xq, xs, xn
 
+    def _w(self, qw, tag: str):
+        """The weight a GEMM of this path multiplies: ``qw`` itself, or its bf16 copy (resident, or de-quantised now
+        into the scratch buffer ``tag``)."""
+        if not self.bf16_copies or qw.scale is None:
+            return qw
+        key = qw.data.data_ptr()
+        hit = self._bf16.get(key)
+        if hit is not None:
+            return hit
+        out = (torch.empty(qw.data.shape, dtype=torch.bfloat16, device=qw.data.device) if self._resident
+               else self._buf("w_" + tag, tuple(qw.data.shape), torch.bfloat16))
+        if qw.data.dim() == 3:
+            step = max(1, (256 << 20) // max(1, qw.data[0].numel()))       # fp32 temporaries of ~1 GB at most
+            for e0 in range(0, qw.data.shape[0], step):
+                out[e0:e0 + step] = qw.select(slice(e0, e0 + step)).dequant(torch.bfloat16)
+        else:
+            out.copy_(qw.dequant(torch.bfloat16))
+        res = QWeight(out)
+        if self._resident:
+            self._bf16[key] = res
+        return res
+
     def _linear(self, qw, xq, xs, T: int, tag: str) -> torch.Tensor:
         """[T, K] x W[rows, K]^T on the tensor cores."""
         a = K.IhbTcArgs()
-        K.tc_fill_weight(a, qw)
+        K.tc_fill_weight(a, self._w(qw, tag))
         rows = a.rows
         out = self._buf("o_" + tag, (T, rows), torch.float32)
         a.X, a.mode, a.out_stride = xq.data_ptr(), K.TC_LINEAR, rows
         if xs is not None:
             a.xscale = xs.data_ptr()
         a.T_total, a.err = T, self.err.data_ptr()
-        tiles = (rows + 127) // 128
         nkb = (a.K * self.es + 127) // 128
-        a.ks = max(1, min(nkb, 16, -(-2 * self.sms // tiles)))
-        a.T = min(T, TILE)
+        a.T, a.tok0, a.out = T, 0, out.data_ptr()
+        if T > TILE:
+            a.tok_tile, a.tok_tiles = TILE, -(-T // TILE)
+        tiles = ((rows + 127) // 128) * max(1, a.tok_tiles)
+        # split K only while the (row tile, token tile) units do not fill the GPU
+        a.ks = max(1, min(nkb, 16, (2 * self.sms) // tiles))
         part = self._buf("part", (max(1, K.tc_partial_floats(a)),), torch.float32)
         ctr = self._buf("ctr", (max(tiles, 1),), torch.int32)
         a.partial, a.tile_counters = part.data_ptr(), ctr.data_ptr()
-        for t0 in range(0, T, TILE):                      # token tiles of one launch each
-            a.T, a.tok0 = min(TILE, T - t0), t0
-            a.out = out[t0:].data_ptr()
-            K.tc_gemm(a, False)
-            self.n_gemm_launches += 1
+        K.tc_gemm(a, False)
+        self.n_gemm_launches += 1
         return out
 
     def _grouped(self, qw, mode, rows: int, xq, xs, groups, n_groups, max_groups: int, nt: int, n_pairs: int, tag: str):
         a = K.IhbTcArgs()
-        K.tc_fill_weight(a, qw)
+        K.tc_fill_weight(a, self._w(qw, tag))
         a.rows = rows
         out = self._buf("g_" + tag, (n_pairs, rows), torch.float32)
         a.X, a.mode, a.out, a.out_stride = xq.data_ptr(), mode, out.data_ptr(), rows
@@ -141,33 +190,41 @@ class GpuWindow:
             K.window_attention(qkv, d.k_cache[L], d.v_cache[L], nq, nkv, d.max_seq, base, mask_u8, attn)
             aq, asc, _ = self._quant(attn, None, "a")
             o = self._linear(lw.wo, aq, asc, T, "wo")
-            x = x + d.comm_ref.all_reduce_tp(o.clone() if d.cfg.parallel.tp > 1 else o)
+            x = x + d.comm_ref.all_reduce_tp(o.clone() if d.cfg.parallel.tp > 1 else o)        # a new tensor: x's old buffer is free again
             hq, hs, h2 = self._quant(x, lw.post_ln, "h", want_norm=True)
-            # router (tiny GEMM) + top-k, on the device
-            logits = h2 @ lw.router.float().t()
-            p = torch.softmax(logits, -1)
-            tw, ti = torch.topk(p, k, dim=-1)
-            if m.norm_topk_prob:
-                tw = tw / tw.sum(-1, keepdim=True)
-            d.sel_idx[L].copy_(ti[-1].to(torch.int32))          # routing telemetry of the window's last token
-            d.sel_w[L].copy_(tw[-1])
-            # grouped expert GEMMs over (token, slot) pairs sorted by expert
-            flat_e = ti.reshape(-1)
+            # fused router (logits, softmax, top-k) and the expert group table: kernels of this package, on the device
             pairs = T * k
             E_l = lw.w_gu.data.shape[0]
+            ti = self._buf("ti", (T, k), torch.int32)
+            tw = self._buf("tw", (T, k), torch.float32)
+            K.router_topk_rows(h2, lw.router, k, bool(m.norm_topk_prob), ti, tw)
+            d.sel_idx[L].copy_(ti[-1])                          # routing telemetry of the window's last token
+            d.sel_w[L].copy_(tw[-1])
             per = max(1, pairs // E_l)
             nt = 16 if per <= 12 else 32 if per <= 28 else 64
-            order, groups, n_groups, gmax = self._group_table(flat_e, E_l, nt)
-            tok_of = order // k
-            gq = hq[tok_of].contiguous()
-            gs = hs[:, tok_of].contiguous() if hs is not None else None
+            gmax = E_l + pairs // nt + 1
+            order = self._buf("order", (pairs,), torch.int32)
+            inv = self._buf("inv", (pairs,), torch.int32)
+            groups = self._buf("groups", (gmax, 4), torch.int32)
+            n_groups = self._buf("n_groups", (1,), torch.int32)
+            K.moe_group_table(ti, 0, E_l, nt, order, inv, groups, n_groups)
+            # grouped expert GEMMs over the (token, slot) pairs in expert order
+            gq = self._buf("gq", (pairs, hq.shape[1]), torch.uint8)
+            K.moe_gather_rows(hq, order, k, gq)
+            gs = None
+            if hs is not None:
+                gs = hs[:, (order // k).long()].contiguous()
             act = self._grouped(lw.w_gu, K.TC_GATEUP, I, gq, gs, groups, n_groups, gmax, nt, pairs, "act")
             cq, cs, _ = self._quant(act, None, "c")
             yg = self._grouped(lw.w_d, K.TC_DOWN, H, cq, cs, groups, n_groups, gmax, nt, pairs, "y")
-            inv = torch.empty_like(order)
-            inv[order] = torch.arange(pairs, device=dev)
-            y = (yg[inv].reshape(T, k, H) * tw[..., None]).sum(1)       # slot order: deterministic
-            x = x + d.comm_ref.all_reduce_tp(y)
+            y = self._buf("ycomb", (T, H), torch.float32)
+            if d.cfg.parallel.tp > 1:
+                K.moe_combine_rows(yg, inv, tw, k, y)               # slot order: deterministic
+                x = x + d.comm_ref.all_reduce_tp(y)
+            else:
+                xnew = self._buf("xres" + str(L & 1), (T, H), torch.float32)
+                K.moe_combine_rows(yg, inv, tw, k, xnew, resid=x)
+                x = xnew
             if L in aux_layers:
                 self.aux_taps[L] = x.clone()
         return x

@@ -27,7 +27,7 @@ def test_cuda_decode_matches_torch_reference(weights, pipeline, graph, monkeypat
     # the oracle rounds activations the way the kernels store them: per-token fp8 / bf16 in the tensor-core GEMMs
     # (per-op pipeline, and the batched prompt pass of the other pipelines), fp16 in the CUDA-core GEMVs
     decode_mode = tc_mode if (eng.gpu.use_tc and not eng.gpu.use_mega) else None
-    ref.model.act_mode = tc_mode if eng.gpu.has_window() else decode_mode
+    ref.model.act_mode = eng.gpu.window().act_mode if eng.gpu.has_window() else decode_mode
     pr = ref.prefill(_prompt(), return_logits=True)
     pe = eng.prefill(_prompt(), return_logits=True)
     scale = float(pr.logits.abs().max())

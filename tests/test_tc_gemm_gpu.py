@@ -159,3 +159,31 @@ def test_tc_moe_gateup_down(fp8, tiled, H, I, E, k, T):
         ref += sw[s] * (af[s] @ wd.select(int(sel[s])).dequant().t())
     assert int(err.item()) == 0
     assert float((out - ref).abs().max()) < 2e-3 * float(ref.abs().max()) + 1e-3
+
+
+@pytest.mark.parametrize("fp8", [True, False])
+@pytest.mark.parametrize("rows,K,T,tile,ks", [(384, 1024, 300, 128, 1), (1152, 4096, 1024, 128, 2), (200, 512, 70, 32, 4)])
+def test_tc_linear_over_many_token_tiles_in_one_launch(fp8, rows, K, T, tile, ks):
+    """One launch covers all token tiles of a window (units = row tile x token tile x K split)."""
+    lib = _K()
+    g = torch.Generator(device=_dev()).manual_seed(rows + K + T)
+    qw = _weights(rows, K, fp8, g)
+    xq, xs, xf = _acts(T, K, fp8, g)
+    out = torch.full((T, rows), float("nan"), device=_dev())
+    a = lib.IhbTcArgs()
+    lib.tc_fill_weight(a, qw)
+    a.X, a.mode, a.out, a.out_stride, a.ks = xq.data_ptr(), lib.TC_LINEAR, out.data_ptr(), rows, ks
+    if fp8:
+        a.xscale = xs.data_ptr()
+    a.T, a.T_total, a.tok0 = T, T, 0
+    a.tok_tile, a.tok_tiles = tile, -(-T // tile)
+    err = torch.zeros(1, dtype=torch.int32, device=_dev())
+    a.err = err.data_ptr()
+    part = torch.zeros(max(1, lib.tc_partial_floats(a)), device=_dev())
+    ctr = torch.zeros(((rows + 127) // 128) * a.tok_tiles, dtype=torch.int32, device=_dev())
+    a.partial, a.tile_counters = part.data_ptr(), ctr.data_ptr()
+    lib.tc_gemm(a, False)
+    torch.cuda.synchronize()
+    assert int(err.item()) == 0
+    ref = xf @ qw.dequant().t()
+    assert float((out - ref).abs().max()) < 3e-3 * float(ref.abs().max()) + 1e-3

@@ -1,0 +1,158 @@
+"""Weight input / output on CPU: a Hugging Face style safetensors directory, this package's converted layout (save,
+load, the convert command) and a directory in the exact format of the reference's converter
+(tools/conifer_weight_convert.py: per-row fp8 scales, no manifest, K / V replicated in the QKV matrix)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from inferencehackathon_b200.config import ParallelConfig, QuantConfig, get_model_config
+from inferencehackathon_b200.models.qwen3_moe import Qwen3MoE
+from inferencehackathon_b200.models.weights import (load_engine_layout, random_state_dict, save_engine_layout,
+                                                    shard_state_dict)
+from inferencehackathon_b200.parallel.collectives import Collectives
+
+
+def _logits(w, toks):
+    par = w.par
+    m = Qwen3MoE(w, Collectives(ParallelConfig(tp=1, ep=1, rank=0, world=1)) if par.world == 1 else None)
+    cache = m.new_cache(64, torch.float32, "cpu")
+    return m.forward(torch.tensor(toks), cache)
+
+
+def _same(a, b):
+    assert a.data.dtype == b.data.dtype and torch.equal(a.data.view(torch.uint8), b.data.view(torch.uint8))
+    assert (a.scale is None) == (b.scale is None)
+    if a.scale is not None:
+        assert torch.equal(a.scale, b.scale) and (a.rb, a.kb) == (b.rb, b.kb)
+
+
+@pytest.mark.parametrize("weights", ["fp32", "fp8_block"])
+def test_converted_layout_round_trip(tmp_path, weights):
+    cfg = get_model_config("tiny")
+    q = QuantConfig(weights=weights, kv="fp32")
+    for rank in range(2):
+        par = ParallelConfig(tp=2, ep=1, rank=rank, world=2)
+        w = shard_state_dict(random_state_dict(cfg, 0), cfg, par, q)
+        save_engine_layout(w, str(tmp_path))
+        back = load_engine_layout(str(tmp_path), cfg, par, q)
+        assert torch.equal(back.embed.float(), w.embed.float()) and torch.equal(back.final_norm, w.final_norm)
+        _same(back.lm_head, w.lm_head)
+        for a, b in zip(back.layers, w.layers):
+            for nm in ("wqkv", "wo", "w_gu", "w_d"):
+                _same(getattr(a, nm), getattr(b, nm))
+            assert torch.equal(a.router.float(), b.router.float())
+            for nm in ("in_ln", "post_ln", "q_norm", "k_norm"):
+                assert torch.equal(getattr(a, nm), getattr(b, nm))
+
+
+def test_safetensors_directory_and_convert_command(tmp_path):
+    from safetensors.torch import save_file
+    from inferencehackathon_b200.models import convert
+    cfg = get_model_config("tiny")
+    sd = random_state_dict(cfg, 3)
+    src = tmp_path / "hf"
+    src.mkdir()
+    names = sorted(sd)
+    half = len(names) // 2                                       # two shard files, no index: the loader scans them
+    save_file({k: sd[k].contiguous() for k in names[:half]}, str(src / "model-00001-of-00002.safetensors"))
+    save_file({k: sd[k].contiguous() for k in names[half:]}, str(src / "model-00002-of-00002.safetensors"))
+    one = ParallelConfig(tp=1, ep=1, rank=0, world=1)
+    q = QuantConfig(weights="fp32", kv="fp32")
+    from_dir = shard_state_dict(str(src), cfg, one, q)
+    from_dict = shard_state_dict(sd, cfg, one, q)
+    toks = [1, 5, 9, 2, 7]
+    assert torch.equal(_logits(from_dir, toks), _logits(from_dict, toks))
+    # the command writes one directory per rank, which loads back to the same shards
+    dst = tmp_path / "out"
+    assert convert.main(["--src", str(src), "--dst", str(dst), "--model", "tiny", "--tp", "2", "--weights", "fp32"]) == 0
+    for rank in range(2):
+        par = ParallelConfig(tp=2, ep=1, rank=rank, world=2)
+        back = load_engine_layout(str(dst / f"rank{rank:02d}"), cfg, par, q)
+        want = shard_state_dict(sd, cfg, par, q)
+        for a, b in zip(back.layers, want.layers):
+            _same(a.wqkv, b.wqkv); _same(a.w_gu, b.w_gu); _same(a.w_d, b.w_d); _same(a.wo, b.wo)
+
+
+def _rowwise(w):
+    w = w.float()
+    scale = w.abs().amax(dim=1).clamp_min(1e-8) / 448.0
+    q = (w / scale[:, None]).clamp(-448.0, 448.0).to(torch.float8_e4m3fn)
+    return q, scale.float()
+
+
+def _write_reference_format(sd, cfg, tp, out):
+    """The file set of tools/conifer_weight_convert.py for a model of any size (the tool itself hard-codes the
+    235B shapes): per-row scales, K / V of all heads in every rank's wqkv, router as fp8, embed on rank 0 only."""
+    hd, H = cfg.head_dim, cfg.hidden
+    qr, ir, vr = cfg.n_q_heads * hd // tp, cfg.moe_inter // tp, cfg.vocab // tp
+    expect = {}
+    for r in range(tp):
+        rd = os.path.join(out, f"rank{r}")
+        os.makedirs(rd)
+        if r == 0:
+            sd["model.embed_tokens.weight"].to(torch.bfloat16).view(torch.int16).numpy().tofile(os.path.join(rd, "embed.bf16"))
+        sd["model.norm.weight"].float().numpy().tofile(os.path.join(rd, "norm_final.f32"))
+
+        def put(path, w, key):
+            q, s = _rowwise(w.contiguous())
+            q.view(torch.uint8).numpy().tofile(path + ".fp8")
+            s.numpy().tofile(path + ".scale")
+            expect[(r, key)] = q.float() * s[:, None]
+
+        put(os.path.join(rd, "lm_head"), sd["lm_head.weight"][r * vr:(r + 1) * vr], "lm_head")
+        for L in range(cfg.n_layers):
+            ld = os.path.join(rd, f"layer{L}")
+            os.makedirs(ld)
+            p = f"model.layers.{L}."
+            for nm, fn in (("input_layernorm", "in_ln"), ("post_attention_layernorm", "post_ln"),
+                           ("self_attn.q_norm", "q_norm"), ("self_attn.k_norm", "k_norm")):
+                sd[p + nm + ".weight"].float().numpy().tofile(os.path.join(ld, fn + ".f32"))
+            wqkv = torch.cat([sd[p + "self_attn.q_proj.weight"][r * qr:(r + 1) * qr], sd[p + "self_attn.k_proj.weight"],
+                              sd[p + "self_attn.v_proj.weight"]], 0)
+            put(os.path.join(ld, "wqkv"), wqkv, (L, "wqkv"))
+            put(os.path.join(ld, "wo"), sd[p + "self_attn.o_proj.weight"][:, r * qr:(r + 1) * qr], (L, "wo"))
+            put(os.path.join(ld, "wgate"), sd[p + "mlp.gate.weight"], (L, "wgate"))
+            for E in range(cfg.n_experts):
+                ep = p + f"mlp.experts.{E}."
+                wgu = torch.cat([sd[ep + "gate_proj.weight"][r * ir:(r + 1) * ir], sd[ep + "up_proj.weight"][r * ir:(r + 1) * ir]], 0)
+                put(os.path.join(ld, f"e{E}_wgu"), wgu, (L, f"e{E}_wgu"))
+                put(os.path.join(ld, f"e{E}_wd"), sd[ep + "down_proj.weight"][:, r * ir:(r + 1) * ir], (L, f"e{E}_wd"))
+    return expect
+
+
+def test_directory_written_by_the_reference_converter_loads(tmp_path):
+    cfg = get_model_config("tiny")
+    sd = random_state_dict(cfg, 1)
+    tp = 2
+    expect = _write_reference_format(sd, cfg, tp, str(tmp_path))
+    q = QuantConfig(weights="fp8_block", kv="fp32")
+    hd = cfg.head_dim
+    for r in range(tp):
+        par = ParallelConfig(tp=tp, ep=1, rank=r, world=tp)
+        w = load_engine_layout(str(tmp_path), cfg, par, q)
+        g = w.geom
+        assert torch.equal(w.lm_head.dequant(), expect[(r, "lm_head")])
+        for L, lw in enumerate(w.layers):
+            full = expect[(r, (L, "wqkv"))]
+            nq = g.nq_local * hd
+            k0 = nq + g.kv_head0 * hd
+            v0 = nq + cfg.n_kv_heads * hd + g.kv_head0 * hd
+            want = torch.cat([full[:nq], full[k0:k0 + g.nkv_local * hd], full[v0:v0 + g.nkv_local * hd]], 0)
+            assert lw.wqkv.data.shape[0] == (g.nq_local + 2 * g.nkv_local) * hd
+            assert torch.equal(lw.wqkv.dequant(), want)
+            assert torch.equal(lw.wo.dequant(), expect[(r, (L, "wo"))])
+            assert torch.allclose(lw.router.float(), expect[(r, (L, "wgate"))], atol=0, rtol=1e-2)      # stored as bf16
+            for E in range(cfg.n_experts):
+                assert torch.equal(lw.w_gu.select(E).dequant(), expect[(r, (L, f"e{E}_wgu"))])
+                assert torch.equal(lw.w_d.select(E).dequant(), expect[(r, (L, f"e{E}_wd"))])
+    # and the loaded shards are a usable model: next to the fp32 model of the same state dict, within the e4m3 grid
+    one = ParallelConfig(tp=1, ep=1, rank=0, world=1)
+    exp1 = _write_reference_format(sd, cfg, 1, str(tmp_path / "tp1"))
+    w1 = load_engine_layout(str(tmp_path / "tp1"), cfg, one, q)
+    ref = shard_state_dict(sd, cfg, one, QuantConfig(weights="fp32", kv="fp32"))
+    toks = [3, 1, 4, 1, 5, 9, 2, 6]
+    a, b = _logits(w1, toks), _logits(ref, toks)
+    assert torch.isfinite(a).all()
+    assert float((a - b).abs().max()) < 0.15 * float(b.abs().max())

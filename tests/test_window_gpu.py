@@ -16,7 +16,7 @@ def _pair(weights, max_seq=512):
     dev = "cuda:0"
     ref = InferenceEngine.build("small", weights=weights, device=dev, backend="torch", max_seq=max_seq)
     eng = InferenceEngine.build("small", weights=weights, device=dev, backend="cuda", max_seq=max_seq)
-    ref.model.act_mode = "fp8" if weights == "fp8_block" else "bf16"     # the window GEMMs quantise activations per token
+    ref.model.act_mode = eng.gpu.window().act_mode       # the oracle rounds activations the way the window GEMMs read them
     return ref, eng
 
 
@@ -54,10 +54,78 @@ def test_grouped_gemm_matches_per_expert_reference():
     assert int(n_groups.item()) == int(((torch.bincount(flat_e, minlength=E) + nt - 1) // nt).sum())
 
 
+def test_router_grouping_gather_and_combine_kernels():
+    """The device-side routing of a window: fused router (fp32 logits from bf16 rows, softmax, top-k, renormalisation),
+    expert group table, dispatch gather and weighted combine, each against plain PyTorch."""
+    from inferencehackathon_b200.ops import lib as K
+    K.load()
+    d = torch.device("cuda", 0)
+    g = torch.Generator(device=d).manual_seed(1)
+    for (T, H, E, k, renorm) in [(37, 512, 16, 4, True), (300, 2048, 128, 8, True), (9, 1024, 200, 8, False)]:
+        h = torch.randn(T, H, device=d, generator=g)
+        W = (torch.randn(E, H, device=d, generator=g) * 0.05).to(torch.bfloat16)
+        ti = torch.zeros(T, k, dtype=torch.int32, device=d)
+        tw = torch.zeros(T, k, device=d)
+        lg = torch.zeros(T, E, device=d)
+        K.router_topk_rows(h, W, k, renorm, ti, tw, lg)
+        ref_lg = h @ W.float().t()
+        assert float((lg - ref_lg).abs().max()) < 1e-3 * float(ref_lg.abs().max()) + 1e-4
+        p = torch.softmax(lg, -1)                                 # selection checked on the kernel's own logits
+        rw, ri = torch.topk(p, k, dim=-1)
+        if renorm:
+            rw = rw / rw.sum(-1, keepdim=True)
+        assert torch.equal(ti.long(), ri)
+        assert float((tw - rw).abs().max()) < 1e-5
+        # group table
+        nt = 16
+        pairs = T * k
+        gmax = E + pairs // nt + 1
+        order = torch.full((pairs,), -1, dtype=torch.int32, device=d)
+        inv = torch.full((pairs,), -7, dtype=torch.int32, device=d)
+        groups = torch.zeros(gmax, 4, dtype=torch.int32, device=d)
+        ng = torch.zeros(1, dtype=torch.int32, device=d)
+        K.moe_group_table(ti, 0, E, nt, order, inv, groups, ng)
+        flat = ti.reshape(-1).long()
+        assert sorted(order.tolist()) == list(range(pairs))       # a permutation
+        assert torch.equal(inv.long()[order.long()], torch.arange(pairs, device=d))
+        n = int(ng.item())
+        cnt = torch.bincount(flat, minlength=E)
+        assert n == int(((cnt + nt - 1) // nt).sum())
+        covered = torch.zeros(pairs, dtype=torch.int32, device=d)
+        for e_, r0, nr, _ in groups[:n].tolist():
+            assert 1 <= nr <= nt
+            assert bool((flat[order[r0:r0 + nr].long()] == e_).all())
+            covered[r0:r0 + nr] += 1
+        assert bool((covered == 1).all())
+        # gather and combine
+        rows = torch.randint(0, 255, (T, 64), dtype=torch.uint8, device=d, generator=g)
+        out = torch.zeros(pairs, 64, dtype=torch.uint8, device=d)
+        K.moe_gather_rows(rows, order, k, out)
+        assert torch.equal(out, rows[(order // k).long()])
+        yg = torch.randn(pairs, H, device=d, generator=g)
+        resid = torch.randn(T, H, device=d, generator=g)
+        y = torch.zeros(T, H, device=d)
+        K.moe_combine_rows(yg, inv, tw, k, y, resid=resid)
+        want = resid + (yg[inv.long()].reshape(T, k, H) * tw[..., None]).sum(1)
+        assert float((y - want).abs().max()) < 1e-4
+
+
+def test_window_on_the_block_fp8_gemm_path(monkeypatch):
+    """IHB_WINDOW_BF16=0 keeps the block-scaled fp8 GEMMs (per-token e4m3 activations) of the window path alive."""
+    monkeypatch.setenv("IHB_WINDOW_BF16", "0")
+    ref, eng = _pair("fp8_block")
+    assert eng.gpu.window().act_mode == "fp8"
+    toks = _prompt(150)
+    a = ref.logits_for(toks, commit=True)
+    b = eng.logits_for(toks, commit=True)
+    assert float((a - b).abs().max()) < 0.08 * float(a.abs().max())
+    eng.gpu.check_error()
+
+
 @pytest.mark.parametrize("weights", ["bf16", "fp8_block"])
 def test_window_logits_match_reference_chain_and_chunks(weights):
     ref, eng = _pair(weights)
-    toks = _prompt(150)                                          # two chunks: 128 + 22
+    toks = _prompt(150)                                          # two token tiles: 128 + 22
     a = ref.logits_for(toks[:150], commit=True)
     b = eng.logits_for(toks[:150], commit=True)
     assert b.shape == a.shape and eng.seq_len == 150
