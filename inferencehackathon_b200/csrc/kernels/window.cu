@@ -223,6 +223,158 @@ __global__ void __launch_bounds__(WA_WARPS * 32) window_attn_kernel(
   }
 }
 
+
+// ---- window attention on the tensor cores: grid (ceil(T / 16), nkv, q_per_kv / 8), 8 warps -----------------------------------
+// A CTA takes 16 consecutive window tokens and up to 8 query heads of one KV head: warp w owns head w, its 16 tokens
+// are the 16 rows of m16n8k16 tiles. K / V blocks of 64 positions are staged once in shared memory for all heads
+// (the per-token kernel above re-reads the whole context for every query token). Scores: q (bf16 head + bf16
+// remainder, so that the product keeps fp32 accuracy against the bf16 cache rows) times K^T; online softmax in the
+// log2 domain on the accumulator fragments; the probabilities (split the same way) go back in as the A operand of P V
+// without leaving registers (the accumulator layout of two neighbouring 8-wide tiles is the A layout of one 16-deep step).
+// Reference: kernels/prefill_attn.cu:212-271 (SIMT flash_attn_causal), engine/native/tc_verify_attn.cuh:48-119.
+constexpr int WM_KB = 64;                 // key positions per block
+constexpr int WM_LD = WHD + 8;            // padded row: fragment loads of a quarter warp cover all banks
+
+__device__ __forceinline__ void wm_mma(float (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0, unsigned b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned wm_pack_bf16(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const unsigned*>(&v);
+}
+// (x, y) -> bf16 heads packed, and the packed bf16 remainders
+__device__ __forceinline__ void wm_split2(float x, float y, unsigned& hi, unsigned& lo) {
+  const __nv_bfloat16 hx = __float2bfloat16(x), hy = __float2bfloat16(y);
+  const __nv_bfloat162 h = __halves2bfloat162(hx, hy);
+  hi = *reinterpret_cast<const unsigned*>(&h);
+  lo = wm_pack_bf16(x - __bfloat162float(hx), y - __bfloat162float(hy));
+}
+
+__global__ void __launch_bounds__(256) window_attn_mma_kernel(
+    const float* __restrict__ qkv, int qkv_stride, const __nv_bfloat16* __restrict__ k_cache,
+    const __nv_bfloat16* __restrict__ v_cache, int nq, int nkv, int max_seq, int base, int T,
+    const uint8_t* __restrict__ mask, float* __restrict__ out) {
+  __shared__ __align__(16) __nv_bfloat16 ks[WM_KB][WM_LD];
+  __shared__ __align__(16) __nv_bfloat16 vs[WM_KB][WM_LD];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t4 = lane & 3;
+  const int t0 = blockIdx.x * 16, kvh = blockIdx.y, grp = blockIdx.z;
+  const int q_per_kv = nq / nkv;
+  const int gq = min(8, q_per_kv - grp * 8);
+  const int head = kvh * q_per_kv + grp * 8 + warp;
+  const bool active = warp < gq;
+  const float qscale = 0.08838834764831845f * 1.4426950408889634f;   // 1 / sqrt(128) * log2(e)
+  const int r0 = t0 + g, r1 = t0 + g + 8;                              // this thread's two rows (window tokens)
+  // Q fragments of the whole head dimension: 8 steps of 16 channels, head and remainder
+  unsigned qh[8][4], ql[8][4];
+#pragma unroll
+  for (int ksi = 0; ksi < 8; ++ksi) {
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int c = ksi * 16 + half * 8 + 2 * t4;
+      float2 a = make_float2(0.f, 0.f), b = make_float2(0.f, 0.f);
+      if (active && r0 < T) a = *reinterpret_cast<const float2*>(qkv + static_cast<size_t>(r0) * qkv_stride + static_cast<size_t>(head) * WHD + c);
+      if (active && r1 < T) b = *reinterpret_cast<const float2*>(qkv + static_cast<size_t>(r1) * qkv_stride + static_cast<size_t>(head) * WHD + c);
+      wm_split2(a.x * qscale, a.y * qscale, qh[ksi][2 * half], ql[ksi][2 * half]);
+      wm_split2(b.x * qscale, b.y * qscale, qh[ksi][2 * half + 1], ql[ksi][2 * half + 1]);
+    }
+  }
+  float o[16][4];
+#pragma unroll
+  for (int nd = 0; nd < 16; ++nd) o[nd][0] = o[nd][1] = o[nd][2] = o[nd][3] = 0.f;
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+  const int n_keys = mask != nullptr ? base + T : min(base + T, base + t0 + 16);
+  const __nv_bfloat16* kbase = k_cache + static_cast<size_t>(kvh) * max_seq * WHD;
+  const __nv_bfloat16* vbase = v_cache + static_cast<size_t>(kvh) * max_seq * WHD;
+  for (int kb0 = 0; kb0 < n_keys; kb0 += WM_KB) {
+    __syncthreads();                                   // the previous block's readers are done
+    for (int i = tid; i < WM_KB * 16; i += 256) {
+      const int r = i >> 4, ch = i & 15;
+      const int p = min(kb0 + r, n_keys - 1);          // rows past the end repeat a valid row; they are masked below
+      *reinterpret_cast<uint4*>(&ks[r][ch * 8]) = *reinterpret_cast<const uint4*>(kbase + static_cast<size_t>(p) * WHD + ch * 8);
+      *reinterpret_cast<uint4*>(&vs[r][ch * 8]) = *reinterpret_cast<const uint4*>(vbase + static_cast<size_t>(p) * WHD + ch * 8);
+    }
+    __syncthreads();
+    if (!active) continue;
+    // ---- scores of 64 keys: 8 tiles of 8 keys ----
+    float sc[8][4];
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) {
+      float d[4] = {0.f, 0.f, 0.f, 0.f}, e[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int ksi = 0; ksi < 8; ++ksi) {
+        const unsigned b0 = *reinterpret_cast<const unsigned*>(&ks[nt * 8 + g][ksi * 16 + 2 * t4]);
+        const unsigned b1 = *reinterpret_cast<const unsigned*>(&ks[nt * 8 + g][ksi * 16 + 8 + 2 * t4]);
+        wm_mma(d, qh[ksi][0], qh[ksi][1], qh[ksi][2], qh[ksi][3], b0, b1);
+        wm_mma(e, ql[ksi][0], ql[ksi][1], ql[ksi][2], ql[ksi][3], b0, b1);
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int p = kb0 + nt * 8 + 2 * t4 + (j & 1);
+        const int r = (j < 2) ? r0 : r1;
+        bool vis = r < T && p < n_keys;
+        if (vis && p >= base) vis = mask != nullptr ? (mask[static_cast<size_t>(r) * T + (p - base)] != 0) : (p - base <= r);
+        sc[nt][j] = vis ? d[j] + e[j] : -INFINITY;
+      }
+    }
+    // ---- online softmax (rows r0: elements 0, 1; r1: elements 2, 3 of every tile) ----
+    float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) {
+      mx0 = fmaxf(mx0, fmaxf(sc[nt][0], sc[nt][1]));
+      mx1 = fmaxf(mx1, fmaxf(sc[nt][2], sc[nt][3]));
+    }
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+    const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+    const float c0 = (m0 == -INFINITY) ? 0.f : exp2f(m0 - mn0), c1 = (m1 == -INFINITY) ? 0.f : exp2f(m1 - mn1);
+    m0 = mn0; m1 = mn1;
+    float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) {
+      sc[nt][0] = (sc[nt][0] == -INFINITY) ? 0.f : exp2f(sc[nt][0] - mn0);
+      sc[nt][1] = (sc[nt][1] == -INFINITY) ? 0.f : exp2f(sc[nt][1] - mn0);
+      sc[nt][2] = (sc[nt][2] == -INFINITY) ? 0.f : exp2f(sc[nt][2] - mn1);
+      sc[nt][3] = (sc[nt][3] == -INFINITY) ? 0.f : exp2f(sc[nt][3] - mn1);
+      s0 += sc[nt][0] + sc[nt][1];
+      s1 += sc[nt][2] + sc[nt][3];
+    }
+    s0 += __shfl_xor_sync(0xffffffffu, s0, 1); s0 += __shfl_xor_sync(0xffffffffu, s0, 2);
+    s1 += __shfl_xor_sync(0xffffffffu, s1, 1); s1 += __shfl_xor_sync(0xffffffffu, s1, 2);
+    l0 = l0 * c0 + s0;
+    l1 = l1 * c1 + s1;
+#pragma unroll
+    for (int nd = 0; nd < 16; ++nd) { o[nd][0] *= c0; o[nd][1] *= c0; o[nd][2] *= c1; o[nd][3] *= c1; }
+    // ---- O += P V: 4 steps of 16 keys; the probabilities go in as a bf16 head plus a bf16 remainder ----
+#pragma unroll
+    for (int kk = 0; kk < 4; ++kk) {
+      unsigned ah[4], al[4];
+      wm_split2(sc[2 * kk][0], sc[2 * kk][1], ah[0], al[0]);
+      wm_split2(sc[2 * kk][2], sc[2 * kk][3], ah[1], al[1]);
+      wm_split2(sc[2 * kk + 1][0], sc[2 * kk + 1][1], ah[2], al[2]);
+      wm_split2(sc[2 * kk + 1][2], sc[2 * kk + 1][3], ah[3], al[3]);
+#pragma unroll
+      for (int nd = 0; nd < 16; ++nd) {
+        unsigned b0, b1;
+        asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];"
+                     : "=r"(b0), "=r"(b1) : "r"(smem_u32(&vs[kk * 16 + (lane & 15)][nd * 8])));
+        wm_mma(o[nd], ah[0], ah[1], ah[2], ah[3], b0, b1);
+        wm_mma(o[nd], al[0], al[1], al[2], al[3], b0, b1);
+      }
+    }
+  }
+  if (active) {
+    const float i0 = l0 > 0.f ? 1.f / l0 : 0.f, i1 = l1 > 0.f ? 1.f / l1 : 0.f;
+#pragma unroll
+    for (int nd = 0; nd < 16; ++nd) {
+      const int c = nd * 8 + 2 * t4;
+      if (r0 < T) *reinterpret_cast<float2*>(out + static_cast<size_t>(r0) * nq * WHD + static_cast<size_t>(head) * WHD + c) = make_float2(o[nd][0] * i0, o[nd][1] * i0);
+      if (r1 < T) *reinterpret_cast<float2*>(out + static_cast<size_t>(r1) * nq * WHD + static_cast<size_t>(head) * WHD + c) = make_float2(o[nd][2] * i1, o[nd][3] * i1);
+    }
+  }
+}
+
 }  // namespace ihb
 
 using namespace ihb;
@@ -245,10 +397,18 @@ extern "C" int ihb_qk_norm_rope_rows(float* qkv, int nq, int nkv, const float* q
 }
 
 extern "C" int ihb_window_attention(const float* qkv, int qkv_stride, const void* k_cache, const void* v_cache, int nq,
-                                    int nkv, int max_seq, int base, int T, const unsigned char* mask, float* out,
+                                    int nkv, int max_seq, int base, int T, const unsigned char* mask, float* out, int mode,
                                     cudaStream_t stream) {
   if (T < 1 || nq % nkv || base + T > max_seq) return cudaErrorInvalidValue;
   const int q_per_kv = nq / nkv;
+  if (mode != 1) {          // tensor-core tiles (the default); mode 1 keeps the per-token CUDA-core kernel
+    if (qkv_stride % 2) return cudaErrorInvalidValue;
+    const dim3 grid((T + 15) / 16, nkv, (q_per_kv + 7) / 8);
+    window_attn_mma_kernel<<<grid, 256, 0, stream>>>(qkv, qkv_stride, reinterpret_cast<const __nv_bfloat16*>(k_cache),
+                                                      reinterpret_cast<const __nv_bfloat16*>(v_cache), nq, nkv, max_seq, base, T,
+                                                      mask, out);
+    return cudaGetLastError();
+  }
   const dim3 grid(T, nkv, (q_per_kv + 7) / 8);
   window_attn_kernel<8><<<grid, WA_WARPS * 32, 0, stream>>>(qkv, qkv_stride, reinterpret_cast<const __nv_bfloat16*>(k_cache),
                                                            reinterpret_cast<const __nv_bfloat16*>(v_cache), nq, nkv, max_seq,

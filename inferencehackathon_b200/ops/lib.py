@@ -164,7 +164,7 @@ def load(build_if_missing: bool = True) -> C.CDLL:
     lib.ihb_qk_norm_rope_rows.argtypes = [_vp, C.c_int, C.c_int, _vp, _vp, C.c_float, _vp, _vp, _vp, _vp, _vp, _vp,
                                           C.c_int, C.c_int, _vp]
     lib.ihb_qk_norm_rope_rows.restype = C.c_int
-    lib.ihb_window_attention.argtypes = [_vp, C.c_int, _vp, _vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _vp, _vp, _vp]
+    lib.ihb_window_attention.argtypes = [_vp, C.c_int, _vp, _vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _vp, _vp, C.c_int, _vp]
     lib.ihb_window_attention.restype = C.c_int
     lib.ihb_a2a_rows.argtypes = [C.POINTER(IhbA2AArgs), C.c_int, _vp]
     lib.ihb_a2a_rows.restype = C.c_int
@@ -432,9 +432,12 @@ def qk_norm_rope_rows(qkv: torch.Tensor, nq: int, nkv: int, q_gamma, k_gamma, ep
 
 
 def window_attention(qkv: torch.Tensor, k_cache, v_cache, nq: int, nkv: int, max_seq: int, base: int,
-                     mask: Optional[torch.Tensor], out: torch.Tensor) -> None:
+                     mask: Optional[torch.Tensor], out: torch.Tensor, mode: Optional[int] = None) -> None:
+    """``mode`` 0: tensor-core tiles, 1: per-token CUDA-core kernel; default from ``IHB_WINDOW_ATTN`` (0)."""
+    if mode is None:
+        mode = int(os.environ.get("IHB_WINDOW_ATTN", "0"))
     check(load().ihb_window_attention(qkv.data_ptr(), qkv.shape[1], k_cache.data_ptr(), v_cache.data_ptr(), nq, nkv,
-                                      max_seq, base, qkv.shape[0], ptr(mask), out.data_ptr(), stream_ptr()),
+                                      max_seq, base, qkv.shape[0], ptr(mask), out.data_ptr(), mode, stream_ptr()),
           "ihb_window_attention")
 
 

@@ -60,7 +60,40 @@ class GpuWindow:
         self.sms = torch.cuda.get_device_properties(dev).multi_processor_count
         self.err = dec.err
         self._ws = {}
+        self._views = {}
+        self._args = {}                       # argument blocks of the GEMM launches, built once per (weight, tokens)
         self.n_gemm_launches = 0
+        # tensor parallel: the two all-reduces of a layer run as this package's fused kernel (reduce in the switch or
+        # over peer loads, residual add, RMSNorm of the next block) on a symmetric buffer of its own; IHB_WINDOW_FUSED_AR=0
+        # falls back to NCCL + separate norm. Building the buffer is a collective: every rank builds its window together.
+        self.ar = None
+        par = dec.cfg.parallel
+        if par.tp > 1 and par.world == par.tp and env_flag("IHB_WINDOW_FUSED_AR", 1):
+            from ..parallel.symm import SymmetricComm
+            self.ar = SymmetricComm(par, dev, slot_floats=2 * CHUNK * dec.H)
+            self.ar_epoch = torch.zeros(4, dtype=torch.int32, device=dev)
+            self.ar_counter = torch.zeros(8, dtype=torch.int32, device=dev)
+            self.ar_cm = self.ar.comm_block(self.ar_epoch)
+
+    def _all_reduce(self, part: torch.Tensor, resid: torch.Tensor, gamma: Optional[torch.Tensor], tag: str):
+        """sum over ranks of ``part`` + ``resid`` -> (new residual stream, its RMSNorm * gamma or None)."""
+        d = self.d
+        T, H = part.shape
+        if self.ar is None:
+            x = resid + d.comm_ref.all_reduce_tp(part.clone() if d.cfg.parallel.tp > 1 else part)
+            return x, None
+        out = self._buf("ar_out_" + tag, (T, H), torch.float32)
+        outn = self._buf("ar_norm_" + tag, (T, H), torch.float32) if gamma is not None else None
+        K.allreduce_norm(self.ar_cm, part, out, self.ar_counter, self.err, resid=resid, gamma=gamma,
+                         eps=d.cfg.model.rms_eps, out_norm=outn, algo=2)
+        return out, outn
+
+    def routing(self):
+        """Expert ids ``[layers, T, k]`` (int32) and weights of the last chunk that went through this path: every
+        token's routing decision as the device router took it."""
+        if getattr(self, "_last_route_shape", None) is None:
+            raise RuntimeError("no window has run yet")
+        return (self._buf("ti_all", self._last_route_shape, torch.int32), self._buf("tw_all", self._last_route_shape, torch.float32))
 
     @property
     def act_mode(self) -> str:
@@ -69,6 +102,13 @@ class GpuWindow:
 
     # ---- small helpers ---------------------------------------------------------------------------------------------
     def _buf(self, name: str, shape, dtype) -> torch.Tensor:
+        """Workspace tensor ``name`` of the given shape: the same storage (and the same view object) every time it is
+        asked for with the same shape, so that argument blocks built once stay valid and the host does no tensor
+        bookkeeping per launch."""
+        key = (name, tuple(shape), dtype)
+        v = self._views.get(key)
+        if v is not None:
+            return v
         t = self._ws.get(name)
         n = 1
         for s in shape:
@@ -76,7 +116,11 @@ class GpuWindow:
         if t is None or t.numel() < n or t.dtype != dtype:
             t = torch.zeros(max(n, 1), dtype=dtype, device=self.d.device)
             self._ws[name] = t
-        return t[:n].view(*shape)
+            self._views = {k: w for k, w in self._views.items() if k[0] != name}      # views of the old storage
+            self._args = {}                                                           # and blocks that point into it
+        v = t[:n].view(*shape)
+        self._views[key] = v
+        return v
 
     def _quant(self, x: torch.Tensor, gamma: Optional[torch.Tensor], tag: str, want_norm: bool = False):
         """x [T, K] fp32 -> (xq [T, K] e4m3|bf16 bytes, xs [ceil(K / 128), T] or None, xn or None)."""
@@ -111,42 +155,54 @@ class GpuWindow:
 
     def _linear(self, qw, xq, xs, T: int, tag: str) -> torch.Tensor:
         """[T, K] x W[rows, K]^T on the tensor cores."""
-        a = K.IhbTcArgs()
-        K.tc_fill_weight(a, self._w(qw, tag))
-        rows = a.rows
-        out = self._buf("o_" + tag, (T, rows), torch.float32)
-        a.X, a.mode, a.out_stride = xq.data_ptr(), K.TC_LINEAR, rows
-        if xs is not None:
-            a.xscale = xs.data_ptr()
-        a.T_total, a.err = T, self.err.data_ptr()
-        nkb = (a.K * self.es + 127) // 128
-        a.T, a.tok0, a.out = T, 0, out.data_ptr()
-        if T > TILE:
-            a.tok_tile, a.tok_tiles = TILE, -(-T // TILE)
-        tiles = ((rows + 127) // 128) * max(1, a.tok_tiles)
-        # split K only while the (row tile, token tile) units do not fill the GPU
-        a.ks = max(1, min(nkb, 16, (2 * self.sms) // tiles))
-        part = self._buf("part", (max(1, K.tc_partial_floats(a)),), torch.float32)
-        ctr = self._buf("ctr", (max(tiles, 1),), torch.int32)
-        a.partial, a.tile_counters = part.data_ptr(), ctr.data_ptr()
-        K.tc_gemm(a, False)
+        wq = self._w(qw, tag)
+        key = ("lin", wq.data.data_ptr(), xq.data_ptr(), T, tag)
+        hit = self._args.get(key)
+        if hit is None:
+            a = K.IhbTcArgs()
+            K.tc_fill_weight(a, wq)
+            rows = a.rows
+            out = self._buf("o_" + tag, (T, rows), torch.float32)
+            a.X, a.mode, a.out_stride = xq.data_ptr(), K.TC_LINEAR, rows
+            if xs is not None:
+                a.xscale = xs.data_ptr()
+            a.T_total, a.err = T, self.err.data_ptr()
+            nkb = (a.K * self.es + 127) // 128
+            a.T, a.tok0, a.out = T, 0, out.data_ptr()
+            if T > TILE:
+                a.tok_tile, a.tok_tiles = TILE, -(-T // TILE)
+            tiles = ((rows + 127) // 128) * max(1, a.tok_tiles)
+            # split K only while the (row tile, token tile) units do not fill the GPU
+            a.ks = max(1, min(nkb, 16, (2 * self.sms) // tiles))
+            part = self._buf("part", (max(1, K.tc_partial_floats(a)),), torch.float32)
+            ctr = self._buf("ctr", (max(tiles, 1),), torch.int32)
+            a.partial, a.tile_counters = part.data_ptr(), ctr.data_ptr()
+            hit = (a, out)
+            self._args[key] = hit
+        K.tc_gemm(hit[0], False)
         self.n_gemm_launches += 1
-        return out
+        return hit[1]
 
     def _grouped(self, qw, mode, rows: int, xq, xs, groups, n_groups, max_groups: int, nt: int, n_pairs: int, tag: str):
-        a = K.IhbTcArgs()
-        K.tc_fill_weight(a, self._w(qw, tag))
-        a.rows = rows
-        out = self._buf("g_" + tag, (n_pairs, rows), torch.float32)
-        a.X, a.mode, a.out, a.out_stride = xq.data_ptr(), mode, out.data_ptr(), rows
-        if xs is not None:
-            a.xscale = xs.data_ptr()
-        a.T, a.T_total, a.tok0, a.err = nt, n_pairs, 0, self.err.data_ptr()
-        a.top_k, a.ks = 1, 1
-        a.groups, a.n_groups, a.max_groups = groups.data_ptr(), n_groups.data_ptr(), max_groups
-        K.tc_gemm(a, False)
+        wq = self._w(qw, tag)
+        key = ("grp", wq.data.data_ptr(), xq.data_ptr(), n_pairs, nt, tag)
+        hit = self._args.get(key)
+        if hit is None:
+            a = K.IhbTcArgs()
+            K.tc_fill_weight(a, wq)
+            a.rows = rows
+            out = self._buf("g_" + tag, (n_pairs, rows), torch.float32)
+            a.X, a.mode, a.out, a.out_stride = xq.data_ptr(), mode, out.data_ptr(), rows
+            if xs is not None:
+                a.xscale = xs.data_ptr()
+            a.T, a.T_total, a.tok0, a.err = nt, n_pairs, 0, self.err.data_ptr()
+            a.top_k, a.ks = 1, 1
+            a.groups, a.n_groups, a.max_groups = groups.data_ptr(), n_groups.data_ptr(), max_groups
+            hit = (a, out)
+            self._args[key] = hit
+        K.tc_gemm(hit[0], False)
         self.n_gemm_launches += 1
-        return out
+        return hit[1]
 
     @staticmethod
     def _group_table(flat_e: torch.Tensor, n_experts: int, nt: int):
@@ -181,8 +237,10 @@ class GpuWindow:
         nq, nkv, H, I, k = d.nq, d.nkv, d.H, d.I, m.top_k
         mask_u8 = mask.to(torch.uint8).contiguous() if mask is not None else None
         self.aux_taps = {}
+        xn = None                                                # RMSNorm(x) * in_ln when the last all-reduce produced it
+        n_layers = len(w.layers)
         for L, lw in enumerate(w.layers):
-            xq, xs, _ = self._quant(x, lw.in_ln, "x")
+            xq, xs, _ = self._quant(xn, None, "x") if xn is not None else self._quant(x, lw.in_ln, "x")
             qkv = self._linear(lw.wqkv, xq, xs, T, "qkv")
             K.qk_norm_rope_rows(qkv, nq, nkv, lw.q_norm, lw.k_norm, m.rms_eps, d.cos, d.sin, pos32, slots,
                                 d.k_cache[L], d.v_cache[L], d.max_seq)
@@ -190,16 +248,17 @@ class GpuWindow:
             K.window_attention(qkv, d.k_cache[L], d.v_cache[L], nq, nkv, d.max_seq, base, mask_u8, attn)
             aq, asc, _ = self._quant(attn, None, "a")
             o = self._linear(lw.wo, aq, asc, T, "wo")
-            x = x + d.comm_ref.all_reduce_tp(o.clone() if d.cfg.parallel.tp > 1 else o)        # a new tensor: x's old buffer is free again
-            hq, hs, h2 = self._quant(x, lw.post_ln, "h", want_norm=True)
+            x, h2 = self._all_reduce(o, x, lw.post_ln, "a" + str(L & 1))
+            if h2 is not None:
+                hq, hs, _ = self._quant(h2, None, "h")
+            else:
+                hq, hs, h2 = self._quant(x, lw.post_ln, "h", want_norm=True)
             # fused router (logits, softmax, top-k) and the expert group table: kernels of this package, on the device
             pairs = T * k
             E_l = lw.w_gu.data.shape[0]
-            ti = self._buf("ti", (T, k), torch.int32)
-            tw = self._buf("tw", (T, k), torch.float32)
+            ti = self._buf("ti_all", (n_layers, T, k), torch.int32)[L]
+            tw = self._buf("tw_all", (n_layers, T, k), torch.float32)[L]
             K.router_topk_rows(h2, lw.router, k, bool(m.norm_topk_prob), ti, tw)
-            d.sel_idx[L].copy_(ti[-1])                          # routing telemetry of the window's last token
-            d.sel_w[L].copy_(tw[-1])
             per = max(1, pairs // E_l)
             nt = 16 if per <= 12 else 32 if per <= 28 else 64
             gmax = E_l + pairs // nt + 1
@@ -217,16 +276,22 @@ class GpuWindow:
             act = self._grouped(lw.w_gu, K.TC_GATEUP, I, gq, gs, groups, n_groups, gmax, nt, pairs, "act")
             cq, cs, _ = self._quant(act, None, "c")
             yg = self._grouped(lw.w_d, K.TC_DOWN, H, cq, cs, groups, n_groups, gmax, nt, pairs, "y")
-            y = self._buf("ycomb", (T, H), torch.float32)
             if d.cfg.parallel.tp > 1:
+                y = self._buf("ycomb", (T, H), torch.float32)
                 K.moe_combine_rows(yg, inv, tw, k, y)               # slot order: deterministic
-                x = x + d.comm_ref.all_reduce_tp(y)
+                nxt = w.layers[L + 1].in_ln if L + 1 < n_layers else None
+                x, xn = self._all_reduce(y, x, nxt, "m" + str(L & 1))
             else:
                 xnew = self._buf("xres" + str(L & 1), (T, H), torch.float32)
                 K.moe_combine_rows(yg, inv, tw, k, xnew, resid=x)
                 x = xnew
             if L in aux_layers:
                 self.aux_taps[L] = x.clone()
+        self._last_route_shape = (n_layers, T, k)
+        if n_layers:
+            # routing telemetry of the window's last token, all layers in one copy
+            d.sel_idx.copy_(self._buf("ti_all", (n_layers, T, k), torch.int32)[:, -1])
+            d.sel_w.copy_(self._buf("tw_all", (n_layers, T, k), torch.float32)[:, -1])
         return x
 
     def _head(self, x: torch.Tensor) -> torch.Tensor:

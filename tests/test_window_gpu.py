@@ -12,6 +12,36 @@ def _prompt(n, seed=3):
     return torch.randint(0, SMALL.vocab, (n,), generator=torch.Generator().manual_seed(seed)).tolist()
 
 
+def _forced_routing(ref, eng):
+    """Makes the reference model take the expert choices the engine's device router took in its last window (the
+    weights still come from the reference's own logits). A router near-tie can be decided either way by rounding noise
+    far below any tolerance, and the flipped expert then moves that token's logits by several per cent: comparing with
+    the routing pinned removes that lottery, and the agreement of the free routing is checked on its own. Returns a
+    function that restores free routing and reports the share of (layer, token) pairs whose expert SETS agreed."""
+    ti, _ = eng.gpu.window().routing()
+    ti = ti.clone().long()
+    stats = {"same": 0, "all": 0}
+
+    def route_fn(L, h, router_w, top_k, renorm):
+        logits = h.float() @ router_w.float().t()
+        probs = torch.softmax(logits, -1)
+        free = torch.topk(probs, top_k, dim=-1).indices
+        idx = ti[L, : h.shape[0]]
+        stats["same"] += int((free.sort(-1).values == idx.sort(-1).values).all(-1).sum())
+        stats["all"] += h.shape[0]
+        w = probs.gather(-1, idx)
+        if renorm:
+            w = w / w.sum(-1, keepdim=True)
+        return idx, w, logits
+
+    ref.model.route_fn = route_fn
+
+    def done():
+        ref.model.route_fn = None
+        return stats["same"] / max(1, stats["all"])
+    return done
+
+
 def _pair(weights, max_seq=512):
     dev = "cuda:0"
     ref = InferenceEngine.build("small", weights=weights, device=dev, backend="torch", max_seq=max_seq)
@@ -116,9 +146,12 @@ def test_window_on_the_block_fp8_gemm_path(monkeypatch):
     ref, eng = _pair("fp8_block")
     assert eng.gpu.window().act_mode == "fp8"
     toks = _prompt(150)
-    a = ref.logits_for(toks, commit=True)
     b = eng.logits_for(toks, commit=True)
-    assert float((a - b).abs().max()) < 0.08 * float(a.abs().max())
+    done = _forced_routing(ref, eng)
+    a = ref.logits_for(toks, commit=True)
+    done()
+    # e4m3 activations sit on rounding boundaries: a flipped code in one layer moves later rows a little
+    assert float((a - b).abs().max()) < 0.06 * float(a.abs().max())
     eng.gpu.check_error()
 
 
@@ -126,19 +159,23 @@ def test_window_on_the_block_fp8_gemm_path(monkeypatch):
 def test_window_logits_match_reference_chain_and_chunks(weights):
     ref, eng = _pair(weights)
     toks = _prompt(150)                                          # two token tiles: 128 + 22
-    a = ref.logits_for(toks[:150], commit=True)
     b = eng.logits_for(toks[:150], commit=True)
+    done = _forced_routing(ref, eng)
+    a = ref.logits_for(toks[:150], commit=True)
+    assert done() > 0.97                                         # the device router agrees with the free reference routing
     assert b.shape == a.shape and eng.seq_len == 150
     scale = float(a.abs().max())
-    # e4m3 activations sit on rounding boundaries: a flipped code in one layer moves later rows a little
-    tol = 0.03 if weights == "bf16" else 0.08
+    # with the routing pinned the logits agree closely; block-fp8 weights are multiplied as their bf16 copies (0.2 % per
+    # weight on top of the bf16 activation rounding both sides share)
+    tol = 0.01 if weights == "bf16" else 0.025
     assert float((a - b).abs().max()) < tol * scale
-    assert float((a[:4] - b[:4]).abs().max()) < 0.01 * scale
-    assert float((a.argmax(-1) == b.argmax(-1)).float().mean()) > 0.85
+    assert float((a.argmax(-1) == b.argmax(-1)).float().mean()) > 0.9
     # a second window on top of the cached context
     more = _prompt(9, seed=5)
-    a2 = ref.logits_for(more)
     b2 = eng.logits_for(more)
+    done = _forced_routing(ref, eng)
+    a2 = ref.logits_for(more)
+    done()
     assert float((a2 - b2).abs().max()) < tol * float(a2.abs().max())
     eng.gpu.check_error()
 
@@ -147,7 +184,10 @@ def test_window_logits_match_reference_chain_and_chunks(weights):
 def test_window_tree_mask_and_rollback(weights):
     ref, eng = _pair(weights)
     ctx = _prompt(40)
-    ref.logits_for(ctx); eng.logits_for(ctx)
+    eng.logits_for(ctx)
+    done = _forced_routing(ref, eng)
+    ref.logits_for(ctx)
+    done()
     # root + 5 nodes: 0 -> {1, 2}, 1 -> {3, 4}, 2 -> {5}
     parent = [0, 0, 0, 1, 1, 2]
     n = len(parent)
@@ -162,10 +202,12 @@ def test_window_tree_mask_and_rollback(weights):
             j = parent[j]
     toks = _prompt(n, seed=9)
     pos = torch.tensor([40 + dpt for dpt in depth], device="cuda:0")
-    a = ref.logits_for(toks, commit=False, tree_mask=mask, positions=pos)
     b = eng.logits_for(toks, commit=False, tree_mask=mask, positions=pos)
+    done = _forced_routing(ref, eng)
+    a = ref.logits_for(toks, commit=False, tree_mask=mask, positions=pos)
+    done()
     assert eng.seq_len == 40 and ref.seq_len == 40
-    assert float((a - b).abs().max()) < (0.03 if weights == "bf16" else 0.08) * float(a.abs().max())
+    assert float((a - b).abs().max()) < (0.01 if weights == "bf16" else 0.025) * float(a.abs().max())
     # node 3's row must equal a plain chain root -> 1 -> 3
     chain = [toks[0], toks[1], toks[3]]
     c = eng.logits_for(chain, commit=False)
@@ -206,3 +248,37 @@ def test_speculative_driver_on_gpu_engine_equals_its_own_greedy():
     out, tel = se.decode(prompt, DecodeStop(16), Rng(0))
     assert out == plain
     assert r2.forwards <= 16
+
+
+@pytest.mark.parametrize("T,base,nq,nkv,masked", [(40, 0, 8, 1, False), (130, 77, 16, 2, False), (23, 300, 8, 2, True),
+                                                   (16, 0, 4, 1, True), (257, 1000, 8, 1, False)])
+def test_window_attention_tensor_core_tiles_against_fp32(T, base, nq, nkv, masked):
+    """Both window attention kernels (tensor-core tiles; one CTA per token) against plain fp32 PyTorch on the same
+    bf16 cache rows: cached context + the window's own rows, causal or with an explicit visibility mask."""
+    import math
+    from inferencehackathon_b200.ops import lib as K
+    K.load()
+    d = torch.device("cuda", 0)
+    g = torch.Generator(device=d).manual_seed(T + base)
+    max_seq = base + T + 5
+    kc = torch.randn(nkv, max_seq, 128, device=d, generator=g).to(torch.bfloat16)
+    vc = torch.randn(nkv, max_seq, 128, device=d, generator=g).to(torch.bfloat16)
+    qkv = torch.randn(T, (nq + 2 * nkv) * 128, device=d, generator=g)
+    mask = None
+    vis = torch.ones(T, base + T, dtype=torch.bool, device=d)
+    if masked:
+        mask = torch.rand(T, T, device=d, generator=g) < 0.4
+        mask |= torch.eye(T, dtype=torch.bool, device=d)                 # a token always sees itself
+        vis[:, base:] = mask
+    else:
+        vis[:, base:] = torch.tril(torch.ones(T, T, dtype=torch.bool, device=d))
+    q = qkv[:, : nq * 128].reshape(T, nkv, nq // nkv, 128)
+    s = torch.einsum("tkgd,ksd->tkgs", q, kc[:, : base + T].float()) / math.sqrt(128)
+    s = s.masked_fill(~vis[:, None, None, :], float("-inf"))
+    want = torch.einsum("tkgs,ksd->tkgd", torch.softmax(s, -1), vc[:, : base + T].float()).reshape(T, nq * 128)
+    mu8 = mask.to(torch.uint8).contiguous() if mask is not None else None
+    for mode in (0, 1):
+        out = torch.full((T, nq * 128), float("nan"), device=d)
+        K.window_attention(qkv, kc, vc, nq, nkv, max_seq, base, mu8, out, mode=mode)
+        torch.cuda.synchronize()
+        assert float((out - want).abs().max()) < 2e-3, mode
