@@ -250,6 +250,10 @@ int ihb_moe_gather_rows(const void* src, const int* order, int k, int row_bytes,
 int ihb_moe_combine_rows(const float* yg, const int* inv, const float* tw, int k, int H, int T, const float* resid, float* y,
                          cudaStream_t stream);
 
+// Block-scaled e4m3 weights W [nmat][rows][K] with scale [nmat][nrb][nkb] (one fp32 per rb x kb block) -> bf16 copies.
+int ihb_dequant_bf16(const void* W, const float* scale, long long nmat, int rows, int K, int rb, int kb, int nrb, int nkb, void* out,
+                     cudaStream_t stream);
+
 // ---- stand-alone fused all-reduce (+ residual + RMSNorm) over symmetric memory -----------------------------------------
 // x [T, H] fp32 partial of this rank -> out = sum over ranks (+ resid); out_norm = RMSNorm(out) * gamma (gamma != NULL).
 // algo 0 = by size, 1 = one-shot (push + one barrier, every rank adds), 2 = two-shot (row owners reduce with

@@ -7,6 +7,7 @@
 //   * combine: the experts' outputs, weighted, summed in slot order (deterministic) and added to the residual.
 // The reference does this per token at batch 1 (kernels/k4_router.cu) and, for prefill, with a per-expert loop driven
 // from the host (kernels/prefill_moe.cu:61-170).
+#include <algorithm>
 #include "common.cuh"
 
 namespace ihb {
@@ -72,6 +73,133 @@ __global__ void __launch_bounds__(RT_THREADS) router_topk_rows_kernel(const floa
     for (int j = 0; j < 8; ++j) {
       const int e = lane + 32 * j;
       v[j] = e < E ? lg[warp][e] : -INFINITY;
+      mx = fmaxf(mx, v[j]);
+      if (logits_out != nullptr && e < E) logits_out[static_cast<size_t>(t) * E + e] = v[j];
+    }
+    mx = warp_max(mx);
+    float sum = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) sum += (lane + 32 * j < E) ? __expf(v[j] - mx) : 0.f;
+    sum = warp_sum(sum);
+    float my_p = 0.f;
+    int my_e = 0;
+    for (int k = 0; k < top_k; ++k) {
+      float bv = -INFINITY;
+      int bi = 0x7fffffff;
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (v[j] > bv) { bv = v[j]; bi = lane + 32 * j; }
+      const float mv = warp_max(bv);
+      const int wi = __reduce_min_sync(0xffffffffu, bv == mv ? bi : 0x7fffffff);
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (lane + 32 * j == wi) v[j] = -INFINITY;
+      if (lane == k) { my_p = __expf(mv - mx) / sum; my_e = wi; }
+    }
+    float den = 1.f;
+    if (renorm) den = warp_sum(lane < top_k ? my_p : 0.f);
+    if (lane < top_k) {
+      ti[static_cast<size_t>(t) * top_k + lane] = my_e;
+      tw[static_cast<size_t>(t) * top_k + lane] = my_p / den;
+    }
+  }
+}
+
+// ---- the same router on the tensor cores: 16 tokens per CTA, logits as m16n8k16 tiles ---------------------------------------------
+// h stays fp32 in shared memory and is split into a bf16 head and a bf16 remainder when a fragment is built, so the
+// logits keep fp32 accuracy against the bf16 router rows (a router decision must not depend on activation rounding).
+// Chunks of 64 channels of h [16][64] and of the router [E][64] arrive by cp.async, double buffered; warp w owns the
+// expert tiles w, w + 8, ... (8 experts each).
+constexpr int RM_TOK = 16, RM_KC = 64, RM_HLD = RM_KC + 4, RM_WLD = RM_KC + 8;
+struct RmSmem {
+  float h[2][RM_TOK][RM_HLD];
+  __nv_bfloat16 w[2][256][RM_WLD];
+  float lg[RM_TOK][256];
+};
+__device__ __forceinline__ void rm_cp16(void* dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void rm_split2(float x, float y, unsigned& hi, unsigned& lo) {
+  const __nv_bfloat16 hx = __float2bfloat16(x), hy = __float2bfloat16(y);
+  const __nv_bfloat162 h = __halves2bfloat162(hx, hy);
+  const __nv_bfloat162 l = __floats2bfloat162_rn(x - __bfloat162float(hx), y - __bfloat162float(hy));
+  hi = *reinterpret_cast<const unsigned*>(&h);
+  lo = *reinterpret_cast<const unsigned*>(&l);
+}
+__global__ void __launch_bounds__(256) router_topk_rows_mma_kernel(const float* __restrict__ h, const __nv_bfloat16* __restrict__ W,
+                                                                   int T, int H, int E, int top_k, int renorm,
+                                                                   float* __restrict__ logits_out, int* __restrict__ ti,
+                                                                   float* __restrict__ tw) {
+  extern __shared__ __align__(16) uint8_t rm_raw[];
+  RmSmem& sm = *reinterpret_cast<RmSmem*>(rm_raw);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
+  const int t0 = blockIdx.x * RM_TOK;
+  const int nchunks = H / RM_KC;
+  auto issue = [&](int c, int buf) {
+    const int k0 = c * RM_KC;
+    for (int i = tid; i < RM_TOK * (RM_KC / 4); i += 256) {           // 16 tokens x 16 pieces of 4 floats
+      const int r = i / (RM_KC / 4), p = i % (RM_KC / 4);
+      rm_cp16(&sm.h[buf][r][p * 4], h + static_cast<size_t>(min(t0 + r, T - 1)) * H + k0 + p * 4);
+    }
+    for (int i = tid; i < E * (RM_KC / 8); i += 256) {                 // E rows x 8 pieces of 8 bf16
+      const int r = i / (RM_KC / 8), p = i % (RM_KC / 8);
+      rm_cp16(&sm.w[buf][r][p * 8], W + static_cast<size_t>(r) * H + k0 + p * 8);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  float acc[4][4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+  issue(0, 0);
+  for (int c = 0; c < nchunks; ++c) {
+    const int buf = c & 1;
+    if (c + 1 < nchunks) { issue(c + 1, buf ^ 1); asm volatile("cp.async.wait_group 1;" ::: "memory"); }
+    else asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
+#pragma unroll
+    for (int ks = 0; ks < RM_KC / 16; ++ks) {
+      const int k0 = ks * 16 + 2 * t4;
+      unsigned ah[4], al[4];
+      const float2 a0 = *reinterpret_cast<const float2*>(&sm.h[buf][g][k0]), a1 = *reinterpret_cast<const float2*>(&sm.h[buf][g + 8][k0]);
+      const float2 a2 = *reinterpret_cast<const float2*>(&sm.h[buf][g][k0 + 8]), a3 = *reinterpret_cast<const float2*>(&sm.h[buf][g + 8][k0 + 8]);
+      rm_split2(a0.x, a0.y, ah[0], al[0]); rm_split2(a1.x, a1.y, ah[1], al[1]);
+      rm_split2(a2.x, a2.y, ah[2], al[2]); rm_split2(a3.x, a3.y, ah[3], al[3]);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int e = (warp + 8 * j) * 8 + g;
+        if ((warp + 8 * j) * 8 < E) {
+          const unsigned b0 = *reinterpret_cast<const unsigned*>(&sm.w[buf][e][k0]);
+          const unsigned b1 = *reinterpret_cast<const unsigned*>(&sm.w[buf][e][k0 + 8]);
+          asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                       : "+f"(acc[j][0]), "+f"(acc[j][1]), "+f"(acc[j][2]), "+f"(acc[j][3])
+                       : "r"(ah[0]), "r"(ah[1]), "r"(ah[2]), "r"(ah[3]), "r"(b0), "r"(b1));
+          asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                       : "+f"(acc[j][0]), "+f"(acc[j][1]), "+f"(acc[j][2]), "+f"(acc[j][3])
+                       : "r"(al[0]), "r"(al[1]), "r"(al[2]), "r"(al[3]), "r"(b0), "r"(b1));
+        }
+      }
+    }
+    __syncthreads();                 // the buffer is refilled two iterations later
+  }
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int e = (warp + 8 * j) * 8 + 2 * t4;
+    if ((warp + 8 * j) * 8 < E) {
+      if (e < E) { sm.lg[g][e] = acc[j][0]; sm.lg[g + 8][e] = acc[j][2]; }
+      if (e + 1 < E) { sm.lg[g][e + 1] = acc[j][1]; sm.lg[g + 8][e + 1] = acc[j][3]; }
+    }
+  }
+  __syncthreads();
+  // softmax + top-k: a warp takes tokens warp and warp + 8
+  for (int r = warp; r < RM_TOK; r += 8) {
+    const int t = t0 + r;
+    if (t >= T) continue;
+    float v[8];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int e = lane + 32 * j;
+      v[j] = e < E ? sm.lg[r][e] : -INFINITY;
       mx = fmaxf(mx, v[j]);
       if (logits_out != nullptr && e < E) logits_out[static_cast<size_t>(t) * E + e] = v[j];
     }
@@ -191,13 +319,66 @@ __global__ void __launch_bounds__(256) moe_combine_rows_kernel(const float* __re
   }
 }
 
+// ---- block-scaled e4m3 -> bf16 (the window path multiplies bf16 copies of fp8 weights): 16 weights per thread --------------------
+// W [nmat][rows][K] e4m3, scale [nmat][ceil(rows / rb)][nkb] (one fp32 per rb x kb block), out bf16 of W's shape. K % 16 == 0.
+__global__ void __launch_bounds__(256) dequant_bf16_kernel(const uint8_t* __restrict__ W, const float* __restrict__ scale,
+                                                           size_t nmat, int rows, int K, int rb, int kb, int nrb, int nkb,
+                                                           __nv_bfloat16* __restrict__ out) {
+  const size_t per_row = static_cast<size_t>(K) / 16;
+  const size_t total = nmat * rows * per_row;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * 256 + threadIdx.x; i < total; i += static_cast<size_t>(gridDim.x) * 256) {
+    const size_t rowi = i / per_row;
+    const int c16 = static_cast<int>(i - rowi * per_row);
+    const size_t m = rowi / rows;
+    const int r = static_cast<int>(rowi - m * rows);
+    const uint4 w = *reinterpret_cast<const uint4*>(W + rowi * K + static_cast<size_t>(c16) * 16);
+    // a 16-element piece may straddle two K blocks only if kb is not a multiple of 16, which the formats here never have
+    const float sc = scale[(m * nrb + r / rb) * nkb + (c16 * 16) / kb];
+    const unsigned wv[4] = {w.x, w.y, w.z, w.w};
+    unsigned o[8];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const float2 lo = __half22float2(cvt_e4m3x2(static_cast<unsigned short>(wv[q] & 0xffffu)));
+      const float2 hi = __half22float2(cvt_e4m3x2(static_cast<unsigned short>(wv[q] >> 16)));
+      const __nv_bfloat162 a = __floats2bfloat162_rn(lo.x * sc, lo.y * sc), b = __floats2bfloat162_rn(hi.x * sc, hi.y * sc);
+      o[2 * q] = *reinterpret_cast<const unsigned*>(&a);
+      o[2 * q + 1] = *reinterpret_cast<const unsigned*>(&b);
+    }
+    uint4* dst = reinterpret_cast<uint4*>(out + rowi * K + static_cast<size_t>(c16) * 16);
+    dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+    dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+  }
+}
+
 }  // namespace ihb
 
 using namespace ihb;
 
+extern "C" int ihb_dequant_bf16(const void* W, const float* scale, long long nmat, int rows, int K, int rb, int kb, int nrb, int nkb,
+                                void* out, cudaStream_t stream) {
+  if (nmat < 1 || rows < 1 || K < 16 || K % 16 || rb < 1 || kb < 16 || kb % 16) return cudaErrorInvalidValue;
+  const size_t total = static_cast<size_t>(nmat) * rows * (K / 16);
+  const int grid = static_cast<int>(std::min<size_t>((total + 255) / 256, 148 * 16));
+  dequant_bf16_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<const uint8_t*>(W), scale, static_cast<size_t>(nmat), rows, K, rb, kb,
+                                                nrb, nkb, reinterpret_cast<__nv_bfloat16*>(out));
+  return cudaGetLastError();
+}
+
 extern "C" int ihb_router_topk_rows(const float* h, const void* router_bf16, int T, int H, int E, int top_k, int renorm,
                                     float* logits, int* ti, float* tw, cudaStream_t stream) {
   if (T < 1 || E < 1 || E > 256 || top_k < 1 || top_k > 8 || top_k > E || H % 8) return cudaErrorInvalidValue;
+  if (H % RM_KC == 0 && T >= 4) {            // tensor-core tiles; very short windows and odd widths take the plain kernel
+    static bool attr_set = false;
+    if (!attr_set) {
+      cudaError_t e = cudaFuncSetAttribute(router_topk_rows_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           static_cast<int>(sizeof(RmSmem)));
+      if (e != cudaSuccess) return e;
+      attr_set = true;
+    }
+    router_topk_rows_mma_kernel<<<(T + RM_TOK - 1) / RM_TOK, 256, sizeof(RmSmem), stream>>>(
+        h, reinterpret_cast<const __nv_bfloat16*>(router_bf16), T, H, E, top_k, renorm, logits, ti, tw);
+    return cudaGetLastError();
+  }
   router_topk_rows_kernel<<<(T + RT_TOK - 1) / RT_TOK, RT_THREADS, 0, stream>>>(
       h, reinterpret_cast<const __nv_bfloat16*>(router_bf16), T, H, E, top_k, renorm, logits, ti, tw);
   return cudaGetLastError();

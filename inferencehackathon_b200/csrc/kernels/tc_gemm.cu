@@ -380,18 +380,21 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         named_bar_sync(2, 128);
         finisher = sh.last_flag != 0;
         if (finisher) {
+          // members in a fixed order (deterministic sums); all token columns of one member are read together, so
+          // that a member costs one memory round trip instead of one per column
           const float* p0 = a.partial + static_cast<size_t>(un.tile) * members * (NA * NT * TC_BM);
 #pragma unroll
           for (int ai = 0; ai < NA; ++ai)
 #pragma unroll
-            for (int n = 0; n < NT; ++n) {
-              if (n < un.ntok) {
-                float s = 0.f;
-                for (int mbr = 0; mbr < members; ++mbr)
-                  s += ld_cg_f(p0 + (static_cast<size_t>(mbr) * NA * NT + ai * NT + n) * TC_BM + r_in_tile);
-                acc[ai][n] = s;
-              }
-            }
+            for (int n = 0; n < NT; ++n) acc[ai][n] = 0.f;
+          for (int mbr = 0; mbr < members; ++mbr) {
+            const float* pm = p0 + static_cast<size_t>(mbr) * NA * NT * TC_BM + r_in_tile;
+#pragma unroll
+            for (int ai = 0; ai < NA; ++ai)
+#pragma unroll
+              for (int n = 0; n < NT; ++n)
+                if (n < un.ntok) acc[ai][n] += ld_cg_f(pm + static_cast<size_t>(ai * NT + n) * TC_BM);
+          }
         }
         named_bar_sync(2, 128);      // last_flag is rewritten by the next unit
       } else if (a.mode == IHB_TC_DOWN) {

@@ -251,7 +251,8 @@ __device__ __forceinline__ void wm_split2(float x, float y, unsigned& hi, unsign
   lo = wm_pack_bf16(x - __bfloat162float(hx), y - __bfloat162float(hy));
 }
 
-__global__ void __launch_bounds__(256) window_attn_mma_kernel(
+template <int HPC>          // query heads (= warps) per CTA: 8, or 4 when 8 would leave most SMs without a CTA
+__global__ void __launch_bounds__(HPC * 32) window_attn_mma_kernel(
     const float* __restrict__ qkv, int qkv_stride, const __nv_bfloat16* __restrict__ k_cache,
     const __nv_bfloat16* __restrict__ v_cache, int nq, int nkv, int max_seq, int base, int T,
     const uint8_t* __restrict__ mask, float* __restrict__ out) {
@@ -261,8 +262,8 @@ __global__ void __launch_bounds__(256) window_attn_mma_kernel(
   const int g = lane >> 2, t4 = lane & 3;
   const int t0 = blockIdx.x * 16, kvh = blockIdx.y, grp = blockIdx.z;
   const int q_per_kv = nq / nkv;
-  const int gq = min(8, q_per_kv - grp * 8);
-  const int head = kvh * q_per_kv + grp * 8 + warp;
+  const int gq = min(HPC, q_per_kv - grp * HPC);
+  const int head = kvh * q_per_kv + grp * HPC + warp;
   const bool active = warp < gq;
   const float qscale = 0.08838834764831845f * 1.4426950408889634f;   // 1 / sqrt(128) * log2(e)
   const int r0 = t0 + g, r1 = t0 + g + 8;                              // this thread's two rows (window tokens)
@@ -289,7 +290,7 @@ __global__ void __launch_bounds__(256) window_attn_mma_kernel(
   const __nv_bfloat16* vbase = v_cache + static_cast<size_t>(kvh) * max_seq * WHD;
   for (int kb0 = 0; kb0 < n_keys; kb0 += WM_KB) {
     __syncthreads();                                   // the previous block's readers are done
-    for (int i = tid; i < WM_KB * 16; i += 256) {
+    for (int i = tid; i < WM_KB * 16; i += HPC * 32) {
       const int r = i >> 4, ch = i & 15;
       const int p = min(kb0 + r, n_keys - 1);          // rows past the end repeat a valid row; they are masked below
       *reinterpret_cast<uint4*>(&ks[r][ch * 8]) = *reinterpret_cast<const uint4*>(kbase + static_cast<size_t>(p) * WHD + ch * 8);
@@ -403,10 +404,18 @@ extern "C" int ihb_window_attention(const float* qkv, int qkv_stride, const void
   const int q_per_kv = nq / nkv;
   if (mode != 1) {          // tensor-core tiles (the default); mode 1 keeps the per-token CUDA-core kernel
     if (qkv_stride % 2) return cudaErrorInvalidValue;
-    const dim3 grid((T + 15) / 16, nkv, (q_per_kv + 7) / 8);
-    window_attn_mma_kernel<<<grid, 256, 0, stream>>>(qkv, qkv_stride, reinterpret_cast<const __nv_bfloat16*>(k_cache),
-                                                      reinterpret_cast<const __nv_bfloat16*>(v_cache), nq, nkv, max_seq, base, T,
-                                                      mask, out);
+    const int ctas8 = ((T + 15) / 16) * nkv * ((q_per_kv + 7) / 8);
+    if (ctas8 >= 120 || q_per_kv <= 4) {
+      const dim3 grid((T + 15) / 16, nkv, (q_per_kv + 7) / 8);
+      window_attn_mma_kernel<8><<<grid, 256, 0, stream>>>(qkv, qkv_stride, reinterpret_cast<const __nv_bfloat16*>(k_cache),
+                                                           reinterpret_cast<const __nv_bfloat16*>(v_cache), nq, nkv, max_seq, base, T,
+                                                           mask, out);
+    } else {
+      const dim3 grid((T + 15) / 16, nkv, (q_per_kv + 3) / 4);
+      window_attn_mma_kernel<4><<<grid, 128, 0, stream>>>(qkv, qkv_stride, reinterpret_cast<const __nv_bfloat16*>(k_cache),
+                                                           reinterpret_cast<const __nv_bfloat16*>(v_cache), nq, nkv, max_seq, base, T,
+                                                           mask, out);
+    }
     return cudaGetLastError();
   }
   const dim3 grid(T, nkv, (q_per_kv + 7) / 8);

@@ -179,6 +179,8 @@ def load(build_if_missing: bool = True) -> C.CDLL:
     lib.ihb_moe_gather_rows.restype = C.c_int
     lib.ihb_moe_combine_rows.argtypes = [_vp, _vp, _vp, C.c_int, C.c_int, C.c_int, _vp, _vp, _vp]
     lib.ihb_moe_combine_rows.restype = C.c_int
+    lib.ihb_dequant_bf16.argtypes = [_vp, _vp, C.c_longlong, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _vp, _vp]
+    lib.ihb_dequant_bf16.restype = C.c_int
     lib.ihb_mega_decode.argtypes = [C.POINTER(IhbMegaArgs), C.c_int, _vp]
     lib.ihb_mega_decode.restype = C.c_int
     lib.ihb_mega_max_grid.argtypes = [C.POINTER(IhbMegaArgs)]
@@ -467,6 +469,15 @@ def moe_combine_rows(yg: torch.Tensor, inv: torch.Tensor, tw: torch.Tensor, k: i
     T, H = y.shape
     check(load().ihb_moe_combine_rows(yg.data_ptr(), inv.data_ptr(), tw.data_ptr(), k, H, T, ptr(resid), y.data_ptr(),
                                       stream_ptr()), "ihb_moe_combine_rows")
+
+
+def dequant_bf16(qw, out: torch.Tensor) -> None:
+    """bf16 copy of a block-scaled e4m3 :class:`QWeight` (``data [..., rows, K]``, ``scale [..., nrb, nkb]``)."""
+    rows, Kd = qw.data.shape[-2], qw.data.shape[-1]
+    nmat = qw.data.numel() // (rows * Kd)
+    sc = qw.scale.contiguous()
+    check(load().ihb_dequant_bf16(qw.data.data_ptr(), sc.data_ptr(), nmat, rows, Kd, qw.rb, qw.kb, sc.shape[-2], sc.shape[-1],
+                                  out.data_ptr(), stream_ptr()), "ihb_dequant_bf16")
 
 
 def a2a_rows(args: IhbA2AArgs, grid: int = 32) -> None:

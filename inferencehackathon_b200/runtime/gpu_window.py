@@ -142,7 +142,9 @@ class GpuWindow:
             return hit
         out = (torch.empty(qw.data.shape, dtype=torch.bfloat16, device=qw.data.device) if self._resident
                else self._buf("w_" + tag, tuple(qw.data.shape), torch.bfloat16))
-        if qw.data.dim() == 3:
+        if qw.data.shape[-1] % 16 == 0 and qw.kb % 16 == 0 and qw.data.is_contiguous():
+            K.dequant_bf16(qw, out)                                          # one pass: 1 byte read, 2 written per weight
+        elif qw.data.dim() == 3:
             step = max(1, (256 << 20) // max(1, qw.data[0].numel()))       # fp32 temporaries of ~1 GB at most
             for e0 in range(0, qw.data.shape[0], step):
                 out[e0:e0 + step] = qw.select(slice(e0, e0 + step)).dequant(torch.bfloat16)
@@ -172,8 +174,8 @@ class GpuWindow:
             if T > TILE:
                 a.tok_tile, a.tok_tiles = TILE, -(-T // TILE)
             tiles = ((rows + 127) // 128) * max(1, a.tok_tiles)
-            # split K only while the (row tile, token tile) units do not fill the GPU
-            a.ks = max(1, min(nkb, 16, (2 * self.sms) // tiles))
+            # split K only while the (row tile, token tile) units do not fill the GPU once
+            a.ks = max(1, min(nkb, 16, self.sms // tiles))
             part = self._buf("part", (max(1, K.tc_partial_floats(a)),), torch.float32)
             ctr = self._buf("ctr", (max(tiles, 1),), torch.int32)
             a.partial, a.tile_counters = part.data_ptr(), ctr.data_ptr()

@@ -91,7 +91,8 @@ def test_router_grouping_gather_and_combine_kernels():
     K.load()
     d = torch.device("cuda", 0)
     g = torch.Generator(device=d).manual_seed(1)
-    for (T, H, E, k, renorm) in [(37, 512, 16, 4, True), (300, 2048, 128, 8, True), (9, 1024, 200, 8, False)]:
+    for (T, H, E, k, renorm) in [(37, 512, 16, 4, True), (300, 2048, 128, 8, True), (9, 1024, 200, 8, False), (3, 512, 16, 4, True),
+                                 (20, 520, 64, 8, True)]:
         h = torch.randn(T, H, device=d, generator=g)
         W = (torch.randn(E, H, device=d, generator=g) * 0.05).to(torch.bfloat16)
         ti = torch.zeros(T, k, dtype=torch.int32, device=d)
@@ -138,6 +139,33 @@ def test_router_grouping_gather_and_combine_kernels():
         K.moe_combine_rows(yg, inv, tw, k, y, resid=resid)
         want = resid + (yg[inv.long()].reshape(T, k, H) * tw[..., None]).sum(1)
         assert float((y - want).abs().max()) < 1e-4
+
+
+def test_dequant_kernel_matches_the_reference_dequantisation():
+    from inferencehackathon_b200.models.quant import quant_block
+    from inferencehackathon_b200.ops import lib as K
+    K.load()
+    d = torch.device("cuda", 0)
+    g = torch.Generator(device=d).manual_seed(5)
+    for shape, rb, kb in [((3, 200, 512), 128, 128), ((384, 1024), 64, 128), ((2, 130, 192), 1, 256)]:
+        w = torch.randn(*shape, device=d, generator=g) * 0.07
+        qw = quant_block(w, rb, kb)
+        out = torch.zeros(shape, dtype=torch.bfloat16, device=d)
+        K.dequant_bf16(qw, out)
+        assert torch.equal(out, qw.dequant(torch.bfloat16))
+
+
+def test_window_scratch_dequantisation_mode(monkeypatch):
+    """IHB_WINDOW_BF16_SCRATCH=1: no resident bf16 copies, every layer's weights are de-quantised right before its GEMMs
+    (what a model that fills the GPU does); same logits as with resident copies."""
+    ref, eng = _pair("fp8_block")
+    toks = _prompt(70)
+    a = eng.logits_for(toks, commit=True)
+    monkeypatch.setenv("IHB_WINDOW_BF16_SCRATCH", "1")
+    eng2 = InferenceEngine.build("small", weights="fp8_block", device="cuda:0", backend="cuda", max_seq=512)
+    b = eng2.logits_for(toks, commit=True)
+    assert not eng2.gpu.window()._resident and eng.gpu.window()._resident
+    assert torch.equal(a, b)
 
 
 def test_window_on_the_block_fp8_gemm_path(monkeypatch):
