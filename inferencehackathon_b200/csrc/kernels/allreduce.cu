@@ -245,9 +245,113 @@ __global__ void __launch_bounds__(AR_THREADS) ar_twoshot_kernel(const ArArgs a) 
   }
 }
 
+// ---- counted: latency-optimal for a few rows --------------------------------------------------------------------------------
+// One CTA per row, plain launch, no grid barrier, no arrival counter: every rank adds its row into 64-bit slots on every
+// GPU (top 8 bits count contributions, low 56 bits hold the biased fixed-point sum; multimem.red.add.u64 through
+// NVSwitch or one red per peer), then polls ITS OWN copy of the slots until every word has counted all ranks, decodes,
+// clears the word for its next use and finishes the row (residual, RMSNorm). One one-way trip through the switch;
+// integer sums make every rank decode the same bits. Slot region: [4 call parities][T * H] 64-bit words, which must
+// start zeroed and must not be shared with the one-shot / two-shot regions. `x` may be fp32 or bf16.
+constexpr unsigned long long ARC_ONE = 1ull << 56;
+constexpr long long ARC_BIAS = 1ll << 51, ARC_QMAX = 1ll << 50;
+constexpr float ARC_FIX = 268435456.f;                 // 2^28
+constexpr int ARC_THREADS = 512, ARC_MAXV = 4;         // H <= 8192
+struct ArcArgs {
+  ArArgs a;
+  int x_is_bf16;
+  unsigned* call_counter;      // local: calls made so far on this slot region (selects the parity)
+};
+__global__ void __launch_bounds__(ARC_THREADS) ar_counted_kernel(const ArcArgs q) {
+  __shared__ float red[ARC_THREADS / 32];
+  const ArArgs& a = q.a;
+  const IhbComm& cm = a.comm;
+  const int H = a.H, t = blockIdx.x, tid = threadIdx.x;
+  const unsigned call = *q.call_counter;
+  const size_t n = static_cast<size_t>(a.T) * H;
+  const size_t off0 = static_cast<size_t>(call & 3u) * n + static_cast<size_t>(t) * H;
+  unsigned long long* local = reinterpret_cast<unsigned long long*>(cm.slots_local) + off0;
+  const unsigned nr = static_cast<unsigned>(cm.nranks);
+  for (int i = tid; i < H; i += ARC_THREADS) {
+    const float v = q.x_is_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.x)[static_cast<size_t>(t) * H + i])
+                                : a.x[static_cast<size_t>(t) * H + i];
+    long long fx = __float2ll_rn(v * ARC_FIX);
+    fx = fx > ARC_QMAX ? ARC_QMAX : (fx < -ARC_QMAX ? -ARC_QMAX : fx);
+    const unsigned long long w = ARC_ONE + static_cast<unsigned long long>(fx + ARC_BIAS);
+    if (nr == 1) {
+      local[i] = w;
+    } else if (cm.slots_mc != nullptr) {
+      asm volatile("multimem.red.relaxed.sys.global.add.u64 [%0], %1;" ::"l"(reinterpret_cast<unsigned long long*>(cm.slots_mc) + off0 + i), "l"(w) : "memory");
+    } else {
+      for (int p = 0; p < cm.nranks; ++p)
+        asm volatile("red.relaxed.sys.global.add.u64 [%0], %1;" ::"l"(reinterpret_cast<unsigned long long*>(cm.slots_peer[p]) + off0 + i), "l"(w) : "memory");
+    }
+  }
+  __threadfence_block();
+  float4 v[ARC_MAXV];
+  bool ok = true;
+  const unsigned long long t0 = globaltimer_ns();
+  for (int j = 0; j < ARC_MAXV; ++j) {
+    const int i = (tid + ARC_THREADS * j) * 4;
+    v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (i >= H) continue;
+    unsigned long long w[4];
+    unsigned spins = 0;
+    for (;;) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w[e]) : "l"(local + i + e) : "memory");
+      if (!ok || ((w[0] >> 56) == nr && (w[1] >> 56) == nr && (w[2] >> 56) == nr && (w[3] >> 56) == nr)) break;
+      if ((++spins & 63u) == 0u && (ld_cg_u(a.err) != 0u || globaltimer_ns() - t0 > IHB_PEER_WAIT_NS)) {
+        set_error(a.err, ERR_PEER_BARRIER_TIMEOUT);
+        ok = false;
+      }
+    }
+    float f[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const long long sfx = static_cast<long long>(w[e] & (ARC_ONE - 1ull)) - static_cast<long long>(nr) * ARC_BIAS;
+      f[e] = __ll2float_rn(sfx) * (1.f / ARC_FIX);
+      local[i + e] = 0ull;                               // this thread is the word's only reader: clear it for its next use
+    }
+    v[j] = make_float4(f[0], f[1], f[2], f[3]);
+  }
+  ar_finish_row<ARC_THREADS>(a, t, v, ARC_MAXV, red);
+  for (int j = 0; j < ARC_MAXV; ++j) {
+    const int i = (tid + ARC_THREADS * j) * 4;
+    if (i < H) *reinterpret_cast<float4*>(a.out + static_cast<size_t>(t) * H + i) = v[j];
+  }
+  // the last CTA to finish advances the call counter (read by every CTA of the next launch at its start)
+  __syncthreads();
+  if (tid == 0) {
+    __threadfence();
+    const unsigned done = atomicAdd(a.counter + 5, 1u);
+    if (done == gridDim.x - 1) {
+      a.counter[5] = 0u;
+      *q.call_counter = call + 1u;
+      __threadfence();
+    }
+  }
+}
+
 }  // namespace ihb
 
 using namespace ihb;
+
+// The latency-optimal variant for a few rows (see ar_counted_kernel). slots: 4 * T * H 64-bit words of the symmetric buffer
+// that start zeroed and are used by this variant only; counter: 8 unsigned (word 5 used), call_counter: 1 unsigned, both
+// zero before the first call. x: fp32, or bf16 when x_is_bf16. T <= 64, H % 4 == 0, H <= 8192.
+extern "C" int ihb_allreduce_counted(const IhbComm* comm, const void* x, int x_is_bf16, const float* resid, const float* gamma,
+                                     float eps, int T, int H, float* out, float* out_norm, unsigned* counter,
+                                     unsigned* call_counter, unsigned* err, cudaStream_t stream) {
+  if (T < 1 || T > 64 || H < 4 || (H % 4) || H > ARC_MAXV * ARC_THREADS * 4 || comm == nullptr || counter == nullptr ||
+      call_counter == nullptr) return cudaErrorInvalidValue;
+  ArcArgs q;
+  q.a.comm = *comm; q.a.x = reinterpret_cast<const float*>(x); q.a.resid = resid; q.a.gamma = gamma; q.a.out = out;
+  q.a.out_norm = out_norm; q.a.eps = eps; q.a.T = T; q.a.H = H; q.a.counter = counter; q.a.err = err;
+  q.x_is_bf16 = x_is_bf16;
+  q.call_counter = call_counter;
+  ar_counted_kernel<<<T, ARC_THREADS, 0, stream>>>(q);
+  return cudaGetLastError();
+}
 
 // algo: 0 = choose by size, 1 = one-shot, 2 = two-shot. Slot region needed (floats): one-shot 2 * nranks * T * H,
 // two-shot 2 * T * H. counter: 8 unsigned, zero before the first launch.

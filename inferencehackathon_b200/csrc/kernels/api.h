@@ -263,6 +263,15 @@ int ihb_allreduce_norm(const IhbComm* comm, const float* x, const float* resid, 
                        int H, float* out, float* out_norm, unsigned* counter, unsigned* err, int algo, int grid,
                        cudaStream_t stream);
 
+// Latency-optimal all-reduce (+ residual + RMSNorm) of a few rows: one CTA per row, plain launch; every rank ADDS its row
+// into 64-bit counted fixed-point slots on every GPU (multimem.red.add.u64 or peer reds) and waits for the contribution
+// count on its own copy: one one-way trip through NVSwitch, no barrier. comm->slots_*: 4 * T * H 64-bit words, zeroed
+// before the first call and used by this entry only; counter: 8 unsigned; call_counter: 1 unsigned (both zero at first).
+// x fp32, or bf16 when x_is_bf16. T <= 64, H % 4 == 0, H <= 8192.
+int ihb_allreduce_counted(const IhbComm* comm, const void* x, int x_is_bf16, const float* resid, const float* gamma, float eps,
+                          int T, int H, float* out, float* out_norm, unsigned* counter, unsigned* call_counter, unsigned* err,
+                          cudaStream_t stream);
+
 // ---- all-to-all exchange of rows over peer memory (expert-parallel dispatch / combine for multi-token windows) -----
 // Rows for destination d are pairs offsets[d] .. offsets[d + 1] of `send` (through `gather` when given). Receive region
 // of every rank: [2 parities][nranks sources][cap rows][row_floats]; counts: [2][nranks] ints; flag: one arrival
@@ -352,6 +361,8 @@ typedef struct {
   int max_split;                // attention splits available per (kv head, group of 8 query heads) in the long-context mode
   int steps;                    // tokens per launch
   int ar_loopback;              // one rank only: k > 1 makes every all-reduce slot receive k adds (the traffic of k ranks)
+  int delay_cta, delay_ns;      // test aid: CTA delay_cta idles delay_ns (at most 1 ms) before each of its all-reduce reads,
+                                // so that a test can make one CTA of one GPU lag behind every other; delay_ns = 0: off
   IhbComm comm;
 } IhbMegaArgs;
 

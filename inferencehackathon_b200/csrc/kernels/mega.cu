@@ -472,7 +472,10 @@ __device__ __forceinline__ int mg_gemv_shape(int nch, int rows) {
 #ifdef MG_ONE_SHAPE
   return 2;
 #else
-  if (nch > 128) return rows > static_cast<int>(gridDim.x) * MG_WARPS ? 0 : 1;
+#ifndef MG_R2_WAVES
+#define MG_R2_WAVES 1
+#endif
+  if (nch > 128) return rows > MG_R2_WAVES * static_cast<int>(gridDim.x) * MG_WARPS ? 0 : 1;
   return nch > 64 ? 2 : 3;
 #endif
 }
@@ -558,6 +561,12 @@ __device__ __noinline__ float mg_residual_norm_fn(const IhbMegaArgs* ap, unsigne
   const unsigned long long* base = nullptr;
   const unsigned n = c.ar_n;
   bool ok = c.flags[0] == 0;
+  if (add_slots && a.delay_ns > 0 && static_cast<int>(blockIdx.x) == a.delay_cta) {
+    // test aid: this CTA lags (bounded) before it reads the round; everything else has to cope
+    const unsigned long long t0 = globaltimer_ns();
+    const unsigned long long lim = static_cast<unsigned long long>(min(a.delay_ns, 1000000));
+    while (globaltimer_ns() - t0 < lim) { }
+  }
   if (add_slots) {
     // c.epoch - 1: the round that ended with the last push
     base = reinterpret_cast<const unsigned long long*>(a.comm.slots_local) + static_cast<size_t>((c.epoch - 1u) & (MG_NPAR - 1)) * H;

@@ -123,7 +123,7 @@ class IhbMegaArgs(C.Structure):
                 ("token_ring_size", C.c_int), ("forced", _vp), ("n_forced", _vp),
                 ("qkv", _vp), ("attn_part", _vp), ("attn", _vp), ("attn_rec", _vp), ("act", _vp), ("argmax_partial", _vp),
                 ("bar", _vp), ("err", _vp), ("prof", _vp), ("prof_n", C.c_int), ("max_split", C.c_int), ("steps", C.c_int),
-                ("ar_loopback", C.c_int), ("comm", IhbComm)]
+                ("ar_loopback", C.c_int), ("delay_cta", C.c_int), ("delay_ns", C.c_int), ("comm", IhbComm)]
 
 
 def load(build_if_missing: bool = True) -> C.CDLL:
@@ -179,6 +179,9 @@ def load(build_if_missing: bool = True) -> C.CDLL:
     lib.ihb_moe_gather_rows.restype = C.c_int
     lib.ihb_moe_combine_rows.argtypes = [_vp, _vp, _vp, C.c_int, C.c_int, C.c_int, _vp, _vp, _vp]
     lib.ihb_moe_combine_rows.restype = C.c_int
+    lib.ihb_allreduce_counted.argtypes = [C.POINTER(IhbComm), _vp, C.c_int, _vp, _vp, C.c_float, C.c_int, C.c_int, _vp, _vp, _vp, _vp,
+                                          _vp, _vp]
+    lib.ihb_allreduce_counted.restype = C.c_int
     lib.ihb_dequant_bf16.argtypes = [_vp, _vp, C.c_longlong, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _vp, _vp]
     lib.ihb_dequant_bf16.restype = C.c_int
     lib.ihb_mega_decode.argtypes = [C.POINTER(IhbMegaArgs), C.c_int, _vp]
@@ -469,6 +472,17 @@ def moe_combine_rows(yg: torch.Tensor, inv: torch.Tensor, tw: torch.Tensor, k: i
     T, H = y.shape
     check(load().ihb_moe_combine_rows(yg.data_ptr(), inv.data_ptr(), tw.data_ptr(), k, H, T, ptr(resid), y.data_ptr(),
                                       stream_ptr()), "ihb_moe_combine_rows")
+
+
+def allreduce_counted(comm: IhbComm, x: torch.Tensor, out: torch.Tensor, counter: torch.Tensor, call_counter: torch.Tensor,
+                      err: torch.Tensor, resid: Optional[torch.Tensor] = None, gamma: Optional[torch.Tensor] = None,
+                      eps: float = 1e-6, out_norm: Optional[torch.Tensor] = None) -> None:
+    """Latency-optimal fused all-reduce (+ residual + RMSNorm) of ``x [T, H]`` (fp32 or bf16), ``T <= 64``: counted
+    fixed-point slots, one one-way trip, no barrier (``csrc/kernels/allreduce.cu::ar_counted_kernel``)."""
+    T, H = x.shape
+    check(load().ihb_allreduce_counted(C.byref(comm), x.data_ptr(), int(x.dtype == torch.bfloat16), ptr(resid), ptr(gamma), eps,
+                                       T, H, out.data_ptr(), ptr(out_norm), counter.data_ptr(), call_counter.data_ptr(),
+                                       err.data_ptr(), stream_ptr()), "ihb_allreduce_counted")
 
 
 def dequant_bf16(qw, out: torch.Tensor) -> None:

@@ -62,7 +62,20 @@ class SymmetricComm:
         torch.cuda.synchronize(self.device)
         dist.barrier(group=self.group)
 
-    def comm_block(self, epoch: torch.Tensor) -> K.IhbComm:
+    def comm_block(self, epoch: torch.Tensor, slot_offset_bytes: int = 0) -> K.IhbComm:
+        """The kernels' view of this buffer. ``slot_offset_bytes`` (a multiple of 16) moves the slot pointers into the
+        buffer, e.g. to the caller-defined tail region (``self.extra_off``): kernels that keep different slot layouts
+        must not share storage."""
+        cm = self._comm_block(epoch)
+        if slot_offset_bytes:
+            cm.slots_local = self.local_ptr + slot_offset_bytes
+            if self.use_multicast:
+                cm.slots_mc = self.mc_ptr + slot_offset_bytes
+            for r in range(self.nranks):
+                cm.slots_peer[r] = self.peer_ptrs[r] + slot_offset_bytes
+        return cm
+
+    def _comm_block(self, epoch: torch.Tensor) -> K.IhbComm:
         cm = K.IhbComm()
         cm.nranks, cm.rank = self.nranks, self.rank
         f_off, a_off = self.slot_bytes, self.slot_bytes + _FLAG_BYTES

@@ -22,6 +22,24 @@ from ..utils.timing import StepTimer
 from .sampler import Sampler, SamplingParams
 
 
+class _nvtx:
+    """NVTX range around a device-side stage (prefill, decode step, verify window): shows up in timeline tools, costs a
+    few hundred nanoseconds otherwise. A no-op on the CPU."""
+
+    def __init__(self, name: str, device):
+        self.name, self.on = name, torch.device(device).type == "cuda"
+
+    def __enter__(self):
+        if self.on:
+            torch.cuda.nvtx.range_push(self.name)
+        return self
+
+    def __exit__(self, *exc):
+        if self.on:
+            torch.cuda.nvtx.range_pop()
+        return False
+
+
 @dataclass
 class PrefillOutput:
     n_prompt_tokens: int
@@ -154,7 +172,8 @@ class InferenceEngine:
         self._timer.start()
         if self.gpu is not None:
             try:
-                nxt, logits = self.gpu.prefill(toks, self.sampler, return_logits)
+                with _nvtx("ihb.prefill", self.device):
+                    nxt, logits = self.gpu.prefill(toks, self.sampler, return_logits)
             except RuntimeError as e:
                 self._fall_back(e, drop=len(toks))
                 return self.prefill_torch(toks, return_logits)
@@ -217,7 +236,8 @@ class InferenceEngine:
         self._history.append(int(tok))
         if self.gpu is not None:
             try:
-                out_tok, seconds, routes = self.gpu.decode_step(tok, self.sampler, want_routes=want_routes)
+                with _nvtx("ihb.decode_step", self.device):
+                    out_tok, seconds, routes = self.gpu.decode_step(tok, self.sampler, want_routes=want_routes)
             except RuntimeError as e:
                 self._fall_back(e, drop=1)
         if self.gpu is None:
@@ -236,8 +256,9 @@ class InferenceEngine:
                    aux_layers=()) -> torch.Tensor:
         """Logits ``[T, V]`` of a window of new tokens (speculative verify, chains and token trees)."""
         if self.gpu is not None:
-            logits = self.gpu.logits_for(tokens, commit=commit, tree_mask=tree_mask, positions=positions,
-                                         aux_layers=tuple(aux_layers))
+            with _nvtx("ihb.verify_window" if not commit or tree_mask is not None else "ihb.window", self.device):
+                logits = self.gpu.logits_for(tokens, commit=commit, tree_mask=tree_mask, positions=positions,
+                                             aux_layers=tuple(aux_layers))
             self.model.aux_taps = getattr(self.gpu.window(), "aux_taps", {})
             return logits
         t = torch.as_tensor(list(tokens), dtype=torch.long, device=self.device)

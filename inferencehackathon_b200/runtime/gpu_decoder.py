@@ -231,6 +231,12 @@ class GpuDecoder:
         a.steps = 1
         # profiling aid on one GPU: every all-reduce slot receives k adds, the traffic of k ranks
         a.ar_loopback = env_flag("IHB_MEGA_LOOPBACK", 0) if par.world == 1 else 0
+        # test aid: IHB_MEGA_DELAY="rank:cta:ns" makes one CTA of one rank lag before each all-reduce read
+        spec = os.environ.get("IHB_MEGA_DELAY", "")
+        if spec:
+            r_, c_, ns_ = (int(x) for x in spec.split(":"))
+            if r_ == par.rank:
+                a.delay_cta, a.delay_ns = c_, ns_
         a.comm = self._comm()
         self.mega_prof = None
         if env_flag("IHB_MEGA_PROF", 0):

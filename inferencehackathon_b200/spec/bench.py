@@ -70,6 +70,44 @@ def run_spec(engine, source, prompt: Sequence[int], n: int, *, depth: int, width
             "forwards_per_token": drv.runner.forwards / max(1, len(out) - 1)}
 
 
+def verify_forward_sweep(engine, prompt: Sequence[int], ms=(1, 4, 8, 16), reps: int = 10) -> dict:
+    """Full-forward time of a verify window of M tokens, T(M), device-timed, for the M of a speculative round, beside
+    the plain decode step: how flat the verify cost is in M decides what a drafter's accept length is worth
+    (reference: the T(M) table of kernels/decode_step_tp8.cu:3154-3175; T(16) / T(1) = 1.003 for its GEMM path)."""
+    if engine.device.type != "cuda":
+        return {}
+    engine.reset()
+    pre = engine.prefill(list(prompt))
+    dev = engine.device
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize(dev)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize(dev)
+        return e0.elapsed_time(e1) * 1e3 / reps
+
+    base = engine.seq_len
+    out = {}
+    toks = list(prompt[:max(ms)])
+    for m in ms:
+        out[f"T({m})_us"] = round(timed(lambda: engine.logits_for(toks[:m], commit=False)), 1)
+    def step():
+        engine.gpu.run_steps(1)
+        engine.gpu.rollback(base)
+    out["decode_step_us"] = round(timed(step), 1)
+    engine.gpu.cur_token.fill_(pre.next_token)
+    for m in ms:
+        out[f"T({m})/T(1)"] = round(out[f"T({m})_us"] / out[f"T({ms[0]})_us"], 3)
+    out["T(1)/decode_step"] = round(out[f"T({ms[0]})_us"] / out["decode_step_us"], 2)
+    return out
+
+
 def main(argv: Optional[Sequence[str]] = None) -> int:
     p = argparse.ArgumentParser(prog="python -m inferencehackathon_b200.spec.bench")
     p.add_argument("--model", default="tiny")
@@ -84,6 +122,7 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     p.add_argument("--tree", default="4x4", help="depth x branch of the EAGLE tree")
     p.add_argument("--max-candidates", type=int, default=16, help="beam budget of the tree (candidates verified per round)")
     p.add_argument("--skip-eagle", action="store_true")
+    p.add_argument("--tm-sweep", action="store_true", help="also time verify windows of 1, 4, 8, 16 tokens (GPU only)")
     a = p.parse_args(argv)
     n_prompt = a.block * a.repeats
     eng = InferenceEngine.build(a.model, weights=a.weights, device=a.device, backend=a.backend, n_layers=a.layers,
@@ -109,6 +148,8 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
         out["eagle_tree"] = {k: v for k, v in eg.items() if k != "tokens"}
         out["eagle_tree"]["lossless"] = eg["tokens"] == plain["tokens"]
         out["eagle_tree"]["speedup"] = eg["decode_tok_s"] / plain["decode_tok_s"] if plain["decode_tok_s"] else 0.0
+    if a.tm_sweep:
+        out["verify_forward"] = verify_forward_sweep(eng, prompt)
     print(json.dumps(out))
     return 0 if out["ngram"]["lossless"] and out.get("eagle_tree", {}).get("lossless", True) else 1
 

@@ -1,6 +1,6 @@
 """Stress and precision of the stand-alone fused all-reduce kernel over peer memory (needs >= 2 B200s; one process per
 GPU): 100 rounds with a rank-skewed busy kernel before each pair of back-to-back all-reduces and no host
-synchronisation between collectives, then a precision probe with fractional data against a float64 sum. The same
+synchronisation between collectives, for the one-shot, the two-shot and the counted fixed-point variant, then a precision probe with fractional data against a float64 sum. The same
 protocol the reference uses for its multicast all-reduce (kernels/nvls_engine_test.cu:46-68,
 kernels/nvls_precision_test.cu:15-51)."""
 import json
@@ -29,20 +29,26 @@ dev = torch.device("cuda", local)
 K.load()
 T, H = 4, 1024
 par = ParallelConfig(tp=world, ep=1, rank=rank, world=world)
-comm = SymmetricComm(par, dev, slot_floats=2 * world * T * H)
+comm = SymmetricComm(par, dev, slot_floats=2 * world * T * H, extra_bytes=4 * T * H * 8)
 epoch = torch.zeros(4, dtype=torch.int32, device=dev)
 counter = torch.zeros(8, dtype=torch.int32, device=dev)
 err = torch.zeros(1, dtype=torch.int32, device=dev)
 cm = comm.comm_block(epoch)
+cm_small = comm.comm_block(epoch, slot_offset_bytes=comm.extra_off)     # the counted variant keeps its own slot region
+calls = torch.zeros(1, dtype=torch.int32, device=dev)
+def counted(src, dst):
+    K.allreduce_counted(cm_small, src, dst, counter, calls, err)
+def plain(algo):
+    return lambda src, dst: K.allreduce_norm(cm, src, dst, counter, err, algo=algo)
 res = {"mode": "multicast" if comm.use_multicast else "p2p"}
-for name, algo in (("oneshot", 1), ("twoshot", 2)):
+for name, ar in (("oneshot", plain(1)), ("twoshot", plain(2)), ("counted", counted)):
     bad = 0
     x, a, b = torch.empty(T, H, device=dev), torch.empty(T, H, device=dev), torch.empty(T, H, device=dev)
     for rnd in range(100):
         x.fill_(float(rnd % 7 + rank + 1))
         torch.cuda._sleep(200000 * ((rank + rnd) % world))          # skew: ranks reach the collective at different times
-        K.allreduce_norm(cm, x, a, counter, err, algo=algo)
-        K.allreduce_norm(cm, a, b, counter, err, algo=algo)          # second collective right behind the first
+        ar(x, a)
+        ar(a, b)                                                     # second collective right behind the first
         want1 = float(sum(rnd % 7 + r + 1 for r in range(world)))
         bad += int((a != want1).any()) + int((b != want1 * world).any())
     torch.cuda.synchronize(dev)
@@ -54,7 +60,7 @@ for name, algo in (("oneshot", 1), ("twoshot", 2)):
     parts = [torch.rand(T, H, generator=g, dtype=torch.float64) * 2 - 1 for _ in range(world)]
     mine = parts[rank].float().to(dev)
     out = torch.empty(T, H, device=dev)
-    K.allreduce_norm(cm, mine, out, counter, err, algo=algo)
+    ar(mine, out)
     torch.cuda.synchronize(dev)
     exact = sum(p.float().double() for p in parts)
     res[name + "_max_abs_err"] = float((out.double().cpu() - exact).abs().max())
@@ -87,7 +93,7 @@ def test_fused_allreduce_survives_skewed_back_to_back_rounds(mode):
     assert r.returncode == 0, r.stdout[-3000:]
     out = json.loads([l for l in r.stdout.splitlines() if l.startswith("RESULT ")][-1][7:])
     for res in out:
-        for name in ("oneshot", "twoshot"):
+        for name in ("oneshot", "twoshot", "counted"):
             assert res[name + "_bad_rounds"] == 0 and res[name + "_err"] == 0, out
             assert res[name + "_max_abs_err"] < 1e-5 * n, out
             assert res[name + "_identical_on_all_ranks"], out

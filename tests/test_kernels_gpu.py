@@ -259,3 +259,35 @@ def test_embed_norm_quantised_copy():
     deq = (xq.view(torch.float8_e4m3fn).float().reshape(-1, 128) * xs[:, None]).reshape(-1)
     assert float((deq - xn).abs().max()) <= 0.07 * float(xn.abs().max())
     assert torch.equal(xb.view(torch.bfloat16), xn.to(torch.bfloat16))
+
+
+@pytest.mark.parametrize("payload", ["fp32", "bf16"])
+def test_counted_allreduce_single_rank_adds_residual_and_norms(payload):
+    """With one rank the counted small-message all-reduce is residual add + RMSNorm through the 64-bit fixed-point
+    slots: the result must match the fp32 formula to the slot's resolution (2^-28), on every one of the four call
+    parities and again after they wrap."""
+    from inferencehackathon_b200.ops import lib
+    lib.load()
+    d = _dev()
+    T, H = 5, 4096
+    g = torch.Generator(device=d).manual_seed(3)
+    slots = torch.zeros(4 * T * H, dtype=torch.int64, device=d)
+    epoch = torch.zeros(4, dtype=torch.int32, device=d)
+    cm = lib.single_comm(slots, epoch)
+    counter = torch.zeros(8, dtype=torch.int32, device=d)
+    calls = torch.zeros(1, dtype=torch.int32, device=d)
+    err = torch.zeros(1, dtype=torch.int32, device=d)
+    gamma = torch.rand(H, device=d, generator=g) + 0.5
+    for it in range(9):
+        x = torch.randn(T, H, device=d, generator=g) * (1 + it)
+        if payload == "bf16":
+            x = x.to(torch.bfloat16)
+        resid = torch.randn(T, H, device=d, generator=g)
+        out, outn = torch.empty(T, H, device=d), torch.empty(T, H, device=d)
+        lib.allreduce_counted(cm, x, out, counter, calls, err, resid=resid, gamma=gamma, out_norm=outn)
+        ref = x.float() + resid
+        refn = ref * torch.rsqrt(ref.pow(2).mean(-1, keepdim=True) + 1e-6) * gamma
+        assert float((out - ref).abs().max()) < 4e-6 * (1 + it)
+        assert float((outn - refn).abs().max()) < 1e-5
+    assert int(err.item()) == 0 and int(calls.item()) == 9
+    assert int(slots.abs().max()) == 0                   # every reader cleared what it consumed

@@ -23,24 +23,34 @@ weights = os.environ.get("IHB_TEST_WEIGHTS", "bf16")
 prompt = torch.randint(0, 4096, (20,), generator=torch.Generator().manual_seed(3)).tolist()
 plan = os.environ.get("IHB_TEST_PLAN", "tp")
 tp, ep = {"tp": (world, 1), "ep": (1, world), "hybrid": (world, world)}[plan]
+os.environ["IHB_WINDOW_PREFILL"] = "0"          # the prompt goes through the persistent decode kernel, token by token
 eng = InferenceEngine.build("small", tp=tp, ep=ep, rank=rank, world=world, weights=weights, device=dev, backend="cuda", max_seq=128)
-res = eng.generate(prompt, 12)
+pre = eng.prefill(prompt, return_logits=True)
+tokens = [pre.next_token]
+for _ in range(11):
+    tokens.append(eng.decode_step(want_routes=False).token_id)
 eng.gpu.check_error()
-ref_tokens = None
+ref_tokens, rel_err = None, None
 if rank == 0:
     ref = InferenceEngine.build("small", weights=weights, device=dev, backend="cuda", max_seq=128)
-    ref_tokens = ref.generate(prompt, 12).tokens
+    pr = ref.prefill(prompt, return_logits=True)
+    ref_tokens = [pr.next_token]
+    for t in tokens[:-1]:                        # teacher forcing: one near-tie cannot derail the rest
+        ref_tokens.append(ref.decode_step(t, want_routes=False).token_id)
+    rel_err = float((pr.logits[0].float() - pre.logits[0].float()).abs().max() / pr.logits.abs().max())
 toks = [None] * world
-dist.all_gather_object(toks, res.tokens)
+dist.all_gather_object(toks, tokens)
 if rank == 0:
-    print("RESULT " + json.dumps({"tokens": toks, "ref": ref_tokens, "mc": bool(eng.gpu.symm.use_multicast)}))
+    print("RESULT " + json.dumps({"tokens": toks, "ref": ref_tokens, "logits_rel_err": rel_err,
+                                  "mc": bool(eng.gpu.symm.use_multicast)}))
 dist.barrier()
 dist.destroy_process_group()
 """
 
 
-def _run(n, mode, weights, plan="tp"):
+def _run(n, mode, weights, plan="tp", extra_env=None):
     env = dict(os.environ, IHB_ROOT=ROOT, IHB_COMM_MODE=mode, IHB_TEST_WEIGHTS=weights, IHB_TEST_PLAN=plan)
+    env.update(extra_env or {})
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
            "--master-addr", "127.0.0.1", "--master-port", "29533", "-c", WORKER]
     # torchrun has no -c: write the worker to a temp file instead
@@ -65,8 +75,25 @@ def test_tp2_decode_matches_single_gpu(mode, weights):
     out = _run(2, mode, weights)
     assert out["tokens"][0] == out["tokens"][1], out          # ranks stay in lock step
     agree = sum(int(a == b) for a, b in zip(out["tokens"][0], out["ref"]))
-    # TP changes the summation order (and, for fp8, the quantisation blocks of the shards)
-    assert agree >= (9 if weights == "bf16" else 4), out
+    # bf16 shards hold the same numbers as the unsharded model: the logits after the prompt agree to rounding noise and
+    # (teacher-forced) nearly every token. Block-fp8 shards are quantised per shard (other blocks, other scales): that
+    # is a different set of weights, so only a loose bound applies there.
+    if weights == "bf16":
+        assert out["logits_rel_err"] < 0.02 and agree >= 11, out
+    else:
+        assert out["logits_rel_err"] < 0.25 and agree >= 8, out
+
+
+def test_one_lagging_cta_changes_nothing():
+    """One CTA of rank 1 idles 30 us before every all-reduce read (host-configured, bounded): every other CTA of
+    both GPUs has to wait for it at the next round, nothing may time out, and the tokens are those of the undelayed
+    run (the slot protocol depends on no CTA being 'only a reader')."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    base = _run(2, "auto", "bf16")
+    for cta in (0, 17):
+        out = _run(2, "auto", "bf16", extra_env={"IHB_MEGA_DELAY": f"1:{cta}:30000"})
+        assert out["tokens"] == base["tokens"], (out, base)
 
 
 @pytest.mark.parametrize("plan", ["ep", "hybrid"])
@@ -78,4 +105,4 @@ def test_expert_parallel_decode_in_the_persistent_kernel(plan):
     out = _run(2, "auto", "bf16", plan)
     assert out["tokens"][0] == out["tokens"][1], out
     agree = sum(int(a == b) for a, b in zip(out["tokens"][0], out["ref"]))
-    assert agree >= 9, out
+    assert out["logits_rel_err"] < 0.02 and agree >= 11, out
