@@ -5,6 +5,13 @@
 ``kernels/`` directory, compiled here with the build lines from the sources' own headers
 (kernels/decode_step.cu "Build" comment, kernels/decode_step_tp8.cu:65-72) with ``-arch=sm_100a`` in place of
 ``sm_90a``. The binaries are the reference's public entry points: ``main(ctx_len, iters, HBM_GBs[, run_check])``.
+
+Also built: two of the reference's single-process 8-GPU microbenches, for same-box comparison rows:
+``nvls_ar`` (kernels/nvls_ar.cu: one multimem ld_reduce + st kernel over an 8 KB fp16 vector, no flags, no waits) and
+``ep_moe_sharded`` (kernels/ep_moe_sharded.cu: expert-parallel MoE layer with balanced / skewed / adversarial routing,
+combined by ncclAllReduce). ``python baseline/build_reference.py --run-comms`` runs both on an 8-GPU box and prints
+their result lines. kernels/oneshot_allreduce.cu is NOT built or run: its device code spins on peer flags without
+a bound (kernels/oneshot_allreduce.cu:152), so one rank that fails to launch would hang the other seven GPUs.
 """
 from __future__ import annotations
 
@@ -37,8 +44,31 @@ def build(reference_root: str = "") -> None:
     subprocess.check_call(common + [os.path.join(kdir, "decode_step.cu"), "-o", os.path.join(REF, "bin", "decode_step")])
     subprocess.check_call(common + ["-I", inc, os.path.join(kdir, "decode_step_tp8.cu"), "-L", lib, "-l:libnccl.so.2",
                                     "-lcublasLt", "-lcuda", "-o", os.path.join(REF, "bin", "decode_step_tp8")])
+    subprocess.check_call(common + [os.path.join(kdir, "nvls_ar.cu"), "-lcuda", "-o", os.path.join(REF, "bin", "nvls_ar")])
+    subprocess.check_call(common + ["-I", inc, os.path.join(kdir, "ep_moe_sharded.cu"), "-L", lib, "-l:libnccl.so.2",
+                                    "-o", os.path.join(REF, "bin", "ep_moe_sharded")])
+
+
+def run_comms(timeout_s: int = 180) -> dict:
+    """Runs the two microbenches and returns their headline lines (``{"nvls_ar": [...], "ep_moe_sharded": [...]}``)."""
+    _, lib = nccl_dirs()
+    env = dict(os.environ, LD_LIBRARY_PATH=lib + ":" + os.environ.get("LD_LIBRARY_PATH", ""))
+    out = {}
+    for name, keys in (("nvls_ar", ("validate", "C =")), ("ep_moe_sharded", ("balanced", "skewed", "adversarial", "per-token"))):
+        exe = os.path.join(REF, "bin", name)
+        if not os.path.exists(exe):
+            out[name] = ["not built"]
+            continue
+        r = subprocess.run([exe], env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=timeout_s)
+        lines = [l.strip() for l in r.stdout.splitlines() if any(k in l for k in keys)]
+        out[name] = lines if r.returncode == 0 else [f"exit {r.returncode}"] + r.stdout.splitlines()[-5:]
+    return out
 
 
 if __name__ == "__main__":
-    build(*sys.argv[1:])
-    print("built", os.listdir(os.path.join(REF, "bin")))
+    if "--run-comms" in sys.argv[1:]:
+        import json
+        print(json.dumps(run_comms(), indent=1))
+    else:
+        build(*sys.argv[1:])
+        print("built", os.listdir(os.path.join(REF, "bin")))

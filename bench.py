@@ -49,6 +49,8 @@ def parse_args():
     p.add_argument("--tp", type=int, default=2, help="attention tensor-parallel degree of the hybrid plan")
     p.add_argument("--hot-experts", type=int, default=0, help="skewed routing: scale the router rows of the first N experts")
     p.add_argument("--hot-scale", type=float, default=4.0)
+    p.add_argument("--ctx-sweep", default="", help="comma-separated context lengths: after the main run, the prompt pass "
+                   "(TTFT) and 16 decode steps are timed at each of them and reported under context_sweep")
     p.add_argument("--gate-layers", type=int, default=2, help="layers of the model the distributed correctness gate runs (0: no gate)")
     return p.parse_args()
 
@@ -213,7 +215,8 @@ def main() -> None:
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     mcfg = get_model_config(args.model, args.layers)
-    max_seq = args.max_seq or (args.prompt + args.steps + args.warmup + 64)
+    sweep = [int(v) for v in args.ctx_sweep.split(",") if v.strip()]
+    max_seq = args.max_seq or (max([args.prompt] + sweep) + args.steps + args.warmup + 64)
     distinct = args.distinct_layers
     if distinct < 0:
         # bytes per layer shard vs free memory (keep 12 GB for embeddings, head, KV cache, workspace)
@@ -300,6 +303,26 @@ def main() -> None:
             dist.all_reduce(te, op=dist.ReduceOp.MAX)
         e2e = {"value": n_e2e / float(te.item()), "unit": "tok/s", "h2d_bytes_per_step": gpu.h2d_bytes_per_step,
                "d2h_bytes_per_step": gpu.d2h_bytes_per_step, "steps": n_e2e}
+    # ---- optional: the same decode loop and the prompt pass at other context lengths (one engine, one process) ----
+    ctx_rows = []
+    for ctx in sweep:
+        eng.reset()
+        pr = torch.randint(0, mcfg.vocab, (ctx,), generator=g).tolist()
+        sync_all()
+        t_pre = eng.prefill(pr).seconds
+        gpu.run_steps(3)
+        sync_all()
+        c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        c0.record()
+        gpu.run_steps(16)
+        c1.record()
+        sync_all()
+        gpu.check_error()
+        tc = torch.tensor([c0.elapsed_time(c1) / 16, t_pre * 1e3], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(tc, op=dist.ReduceOp.MAX)
+        ctx_rows.append({"ctx": ctx, "ms_per_token": round(float(tc[0]), 4), "tok_s": round(1000.0 / float(tc[0]), 2),
+                         "ttft_ms": round(float(tc[1]), 2)})
     if rank == 0:
         per_sorted = sorted(per)
         p50 = statistics.median(per)
@@ -327,6 +350,8 @@ def main() -> None:
                "pipeline": "persistent" if gpu.use_mega else ("tcgen05 per-op" if gpu.use_tc else "simt per-op"),
                "clocks": clocks, "e2e": e2e, "gpu_launches": gpu.n_launches_per_step * args.steps,
                "impl": "ours"}
+        if ctx_rows:
+            out["context_sweep"] = ctx_rows
         if getattr(gpu, "mega_prof", None) is not None:
             out["phase_us"] = {k: round(v, 2) for k, v in gpu.mega_phase_us().items()}
         print(json.dumps(out))

@@ -259,14 +259,15 @@ constexpr int ARC_THREADS = 512, ARC_MAXV = 4;         // H <= 8192
 struct ArcArgs {
   ArArgs a;
   int x_is_bf16;
-  unsigned* call_counter;      // local: calls made so far on this slot region (selects the parity)
+  unsigned* call_counter;      // local, one word per row: calls made so far on this slot region (selects the parity)
 };
 __global__ void __launch_bounds__(ARC_THREADS) ar_counted_kernel(const ArcArgs q) {
   __shared__ float red[ARC_THREADS / 32];
   const ArArgs& a = q.a;
   const IhbComm& cm = a.comm;
   const int H = a.H, t = blockIdx.x, tid = threadIdx.x;
-  const unsigned call = *q.call_counter;
+  pdl_wait();                                            // the previous call on this stream wrote the counter and cleared its words
+  const unsigned call = q.call_counter[t];
   const size_t n = static_cast<size_t>(a.T) * H;
   const size_t off0 = static_cast<size_t>(call & 3u) * n + static_cast<size_t>(t) * H;
   unsigned long long* local = reinterpret_cast<unsigned long long*>(cm.slots_local) + off0;
@@ -314,22 +315,14 @@ __global__ void __launch_bounds__(ARC_THREADS) ar_counted_kernel(const ArcArgs q
     }
     v[j] = make_float4(f[0], f[1], f[2], f[3]);
   }
+  pdl_launch_dependents();                               // the next kernel's launch overlaps the row's tail
   ar_finish_row<ARC_THREADS>(a, t, v, ARC_MAXV, red);
   for (int j = 0; j < ARC_MAXV; ++j) {
     const int i = (tid + ARC_THREADS * j) * 4;
     if (i < H) *reinterpret_cast<float4*>(a.out + static_cast<size_t>(t) * H + i) = v[j];
   }
-  // the last CTA to finish advances the call counter (read by every CTA of the next launch at its start)
-  __syncthreads();
-  if (tid == 0) {
-    __threadfence();
-    const unsigned done = atomicAdd(a.counter + 5, 1u);
-    if (done == gridDim.x - 1) {
-      a.counter[5] = 0u;
-      *q.call_counter = call + 1u;
-      __threadfence();
-    }
-  }
+  // every row keeps its own call count (read by the same row of the next launch): no cross-CTA bookkeeping
+  if (tid == 0) q.call_counter[t] = call + 1u;
 }
 
 }  // namespace ihb
@@ -337,20 +330,28 @@ __global__ void __launch_bounds__(ARC_THREADS) ar_counted_kernel(const ArcArgs q
 using namespace ihb;
 
 // The latency-optimal variant for a few rows (see ar_counted_kernel). slots: 4 * T * H 64-bit words of the symmetric buffer
-// that start zeroed and are used by this variant only; counter: 8 unsigned (word 5 used), call_counter: 1 unsigned, both
-// zero before the first call. x: fp32, or bf16 when x_is_bf16. T <= 64, H % 4 == 0, H <= 8192.
+// that start zeroed and are used by this variant only; call_counter: 64 unsigned (one per row), zero before the first call
+// and used with ONE value of T only (the slot layout depends on T); counter is unused. x: fp32, or bf16 when x_is_bf16.
+// T <= 64, H % 4 == 0, H <= 8192. Launched with programmatic stream serialisation: back-to-back calls overlap the
+// launch of one with the tail of the other.
 extern "C" int ihb_allreduce_counted(const IhbComm* comm, const void* x, int x_is_bf16, const float* resid, const float* gamma,
                                      float eps, int T, int H, float* out, float* out_norm, unsigned* counter,
                                      unsigned* call_counter, unsigned* err, cudaStream_t stream) {
-  if (T < 1 || T > 64 || H < 4 || (H % 4) || H > ARC_MAXV * ARC_THREADS * 4 || comm == nullptr || counter == nullptr ||
+  if (T < 1 || T > 64 || H < 4 || (H % 4) || H > ARC_MAXV * ARC_THREADS * 4 || comm == nullptr ||
       call_counter == nullptr) return cudaErrorInvalidValue;
+  (void)counter;
   ArcArgs q;
   q.a.comm = *comm; q.a.x = reinterpret_cast<const float*>(x); q.a.resid = resid; q.a.gamma = gamma; q.a.out = out;
   q.a.out_norm = out_norm; q.a.eps = eps; q.a.T = T; q.a.H = H; q.a.counter = counter; q.a.err = err;
   q.x_is_bf16 = x_is_bf16;
   q.call_counter = call_counter;
-  ar_counted_kernel<<<T, ARC_THREADS, 0, stream>>>(q);
-  return cudaGetLastError();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(T); cfg.blockDim = dim3(ARC_THREADS); cfg.dynamicSmemBytes = 0; cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr; cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, ar_counted_kernel, q);
 }
 
 // algo: 0 = choose by size, 1 = one-shot, 2 = two-shot. Slot region needed (floats): one-shot 2 * nranks * T * H,

@@ -231,8 +231,15 @@ int ihb_qk_norm_rope_rows(float* qkv, int nq, int nkv, const float* q_gamma, con
 // Query t (row t of qkv, qkv_stride floats apart) attends to cache rows [0, base) and to window row base + j when
 // mask[t][j] != 0 (mask == NULL: causal, j <= t). out [T][nq * 128] fp32. mode 0: tensor-core tiles (16 tokens x 8
 // heads per CTA, K / V blocks staged once for all of them); mode 1: one CTA per token on the CUDA cores.
+// scratch (mode 0 only; may be NULL): ihb_window_attention_scratch_floats(nq, nkv, T) floats. With it, windows of few query
+// tiles slice the keys over ihb_window_attention_splits(nq, nkv, base, T) CTAs per tile and a second kernel folds the
+// slices' partial results; without it one CTA per tile walks all keys.
+#define IHB_WINDOW_MAX_SPLITS 32
 int ihb_window_attention(const float* qkv, int qkv_stride, const void* k_cache, const void* v_cache, int nq, int nkv,
-                         int max_seq, int base, int T, const unsigned char* mask, float* out, int mode, cudaStream_t stream);
+                         int max_seq, int base, int T, const unsigned char* mask, float* out, int mode, float* scratch,
+                         cudaStream_t stream);
+int ihb_window_attention_splits(int nq, int nkv, int base, int T);
+size_t ihb_window_attention_scratch_floats(int nq, int nkv, int T);
 
 // ---- routing of a window of tokens on the device (moe_rows.cu) --------------------------------------------------------------------
 // Fused router: logits = h W_r^T (h [T][H] fp32, router rows bf16 [E][H]), softmax, top-k with ties to the lowest id,

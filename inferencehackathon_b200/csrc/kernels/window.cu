@@ -233,6 +233,7 @@ __global__ void __launch_bounds__(WA_WARPS * 32) window_attn_kernel(
 // without leaving registers (the accumulator layout of two neighbouring 8-wide tiles is the A layout of one 16-deep step).
 // Reference: kernels/prefill_attn.cu:212-271 (SIMT flash_attn_causal), engine/native/tc_verify_attn.cuh:48-119.
 constexpr int WM_KB = 64;                 // key positions per block
+constexpr int WM_REC = WHD + 4;           // partial record of a key slice: 128 channels, m, l, 2 pad (16-byte multiple)
 constexpr int WM_LD = WHD + 8;            // padded row: fragment loads of a quarter warp cover all banks
 
 __device__ __forceinline__ void wm_mma(float (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0, unsigned b1) {
@@ -255,12 +256,13 @@ template <int HPC>          // query heads (= warps) per CTA: 8, or 4 when 8 wou
 __global__ void __launch_bounds__(HPC * 32) window_attn_mma_kernel(
     const float* __restrict__ qkv, int qkv_stride, const __nv_bfloat16* __restrict__ k_cache,
     const __nv_bfloat16* __restrict__ v_cache, int nq, int nkv, int max_seq, int base, int T,
-    const uint8_t* __restrict__ mask, float* __restrict__ out) {
+    const uint8_t* __restrict__ mask, float* __restrict__ out, int nsplit, float* __restrict__ part) {
   __shared__ __align__(16) __nv_bfloat16 ks[WM_KB][WM_LD];
   __shared__ __align__(16) __nv_bfloat16 vs[WM_KB][WM_LD];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t4 = lane & 3;
-  const int t0 = blockIdx.x * 16, kvh = blockIdx.y, grp = blockIdx.z;
+  const int split = blockIdx.x % nsplit;                // nsplit > 1: this CTA walks one slice of the key blocks
+  const int t0 = (blockIdx.x / nsplit) * 16, kvh = blockIdx.y, grp = blockIdx.z;
   const int q_per_kv = nq / nkv;
   const int gq = min(HPC, q_per_kv - grp * HPC);
   const int head = kvh * q_per_kv + grp * HPC + warp;
@@ -288,7 +290,9 @@ __global__ void __launch_bounds__(HPC * 32) window_attn_mma_kernel(
   const int n_keys = mask != nullptr ? base + T : min(base + T, base + t0 + 16);
   const __nv_bfloat16* kbase = k_cache + static_cast<size_t>(kvh) * max_seq * WHD;
   const __nv_bfloat16* vbase = v_cache + static_cast<size_t>(kvh) * max_seq * WHD;
-  for (int kb0 = 0; kb0 < n_keys; kb0 += WM_KB) {
+  const int blocks_per_split = ((n_keys + WM_KB - 1) / WM_KB + nsplit - 1) / nsplit;
+  const int key_end = min(n_keys, (split + 1) * blocks_per_split * WM_KB);
+  for (int kb0 = split * blocks_per_split * WM_KB; kb0 < key_end; kb0 += WM_KB) {
     __syncthreads();                                   // the previous block's readers are done
     for (int i = tid; i < WM_KB * 16; i += HPC * 32) {
       const int r = i >> 4, ch = i & 15;
@@ -365,7 +369,21 @@ __global__ void __launch_bounds__(HPC * 32) window_attn_mma_kernel(
       }
     }
   }
-  if (active) {
+  if (active && nsplit > 1) {
+    // un-normalised partial of this slice: [token][head][split][128 channels, m, l]; window_attn_merge_kernel folds them
+    float* p0 = part + ((static_cast<size_t>(r0) * nq + head) * nsplit + split) * WM_REC;
+    float* p1 = part + ((static_cast<size_t>(r1) * nq + head) * nsplit + split) * WM_REC;
+#pragma unroll
+    for (int nd = 0; nd < 16; ++nd) {
+      const int c = nd * 8 + 2 * t4;
+      if (r0 < T) *reinterpret_cast<float2*>(p0 + c) = make_float2(o[nd][0], o[nd][1]);
+      if (r1 < T) *reinterpret_cast<float2*>(p1 + c) = make_float2(o[nd][2], o[nd][3]);
+    }
+    if (t4 == 0) {
+      if (r0 < T) *reinterpret_cast<float2*>(p0 + WHD) = make_float2(m0, l0);
+      if (r1 < T) *reinterpret_cast<float2*>(p1 + WHD) = make_float2(m1, l1);
+    }
+  } else if (active) {
     const float i0 = l0 > 0.f ? 1.f / l0 : 0.f, i1 = l1 > 0.f ? 1.f / l1 : 0.f;
 #pragma unroll
     for (int nd = 0; nd < 16; ++nd) {
@@ -374,6 +392,28 @@ __global__ void __launch_bounds__(HPC * 32) window_attn_mma_kernel(
       if (r1 < T) *reinterpret_cast<float2*>(out + static_cast<size_t>(r1) * nq * WHD + static_cast<size_t>(head) * WHD + c) = make_float2(o[nd][2] * i1, o[nd][3] * i1);
     }
   }
+}
+
+// One warp per (token, head): folds the slices' partials (scores are in the log2 domain).
+__global__ void __launch_bounds__(128) window_attn_merge_kernel(const float* __restrict__ part, int nq, int nsplit, int T,
+                                                                float* __restrict__ out) {
+  const int w = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (w >= T * nq) return;
+  const float* rec = part + static_cast<size_t>(w) * nsplit * WM_REC;
+  float mx = -INFINITY;
+  for (int s = 0; s < nsplit; ++s) mx = fmaxf(mx, rec[s * WM_REC + WHD]);
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  float l = 0.f;
+  for (int s = 0; s < nsplit; ++s) {
+    const float m = rec[s * WM_REC + WHD];
+    if (m == -INFINITY) continue;
+    const float f = exp2f(m - mx);
+    const float4 v = *reinterpret_cast<const float4*>(rec + s * WM_REC + lane * 4);
+    acc.x += f * v.x; acc.y += f * v.y; acc.z += f * v.z; acc.w += f * v.w;
+    l += f * rec[s * WM_REC + WHD + 1];
+  }
+  const float inv = l > 0.f ? 1.f / l : 0.f;
+  *reinterpret_cast<float4*>(out + static_cast<size_t>(w) * WHD + lane * 4) = make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
 }
 
 }  // namespace ihb
@@ -397,25 +437,51 @@ extern "C" int ihb_qk_norm_rope_rows(float* qkv, int nq, int nkv, const float* q
   return cudaGetLastError();
 }
 
+// Key slices per query tile for a window of T tokens: enough CTAs to cover the GPU when the tiles alone do not, at
+// most one slice per 64-key block and IHB_WINDOW_MAX_SPLITS.
+static int window_split_bound(int nq, int nkv, int T) {          // slices wanted, before the cap by the number of key blocks
+  const int q_per_kv = nq / nkv;
+  const int ctas8 = ((T + 15) / 16) * nkv * ((q_per_kv + 7) / 8);
+  const int ctas = (ctas8 >= 120 || q_per_kv <= 4) ? ctas8 : ((T + 15) / 16) * nkv * ((q_per_kv + 3) / 4);
+  if (ctas >= 74) return 1;
+  const int s = (148 + ctas - 1) / ctas;
+  return s > IHB_WINDOW_MAX_SPLITS ? IHB_WINDOW_MAX_SPLITS : s;
+}
+
+extern "C" int ihb_window_attention_splits(int nq, int nkv, int base, int T) {
+  if (nq < 1 || nkv < 1 || nq % nkv || T < 1) return 1;
+  const int blocks = (base + T + WM_KB - 1) / WM_KB;
+  const int s = window_split_bound(nq, nkv, T);
+  return s > blocks ? blocks : s;
+}
+
+extern "C" size_t ihb_window_attention_scratch_floats(int nq, int nkv, int T) {
+  if (nq < 1 || nkv < 1 || nq % nkv || T < 1) return 0;
+  return static_cast<size_t>(T) * nq * window_split_bound(nq, nkv, T) * WM_REC;
+}
+
 extern "C" int ihb_window_attention(const float* qkv, int qkv_stride, const void* k_cache, const void* v_cache, int nq,
                                     int nkv, int max_seq, int base, int T, const unsigned char* mask, float* out, int mode,
-                                    cudaStream_t stream) {
+                                    float* scratch, cudaStream_t stream) {
   if (T < 1 || nq % nkv || base + T > max_seq) return cudaErrorInvalidValue;
   const int q_per_kv = nq / nkv;
   if (mode != 1) {          // tensor-core tiles (the default); mode 1 keeps the per-token CUDA-core kernel
     if (qkv_stride % 2) return cudaErrorInvalidValue;
     const int ctas8 = ((T + 15) / 16) * nkv * ((q_per_kv + 7) / 8);
+    // few query tiles (verify windows, short prompts): slice the keys so that the whole GPU works on them
+    const int nsplit = scratch != nullptr ? ihb_window_attention_splits(nq, nkv, base, T) : 1;
     if (ctas8 >= 120 || q_per_kv <= 4) {
-      const dim3 grid((T + 15) / 16, nkv, (q_per_kv + 7) / 8);
+      const dim3 grid(((T + 15) / 16) * nsplit, nkv, (q_per_kv + 7) / 8);
       window_attn_mma_kernel<8><<<grid, 256, 0, stream>>>(qkv, qkv_stride, reinterpret_cast<const __nv_bfloat16*>(k_cache),
                                                            reinterpret_cast<const __nv_bfloat16*>(v_cache), nq, nkv, max_seq, base, T,
-                                                           mask, out);
+                                                           mask, out, nsplit, scratch);
     } else {
-      const dim3 grid((T + 15) / 16, nkv, (q_per_kv + 3) / 4);
+      const dim3 grid(((T + 15) / 16) * nsplit, nkv, (q_per_kv + 3) / 4);
       window_attn_mma_kernel<4><<<grid, 128, 0, stream>>>(qkv, qkv_stride, reinterpret_cast<const __nv_bfloat16*>(k_cache),
                                                            reinterpret_cast<const __nv_bfloat16*>(v_cache), nq, nkv, max_seq, base, T,
-                                                           mask, out);
+                                                           mask, out, nsplit, scratch);
     }
+    if (nsplit > 1) window_attn_merge_kernel<<<(T * nq + 3) / 4, 128, 0, stream>>>(scratch, nq, nsplit, T, out);
     return cudaGetLastError();
   }
   const dim3 grid(T, nkv, (q_per_kv + 7) / 8);

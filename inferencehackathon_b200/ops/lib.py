@@ -164,8 +164,13 @@ def load(build_if_missing: bool = True) -> C.CDLL:
     lib.ihb_qk_norm_rope_rows.argtypes = [_vp, C.c_int, C.c_int, _vp, _vp, C.c_float, _vp, _vp, _vp, _vp, _vp, _vp,
                                           C.c_int, C.c_int, _vp]
     lib.ihb_qk_norm_rope_rows.restype = C.c_int
-    lib.ihb_window_attention.argtypes = [_vp, C.c_int, _vp, _vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _vp, _vp, C.c_int, _vp]
+    lib.ihb_window_attention.argtypes = [_vp, C.c_int, _vp, _vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _vp, _vp, C.c_int, _vp,
+                                         _vp]
     lib.ihb_window_attention.restype = C.c_int
+    lib.ihb_window_attention_splits.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int]
+    lib.ihb_window_attention_splits.restype = C.c_int
+    lib.ihb_window_attention_scratch_floats.argtypes = [C.c_int, C.c_int, C.c_int]
+    lib.ihb_window_attention_scratch_floats.restype = C.c_size_t
     lib.ihb_a2a_rows.argtypes = [C.POINTER(IhbA2AArgs), C.c_int, _vp]
     lib.ihb_a2a_rows.restype = C.c_int
     lib.ihb_allreduce_norm.argtypes = [C.POINTER(IhbComm), _vp, _vp, _vp, C.c_float, C.c_int, C.c_int, _vp, _vp, _vp, _vp,
@@ -436,13 +441,22 @@ def qk_norm_rope_rows(qkv: torch.Tensor, nq: int, nkv: int, q_gamma, k_gamma, ep
           "ihb_qk_norm_rope_rows")
 
 
+def window_attention_scratch_floats(nq: int, nkv: int, T: int) -> int:
+    return max(1, int(load().ihb_window_attention_scratch_floats(nq, nkv, T)))
+
+
 def window_attention(qkv: torch.Tensor, k_cache, v_cache, nq: int, nkv: int, max_seq: int, base: int,
-                     mask: Optional[torch.Tensor], out: torch.Tensor, mode: Optional[int] = None) -> None:
-    """``mode`` 0: tensor-core tiles, 1: per-token CUDA-core kernel; default from ``IHB_WINDOW_ATTN`` (0)."""
+                     mask: Optional[torch.Tensor], out: torch.Tensor, mode: Optional[int] = None,
+                     scratch: Optional[torch.Tensor] = None) -> None:
+    """``mode`` 0: tensor-core tiles, 1: per-token CUDA-core kernel; default from ``IHB_WINDOW_ATTN`` (0). ``scratch``
+    (``window_attention_scratch_floats(nq, nkv, T)`` floats) lets short windows slice the keys over many CTAs."""
     if mode is None:
         mode = int(os.environ.get("IHB_WINDOW_ATTN", "0"))
+    if scratch is not None and scratch.numel() < window_attention_scratch_floats(nq, nkv, qkv.shape[0]):
+        raise ValueError("window attention scratch too small")
     check(load().ihb_window_attention(qkv.data_ptr(), qkv.shape[1], k_cache.data_ptr(), v_cache.data_ptr(), nq, nkv,
-                                      max_seq, base, qkv.shape[0], ptr(mask), out.data_ptr(), mode, stream_ptr()),
+                                      max_seq, base, qkv.shape[0], ptr(mask), out.data_ptr(), mode, ptr(scratch),
+                                      stream_ptr()),
           "ihb_window_attention")
 
 
@@ -478,7 +492,8 @@ def allreduce_counted(comm: IhbComm, x: torch.Tensor, out: torch.Tensor, counter
                       err: torch.Tensor, resid: Optional[torch.Tensor] = None, gamma: Optional[torch.Tensor] = None,
                       eps: float = 1e-6, out_norm: Optional[torch.Tensor] = None) -> None:
     """Latency-optimal fused all-reduce (+ residual + RMSNorm) of ``x [T, H]`` (fp32 or bf16), ``T <= 64``: counted
-    fixed-point slots, one one-way trip, no barrier (``csrc/kernels/allreduce.cu::ar_counted_kernel``)."""
+    fixed-point slots, one one-way trip, no barrier (``csrc/kernels/allreduce.cu::ar_counted_kernel``). ``call_counter``:
+    64 int32 zeros owned by this (slot region, T) pair; ``counter`` is unused (kept for signature symmetry)."""
     T, H = x.shape
     check(load().ihb_allreduce_counted(C.byref(comm), x.data_ptr(), int(x.dtype == torch.bfloat16), ptr(resid), ptr(gamma), eps,
                                        T, H, out.data_ptr(), ptr(out_norm), counter.data_ptr(), call_counter.data_ptr(),

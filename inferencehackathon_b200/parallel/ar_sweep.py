@@ -101,7 +101,7 @@ def main(argv=None) -> int:
                 err.zero_()
         if T <= small_rows:
             # one call counter per shape: the slot layout [4][T * H] depends on T
-            cc = small_calls.setdefault(T, torch.zeros(1, dtype=torch.int32, device=dev))
+            cc = small_calls.setdefault(T, torch.zeros(64, dtype=torch.int32, device=dev))
             comm.extra(4 * small_rows * H * 8).zero_()
             comm.barrier_host()
             xin = x.to(torch.bfloat16) if a.payload == "bf16" else x

@@ -247,7 +247,8 @@ class GpuWindow:
             K.qk_norm_rope_rows(qkv, nq, nkv, lw.q_norm, lw.k_norm, m.rms_eps, d.cos, d.sin, pos32, slots,
                                 d.k_cache[L], d.v_cache[L], d.max_seq)
             attn = self._buf("attn", (T, nq * 128), torch.float32)
-            K.window_attention(qkv, d.k_cache[L], d.v_cache[L], nq, nkv, d.max_seq, base, mask_u8, attn)
+            K.window_attention(qkv, d.k_cache[L], d.v_cache[L], nq, nkv, d.max_seq, base, mask_u8, attn,
+                               scratch=self._buf("attn_part", (K.window_attention_scratch_floats(nq, nkv, T),), torch.float32))
             aq, asc, _ = self._quant(attn, None, "a")
             o = self._linear(lw.wo, aq, asc, T, "wo")
             x, h2 = self._all_reduce(o, x, lw.post_ln, "a" + str(L & 1))

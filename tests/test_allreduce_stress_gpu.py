@@ -35,7 +35,7 @@ counter = torch.zeros(8, dtype=torch.int32, device=dev)
 err = torch.zeros(1, dtype=torch.int32, device=dev)
 cm = comm.comm_block(epoch)
 cm_small = comm.comm_block(epoch, slot_offset_bytes=comm.extra_off)     # the counted variant keeps its own slot region
-calls = torch.zeros(1, dtype=torch.int32, device=dev)
+calls = torch.zeros(64, dtype=torch.int32, device=dev)
 def counted(src, dst):
     K.allreduce_counted(cm_small, src, dst, counter, calls, err)
 def plain(algo):

@@ -96,3 +96,26 @@ def test_per_kernel_table_of_the_per_op_pipelines(tc, monkeypatch):
     assert per_token == eng.gpu.n_launches_per_step
     assert all(r["us_per_launch"] > 0 for r in rows) and abs(sum(r["share"] for r in rows) - 1.0) < 1e-6
     assert eng.generate(prompt, 4).tokens == first
+
+
+@pytest.mark.parametrize("ctx", [1500, 2600])
+def test_persistent_kernel_at_longer_contexts(ctx, monkeypatch):
+    """Both attention schemes of the persistent kernel against the PyTorch model: up to 16 blocks of 128 positions
+    the partial records are merged by the o_proj CTAs (ctx 1500: 12 blocks); beyond that the split scheme with a
+    last-arriver merge runs (ctx 2600: 21 blocks). The prompt goes through the batched window path; the decoded
+    tokens are compared under teacher forcing."""
+    monkeypatch.setenv("IHB_MEGA", "1")
+    dev = "cuda:0"
+    g = torch.Generator().manual_seed(ctx)
+    prompt = torch.randint(0, SMALL.vocab, (ctx,), generator=g).tolist()
+    ref = InferenceEngine.build("small", weights="bf16", device=dev, backend="torch", max_seq=ctx + 64)
+    eng = InferenceEngine.build("small", weights="bf16", device=dev, backend="cuda", max_seq=ctx + 64)
+    assert eng.gpu.use_mega
+    a = ref.generate(prompt, 12)
+    pe = eng.prefill(prompt)
+    got = [pe.next_token]
+    for t in a.tokens[:-1]:
+        got.append(eng.decode_step(t, want_routes=False).token_id)
+    eng.gpu.check_error()
+    agree = sum(int(x == y) for x, y in zip(a.tokens[1:], got[1:]))          # the decoded tokens (not the prompt pass)
+    assert agree >= 9, (a.tokens, got)

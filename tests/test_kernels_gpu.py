@@ -275,7 +275,7 @@ def test_counted_allreduce_single_rank_adds_residual_and_norms(payload):
     epoch = torch.zeros(4, dtype=torch.int32, device=d)
     cm = lib.single_comm(slots, epoch)
     counter = torch.zeros(8, dtype=torch.int32, device=d)
-    calls = torch.zeros(1, dtype=torch.int32, device=d)
+    calls = torch.zeros(64, dtype=torch.int32, device=d)
     err = torch.zeros(1, dtype=torch.int32, device=d)
     gamma = torch.rand(H, device=d, generator=g) + 0.5
     for it in range(9):
@@ -289,5 +289,5 @@ def test_counted_allreduce_single_rank_adds_residual_and_norms(payload):
         refn = ref * torch.rsqrt(ref.pow(2).mean(-1, keepdim=True) + 1e-6) * gamma
         assert float((out - ref).abs().max()) < 4e-6 * (1 + it)
         assert float((outn - refn).abs().max()) < 1e-5
-    assert int(err.item()) == 0 and int(calls.item()) == 9
+    assert int(err.item()) == 0 and calls[:T].tolist() == [9] * T and int(calls[T:].abs().max()) == 0
     assert int(slots.abs().max()) == 0                   # every reader cleared what it consumed

@@ -279,7 +279,8 @@ def test_speculative_driver_on_gpu_engine_equals_its_own_greedy():
 
 
 @pytest.mark.parametrize("T,base,nq,nkv,masked", [(40, 0, 8, 1, False), (130, 77, 16, 2, False), (23, 300, 8, 2, True),
-                                                   (16, 0, 4, 1, True), (257, 1000, 8, 1, False)])
+                                                   (16, 0, 4, 1, True), (257, 1000, 8, 1, False), (8, 1000, 8, 1, False),
+                                                   (5, 4000, 16, 2, True)])
 def test_window_attention_tensor_core_tiles_against_fp32(T, base, nq, nkv, masked):
     """Both window attention kernels (tensor-core tiles; one CTA per token) against plain fp32 PyTorch on the same
     bf16 cache rows: cached context + the window's own rows, causal or with an explicit visibility mask."""
@@ -305,8 +306,9 @@ def test_window_attention_tensor_core_tiles_against_fp32(T, base, nq, nkv, maske
     s = s.masked_fill(~vis[:, None, None, :], float("-inf"))
     want = torch.einsum("tkgs,ksd->tkgd", torch.softmax(s, -1), vc[:, : base + T].float()).reshape(T, nq * 128)
     mu8 = mask.to(torch.uint8).contiguous() if mask is not None else None
-    for mode in (0, 1):
+    scratch = torch.full((K.window_attention_scratch_floats(nq, nkv, T),), float("nan"), device=d)
+    for mode, scr in ((0, None), (0, scratch), (1, None)):          # mode 0 with scratch: keys sliced over CTAs + merge
         out = torch.full((T, nq * 128), float("nan"), device=d)
-        K.window_attention(qkv, kc, vc, nq, nkv, max_seq, base, mu8, out, mode=mode)
+        K.window_attention(qkv, kc, vc, nq, nkv, max_seq, base, mu8, out, mode=mode, scratch=scr)
         torch.cuda.synchronize()
-        assert float((out - want).abs().max()) < 2e-3, mode
+        assert float((out - want).abs().max()) < 2e-3, (mode, scr is not None)
