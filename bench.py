@@ -159,7 +159,8 @@ def correctness_gate(args, rank: int, world: int, dev, tp: int, ep: int) -> dict
     try:
         for wts in ("bf16", args.weights):
             eng = InferenceEngine.build(args.model, tp=tp, ep=ep, rank=rank, world=world, weights=wts, device=dev,
-                                        backend="cuda", max_seq=128, n_layers=args.gate_layers)
+                                        backend="cuda", max_seq=128, n_layers=args.gate_layers,
+                                        same_weights_in_every_layout=True)
             pre = eng.prefill(prompt, return_logits=True)
             toks = [pre.next_token]
             for _ in range(7):
@@ -174,7 +175,7 @@ def correctness_gate(args, rank: int, world: int, dev, tp: int, ep: int) -> dict
                 flag = torch.ones(1, device=dev)
                 if rank == 0:
                     ref = InferenceEngine.build(args.model, weights="bf16", device=dev, backend="cuda", max_seq=128,
-                                                n_layers=args.gate_layers)
+                                                n_layers=args.gate_layers, same_weights_in_every_layout=True)
                     pr = ref.prefill(prompt, return_logits=True)
                     scale = float(pr.logits.abs().max())
                     err = float((pr.logits[0].float() - pre.logits[0].float()).abs().max())

@@ -257,6 +257,10 @@ int ihb_moe_gather_rows(const void* src, const int* order, int k, int row_bytes,
 int ihb_moe_combine_rows(const float* yg, const int* inv, const float* tw, int k, int H, int T, const float* resid, float* y,
                          cudaStream_t stream);
 
+// Returns and clears the CUDA runtime's last-error word (a launch refused for its configuration leaves it set; the next
+// entry point that ends in cudaGetLastError would report it as its own).
+int ihb_clear_last_error(void);
+
 // Block-scaled e4m3 weights W [nmat][rows][K] with scale [nmat][nrb][nkb] (one fp32 per rb x kb block) -> bf16 copies.
 int ihb_dequant_bf16(const void* W, const float* scale, long long nmat, int rows, int K, int rb, int kb, int nrb, int nkb, void* out,
                      cudaStream_t stream);

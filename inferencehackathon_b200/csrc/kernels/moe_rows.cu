@@ -16,6 +16,68 @@ constexpr int RT_TOK = 8;          // tokens per CTA of the router kernel
 constexpr int RT_THREADS = 256;
 constexpr int RT_KC = 512;         // channels staged per round
 
+// One warp: softmax over the E logits of token t, top-k (ties -> lowest id), optional renormalisation.
+__device__ __forceinline__ void router_topk_tail(const float* __restrict__ lg_row, int E, int top_k, int renorm, int lane, int t,
+                                                 float* __restrict__ logits_out, int* __restrict__ ti, float* __restrict__ tw) {
+  float v[8];
+  float mx = -INFINITY;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int e = lane + 32 * j;
+    v[j] = e < E ? lg_row[e] : -INFINITY;
+    mx = fmaxf(mx, v[j]);
+    if (logits_out != nullptr && e < E) logits_out[static_cast<size_t>(t) * E + e] = v[j];
+  }
+  mx = warp_max(mx);
+  float sum = 0.f;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) sum += (lane + 32 * j < E) ? __expf(v[j] - mx) : 0.f;
+  sum = warp_sum(sum);
+  float my_p = 0.f;
+  int my_e = 0;
+  for (int k = 0; k < top_k; ++k) {
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (v[j] > bv) { bv = v[j]; bi = lane + 32 * j; }
+    const float mv = warp_max(bv);
+    const int wi = __reduce_min_sync(0xffffffffu, bv == mv ? bi : 0x7fffffff);
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (lane + 32 * j == wi) v[j] = -INFINITY;
+    if (lane == k) { my_p = __expf(mv - mx) / sum; my_e = wi; }
+  }
+  float den = 1.f;
+  if (renorm) den = warp_sum(lane < top_k ? my_p : 0.f);
+  if (lane < top_k) {
+    ti[static_cast<size_t>(t) * top_k + lane] = my_e;
+    tw[static_cast<size_t>(t) * top_k + lane] = my_p / den;
+  }
+}
+
+// ---- short windows (verify, a few prompt tokens): one warp per expert, then one warp per token -------------------------------------
+// The tile kernels below put 8 or 16 tokens on ONE CTA, which then reads the whole router alone (66 us for 128 x 4096).
+// Here the router rows are spread over E / 4 CTAs; the logits go through a caller-provided [T][E] buffer.
+__global__ void __launch_bounds__(128) router_logits_wide_kernel(const float* __restrict__ h, const __nv_bfloat16* __restrict__ W,
+                                                                 int T, int H, int E, float* __restrict__ logits) {
+  const int e = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (e >= E) return;
+  const uint4* wr = reinterpret_cast<const uint4*>(W + static_cast<size_t>(e) * H);
+  for (int t = 0; t < T; ++t) {
+    const float4* x = reinterpret_cast<const float4*>(h + static_cast<size_t>(t) * H);
+    float acc = 0.f;
+    for (int c8 = lane; c8 < H / 8; c8 += 32) acc += dot8_bf16(wr[c8], x[2 * c8], x[2 * c8 + 1]);   // the row stays in L1 after t = 0
+    acc = warp_sum(acc);
+    if (lane == 0) logits[static_cast<size_t>(t) * E + e] = acc;
+  }
+}
+__global__ void __launch_bounds__(128) router_topk_from_logits_kernel(const float* __restrict__ logits, int T, int E, int top_k,
+                                                                      int renorm, int* __restrict__ ti, float* __restrict__ tw) {
+  const int t = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (t < T) router_topk_tail(logits + static_cast<size_t>(t) * E, E, top_k, renorm, lane, t, nullptr, ti, tw);
+}
+
 // logits [T][E] (optional), ti [T][k] int32, tw [T][k] fp32. E <= 256, k <= 8, H % RT_KC == 0 or any multiple of 8.
 __global__ void __launch_bounds__(RT_THREADS) router_topk_rows_kernel(const float* __restrict__ h, const __nv_bfloat16* __restrict__ W,
                                                                        int T, int H, int E, int top_k, int renorm,
@@ -66,43 +128,7 @@ __global__ void __launch_bounds__(RT_THREADS) router_topk_rows_kernel(const floa
   // one warp per token: softmax + top-k
   const int warp = tid >> 5, lane = tid & 31;
   const int t = t0 + warp;
-  if (warp < RT_TOK && t < T) {
-    float v[8];
-    float mx = -INFINITY;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const int e = lane + 32 * j;
-      v[j] = e < E ? lg[warp][e] : -INFINITY;
-      mx = fmaxf(mx, v[j]);
-      if (logits_out != nullptr && e < E) logits_out[static_cast<size_t>(t) * E + e] = v[j];
-    }
-    mx = warp_max(mx);
-    float sum = 0.f;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) sum += (lane + 32 * j < E) ? __expf(v[j] - mx) : 0.f;
-    sum = warp_sum(sum);
-    float my_p = 0.f;
-    int my_e = 0;
-    for (int k = 0; k < top_k; ++k) {
-      float bv = -INFINITY;
-      int bi = 0x7fffffff;
-#pragma unroll
-      for (int j = 0; j < 8; ++j)
-        if (v[j] > bv) { bv = v[j]; bi = lane + 32 * j; }
-      const float mv = warp_max(bv);
-      const int wi = __reduce_min_sync(0xffffffffu, bv == mv ? bi : 0x7fffffff);
-#pragma unroll
-      for (int j = 0; j < 8; ++j)
-        if (lane + 32 * j == wi) v[j] = -INFINITY;
-      if (lane == k) { my_p = __expf(mv - mx) / sum; my_e = wi; }
-    }
-    float den = 1.f;
-    if (renorm) den = warp_sum(lane < top_k ? my_p : 0.f);
-    if (lane < top_k) {
-      ti[static_cast<size_t>(t) * top_k + lane] = my_e;
-      tw[static_cast<size_t>(t) * top_k + lane] = my_p / den;
-    }
-  }
+  if (warp < RT_TOK && t < T) router_topk_tail(lg[warp], E, top_k, renorm, lane, t, logits_out, ti, tw);
 }
 
 // ---- the same router on the tensor cores: 16 tokens per CTA, logits as m16n8k16 tiles ---------------------------------------------
@@ -364,9 +390,16 @@ extern "C" int ihb_dequant_bf16(const void* W, const float* scale, long long nma
   return cudaGetLastError();
 }
 
+extern "C" int ihb_clear_last_error(void) { return static_cast<int>(cudaGetLastError()); }
+
 extern "C" int ihb_router_topk_rows(const float* h, const void* router_bf16, int T, int H, int E, int top_k, int renorm,
                                     float* logits, int* ti, float* tw, cudaStream_t stream) {
   if (T < 1 || E < 1 || E > 256 || top_k < 1 || top_k > 8 || top_k > E || H % 8) return cudaErrorInvalidValue;
+  if (logits != nullptr && T <= 32) {        // short windows with a logits buffer: router rows spread over E / 4 CTAs
+    router_logits_wide_kernel<<<(E + 3) / 4, 128, 0, stream>>>(h, reinterpret_cast<const __nv_bfloat16*>(router_bf16), T, H, E, logits);
+    router_topk_from_logits_kernel<<<(T + 3) / 4, 128, 0, stream>>>(logits, T, E, top_k, renorm, ti, tw);
+    return cudaGetLastError();
+  }
   if (H % RM_KC == 0 && T >= 4) {            // tensor-core tiles; very short windows and odd widths take the plain kernel
     static bool attr_set = false;
     if (!attr_set) {

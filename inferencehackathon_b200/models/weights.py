@@ -171,6 +171,57 @@ def random_state_dict(cfg: ModelConfig, seed: int = 0, std: float = 0.02,
     return sd
 
 
+class DeviceRandomStateDict(dict):
+    """The same full random-init state dict as :func:`random_state_dict` in spirit, for models too large to hold
+    unsharded: a tensor is generated on ``device`` when it is asked for, from a seed derived from its NAME, and is not
+    kept. Every rank and every parallel layout therefore slices the same full tensors, so a tensor-, expert- or
+    hybrid-parallel engine holds exactly the weights of the one-GPU engine built from the same seed (which the
+    per-rank streams of :func:`random_sharded_weights` do not give)."""
+
+    def __init__(self, cfg: ModelConfig, seed: int = 0, device="cuda", std: float = 0.02):
+        super().__init__()
+        self.cfg, self.seed, self.device, self.std = cfg, seed, torch.device(device), std
+        H, hd = cfg.hidden, cfg.head_dim
+        spec = {"model.embed_tokens.weight": ((cfg.vocab, H), "w"), "model.norm.weight": ((H,), "ln")}
+        if not cfg.tie_embeddings:
+            spec["lm_head.weight"] = ((cfg.vocab, H), "w")
+        for L in range(cfg.n_layers):
+            p = hf_layer_prefix(L)
+            spec[p + "input_layernorm.weight"] = ((H,), "ln")
+            spec[p + "post_attention_layernorm.weight"] = ((H,), "ln")
+            spec[p + "self_attn.q_proj.weight"] = ((cfg.q_dim, H), "w")
+            spec[p + "self_attn.k_proj.weight"] = ((cfg.kv_dim, H), "w")
+            spec[p + "self_attn.v_proj.weight"] = ((cfg.kv_dim, H), "w")
+            spec[p + "self_attn.o_proj.weight"] = ((H, cfg.q_dim), "w")
+            spec[p + "self_attn.q_norm.weight"] = ((hd,), "ln")
+            spec[p + "self_attn.k_norm.weight"] = ((hd,), "ln")
+            spec[p + "mlp.gate.weight"] = ((cfg.n_experts, H), "router")
+            for e in range(cfg.n_experts):
+                ep = p + f"mlp.experts.{e}."
+                spec[ep + "gate_proj.weight"] = ((cfg.moe_inter, H), "w")
+                spec[ep + "up_proj.weight"] = ((cfg.moe_inter, H), "w")
+                spec[ep + "down_proj.weight"] = ((H, cfg.moe_inter), "w")
+        self._spec = spec
+
+    def __contains__(self, name) -> bool:
+        return name in self._spec
+
+    def __len__(self) -> int:
+        return len(self._spec)
+
+    def keys(self):
+        return self._spec.keys()
+
+    def __getitem__(self, name: str) -> torch.Tensor:
+        import zlib
+        shape, kind = self._spec[name]
+        g = torch.Generator(device=self.device).manual_seed((zlib.crc32(name.encode()) << 20) ^ (self.seed * 1000003 + 17))
+        t = torch.randn(*shape, device=self.device, dtype=torch.float32, generator=g)
+        if kind == "ln":
+            return 1.0 + 0.1 * t
+        return t * (self.std * 5.0 if kind == "router" else self.std)
+
+
 class _Getter:
     """Uniform tensor access over a dict or a safetensors directory; understands HF fp8 checkpoints."""
 

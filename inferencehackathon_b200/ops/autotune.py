@@ -75,24 +75,34 @@ def sweep_experts(tp: int, fp8: bool, iters: int, dev: torch.device) -> Dict:
 
     sms = torch.cuda.get_device_properties(dev).multi_processor_count
     rows: List[Dict] = []
-    for R_gu, R_d, S, gm in itertools.product((0, 1, 2, 4, 8), (0, 4, 8, 16, 32), (0, 3, 6, 12), (1, 2)):
-        if (R_gu == 0) != (R_d == 0) or (R_gu == 0 and (S or gm != 1)):
+    # grids never exceed the SM count: the down kernel's tail waits for the other CTAs' partial sums, so all CTAs of a
+    # launch must be resident together
+    for R_gu, R_d, S, gdiv in itertools.product((0, 1, 2, 4, 8), (0, 4, 8, 16, 32), (0, 3, 6, 12), (1, 2)):
+        if (R_gu == 0) != (R_d == 0) or (R_gu == 0 and (S or gdiv != 1)):
             continue                                     # (0, 0, 0, default grid) is the kernels' own rule; no mixed cases
-        blocks = [args_for(wgu, wd, R_gu, R_d, S, 0 if R_gu == 0 else sms * gm) for wgu, wd in sets]
+        grid = 0 if R_gu == 0 else sms // gdiv
+        blocks = [args_for(wgu, wd, R_gu, R_d, S, grid) for wgu, wd in sets]
 
         def fn(i, blocks=blocks):
             lib.moe_gateup(blocks[i % len(blocks)], False)
             lib.moe_down(blocks[i % len(blocks)], False)
         try:
+            fn(0)                                        # one launch pair first: a configuration whose bounded waits
+            torch.cuda.synchronize()                     # run out reports through the error word and is not timed
+            code = int(err.item())
+            if code:
+                err.zero_()
+                counter.zero_()
+                rows.append({"R_gu": R_gu, "R_d": R_d, "S": S, "grid": grid, "error_word": code})
+                continue
             us = _time_us(fn, iters)
         except RuntimeError:
             continue                                     # refused by the entry point's validation
-        if int(err.item()):
-            raise RuntimeError("device error word set during the expert sweep")
-        rows.append({"R_gu": R_gu, "R_d": R_d, "S": S, "grid": 0 if R_gu == 0 else sms * gm, "us": round(us, 2),
+        rows.append({"R_gu": R_gu, "R_d": R_d, "S": S, "grid": grid, "us": round(us, 2),
                      "gbs": round(bytes_set / us * 1e-3, 1)})
-    best = min(rows, key=lambda r: r["us"])
-    rule = next(r for r in rows if r["R_gu"] == 0)
+    timed = [r for r in rows if "us" in r]
+    best = min(timed, key=lambda r: r["us"])
+    rule = next(r for r in timed if r["R_gu"] == 0)
     return {"shape": {"H": H, "I": I, "top_k": k, "weights": "fp8_block" if fp8 else "bf16", "bytes": bytes_set},
             "rule": rule, "best": best, "rule_vs_best": round(rule["us"] / best["us"], 3), "all": rows}
 

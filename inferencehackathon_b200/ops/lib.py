@@ -178,6 +178,7 @@ def load(build_if_missing: bool = True) -> C.CDLL:
     lib.ihb_allreduce_norm.restype = C.c_int
     lib.ihb_router_topk_rows.argtypes = [_vp, _vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _vp, _vp, _vp, _vp]
     lib.ihb_router_topk_rows.restype = C.c_int
+    lib.ihb_clear_last_error.restype = C.c_int
     lib.ihb_moe_group_table.argtypes = [_vp, C.c_int, C.c_int, C.c_int, C.c_int, _vp, _vp, _vp, _vp, C.c_int, _vp]
     lib.ihb_moe_group_table.restype = C.c_int
     lib.ihb_moe_gather_rows.argtypes = [_vp, _vp, C.c_int, C.c_int, C.c_int, _vp, _vp]
@@ -210,6 +211,7 @@ def stream_ptr() -> int:
 
 def check(code: int, what: str) -> None:
     if code != 0:
+        _lib.ihb_clear_last_error()          # a refused launch must not be reported again by the next entry point
         raise RuntimeError(f"{what}: CUDA error {code}")
 
 

@@ -16,7 +16,8 @@ import torch
 
 from ..config import EngineConfig, ModelConfig, ParallelConfig, QuantConfig, env_flag, get_model_config
 from ..models.qwen3_moe import Qwen3MoE, RouteRecord
-from ..models.weights import ModelWeights, random_sharded_weights, random_state_dict, shard_state_dict
+from ..models.weights import (DeviceRandomStateDict, ModelWeights, random_sharded_weights, random_state_dict,
+                              shard_state_dict)
 from ..parallel.collectives import Collectives
 from ..utils.timing import StepTimer
 from .sampler import Sampler, SamplingParams
@@ -128,10 +129,12 @@ class InferenceEngine:
               weights: str = "fp32", kv: Optional[str] = None, device="cpu", backend: str = "auto",
               max_seq: int = 2048, seed: int = 0, n_layers: Optional[int] = None, distinct_layers: int = 0,
               state_dict=None, checkpoint: Optional[str] = None, comm: str = "auto",
-              use_graph: bool = True) -> "InferenceEngine":
+              use_graph: bool = True, same_weights_in_every_layout: bool = False) -> "InferenceEngine":
         """Public constructor. Weight source, in order: ``state_dict`` (HF names), ``checkpoint`` (safetensors
         directory), else random init (host-side and layout-independent for small models, streamed on the
-        device otherwise)."""
+        device otherwise: per-rank random streams, fast, but a sharded engine then holds other numbers than the
+        one-GPU engine; ``same_weights_in_every_layout`` generates every full tensor on the device from a seed derived
+        from its name and slices it, for comparisons across layouts)."""
         mcfg = get_model_config(model, n_layers)
         world = world if world is not None else max(tp, ep)
         par = ParallelConfig(tp=tp, ep=ep, rank=rank, world=world)
@@ -143,6 +146,8 @@ class InferenceEngine:
             w = shard_state_dict(state_dict if state_dict is not None else checkpoint, mcfg, par, q, device=device)
         elif mcfg.total_params() <= 300_000_000:
             w = shard_state_dict(random_state_dict(mcfg, seed), mcfg, par, q, device=device)
+        elif same_weights_in_every_layout:
+            w = shard_state_dict(DeviceRandomStateDict(mcfg, seed, device), mcfg, par, q, device=device)
         else:
             w = random_sharded_weights(mcfg, par, q, device, seed, distinct_layers)
         return cls(ecfg, w, device=device)

@@ -594,7 +594,7 @@ class GpuDecoder:
         return self._window
 
     def has_window(self) -> bool:
-        return (self.use_mega or not self.use_tc) and self.cfg.parallel.ep <= 1 and bool(env_flag("IHB_WINDOW", 1))
+        return (self.use_mega or not self.use_tc) and bool(env_flag("IHB_WINDOW", 1))
 
     def logits_for(self, tokens, commit=True, tree_mask=None, positions=None, aux_layers=()):
         """Logits ``[T, V]`` of a window of new tokens: one batched forward on the tensor cores."""

@@ -37,8 +37,6 @@ class GpuWindow:
     def __init__(self, dec):
         self.d = dec
         m, w = dec.cfg.model, dec.w
-        if dec.cfg.parallel.ep > 1:
-            raise NotImplementedError("the window path is tensor-parallel only")
         if w.layers and w.layers[0].wqkv.data.device.type == "meta":
             raise RuntimeError("the window path needs the plain row-major weights (persistent or streaming pipeline)")
         # GEMM operand type of this path: bf16 for bf16 models and (by default) for block-fp8 models as well
@@ -63,12 +61,16 @@ class GpuWindow:
         self._views = {}
         self._args = {}                       # argument blocks of the GEMM launches, built once per (weight, tokens)
         self.n_gemm_launches = 0
-        # tensor parallel: the two all-reduces of a layer run as this package's fused kernel (reduce in the switch or
-        # over peer loads, residual add, RMSNorm of the next block) on a symmetric buffer of its own; IHB_WINDOW_FUSED_AR=0
-        # falls back to NCCL + separate norm. Building the buffer is a collective: every rank builds its window together.
+        # several GPUs (tensor, expert or hybrid parallel): the two all-reduces of a layer run as this package's fused kernel
+        # (reduce in the switch or over peer loads, residual add, RMSNorm of the next block) on a symmetric buffer of its
+        # own; IHB_WINDOW_FUSED_AR=0 falls back to NCCL + separate norm. Building the buffer is a collective: every rank
+        # builds its window together. Attention heads are split tp ways and replicated world / tp times, so the o_proj
+        # partials are scaled by tp / world before the sum over all ranks (the decode kernel does the same); experts are
+        # split ep ways: a rank runs the (token, slot) pairs whose expert it holds, the sum over ranks combines them.
         self.ar = None
         par = dec.cfg.parallel
-        if par.tp > 1 and par.world == par.tp and env_flag("IHB_WINDOW_FUSED_AR", 1):
+        self.attn_scale = float(par.tp) / float(max(par.world, 1))
+        if par.world > 1 and env_flag("IHB_WINDOW_FUSED_AR", 1):
             from ..parallel.symm import SymmetricComm
             self.ar = SymmetricComm(par, dev, slot_floats=2 * CHUNK * dec.H)
             self.ar_epoch = torch.zeros(4, dtype=torch.int32, device=dev)
@@ -80,7 +82,7 @@ class GpuWindow:
         d = self.d
         T, H = part.shape
         if self.ar is None:
-            x = resid + d.comm_ref.all_reduce_tp(part.clone() if d.cfg.parallel.tp > 1 else part)
+            x = resid + d.comm_ref.all_reduce_world(part.clone() if d.cfg.parallel.world > 1 else part)
             return x, None
         out = self._buf("ar_out_" + tag, (T, H), torch.float32)
         outn = self._buf("ar_norm_" + tag, (T, H), torch.float32) if gamma is not None else None
@@ -251,6 +253,8 @@ class GpuWindow:
                                scratch=self._buf("attn_part", (K.window_attention_scratch_floats(nq, nkv, T),), torch.float32))
             aq, asc, _ = self._quant(attn, None, "a")
             o = self._linear(lw.wo, aq, asc, T, "wo")
+            if self.attn_scale != 1.0:
+                o.mul_(self.attn_scale)
             x, h2 = self._all_reduce(o, x, lw.post_ln, "a" + str(L & 1))
             if h2 is not None:
                 hq, hs, _ = self._quant(h2, None, "h")
@@ -261,15 +265,16 @@ class GpuWindow:
             E_l = lw.w_gu.data.shape[0]
             ti = self._buf("ti_all", (n_layers, T, k), torch.int32)[L]
             tw = self._buf("tw_all", (n_layers, T, k), torch.float32)[L]
-            K.router_topk_rows(h2, lw.router, k, bool(m.norm_topk_prob), ti, tw)
-            per = max(1, pairs // E_l)
+            rlog = self._buf("router_logits", (T, m.n_experts), torch.float32) if T <= 32 else None
+            K.router_topk_rows(h2, lw.router, k, bool(m.norm_topk_prob), ti, tw, logits=rlog)
+            per = max(1, pairs // m.n_experts)
             nt = 16 if per <= 12 else 32 if per <= 28 else 64
             gmax = E_l + pairs // nt + 1
             order = self._buf("order", (pairs,), torch.int32)
             inv = self._buf("inv", (pairs,), torch.int32)
             groups = self._buf("groups", (gmax, 4), torch.int32)
             n_groups = self._buf("n_groups", (1,), torch.int32)
-            K.moe_group_table(ti, 0, E_l, nt, order, inv, groups, n_groups)
+            K.moe_group_table(ti, w.geom.expert0, E_l, nt, order, inv, groups, n_groups)
             # grouped expert GEMMs over the (token, slot) pairs in expert order
             gq = self._buf("gq", (pairs, hq.shape[1]), torch.uint8)
             K.moe_gather_rows(hq, order, k, gq)
@@ -279,7 +284,7 @@ class GpuWindow:
             act = self._grouped(lw.w_gu, K.TC_GATEUP, I, gq, gs, groups, n_groups, gmax, nt, pairs, "act")
             cq, cs, _ = self._quant(act, None, "c")
             yg = self._grouped(lw.w_d, K.TC_DOWN, H, cq, cs, groups, n_groups, gmax, nt, pairs, "y")
-            if d.cfg.parallel.tp > 1:
+            if d.cfg.parallel.world > 1:
                 y = self._buf("ycomb", (T, H), torch.float32)
                 K.moe_combine_rows(yg, inv, tw, k, y)               # slot order: deterministic
                 nxt = w.layers[L + 1].in_ln if L + 1 < n_layers else None

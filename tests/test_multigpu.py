@@ -23,7 +23,8 @@ weights = os.environ.get("IHB_TEST_WEIGHTS", "bf16")
 prompt = torch.randint(0, 4096, (20,), generator=torch.Generator().manual_seed(3)).tolist()
 plan = os.environ.get("IHB_TEST_PLAN", "tp")
 tp, ep = {"tp": (world, 1), "ep": (1, world), "hybrid": (world, world)}[plan]
-os.environ["IHB_WINDOW_PREFILL"] = "0"          # the prompt goes through the persistent decode kernel, token by token
+if os.environ.get("IHB_TEST_WINDOW", "0") != "1":
+    os.environ["IHB_WINDOW_PREFILL"] = "0"      # the prompt goes through the persistent decode kernel, token by token
 eng = InferenceEngine.build("small", tp=tp, ep=ep, rank=rank, world=world, weights=weights, device=dev, backend="cuda", max_seq=128)
 pre = eng.prefill(prompt, return_logits=True)
 tokens = [pre.next_token]
@@ -103,6 +104,19 @@ def test_expert_parallel_decode_in_the_persistent_kernel(plan):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     out = _run(2, "auto", "bf16", plan)
+    assert out["tokens"][0] == out["tokens"][1], out
+    agree = sum(int(a == b) for a, b in zip(out["tokens"][0], out["ref"]))
+    assert out["logits_rel_err"] < 0.02 and agree >= 11, out
+
+
+@pytest.mark.parametrize("plan", ["tp", "ep", "hybrid"])
+def test_batched_prompt_pass_on_two_gpus(plan):
+    """The prompt through the batched window path (tensor-core GEMMs, device routing, fused all-reduce + norm) on two
+    GPUs, tensor-, expert- and hybrid-parallel: logits and the tokens decoded after it against the one-GPU engine,
+    whose prompt takes the same path."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    out = _run(2, "auto", "bf16", plan, extra_env={"IHB_TEST_WINDOW": "1"})
     assert out["tokens"][0] == out["tokens"][1], out
     agree = sum(int(a == b) for a, b in zip(out["tokens"][0], out["ref"]))
     assert out["logits_rel_err"] < 0.02 and agree >= 11, out

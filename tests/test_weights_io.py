@@ -156,3 +156,27 @@ def test_directory_written_by_the_reference_converter_loads(tmp_path):
     a, b = _logits(w1, toks), _logits(ref, toks)
     assert torch.isfinite(a).all()
     assert float((a - b).abs().max()) < 0.15 * float(b.abs().max())
+
+
+def test_device_random_state_dict_gives_every_layout_the_same_model():
+    """Tensors generated on demand from a seed derived from their name: a tensor-parallel and an expert-parallel shard
+    are slices of the one-rank model (what the benchmark's distributed correctness gate relies on)."""
+    import torch
+    from inferencehackathon_b200.config import ParallelConfig, QuantConfig, get_model_config
+    from inferencehackathon_b200.models.weights import DeviceRandomStateDict, shard_state_dict
+    m = get_model_config("small", 2)
+    sd = DeviceRandomStateDict(m, 0, "cpu")
+    assert "model.layers.1.mlp.experts.3.up_proj.weight" in sd and "nope" not in sd
+    assert torch.equal(sd["model.norm.weight"], sd["model.norm.weight"])           # regenerated, same numbers
+    q = QuantConfig(weights="bf16", kv="bf16")
+    full = shard_state_dict(sd, m, ParallelConfig(tp=1, ep=1, rank=0, world=1), q, device="cpu")
+    hd = m.head_dim
+    for par in (ParallelConfig(tp=2, ep=1, rank=1, world=2), ParallelConfig(tp=1, ep=2, rank=1, world=2)):
+        sh = shard_state_dict(sd, m, par, q, device="cpu")
+        g = sh.geom
+        f, s = full.layers[1], sh.layers[1]
+        assert torch.equal(s.wqkv.data[: g.nq_local * hd], f.wqkv.data[g.q_head0 * hd:(g.q_head0 + g.nq_local) * hd])
+        assert torch.equal(s.w_gu.data[0][: g.inter_local], f.w_gu.data[g.expert0][g.inter0: g.inter0 + g.inter_local])
+        assert torch.equal(s.w_d.data[0], f.w_d.data[g.expert0][:, g.inter0: g.inter0 + g.inter_local])
+        assert torch.equal(s.router, f.router)
+        assert torch.equal(sh.lm_head.data, full.lm_head.data[g.vocab0: g.vocab0 + g.vocab_local])

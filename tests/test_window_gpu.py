@@ -139,6 +139,21 @@ def test_router_grouping_gather_and_combine_kernels():
         K.moe_combine_rows(yg, inv, tw, k, y, resid=resid)
         want = resid + (yg[inv.long()].reshape(T, k, H) * tw[..., None]).sum(1)
         assert float((y - want).abs().max()) < 1e-4
+        # expert parallel: a rank that holds experts [e0, e0 + El) keeps only its pairs; the others get inv = -1 and add nothing
+        e0, El = E // 2, E - E // 2
+        K.moe_group_table(ti, e0, El, nt, order, inv, groups, ng)
+        local = (flat >= e0) & (flat < e0 + El)
+        n_local = int(local.sum())
+        assert sorted(order[:n_local].tolist()) == torch.nonzero(local).reshape(-1).tolist()
+        assert bool((inv[~local] == -1).all())
+        n = int(ng.item())
+        assert n == int(((cnt[e0:] + nt - 1) // nt).sum())
+        for e_, r0, nr, _ in groups[:n].tolist():
+            assert bool((flat[order[r0:r0 + nr].long()] == e_ + e0).all())
+        K.moe_combine_rows(yg, inv, tw, k, y, resid=None)
+        sel = torch.where(inv >= 0, inv, torch.zeros_like(inv)).long()
+        want = (yg[sel].reshape(T, k, H) * (tw * local.reshape(T, k))[..., None]).sum(1)
+        assert float((y - want).abs().max()) < 1e-4
 
 
 def test_dequant_kernel_matches_the_reference_dequantisation():
