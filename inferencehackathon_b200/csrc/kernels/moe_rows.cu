@@ -134,12 +134,13 @@ __global__ void __launch_bounds__(RT_THREADS) router_topk_rows_kernel(const floa
 // ---- the same router on the tensor cores: 16 tokens per CTA, logits as m16n8k16 tiles ---------------------------------------------
 // h stays fp32 in shared memory and is split into a bf16 head and a bf16 remainder when a fragment is built, so the
 // logits keep fp32 accuracy against the bf16 router rows (a router decision must not depend on activation rounding).
-// Chunks of 64 channels of h [16][64] and of the router [E][64] arrive by cp.async, double buffered; warp w owns the
-// expert tiles w, w + 8, ... (8 experts each).
+// Chunks of 64 channels of h [16][64] and of the router [E][64] arrive by cp.async through a ring of NS buffers (4 when
+// the router has at most 128 experts, else 2: a chunk is small, so the loop runs at the latency of a load unless
+// several are in flight); warp w owns the expert tiles w, w + 8, ... (8 experts each).
 constexpr int RM_TOK = 16, RM_KC = 64, RM_HLD = RM_KC + 4, RM_WLD = RM_KC + 8;
 struct RmSmem {
-  float h[2][RM_TOK][RM_HLD];
-  __nv_bfloat16 w[2][256][RM_WLD];
+  float h[4][RM_TOK][RM_HLD];
+  __nv_bfloat16 w[2 * 256][RM_WLD];          // NS buffers of (512 / NS) rows
   float lg[RM_TOK][256];
 };
 __device__ __forceinline__ void rm_cp16(void* dst, const void* src) {
@@ -152,6 +153,7 @@ __device__ __forceinline__ void rm_split2(float x, float y, unsigned& hi, unsign
   hi = *reinterpret_cast<const unsigned*>(&h);
   lo = *reinterpret_cast<const unsigned*>(&l);
 }
+template <int NS>
 __global__ void __launch_bounds__(256) router_topk_rows_mma_kernel(const float* __restrict__ h, const __nv_bfloat16* __restrict__ W,
                                                                    int T, int H, int E, int top_k, int renorm,
                                                                    float* __restrict__ logits_out, int* __restrict__ ti,
@@ -169,18 +171,23 @@ __global__ void __launch_bounds__(256) router_topk_rows_mma_kernel(const float* 
     }
     for (int i = tid; i < E * (RM_KC / 8); i += 256) {                 // E rows x 8 pieces of 8 bf16
       const int r = i / (RM_KC / 8), p = i % (RM_KC / 8);
-      rm_cp16(&sm.w[buf][r][p * 8], W + static_cast<size_t>(r) * H + k0 + p * 8);
+      rm_cp16(&sm.w[buf * (512 / NS) + r][p * 8], W + static_cast<size_t>(r) * H + k0 + p * 8);
     }
-    asm volatile("cp.async.commit_group;" ::: "memory");
   };
   float acc[4][4];
 #pragma unroll
   for (int j = 0; j < 4; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
-  issue(0, 0);
+  // one commit group per chunk position, empty past the end, so that "all but the newest NS - 1 groups" is always chunk c
+#pragma unroll
+  for (int c = 0; c < NS - 1; ++c) {
+    if (c < nchunks) issue(c, c);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  }
   for (int c = 0; c < nchunks; ++c) {
-    const int buf = c & 1;
-    if (c + 1 < nchunks) { issue(c + 1, buf ^ 1); asm volatile("cp.async.wait_group 1;" ::: "memory"); }
-    else asm volatile("cp.async.wait_group 0;" ::: "memory");
+    const int buf = c % NS;
+    if (c + NS - 1 < nchunks) issue(c + NS - 1, (c + NS - 1) % NS);      // the buffer chunk c - 1 used: its readers passed the barrier below
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_group %0;" ::"n"(NS - 1) : "memory");
     __syncthreads();
 #pragma unroll
     for (int ks = 0; ks < RM_KC / 16; ++ks) {
@@ -194,8 +201,8 @@ __global__ void __launch_bounds__(256) router_topk_rows_mma_kernel(const float* 
       for (int j = 0; j < 4; ++j) {
         const int e = (warp + 8 * j) * 8 + g;
         if ((warp + 8 * j) * 8 < E) {
-          const unsigned b0 = *reinterpret_cast<const unsigned*>(&sm.w[buf][e][k0]);
-          const unsigned b1 = *reinterpret_cast<const unsigned*>(&sm.w[buf][e][k0 + 8]);
+          const unsigned b0 = *reinterpret_cast<const unsigned*>(&sm.w[buf * (512 / NS) + e][k0]);
+          const unsigned b1 = *reinterpret_cast<const unsigned*>(&sm.w[buf * (512 / NS) + e][k0 + 8]);
           asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                        : "+f"(acc[j][0]), "+f"(acc[j][1]), "+f"(acc[j][2]), "+f"(acc[j][3])
                        : "r"(ah[0]), "r"(ah[1]), "r"(ah[2]), "r"(ah[3]), "r"(b0), "r"(b1));
@@ -205,7 +212,7 @@ __global__ void __launch_bounds__(256) router_topk_rows_mma_kernel(const float* 
         }
       }
     }
-    __syncthreads();                 // the buffer is refilled two iterations later
+    __syncthreads();                 // the buffer is refilled by the next iteration's issue
   }
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
@@ -403,13 +410,20 @@ extern "C" int ihb_router_topk_rows(const float* h, const void* router_bf16, int
   if (H % RM_KC == 0 && T >= 4) {            // tensor-core tiles; very short windows and odd widths take the plain kernel
     static bool attr_set = false;
     if (!attr_set) {
-      cudaError_t e = cudaFuncSetAttribute(router_topk_rows_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+      cudaError_t e = cudaFuncSetAttribute(router_topk_rows_mma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            static_cast<int>(sizeof(RmSmem)));
+      if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(router_topk_rows_mma_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(sizeof(RmSmem)));
       if (e != cudaSuccess) return e;
       attr_set = true;
     }
-    router_topk_rows_mma_kernel<<<(T + RM_TOK - 1) / RM_TOK, 256, sizeof(RmSmem), stream>>>(
-        h, reinterpret_cast<const __nv_bfloat16*>(router_bf16), T, H, E, top_k, renorm, logits, ti, tw);
+    if (E <= 128)
+      router_topk_rows_mma_kernel<4><<<(T + RM_TOK - 1) / RM_TOK, 256, sizeof(RmSmem), stream>>>(
+          h, reinterpret_cast<const __nv_bfloat16*>(router_bf16), T, H, E, top_k, renorm, logits, ti, tw);
+    else
+      router_topk_rows_mma_kernel<2><<<(T + RM_TOK - 1) / RM_TOK, 256, sizeof(RmSmem), stream>>>(
+          h, reinterpret_cast<const __nv_bfloat16*>(router_bf16), T, H, E, top_k, renorm, logits, ti, tw);
     return cudaGetLastError();
   }
   router_topk_rows_kernel<<<(T + RT_TOK - 1) / RT_TOK, RT_THREADS, 0, stream>>>(

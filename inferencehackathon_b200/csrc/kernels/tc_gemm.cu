@@ -50,13 +50,16 @@ struct Unit {
   int orow0;           // first output row of the unit
 };
 
-__device__ __forceinline__ Unit decode_unit(const IhbTcArgs& a, int u, int nkb_total) {
+constexpr int TC_GRP_SMEM = 1024;   // group-table entries kept in shared memory (16 KB); larger tables are read from global
+
+__device__ __forceinline__ Unit decode_unit(const IhbTcArgs& a, int u, int nkb_total, const int4* grp_s) {
   Unit un;
   un.e = 0; un.tok0 = a.tok0; un.ntok = a.T; un.orow0 = 0;
   if (a.groups != nullptr) {
     const int rtiles = (a.rows + TC_BM - 1) / TC_BM;
     const int g = u / rtiles, tile = u - g * rtiles;
-    const int4 gr = *reinterpret_cast<const int4*>(a.groups + 4 * g);
+    // every role decodes every unit: from shared memory this costs a few cycles, from global a round trip per unit
+    const int4 gr = grp_s != nullptr ? grp_s[g] : *reinterpret_cast<const int4*>(a.groups + 4 * g);
     un.e = gr.x; un.tok0 = gr.y; un.ntok = gr.z;
     un.tile = u; un.member = 0; un.row0 = tile * TC_BM; un.slot = 0; un.kb0 = 0; un.kb1 = nkb_total;
     un.orow0 = un.tok0;
@@ -103,9 +106,13 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const int esize = (KIND == 0) ? 1 : 2;
   const int nkb_total = (a.K * esize + TC_BKB - 1) / TC_BKB;
   const int nslot_x = (a.mode == IHB_TC_DOWN) ? a.top_k : 1;
-  float* xs_s = reinterpret_cast<float*>(smem + 1024);                     // [nslot_x][nkb_total][NT] (fp8 only)
+  const int grp_n = (a.groups != nullptr && a.max_groups <= TC_GRP_SMEM) ? a.max_groups : 0;
+  const int grp_bytes = (grp_n * 16 + 1023) & ~1023;
+  int4* grp_w = reinterpret_cast<int4*>(smem + 1024);                      // the group table (grouped mode)
+  const int4* grp_s = grp_n > 0 ? grp_w : nullptr;
+  float* xs_s = reinterpret_cast<float*>(smem + 1024 + grp_bytes);         // [nslot_x][nkb_total][NT] (fp8 only)
   const int xs_bytes = (KIND == 0) ? ((nslot_x * nkb_total * NT * 4 + 1023) & ~1023) : 0;
-  uint8_t* stages = smem + 1024 + xs_bytes;
+  uint8_t* stages = smem + 1024 + grp_bytes + xs_bytes;
   constexpr int B_BYTES = NT * TC_BKB;
   constexpr int STAGE_BYTES = NA * TC_A_BYTES + B_BYTES;
   const int S = a.S;
@@ -113,7 +120,11 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   // With few token columns an MMA is over in a handful of cycles but its result takes a pipeline latency to
   // land, so MMAs chained on ONE accumulator run at latency, not throughput. The four K steps of a stage
   // therefore go to SUB = 4 separate accumulators (added up by the epilogue) when N is small.
+#ifdef IHB_TC_SUB_WIDE
+  constexpr int SUB = (NT <= 32) ? 4 : (NT == 64 ? (NA == 1 ? 4 : 2) : 2);
+#else
   constexpr int SUB = (NT <= 32) ? 4 : 1;
+#endif
   constexpr int BUF_COLS = NA * SUB * NT;
   // accumulator ring in tensor memory: up to 8 buffers (512 columns in total)
   constexpr int NBUF = (512 / BUF_COLS) >= 8 ? 8 : (512 / BUF_COLS);
@@ -145,6 +156,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     sh.sel_e[tid] = here ? e : 0;
     sh.sel_w[tid] = here ? ld_cg_f(a.sel_w + tid) : 0.f;
   }
+  if (grp_n > 0) {
+    const int ng = min(ld_cg_i(a.n_groups), grp_n);
+    for (int i = tid; i < ng; i += TC_THREADS) grp_w[i] = *reinterpret_cast<const int4*>(a.groups + 4 * i);
+  }
   if (a.x_rows1) {
     // single-token mode copies only row 0 of each activation tile: clear the other rows once
     for (int i = tid; i < S * (B_BYTES / 16); i += TC_THREADS) {
@@ -175,7 +190,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       int g = 0;
       bool ok = true;
       for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
-        const Unit un = decode_unit(a, u, nkb_total);
+        const Unit un = decode_unit(a, u, nkb_total, grp_s);
         const int e = (a.mode == IHB_TC_LINEAR) ? 0 : (a.groups != nullptr ? un.e : sh.sel_e[un.slot]);
         for (int kb = un.kb0; kb < un.kb1; ++kb, ++g) {
           if (g % TC_PRODUCERS != warp) continue;
@@ -230,7 +245,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       int g = 0, ui = 0;
       bool ok = true;
       for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x, ++ui) {
-        const Unit un = decode_unit(a, u, nkb_total);
+        const Unit un = decode_unit(a, u, nkb_total, grp_s);
         for (int kb = un.kb0; kb < un.kb1 && ok; ++kb, ++g) {
           const int st = g % S;
           ok = tc_wait(&sh.full[st], (g / S) & 1u, abort_flag, a.err, ERR_MBAR_FULL_TIMEOUT);
@@ -249,9 +264,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             const uint64_t adesc = smem_desc_sw128(sA + ai * TC_A_BYTES);
 #pragma unroll
             for (int k = 0; k < TC_BKB / 32; ++k) {
-              const int sub = (SUB == 1) ? 0 : k;
+              const int sub = k % SUB;
               const uint32_t d = tmem_base + static_cast<uint32_t>(b * BUF_COLS + (ai * SUB + sub) * NT);
-              const uint32_t accf = (KIND == 0) ? (SUB == 1 && k > 0) : (kb > un.kb0 || (SUB == 1 && k > 0));
+              const uint32_t accf = (KIND == 0) ? (k >= SUB) : (kb > un.kb0 || k >= SUB);
               tc_mma<KIND>(d, adesc + 2 * k, bdesc + 2 * k, idesc, accf);   // +32 bytes of K per step
             }
           }
@@ -269,7 +284,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     int g = 0, ui = 0;
     bool ok = true;
     for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x, ++ui) {
-      const Unit un = decode_unit(a, u, nkb_total);
+      const Unit un = decode_unit(a, u, nkb_total, grp_s);
       const int e = (a.mode == IHB_TC_LINEAR) ? 0 : (a.groups != nullptr ? un.e : sh.sel_e[un.slot]);
       if (KIND == 0 && (a.groups != nullptr || a.tok_tiles > 1)) {
         // grouped / token-tiled mode: the activation scales of this unit's tokens (the previous unit's readers are done: barrier)
@@ -588,12 +603,17 @@ extern "C" int ihb_tc_gemm(IhbTcArgs* args, int use_pdl, cudaStream_t stream) {
   const int nslot_x = a.mode == IHB_TC_DOWN ? a.top_k : 1;
   const int xs_bytes = is_fp8 ? ((nslot_x * nkb_total * nt * 4 + 1023) & ~1023) : 0;
   const int stage_bytes = na * TC_A_BYTES + nt * TC_BKB;
-  int S = (200 * 1024 - 2048 - xs_bytes) / stage_bytes;
+  const int grp_bytes = (grouped && a.max_groups <= TC_GRP_SMEM) ? ((a.max_groups * 16 + 1023) & ~1023) : 0;
+  int S = (200 * 1024 - 2048 - xs_bytes - grp_bytes) / stage_bytes;
   if (S > 8) S = 8;
   if (a.S > 0 && a.S < S) S = a.S;
-  if (S < 2) return cudaErrorInvalidValue;
+  // With fewer stages than producer warps, the warp that refills a stage for the second time could pass the stage's
+  // "empty" wait before the warp that refills it for the first time has loaded it (an mbarrier wait on the phase after
+  // next succeeds at once): two arrivals on one "full" phase. From three stages up each warp's own earlier waits rule
+  // that out.
+  if (S < TC_PRODUCERS) return cudaErrorInvalidValue;
   a.S = S;
-  const int smem = 1024 /*align slack*/ + 1024 + xs_bytes + S * stage_bytes;
+  const int smem = 1024 /*align slack*/ + 1024 + grp_bytes + xs_bytes + S * stage_bytes;
   int grid = a.grid > 0 ? a.grid : sms;
   if (grid > a.n_units) grid = a.n_units;
 

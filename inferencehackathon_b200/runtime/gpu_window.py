@@ -157,6 +157,22 @@ class GpuWindow:
             self._bf16[key] = res
         return res
 
+    def _k_split(self, tiles: int, nkb: int, T: int) -> int:
+        """K split of a dense launch. Measured on B200 (bf16, 1280 x 4096 weights): with 64 or more token columns per
+        tile a split costs more than it gains even when the tiles cover half the SMs (1024 tokens: 39 us unsplit, 55 us
+        split in two, 90 us in four; 128 tokens split in fourteen: 104 us) because the finishing unit reads every
+        member's 32-64 KB partial; with 16 or 32 columns the partials are small and the split that minimises
+        waves x (K blocks per unit + 2) wins (the head GEMV of one token: 149 row tiles on 148 SMs)."""
+        if T > 32:
+            return 1
+        best, best_cost = 1, None
+        for ks in range(1, min(nkb, 16) + 1):
+            waves = -(-tiles * ks // self.sms)
+            cost = waves * (-(-nkb // ks) + (2 if ks > 1 else 0))
+            if best_cost is None or cost < best_cost:
+                best, best_cost = ks, cost
+        return best
+
     def _linear(self, qw, xq, xs, T: int, tag: str) -> torch.Tensor:
         """[T, K] x W[rows, K]^T on the tensor cores."""
         wq = self._w(qw, tag)
@@ -176,8 +192,7 @@ class GpuWindow:
             if T > TILE:
                 a.tok_tile, a.tok_tiles = TILE, -(-T // TILE)
             tiles = ((rows + 127) // 128) * max(1, a.tok_tiles)
-            # split K only while the (row tile, token tile) units do not fill the GPU once
-            a.ks = max(1, min(nkb, 16, self.sms // tiles))
+            a.ks = self._k_split(tiles, nkb, T)
             part = self._buf("part", (max(1, K.tc_partial_floats(a)),), torch.float32)
             ctr = self._buf("ctr", (max(tiles, 1),), torch.int32)
             a.partial, a.tile_counters = part.data_ptr(), ctr.data_ptr()

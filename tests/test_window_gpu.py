@@ -92,7 +92,7 @@ def test_router_grouping_gather_and_combine_kernels():
     d = torch.device("cuda", 0)
     g = torch.Generator(device=d).manual_seed(1)
     for (T, H, E, k, renorm) in [(37, 512, 16, 4, True), (300, 2048, 128, 8, True), (9, 1024, 200, 8, False), (3, 512, 16, 4, True),
-                                 (20, 520, 64, 8, True)]:
+                                 (20, 520, 64, 8, True), (40, 1024, 200, 8, False)]:
         h = torch.randn(T, H, device=d, generator=g)
         W = (torch.randn(E, H, device=d, generator=g) * 0.05).to(torch.bfloat16)
         ti = torch.zeros(T, k, dtype=torch.int32, device=d)
@@ -295,7 +295,7 @@ def test_speculative_driver_on_gpu_engine_equals_its_own_greedy():
 
 @pytest.mark.parametrize("T,base,nq,nkv,masked", [(40, 0, 8, 1, False), (130, 77, 16, 2, False), (23, 300, 8, 2, True),
                                                    (16, 0, 4, 1, True), (257, 1000, 8, 1, False), (8, 1000, 8, 1, False),
-                                                   (5, 4000, 16, 2, True)])
+                                                   (5, 4000, 16, 2, True), (600, 0, 8, 1, False)])
 def test_window_attention_tensor_core_tiles_against_fp32(T, base, nq, nkv, masked):
     """Both window attention kernels (tensor-core tiles; one CTA per token) against plain fp32 PyTorch on the same
     bf16 cache rows: cached context + the window's own rows, causal or with an explicit visibility mask."""
