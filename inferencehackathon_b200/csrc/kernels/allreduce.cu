@@ -250,8 +250,8 @@ __global__ void __launch_bounds__(AR_THREADS) ar_twoshot_kernel(const ArArgs a) 
 // GPU (top 8 bits count contributions, low 56 bits hold the biased fixed-point sum; multimem.red.add.u64 through
 // NVSwitch or one red per peer), then polls ITS OWN copy of the slots until every word has counted all ranks, decodes,
 // clears the word for its next use and finishes the row (residual, RMSNorm). One one-way trip through the switch;
-// integer sums make every rank decode the same bits. Slot region: [4 call parities][T * H] 64-bit words, which must
-// start zeroed and must not be shared with the one-shot / two-shot regions. `x` may be fp32 or bf16.
+// integer sums make every rank decode the same bits. Slot region: [4 call parities][IHB_ARC_MAX_ROWS * H] 64-bit words,
+// which must start zeroed and must not be shared with the one-shot / two-shot regions. `x` may be fp32 or bf16.
 constexpr unsigned long long ARC_ONE = 1ull << 56;
 constexpr long long ARC_BIAS = 1ll << 51, ARC_QMAX = 1ll << 50;
 constexpr float ARC_FIX = 268435456.f;                 // 2^28
@@ -268,7 +268,9 @@ __global__ void __launch_bounds__(ARC_THREADS) ar_counted_kernel(const ArcArgs q
   const int H = a.H, t = blockIdx.x, tid = threadIdx.x;
   pdl_wait();                                            // the previous call on this stream wrote the counter and cleared its words
   const unsigned call = q.call_counter[t];
-  const size_t n = static_cast<size_t>(a.T) * H;
+  // a row's slots sit at a place that does not depend on T, and every row keeps its own call count: calls with
+  // different numbers of rows can follow each other on the same region
+  const size_t n = static_cast<size_t>(IHB_ARC_MAX_ROWS) * H;
   const size_t off0 = static_cast<size_t>(call & 3u) * n + static_cast<size_t>(t) * H;
   unsigned long long* local = reinterpret_cast<unsigned long long*>(cm.slots_local) + off0;
   const unsigned nr = static_cast<unsigned>(cm.nranks);
@@ -329,15 +331,15 @@ __global__ void __launch_bounds__(ARC_THREADS) ar_counted_kernel(const ArcArgs q
 
 using namespace ihb;
 
-// The latency-optimal variant for a few rows (see ar_counted_kernel). slots: 4 * T * H 64-bit words of the symmetric buffer
-// that start zeroed and are used by this variant only; call_counter: 64 unsigned (one per row), zero before the first call
-// and used with ONE value of T only (the slot layout depends on T); counter is unused. x: fp32, or bf16 when x_is_bf16.
-// T <= 64, H % 4 == 0, H <= 8192. Launched with programmatic stream serialisation: back-to-back calls overlap the
+// The latency-optimal variant for a few rows (see ar_counted_kernel). slots: 4 * IHB_ARC_MAX_ROWS * H 64-bit words of the
+// symmetric buffer that start zeroed and are used by this variant only; call_counter: IHB_ARC_MAX_ROWS unsigned (one per
+// row), zero before the first call; every rank must make the same sequence of calls (any T each); counter is unused.
+// x: fp32, or bf16 when x_is_bf16. T <= IHB_ARC_MAX_ROWS, H % 4 == 0, H <= 8192. Launched with programmatic stream serialisation: back-to-back calls overlap the
 // launch of one with the tail of the other.
 extern "C" int ihb_allreduce_counted(const IhbComm* comm, const void* x, int x_is_bf16, const float* resid, const float* gamma,
                                      float eps, int T, int H, float* out, float* out_norm, unsigned* counter,
                                      unsigned* call_counter, unsigned* err, cudaStream_t stream) {
-  if (T < 1 || T > 64 || H < 4 || (H % 4) || H > ARC_MAXV * ARC_THREADS * 4 || comm == nullptr ||
+  if (T < 1 || T > IHB_ARC_MAX_ROWS || H < 4 || (H % 4) || H > ARC_MAXV * ARC_THREADS * 4 || comm == nullptr ||
       call_counter == nullptr) return cudaErrorInvalidValue;
   (void)counter;
   ArcArgs q;

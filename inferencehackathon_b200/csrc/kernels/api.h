@@ -276,9 +276,11 @@ int ihb_allreduce_norm(const IhbComm* comm, const float* x, const float* resid, 
 
 // Latency-optimal all-reduce (+ residual + RMSNorm) of a few rows: one CTA per row, plain launch; every rank ADDS its row
 // into 64-bit counted fixed-point slots on every GPU (multimem.red.add.u64 or peer reds) and waits for the contribution
-// count on its own copy: one one-way trip through NVSwitch, no barrier. comm->slots_*: 4 * T * H 64-bit words, zeroed
-// before the first call and used by this entry only; counter: 8 unsigned; call_counter: 1 unsigned (both zero at first).
-// x fp32, or bf16 when x_is_bf16. T <= 64, H % 4 == 0, H <= 8192.
+// count on its own copy: one one-way trip through NVSwitch, no barrier. comm->slots_*: 4 * IHB_ARC_MAX_ROWS * H 64-bit
+// words, zeroed before the first call and used by this entry only; call_counter: IHB_ARC_MAX_ROWS unsigned, zero at first
+// (one call count per row, so calls with different T may follow each other; all ranks make the same calls); counter:
+// unused. x fp32, or bf16 when x_is_bf16. T <= IHB_ARC_MAX_ROWS, H % 4 == 0, H <= 8192.
+#define IHB_ARC_MAX_ROWS 64
 int ihb_allreduce_counted(const IhbComm* comm, const void* x, int x_is_bf16, const float* resid, const float* gamma, float eps,
                           int T, int H, float* out, float* out_norm, unsigned* counter, unsigned* call_counter, unsigned* err,
                           cudaStream_t stream);

@@ -65,6 +65,7 @@ class IhbMoeArgs(C.Structure):
 
 
 TC_LINEAR, TC_GATEUP, TC_DOWN = 0, 1, 2
+ARC_MAX_ROWS = 64          # IHB_ARC_MAX_ROWS: rows of the counted small-message all-reduce
 
 
 class IhbTcArgs(C.Structure):
@@ -495,7 +496,8 @@ def allreduce_counted(comm: IhbComm, x: torch.Tensor, out: torch.Tensor, counter
                       eps: float = 1e-6, out_norm: Optional[torch.Tensor] = None) -> None:
     """Latency-optimal fused all-reduce (+ residual + RMSNorm) of ``x [T, H]`` (fp32 or bf16), ``T <= 64``: counted
     fixed-point slots, one one-way trip, no barrier (``csrc/kernels/allreduce.cu::ar_counted_kernel``). ``call_counter``:
-    64 int32 zeros owned by this (slot region, T) pair; ``counter`` is unused (kept for signature symmetry)."""
+    ``ARC_MAX_ROWS`` int32 zeros owned by the slot region (``4 * ARC_MAX_ROWS * H`` 64-bit words, zeroed); ``counter`` is
+    unused (kept for signature symmetry). T may change from call to call."""
     T, H = x.shape
     check(load().ihb_allreduce_counted(C.byref(comm), x.data_ptr(), int(x.dtype == torch.bfloat16), ptr(resid), ptr(gamma), eps,
                                        T, H, out.data_ptr(), ptr(out_norm), counter.data_ptr(), call_counter.data_ptr(),

@@ -29,7 +29,7 @@ dev = torch.device("cuda", local)
 K.load()
 T, H = 4, 1024
 par = ParallelConfig(tp=world, ep=1, rank=rank, world=world)
-comm = SymmetricComm(par, dev, slot_floats=2 * world * T * H, extra_bytes=4 * T * H * 8)
+comm = SymmetricComm(par, dev, slot_floats=2 * world * T * H, extra_bytes=4 * 64 * H * 8)
 epoch = torch.zeros(4, dtype=torch.int32, device=dev)
 counter = torch.zeros(8, dtype=torch.int32, device=dev)
 err = torch.zeros(1, dtype=torch.int32, device=dev)

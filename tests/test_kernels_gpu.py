@@ -271,7 +271,7 @@ def test_counted_allreduce_single_rank_adds_residual_and_norms(payload):
     d = _dev()
     T, H = 5, 4096
     g = torch.Generator(device=d).manual_seed(3)
-    slots = torch.zeros(4 * T * H, dtype=torch.int64, device=d)
+    slots = torch.zeros(4 * 64 * H, dtype=torch.int64, device=d)
     epoch = torch.zeros(4, dtype=torch.int32, device=d)
     cm = lib.single_comm(slots, epoch)
     counter = torch.zeros(8, dtype=torch.int32, device=d)
@@ -279,6 +279,7 @@ def test_counted_allreduce_single_rank_adds_residual_and_norms(payload):
     err = torch.zeros(1, dtype=torch.int32, device=d)
     gamma = torch.rand(H, device=d, generator=g) + 0.5
     for it in range(9):
+        T = (5, 2, 7)[it % 3]                            # the number of rows may change from call to call
         x = torch.randn(T, H, device=d, generator=g) * (1 + it)
         if payload == "bf16":
             x = x.to(torch.bfloat16)
@@ -289,5 +290,5 @@ def test_counted_allreduce_single_rank_adds_residual_and_norms(payload):
         refn = ref * torch.rsqrt(ref.pow(2).mean(-1, keepdim=True) + 1e-6) * gamma
         assert float((out - ref).abs().max()) < 4e-6 * (1 + it)
         assert float((outn - refn).abs().max()) < 1e-5
-    assert int(err.item()) == 0 and calls[:T].tolist() == [9] * T and int(calls[T:].abs().max()) == 0
+    assert int(err.item()) == 0 and calls[:8].tolist() == [9, 9, 6, 6, 6, 3, 3, 0]
     assert int(slots.abs().max()) == 0                   # every reader cleared what it consumed
