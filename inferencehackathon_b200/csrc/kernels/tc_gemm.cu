@@ -186,93 +186,92 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
   if (warp < TC_PRODUCERS) {
     // =============================== TMA producers: warp p feeds the stages with g % 3 == p ============================
-    if (lane == 0) {
-      int g = 0;
-      bool ok = true;
-      for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
-        const Unit un = decode_unit(a, u, nkb_total, grp_s);
-        const int e = (a.mode == IHB_TC_LINEAR) ? 0 : (a.groups != nullptr ? un.e : sh.sel_e[un.slot]);
-        for (int kb = un.kb0; kb < un.kb1; ++kb, ++g) {
-          if (g % TC_PRODUCERS != warp) continue;
-          const int st = g % S;
-          if (g >= S) ok = tc_wait(&sh.empty[st], ((g / S) & 1u) ^ 1u, abort_flag, a.err, ERR_MBAR_EMPTY_TIMEOUT);
-          if (!ok) break;
-          uint8_t* sA = stages + static_cast<size_t>(st) * STAGE_BYTES;
-          uint8_t* sB = sA + NA * TC_A_BYTES;
-          if (a.tiled) {
-            // Pre-tiled weights: [matrix][k block][rows padded to 8][128 B], already in the swizzled order, so a
-            // tile of this K block is ONE contiguous run of up to 16 KB.
-            const int rows_here = min(TC_BM, rows_p8 - un.row0);
-            const uint32_t abytes = static_cast<uint32_t>(rows_here) * TC_BKB;
-            const uint32_t bbytes = a.x_rows1 ? TC_BKB : B_BYTES;
-            mbar_arrive_expect_tx(&sh.full[st], NA * abytes + bbytes);
-            const size_t panel = static_cast<size_t>(rows_p8) * TC_BKB;                 // one K block of one matrix
-            const size_t mat = (a.mode == IHB_TC_GATEUP) ? static_cast<size_t>(e) * 2 : static_cast<size_t>(e);
-            const uint8_t* src = reinterpret_cast<const uint8_t*>(a.W) + (mat * nkb_total + kb) * panel +
-                                 static_cast<size_t>(un.row0) * TC_BKB;
-            bulk_g2s(sA, src, abytes, &sh.full[st]);
-            if (NA == 2) bulk_g2s(sA + TC_A_BYTES, src + static_cast<size_t>(nkb_total) * panel, abytes, &sh.full[st]);
-            if (a.x_rows1) {
-              // one token: row 0 of the (pre-zeroed) activation tile; the swizzle of row 0 is the identity
-              const uint8_t* xs = reinterpret_cast<const uint8_t*>(a.X) +
-                                  (static_cast<size_t>(a.mode == IHB_TC_DOWN ? un.slot : 0) * nkb_total + kb) * TC_BKB;
-              bulk_g2s(sB, xs, TC_BKB, &sh.full[st]);
-            } else if (a.mode == IHB_TC_DOWN) {
-              tma_load_3d(sB, &tmB, kb * kx, un.tok0, un.slot, &sh.full[st]);
-            } else {
-              tma_load_2d(sB, &tmB, kb * kx, un.tok0, &sh.full[st]);
-            }
+    // The whole warp runs the loop and lane 0 issues (see tc_common.cuh: the copies want warp-uniform operands).
+    const unsigned leader = lane == 0 ? 1u : 0u;
+    int g = 0;
+    bool ok = true;
+    for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
+      const Unit un = decode_unit(a, u, nkb_total, grp_s);
+      const int e = (a.mode == IHB_TC_LINEAR) ? 0 : (a.groups != nullptr ? un.e : sh.sel_e[un.slot]);
+      for (int kb = un.kb0; kb < un.kb1; ++kb, ++g) {
+        if (g % TC_PRODUCERS != warp) continue;
+        const int st = g % S;
+        if (g >= S) ok = tc_wait(&sh.empty[st], ((g / S) & 1u) ^ 1u, abort_flag, a.err, ERR_MBAR_EMPTY_TIMEOUT);
+        if (!ok) break;
+        uint8_t* sA = stages + static_cast<size_t>(st) * STAGE_BYTES;
+        uint8_t* sB = sA + NA * TC_A_BYTES;
+        if (a.tiled) {
+          // Pre-tiled weights: [matrix][k block][rows padded to 8][128 B], already in the swizzled order, so a
+          // tile of this K block is ONE contiguous run of up to 16 KB.
+          const int rows_here = min(TC_BM, rows_p8 - un.row0);
+          const uint32_t abytes = static_cast<uint32_t>(rows_here) * TC_BKB;
+          const uint32_t bbytes = a.x_rows1 ? TC_BKB : B_BYTES;
+          mbar_arrive_expect_tx_if(leader, &sh.full[st], NA * abytes + bbytes);
+          const size_t panel = static_cast<size_t>(rows_p8) * TC_BKB;                 // one K block of one matrix
+          const size_t mat = (a.mode == IHB_TC_GATEUP) ? static_cast<size_t>(e) * 2 : static_cast<size_t>(e);
+          const uint8_t* src = reinterpret_cast<const uint8_t*>(a.W) + (mat * nkb_total + kb) * panel +
+                               static_cast<size_t>(un.row0) * TC_BKB;
+          bulk_g2s_if(leader, sA, src, abytes, &sh.full[st]);
+          if (NA == 2) bulk_g2s_if(leader, sA + TC_A_BYTES, src + static_cast<size_t>(nkb_total) * panel, abytes, &sh.full[st]);
+          if (a.x_rows1) {
+            // one token: row 0 of the (pre-zeroed) activation tile; the swizzle of row 0 is the identity
+            const uint8_t* xs = reinterpret_cast<const uint8_t*>(a.X) +
+                                (static_cast<size_t>(a.mode == IHB_TC_DOWN ? un.slot : 0) * nkb_total + kb) * TC_BKB;
+            bulk_g2s_if(leader, sB, xs, TC_BKB, &sh.full[st]);
+          } else if (a.mode == IHB_TC_DOWN) {
+            tma_load_3d_if(leader, sB, &tmB, kb * kx, un.tok0, un.slot, &sh.full[st]);
           } else {
-            mbar_arrive_expect_tx(&sh.full[st], STAGE_BYTES);
-            if (a.mode == IHB_TC_LINEAR) {
-              tma_load_2d(sA, &tmA, kb * kx, un.row0, &sh.full[st]);
-              tma_load_2d(sB, &tmB, kb * kx, un.tok0, &sh.full[st]);
-            } else if (a.mode == IHB_TC_GATEUP) {
-              tma_load_4d(sA, &tmA, kb * kx, un.row0, 0, e, &sh.full[st]);
-              if (NA == 2) tma_load_4d(sA + TC_A_BYTES, &tmA, kb * kx, un.row0, 1, e, &sh.full[st]);
-              tma_load_2d(sB, &tmB, kb * kx, un.tok0, &sh.full[st]);
-            } else {
-              tma_load_3d(sA, &tmA, kb * kx, un.row0, e, &sh.full[st]);
-              tma_load_3d(sB, &tmB, kb * kx, un.tok0, un.slot, &sh.full[st]);
-            }
+            tma_load_2d_if(leader, sB, &tmB, kb * kx, un.tok0, &sh.full[st]);
+          }
+        } else {
+          mbar_arrive_expect_tx_if(leader, &sh.full[st], STAGE_BYTES);
+          if (a.mode == IHB_TC_LINEAR) {
+            tma_load_2d_if(leader, sA, &tmA, kb * kx, un.row0, &sh.full[st]);
+            tma_load_2d_if(leader, sB, &tmB, kb * kx, un.tok0, &sh.full[st]);
+          } else if (a.mode == IHB_TC_GATEUP) {
+            tma_load_4d_if(leader, sA, &tmA, kb * kx, un.row0, 0, e, &sh.full[st]);
+            if (NA == 2) tma_load_4d_if(leader, sA + TC_A_BYTES, &tmA, kb * kx, un.row0, 1, e, &sh.full[st]);
+            tma_load_2d_if(leader, sB, &tmB, kb * kx, un.tok0, &sh.full[st]);
+          } else {
+            tma_load_3d_if(leader, sA, &tmA, kb * kx, un.row0, e, &sh.full[st]);
+            tma_load_3d_if(leader, sB, &tmB, kb * kx, un.tok0, un.slot, &sh.full[st]);
           }
         }
       }
     }
   } else if (warp == TC_MMA_WARP) {
-    // =============================== MMA issuer ========================================================================
-    if (lane == 0) {
-      int g = 0, ui = 0;
-      bool ok = true;
-      for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x, ++ui) {
-        const Unit un = decode_unit(a, u, nkb_total, grp_s);
-        for (int kb = un.kb0; kb < un.kb1 && ok; ++kb, ++g) {
-          const int st = g % S;
-          ok = tc_wait(&sh.full[st], (g / S) & 1u, abort_flag, a.err, ERR_MBAR_FULL_TIMEOUT);
+    // =============================== MMA issuer: the whole warp runs the loop, lane 0 issues ================================
+    const unsigned leader = lane == 0 ? 1u : 0u;
+    int g = 0, ui = 0;
+    bool ok = true;
+    for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x, ++ui) {
+      const Unit un = decode_unit(a, u, nkb_total, grp_s);
+      for (int kb = un.kb0; kb < un.kb1 && ok; ++kb, ++g) {
+        const int st = g % S;
+        ok = tc_wait(&sh.full[st], (g / S) & 1u, abort_flag, a.err, ERR_MBAR_FULL_TIMEOUT);
+        if (!ok) break;
+        const int j = (KIND == 0) ? g : ui;            // accumulator use counter
+        const int b = j % NBUF;
+        if ((KIND == 0 || kb == un.kb0) && j >= NBUF) {
+          ok = tc_wait(&sh.tmem_empty[b], ((j / NBUF) & 1u) ^ 1u, abort_flag, a.err, ERR_TMEM_TIMEOUT);
           if (!ok) break;
-          const int j = (KIND == 0) ? g : ui;            // accumulator use counter
-          const int b = j % NBUF;
-          if ((KIND == 0 || kb == un.kb0) && j >= NBUF) {
-            ok = tc_wait(&sh.tmem_empty[b], ((j / NBUF) & 1u) ^ 1u, abort_flag, a.err, ERR_TMEM_TIMEOUT);
-            if (!ok) break;
-          }
-          tc_fence_after();
-          const uint8_t* sA = stages + static_cast<size_t>(st) * STAGE_BYTES;
-          const uint64_t bdesc = smem_desc_sw128(sA + NA * TC_A_BYTES);
-#pragma unroll
-          for (int ai = 0; ai < NA; ++ai) {
-            const uint64_t adesc = smem_desc_sw128(sA + ai * TC_A_BYTES);
-#pragma unroll
-            for (int k = 0; k < TC_BKB / 32; ++k) {
-              const int sub = k % SUB;
-              const uint32_t d = tmem_base + static_cast<uint32_t>(b * BUF_COLS + (ai * SUB + sub) * NT);
-              const uint32_t accf = (KIND == 0) ? (k >= SUB) : (kb > un.kb0 || k >= SUB);
-              tc_mma<KIND>(d, adesc + 2 * k, bdesc + 2 * k, idesc, accf);   // +32 bytes of K per step
-            }
-          }
-          tc_commit(&sh.empty[st]);                      // stage reusable once these MMAs have read it
-          if (KIND == 0 || kb == un.kb1 - 1) tc_commit(&sh.tmem_full[b]);
         }
+        tc_fence_after();
+        const uint8_t* sA = stages + static_cast<size_t>(st) * STAGE_BYTES;
+        const uint64_t bdesc = smem_desc_sw128(sA + NA * TC_A_BYTES);
+#pragma unroll
+        for (int ai = 0; ai < NA; ++ai) {
+          const uint64_t adesc = smem_desc_sw128(sA + ai * TC_A_BYTES);
+#pragma unroll
+          for (int k = 0; k < TC_BKB / 32; ++k) {
+            const int sub = k % SUB;
+            const uint32_t d = tmem_base + static_cast<uint32_t>(b * BUF_COLS + (ai * SUB + sub) * NT);
+            const uint32_t accf = (KIND == 0) ? (k >= SUB) : (kb > un.kb0 || k >= SUB);
+            tc_mma_if<KIND>(leader, d, adesc + 2 * k, bdesc + 2 * k, idesc, accf);   // +32 bytes of K per step
+          }
+        }
+        tc_commit_if(leader, &sh.empty[st]);             // stage reusable once these MMAs have read it
+        if (KIND == 0 || kb == un.kb1 - 1) tc_commit_if(leader, &sh.tmem_full[b]);
       }
     }
   } else {
