@@ -34,11 +34,9 @@ __device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* tm, in
       "l"(tm), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z), "r"(w)
       : "memory");
 }
-// The same copies and MMAs for code in which the WHOLE warp runs the loop and one lane (pred != 0) issues. tcgen05.mma and
-// the tensor copies take their descriptors, addresses and coordinates from uniform registers; inside an `if (lane == 0)`
-// branch the compiler holds those values in ordinary registers and moves them over before every instruction, which
-// (measured with a one-CTA micro-kernel) costs ~150 cycles per MMA and ~800 per tile copy against 45-64 and a few dozen
-// when the values are warp-uniform.
+// The same copies for code in which the WHOLE warp runs the loop and one lane (pred != 0) issues: used by the producer
+// warps of tc_gemm.cu (measured 4 % faster there than an `if (lane == 0)` branch). The MMA issuer keeps the branch form,
+// which runs at the tensor rate; a predicated tcgen05.mma in a warp-uniform loop did not.
 __device__ __forceinline__ void tma_load_2d_if(unsigned pred, void* dst, const CUtensorMap* tm, int x, int y, uint64_t* bar) {
   asm volatile(
       "{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %5, 0;\n\t"
@@ -76,27 +74,6 @@ __device__ __forceinline__ void bulk_g2s_if(unsigned pred, void* dst, const void
                    smem_u32(dst)),
                "l"(src), "r"(bytes), "r"(smem_u32(bar)), "r"(pred)
                : "memory");
-}
-__device__ __forceinline__ void tc_commit_if(unsigned pred, uint64_t* bar) {
-  asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %1, 0;\n\t"
-               "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}" ::"r"(smem_u32(bar)), "r"(pred)
-               : "memory");
-}
-template <int KIND>   // 0: e4m3 x e4m3, 1: bf16 x bf16; fp32 accumulate
-__device__ __forceinline__ void tc_mma_if(unsigned pred, uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
-  if (KIND == 0) {
-    asm volatile(
-        "{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %4, 0;\n\tsetp.ne.b32 q, %5, 0;\n\t"
-        "@q tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
-        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc), "r"(pred)
-        : "memory");
-  } else {
-    asm volatile(
-        "{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %4, 0;\n\tsetp.ne.b32 q, %5, 0;\n\t"
-        "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
-        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc), "r"(pred)
-        : "memory");
-  }
 }
 __device__ __forceinline__ void tmem_alloc(uint32_t* smem_dst, uint32_t ncols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_dst)),

@@ -240,38 +240,42 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       }
     }
   } else if (warp == TC_MMA_WARP) {
-    // =============================== MMA issuer: the whole warp runs the loop, lane 0 issues ================================
-    const unsigned leader = lane == 0 ? 1u : 0u;
-    int g = 0, ui = 0;
-    bool ok = true;
-    for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x, ++ui) {
-      const Unit un = decode_unit(a, u, nkb_total, grp_s);
-      for (int kb = un.kb0; kb < un.kb1 && ok; ++kb, ++g) {
-        const int st = g % S;
-        ok = tc_wait(&sh.full[st], (g / S) & 1u, abort_flag, a.err, ERR_MBAR_FULL_TIMEOUT);
-        if (!ok) break;
-        const int j = (KIND == 0) ? g : ui;            // accumulator use counter
-        const int b = j % NBUF;
-        if ((KIND == 0 || kb == un.kb0) && j >= NBUF) {
-          ok = tc_wait(&sh.tmem_empty[b], ((j / NBUF) & 1u) ^ 1u, abort_flag, a.err, ERR_TMEM_TIMEOUT);
+    // =============================== MMA issuer ========================================================================
+    // One thread, inside a branch: measured with a one-CTA micro-kernel, this form issues a 128 x 128 x 16 MMA every 64
+    // cycles (the tensor rate) with descriptors that change per instruction, while a warp-uniform loop with a predicated
+    // tcgen05.mma needed 118-180.
+    if (lane == 0) {
+      int g = 0, ui = 0;
+      bool ok = true;
+      for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x, ++ui) {
+        const Unit un = decode_unit(a, u, nkb_total, grp_s);
+        for (int kb = un.kb0; kb < un.kb1 && ok; ++kb, ++g) {
+          const int st = g % S;
+          ok = tc_wait(&sh.full[st], (g / S) & 1u, abort_flag, a.err, ERR_MBAR_FULL_TIMEOUT);
           if (!ok) break;
-        }
-        tc_fence_after();
-        const uint8_t* sA = stages + static_cast<size_t>(st) * STAGE_BYTES;
-        const uint64_t bdesc = smem_desc_sw128(sA + NA * TC_A_BYTES);
-#pragma unroll
-        for (int ai = 0; ai < NA; ++ai) {
-          const uint64_t adesc = smem_desc_sw128(sA + ai * TC_A_BYTES);
-#pragma unroll
-          for (int k = 0; k < TC_BKB / 32; ++k) {
-            const int sub = k % SUB;
-            const uint32_t d = tmem_base + static_cast<uint32_t>(b * BUF_COLS + (ai * SUB + sub) * NT);
-            const uint32_t accf = (KIND == 0) ? (k >= SUB) : (kb > un.kb0 || k >= SUB);
-            tc_mma_if<KIND>(leader, d, adesc + 2 * k, bdesc + 2 * k, idesc, accf);   // +32 bytes of K per step
+          const int j = (KIND == 0) ? g : ui;            // accumulator use counter
+          const int b = j % NBUF;
+          if ((KIND == 0 || kb == un.kb0) && j >= NBUF) {
+            ok = tc_wait(&sh.tmem_empty[b], ((j / NBUF) & 1u) ^ 1u, abort_flag, a.err, ERR_TMEM_TIMEOUT);
+            if (!ok) break;
           }
+          tc_fence_after();
+          const uint8_t* sA = stages + static_cast<size_t>(st) * STAGE_BYTES;
+          const uint64_t bdesc = smem_desc_sw128(sA + NA * TC_A_BYTES);
+#pragma unroll
+          for (int ai = 0; ai < NA; ++ai) {
+            const uint64_t adesc = smem_desc_sw128(sA + ai * TC_A_BYTES);
+#pragma unroll
+            for (int k = 0; k < TC_BKB / 32; ++k) {
+              const int sub = k % SUB;
+              const uint32_t d = tmem_base + static_cast<uint32_t>(b * BUF_COLS + (ai * SUB + sub) * NT);
+              const uint32_t accf = (KIND == 0) ? (k >= SUB) : (kb > un.kb0 || k >= SUB);
+              tc_mma<KIND>(d, adesc + 2 * k, bdesc + 2 * k, idesc, accf);   // +32 bytes of K per step
+            }
+          }
+          tc_commit(&sh.empty[st]);                      // stage reusable once these MMAs have read it
+          if (KIND == 0 || kb == un.kb1 - 1) tc_commit(&sh.tmem_full[b]);
         }
-        tc_commit_if(leader, &sh.empty[st]);             // stage reusable once these MMAs have read it
-        if (KIND == 0 || kb == un.kb1 - 1) tc_commit_if(leader, &sh.tmem_full[b]);
       }
     }
   } else {
