@@ -45,3 +45,10 @@ def test_ep2_matches_single_rank():
 
 def test_hybrid_tp2_ep4_matches_single_rank():
     _check(run_cpu_ranks(_run, 4, (2, 4, 6)), _single(6), 6)
+
+
+def test_tp4_with_replicated_kv_heads_matches_single_rank():
+    """More tensor-parallel ranks than KV heads (2 KV heads on 4 ranks): each KV head lives on two ranks, as at TP8
+    with the four KV heads of the Qwen3 models."""
+    assert TINY.n_kv_heads < 4
+    _check(run_cpu_ranks(_run, 4, (4, 1, 6)), _single(6), 6)
