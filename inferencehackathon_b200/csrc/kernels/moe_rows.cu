@@ -142,6 +142,7 @@ struct RmSmem {
   float h[4][RM_TOK][RM_HLD];
   __nv_bfloat16 w[2 * 256][RM_WLD];          // NS buffers of (512 / NS) rows
   float lg[RM_TOK][256];
+  __nv_bfloat16 hh[RM_TOK][RM_WLD], hl[RM_TOK][RM_WLD];   // the current chunk of h as bf16 heads and remainders
 };
 __device__ __forceinline__ void rm_cp16(void* dst, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
@@ -163,6 +164,12 @@ __global__ void __launch_bounds__(256) router_topk_rows_mma_kernel(const float* 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
   const int t0 = blockIdx.x * RM_TOK;
   const int nchunks = H / RM_KC;
+  // gridDim.y > 1: the experts are split over gridDim.y CTAs per token tile (the router is read by twice as many SMs);
+  // the logits then go to global memory and router_topk_from_logits_kernel selects.
+  const int E_all = E;
+  const int e_first = blockIdx.y * (E_all / gridDim.y);
+  E = E_all / gridDim.y;
+  W += static_cast<size_t>(e_first) * H;
   auto issue = [&](int c, int buf) {
     const int k0 = c * RM_KC;
     for (int i = tid; i < RM_TOK * (RM_KC / 4); i += 256) {           // 16 tokens x 16 pieces of 4 floats
@@ -189,14 +196,25 @@ __global__ void __launch_bounds__(256) router_topk_rows_mma_kernel(const float* 
     asm volatile("cp.async.commit_group;" ::: "memory");
     asm volatile("cp.async.wait_group %0;" ::"n"(NS - 1) : "memory");
     __syncthreads();
+    // split the chunk of h once for all eight warps (each warp doing it for itself was most of the kernel's instructions)
+    {
+      const int r = tid >> 4, p = (tid & 15) * 4;
+      const float4 v = *reinterpret_cast<const float4*>(&sm.h[buf][r][p]);
+      unsigned h0, l0, h1, l1;
+      rm_split2(v.x, v.y, h0, l0);
+      rm_split2(v.z, v.w, h1, l1);
+      *reinterpret_cast<uint2*>(&sm.hh[r][p]) = make_uint2(h0, h1);
+      *reinterpret_cast<uint2*>(&sm.hl[r][p]) = make_uint2(l0, l1);
+    }
+    __syncthreads();
 #pragma unroll
     for (int ks = 0; ks < RM_KC / 16; ++ks) {
       const int k0 = ks * 16 + 2 * t4;
       unsigned ah[4], al[4];
-      const float2 a0 = *reinterpret_cast<const float2*>(&sm.h[buf][g][k0]), a1 = *reinterpret_cast<const float2*>(&sm.h[buf][g + 8][k0]);
-      const float2 a2 = *reinterpret_cast<const float2*>(&sm.h[buf][g][k0 + 8]), a3 = *reinterpret_cast<const float2*>(&sm.h[buf][g + 8][k0 + 8]);
-      rm_split2(a0.x, a0.y, ah[0], al[0]); rm_split2(a1.x, a1.y, ah[1], al[1]);
-      rm_split2(a2.x, a2.y, ah[2], al[2]); rm_split2(a3.x, a3.y, ah[3], al[3]);
+      ah[0] = *reinterpret_cast<const unsigned*>(&sm.hh[g][k0]);     al[0] = *reinterpret_cast<const unsigned*>(&sm.hl[g][k0]);
+      ah[1] = *reinterpret_cast<const unsigned*>(&sm.hh[g + 8][k0]); al[1] = *reinterpret_cast<const unsigned*>(&sm.hl[g + 8][k0]);
+      ah[2] = *reinterpret_cast<const unsigned*>(&sm.hh[g][k0 + 8]); al[2] = *reinterpret_cast<const unsigned*>(&sm.hl[g][k0 + 8]);
+      ah[3] = *reinterpret_cast<const unsigned*>(&sm.hh[g + 8][k0 + 8]); al[3] = *reinterpret_cast<const unsigned*>(&sm.hl[g + 8][k0 + 8]);
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const int e = (warp + 8 * j) * 8 + g;
@@ -223,6 +241,13 @@ __global__ void __launch_bounds__(256) router_topk_rows_mma_kernel(const float* 
     }
   }
   __syncthreads();
+  if (gridDim.y > 1) {
+    for (int i = tid; i < RM_TOK * E; i += 256) {
+      const int r = i / E, e = i - r * E;
+      if (t0 + r < T) logits_out[static_cast<size_t>(t0 + r) * E_all + e_first + e] = sm.lg[r][e];
+    }
+    return;
+  }
   // softmax + top-k: a warp takes tokens warp and warp + 8
   for (int r = warp; r < RM_TOK; r += 8) {
     const int t = t0 + r;
@@ -417,6 +442,13 @@ extern "C" int ihb_router_topk_rows(const float* h, const void* router_bf16, int
                                  static_cast<int>(sizeof(RmSmem)));
       if (e != cudaSuccess) return e;
       attr_set = true;
+    }
+    if (logits != nullptr && T >= 256 && E % 16 == 0 && E <= 256) {
+      // long windows: two CTAs per token tile, each half of the experts (4-deep ring: at most 128 rows per buffer)
+      router_topk_rows_mma_kernel<4><<<dim3((T + RM_TOK - 1) / RM_TOK, 2), 256, sizeof(RmSmem), stream>>>(
+          h, reinterpret_cast<const __nv_bfloat16*>(router_bf16), T, H, E, top_k, renorm, logits, ti, tw);
+      router_topk_from_logits_kernel<<<(T + 3) / 4, 128, 0, stream>>>(logits, T, E, top_k, renorm, ti, tw);
+      return cudaGetLastError();
     }
     if (E <= 128)
       router_topk_rows_mma_kernel<4><<<(T + RM_TOK - 1) / RM_TOK, 256, sizeof(RmSmem), stream>>>(

@@ -289,7 +289,7 @@ class GpuWindow:
             E_l = lw.w_gu.data.shape[0]
             ti = self._buf("ti_all", (n_layers, T, k), torch.int32)[L]
             tw = self._buf("tw_all", (n_layers, T, k), torch.float32)[L]
-            rlog = self._buf("router_logits", (T, m.n_experts), torch.float32) if T <= 32 else None
+            rlog = self._buf("router_logits", (T, m.n_experts), torch.float32) if (T <= 32 or T >= 256) else None
             K.router_topk_rows(h2, lw.router, k, bool(m.norm_topk_prob), ti, tw, logits=rlog)
             per = max(1, pairs // m.n_experts)
             nt = 16 if per <= 12 else 32 if per <= 28 else 64
