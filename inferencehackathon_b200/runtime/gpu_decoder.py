@@ -587,7 +587,7 @@ class GpuDecoder:
 
     def window(self):
         """Multi-token forward (prompt chunks, verify windows); needs the plain row-major weights, i.e. the
-        persistent or the streaming pipeline, and tensor parallelism only."""
+        persistent or the streaming pipeline (tensor-, expert- or hybrid-parallel)."""
         if self._window is None:
             from .gpu_window import GpuWindow
             self._window = GpuWindow(self)

@@ -10,12 +10,18 @@ Block-scaled fp8 weights are multiplied as bf16 here (``IHB_WINDOW_BF16=1``, the
 weight block and per token forces the fp8 kernel to fold every 128-deep K block into fp32 registers on the CUDA
 cores, which is ~20x slower than the MMAs it serves; de-quantised bf16 copies of the weights (e4m3 x scale rounds to
 bf16 with 0.2 % relative error, a thirtieth of the e4m3 grid itself) let a whole K range accumulate in tensor memory
-and need no activation quantisation. The copies stay resident when they fit beside the model (they do from two GPUs
-up); otherwise a layer's weights are de-quantised into a scratch buffer right before its GEMMs.
+and need no activation quantisation. The copies stay resident when they fit beside the model; otherwise a layer's
+weights are de-quantised into a scratch buffer right before its GEMMs.
 
-The contractions and the attention are this package's kernels (``ihb_tc_gemm``, ``ihb_window_attention``,
-``ihb_norm_quant_rows``, ``ihb_qk_norm_rope_rows``); index bookkeeping (sort by expert, top-k, gathers) uses
-PyTorch tensor ops on the device. Reference counterparts: kernels/prefill_attn.cu, kernels/prefill_moe.cu,
+Tensor-, expert- and hybrid-parallel layouts run the same code: the attention heads a rank holds are tp-way shards
+replicated world / tp times (o_proj partials are scaled by tp / world), a rank runs the (token, slot) pairs whose
+expert it holds, and both partial results of a layer are summed over ALL ranks by the fused all-reduce + residual +
+RMSNorm kernels (counted small-message kernel up to 64 tokens, two-shot above).
+
+The contractions, the attention and the routing are this package's kernels (``ihb_tc_gemm``, ``ihb_window_attention``,
+``ihb_norm_quant_rows``, ``ihb_qk_norm_rope_rows``, ``ihb_router_topk_rows``, ``ihb_moe_group_table``,
+``ihb_moe_gather_rows``, ``ihb_moe_combine_rows``); PyTorch tensor ops remain for the embedding gather, position /
+slot vectors and one residual add on a single GPU. Reference counterparts: kernels/prefill_attn.cu, kernels/prefill_moe.cu,
 kernels/prefill_wgmma.cu (prefill) and kernels/spec_verify_forward_gemm.cu, engine/native/tc_verify_attn.cuh
 (verify).
 """
