@@ -20,9 +20,12 @@
 #include "common.cuh"
 #include "tails.cuh"
 
-// The body is compiled twice, into ihb::narrow and ihb::wide: the wide build adds a GEMV shape for CTAs that own many
-// rows per warp (full-width models on one GPU, +4 % tokens/s there); compiled into the same kernel it costs
-// the narrow shapes (tensor parallel over 4 or 8 GPUs) ~5 %, so the host picks the build by the size of the shares.
+// The body is compiled twice, into ihb::narrow and ihb::wide. The wide build lets the warps that produce a gate / up row
+// pair apply SwiGLU and the routing weight themselves (the down phase then reads half as many hand-over values) and
+// adds a GEMV shape for CTAs that own many rows per warp: +9 % tokens/s for a full-width model on one GPU, +2 % at TP2.
+// Compiled into the same kernel, the same code costs the shapes of TP4 / TP8 3-7 % (instruction-cache footprint and
+// register pressure in every function that inlines the shape helpers), so the host picks the build by the size of
+// the expert GEMV's shares (mega_host.inc::mega_wide).
 #define MG_NS narrow
 #define MG_WIDE 0
 #include "mega_body.inc"

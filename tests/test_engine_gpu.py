@@ -15,10 +15,13 @@ def _prompt(n=24):
 
 
 @pytest.mark.parametrize("weights", ["bf16", "fp8_block"])
-@pytest.mark.parametrize("pipeline,graph", [("mega", False), ("tc", False), ("tc", True), ("simt", True)])
+@pytest.mark.parametrize("pipeline,graph", [("mega", False), ("mega_wide", False), ("tc", False), ("tc", True), ("simt", True)])
 def test_cuda_decode_matches_torch_reference(weights, pipeline, graph, monkeypatch):
-    """``mega``: the persistent whole-token kernel; ``tc``: tensor-core linears, one kernel per op; ``simt``: the
-    streaming GEMV kernels."""
+    """``mega``: the persistent whole-token kernel (``mega_wide``: its build for large shares, forced onto the small
+    model); ``tc``: tensor-core linears, one kernel per op; ``simt``: the streaming GEMV kernels."""
+    monkeypatch.setenv("IHB_MEGA_WIDE", "1" if pipeline == "mega_wide" else "0")
+    if pipeline == "mega_wide":
+        pipeline = "mega"
     monkeypatch.setenv("IHB_MEGA", "1" if pipeline == "mega" else "0")
     monkeypatch.setenv("IHB_TC", "0" if pipeline == "simt" else "1")
     dev = "cuda:0"

@@ -120,3 +120,15 @@ def test_batched_prompt_pass_on_two_gpus(plan):
     assert out["tokens"][0] == out["tokens"][1], out
     agree = sum(int(a == b) for a, b in zip(out["tokens"][0], out["ref"]))
     assert out["logits_rel_err"] < 0.02 and agree >= 11, out
+
+
+@pytest.mark.parametrize("plan", ["tp", "ep"])
+def test_wide_build_of_the_persistent_kernel_on_two_gpus(plan):
+    """The kernel build for large per-CTA shares (gate / up pairs with SwiGLU at the producer, 4-rows-per-warp shape),
+    forced onto the small model: same checks as the default build."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    out = _run(2, "auto", "bf16", plan, extra_env={"IHB_MEGA_WIDE": "1"})
+    assert out["tokens"][0] == out["tokens"][1], out
+    agree = sum(int(a == b) for a, b in zip(out["tokens"][0], out["ref"]))
+    assert out["logits_rel_err"] < 0.02 and agree >= 11, out
