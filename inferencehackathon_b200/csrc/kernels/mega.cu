@@ -20,21 +20,28 @@
 #include "common.cuh"
 #include "tails.cuh"
 
-// The body is compiled twice, into ihb::narrow and ihb::wide. The wide build lets the warps that produce a gate / up row
-// pair apply SwiGLU and the routing weight themselves (the down phase then reads half as many hand-over values) and
-// adds a GEMV shape for CTAs that own many rows per warp: +9 % tokens/s for a full-width model on one GPU, +2 % at TP2.
-// Compiled into the same kernel, the same code costs the shapes of TP4 / TP8 3-7 % (instruction-cache footprint and
-// register pressure in every function that inlines the shape helpers), so the host picks the build by the size of
-// the expert GEMV's shares (mega_host.inc::mega_wide).
+// The body is compiled twice, into ihb::narrow and ihb::wide. In both, the warps that produce a gate / up row pair apply
+// SwiGLU and the routing weight themselves (MG_PAIR: the down phase then reads half as many hand-over values; -1.6 % per
+// token at TP8 shapes, -2 % at TP4). The wide build adds a GEMV shape for CTAs that own many rows per warp: with it a
+// full-width model on one GPU runs 9 % faster and TP2 2 %, but compiled into the same kernel that code costs the
+// shapes of TP4 / TP8 3-7 % (instruction-cache footprint and register pressure in every function that inlines the
+// shape helpers), so the host picks the build by the size of the expert GEMV's shares (mega_host.inc::mega_wide).
+#ifndef MG_NARROW_PAIR
+#define MG_NARROW_PAIR 1
+#endif
 #define MG_NS narrow
 #define MG_WIDE 0
+#define MG_PAIR MG_NARROW_PAIR
 #include "mega_body.inc"
 #undef MG_NS
 #undef MG_WIDE
+#undef MG_PAIR
 #define MG_NS wide
 #define MG_WIDE 1
+#define MG_PAIR 1
 #include "mega_body.inc"
 #undef MG_NS
 #undef MG_WIDE
+#undef MG_PAIR
 
 #include "mega_host.inc"
