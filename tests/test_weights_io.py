@@ -180,3 +180,33 @@ def test_device_random_state_dict_gives_every_layout_the_same_model():
         assert torch.equal(s.w_d.data[0], f.w_d.data[g.expert0][:, g.inter0: g.inter0 + g.inter_local])
         assert torch.equal(s.router, f.router)
         assert torch.equal(sh.lm_head.data, full.lm_head.data[g.vocab0: g.vocab0 + g.vocab_local])
+
+
+def test_window_attention_scratch_always_covers_the_slices_it_is_asked_for():
+    """Host-side sizing of the key-sliced window attention (no GPU needed): for every shape the scratch size the
+    library reports must hold one 132-float record per (token, head, slice) for the slice count it will launch, and
+    the slice count never exceeds the number of 64-key blocks or the library's limit."""
+    from inferencehackathon_b200.ops import lib
+    L = lib.load()
+    for nq, nkv in [(8, 1), (8, 2), (16, 2), (64, 4), (4, 1), (32, 4), (1, 1)]:
+        for T in [1, 4, 8, 16, 17, 64, 128, 257, 600, 1024]:
+            need = int(L.ihb_window_attention_scratch_floats(nq, nkv, T))
+            for base in [0, 1, 63, 64, 500, 4096, 32768]:
+                s = int(L.ihb_window_attention_splits(nq, nkv, base, T))
+                assert 1 <= s <= 32
+                assert s <= (base + T + 63) // 64
+                assert s == 1 or need >= T * nq * s * 132, (nq, nkv, T, base, s, need)
+
+
+def test_k_split_rule_of_the_window_gemms():
+    from inferencehackathon_b200.runtime.gpu_window import GpuWindow
+
+    class _W:
+        sms = 148
+    assert GpuWindow._k_split(_W, 80, 64, 1024) == 1          # wide token tiles are never split
+    assert GpuWindow._k_split(_W, 10, 64, 128) == 1
+    assert GpuWindow._k_split(_W, 149, 64, 1) > 1             # the one-token head: 149 tiles on 148 SMs
+    assert GpuWindow._k_split(_W, 1187, 64, 8) == 1           # many tiles: no split
+    for tiles, nkb, T in [(10, 64, 8), (72, 64, 16), (32, 16, 8), (1, 3, 1)]:
+        ks = GpuWindow._k_split(_W, tiles, nkb, T)
+        assert 1 <= ks <= min(nkb, 16)
