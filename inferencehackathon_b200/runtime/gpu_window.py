@@ -238,7 +238,27 @@ class GpuWindow:
         self.n_gemm_launches += 1
         return hit[1]
 
-    # ---- one chunk of up to CHUNK tokens ----------------------------------------------------------------------------------
+    @staticmethod
+    def _group_table(flat_e: torch.Tensor, n_experts: int, nt: int):
+        """Tokens sorted by expert -> (order, groups [G, 4] int32 = {expert, first row, rows, 0}, n_groups [1], G).
+        Everything stays on the device; G is an upper bound that depends only on shapes."""
+        pairs = flat_e.numel()
+        order = torch.argsort(flat_e, stable=True)
+        cnt = torch.bincount(flat_e, minlength=n_experts)
+        offs = torch.cumsum(cnt, 0) - cnt
+        ng = (cnt + nt - 1) // nt
+        cum = torch.cumsum(ng, 0)
+        gmax = n_experts + pairs // nt + 1
+        j = torch.arange(gmax, device=flat_e.device)
+        e_of = torch.searchsorted(cum, j, right=True).clamp_(max=n_experts - 1)
+        k_in = j - (cum[e_of] - ng[e_of])
+        valid = j < cum[-1]
+        tok0 = torch.where(valid, offs[e_of] + k_in * nt, torch.zeros_like(j))
+        ntok = torch.where(valid, (cnt[e_of] - k_in * nt).clamp(0, nt), torch.zeros_like(j))
+        groups = torch.stack([e_of, tok0, ntok, torch.zeros_like(j)], 1).to(torch.int32).contiguous()
+        return order, groups, cum[-1:].to(torch.int32).contiguous(), gmax
+
+    # ---- one chunk of up to 128 tokens ----------------------------------------------------------------------------------
     def _chunk(self, tokens: torch.Tensor, base: int, positions: torch.Tensor, mask: Optional[torch.Tensor],
                aux_layers=()) -> torch.Tensor:
         d = self.d
