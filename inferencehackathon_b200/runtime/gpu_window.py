@@ -240,8 +240,9 @@ class GpuWindow:
 
     @staticmethod
     def _group_table(flat_e: torch.Tensor, n_experts: int, nt: int):
-        """Tokens sorted by expert -> (order, groups [G, 4] int32 = {expert, first row, rows, 0}, n_groups [1], G).
-        Everything stays on the device; G is an upper bound that depends only on shapes."""
+        """Tokens sorted by expert -> (order, groups [G, 4] int32 = {expert, first row, rows, 0}, n_groups [1], G), with
+        plain tensor ops: the oracle of ``moe_group_table_kernel`` (which the forward pass uses), checkable on the CPU.
+        G is an upper bound that depends only on shapes."""
         pairs = flat_e.numel()
         order = torch.argsort(flat_e, stable=True)
         cnt = torch.bincount(flat_e, minlength=n_experts)
@@ -258,7 +259,7 @@ class GpuWindow:
         groups = torch.stack([e_of, tok0, ntok, torch.zeros_like(j)], 1).to(torch.int32).contiguous()
         return order, groups, cum[-1:].to(torch.int32).contiguous(), gmax
 
-    # ---- one chunk of up to 128 tokens ----------------------------------------------------------------------------------
+    # ---- one chunk of up to CHUNK tokens ----------------------------------------------------------------------------------
     def _chunk(self, tokens: torch.Tensor, base: int, positions: torch.Tensor, mask: Optional[torch.Tensor],
                aux_layers=()) -> torch.Tensor:
         d = self.d
