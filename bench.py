@@ -52,6 +52,8 @@ def parse_args():
     p.add_argument("--tp", type=int, default=2, help="attention tensor-parallel degree of the hybrid plan")
     p.add_argument("--hot-experts", type=int, default=0, help="skewed routing: scale the router rows of the first N experts")
     p.add_argument("--hot-scale", type=float, default=4.0)
+    p.add_argument("--steps-per-launch", type=int, default=1, help="tokens produced per cooperative launch of the persistent "
+                   "kernel in the timed loop (the kernel feeds its own arg-max back); --steps must be a multiple")
     p.add_argument("--ctx-sweep", default="", help="comma-separated context lengths: after the main run, the prompt pass "
                    "(TTFT) and 16 decode steps are timed at each of them and reported under context_sweep")
     p.add_argument("--gate-layers", type=int, default=2, help="layers of the model the distributed correctness gate runs (0: no gate)")
@@ -275,14 +277,18 @@ def main() -> None:
         cs.start()
         time.sleep(0.25)
     # ---- device-timed region: exactly K steps, one event per step for the TPOT distribution ----------------
-    evs = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+    spl = max(1, args.steps_per_launch) if gpu.use_mega else 1
+    if args.steps % spl:
+        raise SystemExit("--steps must be a multiple of --steps-per-launch")
+    n_launch = args.steps // spl
+    evs = [torch.cuda.Event(enable_timing=True) for _ in range(n_launch + 1)]
     sync_all()
     evs[0].record()
-    for i in range(args.steps):
-        gpu.run_steps(1)
+    for i in range(n_launch):
+        gpu.run_steps(spl, per_launch=spl)
         evs[i + 1].record()
     sync_all()
-    per = [evs[i].elapsed_time(evs[i + 1]) for i in range(args.steps)]
+    per = [evs[i].elapsed_time(evs[i + 1]) / spl for i in range(n_launch)]       # per token, averaged inside a launch
     total_ms = evs[0].elapsed_time(evs[-1])
     clocks = cs.stop() if rank == 0 else {}
     gpu.check_error()
@@ -352,7 +358,8 @@ def main() -> None:
                "ttft_note": ("batched prompt pass on the tensor cores (tcgen05 GEMMs, grouped experts, window attention)"
                              if gpu.has_window() else "prompt processed token by token with the decode pipeline"),
                "pipeline": "persistent" if gpu.use_mega else ("tcgen05 per-op" if gpu.use_tc else "simt per-op"),
-               "clocks": clocks, "e2e": e2e, "gpu_launches": gpu.n_launches_per_step * args.steps,
+               "clocks": clocks, "e2e": e2e, "gpu_launches": gpu.n_launches_per_step * n_launch,
+               "steps_per_launch": spl,
                "impl": "ours"}
         if ctx_rows:
             out["context_sweep"] = ctx_rows

@@ -257,6 +257,24 @@ class InferenceEngine:
         self._index += 1
         return StepOutput(i, int(out_tok), seconds, routes)
 
+    def decode_many(self, n: int, per_launch: int = 8) -> List[int]:
+        """``n`` greedy tokens with ONE host synchronisation: the persistent kernel produces ``per_launch`` tokens per
+        cooperative launch, feeding its own arg-max back, and logs them in a device ring (no per-token host round
+        trip, no routing telemetry). Other pipelines, samplers and the PyTorch path fall back to ``decode_step``."""
+        if (self.gpu is None or not self.gpu.use_mega or not self.sampler.params.greedy or self._last_token is None
+                or n < 1):
+            return [self.decode_step(want_routes=False).token_id for _ in range(n)]
+        try:
+            with _nvtx("ihb.decode_many", self.device):
+                toks = self.gpu.decode_many(n, per_launch)
+        except RuntimeError as e:
+            self._fall_back(e, drop=0)
+            return [self.decode_step(want_routes=False).token_id for _ in range(n)]
+        self._history += [int(self._last_token)] + [int(t) for t in toks[:-1]]
+        self._last_token = int(toks[-1])
+        self._index += n
+        return [int(t) for t in toks]
+
     def logits_for(self, tokens: Sequence[int], commit: bool = True, tree_mask=None, positions=None,
                    aux_layers=()) -> torch.Tensor:
         """Logits ``[T, V]`` of a window of new tokens (speculative verify, chains and token trees)."""

@@ -580,10 +580,34 @@ class GpuDecoder:
                  "share": (t / reps) / total if total else 0.0} for n, (t, c) in agg.items()]
         return sorted(rows, key=lambda r: -r["us_per_token"])
 
-    def run_steps(self, n: int) -> None:
-        """Enqueue ``n`` decode steps without any host synchronisation (benchmark loop)."""
+    def run_steps(self, n: int, per_launch: int = 1) -> None:
+        """Enqueue ``n`` decode steps without any host synchronisation (benchmark loop). ``per_launch`` > 1 (persistent
+        kernel, greedy decoding): one cooperative launch produces that many tokens in a row; the kernel feeds its own
+        arg-max back and logs the tokens in the token ring."""
+        if per_launch > 1 and self.use_mega:
+            full, rem = divmod(n, per_launch)
+            self.mega.steps = per_launch
+            try:
+                for _ in range(full):
+                    self._step()
+            finally:
+                self.mega.steps = 1
+            n = rem
         for _ in range(n):
             self._step()
+
+    def decode_many(self, n: int, per_launch: int = 8) -> List[int]:
+        """``n`` greedy tokens with one host synchronisation at the end; the tokens come from the device token ring."""
+        if n > self.token_ring.numel():
+            raise ValueError("more tokens than the token ring holds")
+        pos0 = self.seq_len
+        if pos0 + n > self.max_seq:
+            raise ValueError("KV cache overflow")
+        self.run_steps(n, per_launch)
+        idx = (torch.arange(pos0, pos0 + n, device=self.device) % self.token_ring.numel()).long()
+        toks = self.token_ring[idx].tolist()
+        self.check_error()
+        return toks
 
     def window(self):
         """Multi-token forward (prompt chunks, verify windows); needs the plain row-major weights, i.e. the

@@ -157,3 +157,22 @@ def test_one_rank_of_tp8_of_the_large_architecture_against_pytorch(weights):
             eng.gpu.check_error()
     scale = float(outs["torch"].abs().max())
     assert float((outs["torch"] - outs["cuda"]).abs().max()) < 0.02 * scale
+
+
+@pytest.mark.parametrize("per_launch", [1, 4, 5])
+def test_several_tokens_per_launch_give_the_tokens_of_single_steps(per_launch, monkeypatch):
+    """``decode_many``: the persistent kernel loops over tokens inside one cooperative launch (feeding its own arg-max
+    back, logging tokens in the device ring); the result must be the token sequence of one launch per token."""
+    monkeypatch.setenv("IHB_MEGA", "1")
+    dev = "cuda:0"
+    a = InferenceEngine.build("small", weights="fp8_block", device=dev, backend="cuda", max_seq=256)
+    b = InferenceEngine.build("small", weights="fp8_block", device=dev, backend="cuda", max_seq=256)
+    pa, pb = a.prefill(_prompt()), b.prefill(_prompt())
+    assert pa.next_token == pb.next_token
+    single = [a.decode_step(want_routes=False).token_id for _ in range(13)]
+    many = b.decode_many(13, per_launch=per_launch)
+    assert many == single
+    # both engines continue identically afterwards (position, token and history bookkeeping)
+    assert a.decode_step(want_routes=False).token_id == b.decode_step(want_routes=False).token_id
+    assert a.seq_len == b.seq_len
+    b.gpu.check_error()
