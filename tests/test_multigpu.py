@@ -28,8 +28,11 @@ if os.environ.get("IHB_TEST_WINDOW", "0") != "1":
 eng = InferenceEngine.build("small", tp=tp, ep=ep, rank=rank, world=world, weights=weights, device=dev, backend="cuda", max_seq=128)
 pre = eng.prefill(prompt, return_logits=True)
 tokens = [pre.next_token]
-for _ in range(11):
-    tokens.append(eng.decode_step(want_routes=False).token_id)
+if os.environ.get("IHB_TEST_MANY", "0") == "1":
+    tokens += eng.decode_many(11, per_launch=4)          # several tokens per cooperative launch, all-reduces included
+else:
+    for _ in range(11):
+        tokens.append(eng.decode_step(want_routes=False).token_id)
 eng.gpu.check_error()
 ref_tokens, rel_err = None, None
 if rank == 0:
@@ -132,3 +135,14 @@ def test_wide_build_of_the_persistent_kernel_on_two_gpus(plan):
     assert out["tokens"][0] == out["tokens"][1], out
     agree = sum(int(a == b) for a, b in zip(out["tokens"][0], out["ref"]))
     assert out["logits_rel_err"] < 0.02 and agree >= 11, out
+
+
+def test_several_tokens_per_launch_on_two_gpus():
+    """``decode_many``: four tokens per cooperative launch on both GPUs (the in-kernel all-reduce rounds, slot clearing
+    and the arg-max exchange run across token boundaries inside one launch); tokens as with one launch per token."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    base = _run(2, "auto", "bf16")
+    out = _run(2, "auto", "bf16", extra_env={"IHB_TEST_MANY": "1"})
+    assert out["tokens"][0] == out["tokens"][1], out
+    assert out["tokens"] == base["tokens"], (out, base)
