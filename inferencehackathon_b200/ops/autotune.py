@@ -6,6 +6,7 @@ built-in rules are not leaving bandwidth on the table. Same role as the referenc
 (kernels/autotune.cu: threads x grid for the expert kernels, splits for flash-decode at ctx 4096 / 32768).
 
     python -m inferencehackathon_b200.ops.autotune [--tp 8] [--weights fp8_block|bf16] [--iters 50] [--out FILE.json]
+    python -m inferencehackathon_b200.ops.autotune --gemm          # dense tcgen05 GEMMs of the prompt path: us, TFLOP/s
 
 Results that fail the kernel's own validation are skipped (the entry point refuses them before launching anything).
 Timing: CUDA events around ``iters`` launches that rotate over enough independent weight sets to exceed L2.
@@ -174,6 +175,54 @@ def sweep_verify_attention(tp: int, iters: int, dev: torch.device, ctx: int = 40
     return out
 
 
+def sweep_window_gemm(iters: int, dev: torch.device) -> List[Dict]:
+    """Dense tcgen05 GEMMs of the prompt path (bf16 operands, LINEAR mode, 128-token tiles in one launch) at the
+    shapes of a full-width rank and of one rank of TP8: time and TFLOP/s, weight sets rotating so that every launch
+    streams its weights from HBM; cuBLAS (``torch.matmul``) on the largest shape for scale."""
+    from ..models.quant import QWeight
+    from . import lib
+    g = torch.Generator(device=dev).manual_seed(0)
+    err = torch.zeros(1, dtype=torch.int32, device=dev)
+    rows_out: List[Dict] = []
+
+    def run(rows, Kd, T, ks, nsets=6):
+        Ws = [QWeight((torch.randn(rows, Kd, device=dev, generator=g) * 0.02).to(torch.bfloat16)) for _ in range(nsets)]
+        X = torch.randn(T, Kd, device=dev, generator=g).to(torch.bfloat16)
+        blocks = []
+        for W in Ws:
+            a = lib.IhbTcArgs()
+            lib.tc_fill_weight(a, W)
+            out = torch.zeros(T, rows, device=dev)
+            a.X, a.mode, a.out_stride = X.data_ptr(), lib.TC_LINEAR, rows
+            a.T_total, a.err = T, err.data_ptr()
+            a.T, a.tok0, a.out = T, 0, out.data_ptr()
+            if T > 128:
+                a.tok_tile, a.tok_tiles = 128, -(-T // 128)
+            tiles = ((rows + 127) // 128) * max(1, a.tok_tiles)
+            a.ks = ks
+            part = torch.zeros(max(1, lib.tc_partial_floats(a)), device=dev)
+            ctr = torch.zeros(max(tiles, 1), dtype=torch.int32, device=dev)
+            a.partial, a.tile_counters = part.data_ptr(), ctr.data_ptr()
+            blocks.append((a, out, part, ctr))
+        us = _time_us(lambda i: lib.tc_gemm(blocks[i % nsets][0], False), iters)
+        ref = X.float() @ Ws[(iters - 1) % nsets].data.float().t()
+        diff = float((blocks[(iters - 1) % nsets][1] - ref).abs().max())
+        rows_out.append({"rows": rows, "K": Kd, "T": T, "ks": ks, "us": round(us, 1),
+                         "tflops": round(2.0 * rows * Kd * T / us * 1e-6, 1), "maxdiff": diff})
+
+    for rows, Kd, T, ks in [(9216, 4096, 1024, 1), (4096, 8192, 1024, 1), (1280, 4096, 1024, 1), (1280, 4096, 1024, 2),
+                            (4096, 1024, 1024, 1), (9216, 4096, 128, 1), (1280, 4096, 128, 1)]:
+        run(rows, Kd, T, ks)
+    if int(err.item()):
+        raise RuntimeError("device error word set during the GEMM sweep")
+    x = torch.randn(1024, 4096, device=dev).to(torch.bfloat16)
+    w = torch.randn(9216, 4096, device=dev).to(torch.bfloat16)
+    us = _time_us(lambda i: torch.matmul(x, w.t()), iters)
+    rows_out.append({"rows": 9216, "K": 4096, "T": 1024, "ks": 0, "us": round(us, 1), "tflops": round(2.0 * 9216 * 4096 * 1024 / us * 1e-6, 1),
+                     "library": "torch.matmul (cuBLAS)"})
+    return rows_out
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     ap.add_argument("--tp", type=int, default=8)
@@ -181,11 +230,20 @@ def main(argv=None) -> int:
     ap.add_argument("--iters", type=int, default=50)
     ap.add_argument("--out", default="")
     ap.add_argument("--skip-experts", action="store_true")
+    ap.add_argument("--gemm", action="store_true", help="only the dense tcgen05 GEMM table of the prompt path")
     a = ap.parse_args(argv)
     from . import lib
     lib.load()
     dev = torch.device("cuda", 0)
     res: Dict = {"tp": a.tp}
+    if a.gemm:
+        res["window_gemm"] = sweep_window_gemm(a.iters, dev)
+        for r in res["window_gemm"]:
+            print("gemm", r)
+        if a.out:
+            with open(a.out, "w") as f:
+                json.dump(res, f, indent=1)
+        return 0
     if not a.skip_experts:
         res["experts"] = sweep_experts(a.tp, a.weights == "fp8_block", a.iters, dev)
         e = res["experts"]
