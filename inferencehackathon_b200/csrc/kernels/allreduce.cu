@@ -24,6 +24,7 @@ struct ArArgs {
   const float* gamma;    // optional [H]: RMSNorm weight (NULL: plain all-reduce)
   float* out;            // [T, H] reduced (+ residual) rows
   float* out_norm;       // optional [T, H]
+  void* out_norm_bf16;   // optional [T, H] bf16: the normed rows rounded for a tensor-core GEMM that follows
   float eps;
   int T, H;
   unsigned* counter;     // grid arrival counter (zero before the first launch)
@@ -89,10 +90,15 @@ __device__ __forceinline__ void ar_finish_row(const ArArgs& a, int t, float4* v,
   const float rinv = rsqrtf(tot / static_cast<float>(H) + a.eps);
   for (int j = 0; j < nv; ++j) {
     const int i = (threadIdx.x + NTHR * j) * 4;
-    if (i < H && a.out_norm != nullptr) {
+    if (i < H && (a.out_norm != nullptr || a.out_norm_bf16 != nullptr)) {
       const float4 g = *reinterpret_cast<const float4*>(a.gamma + i);
-      *reinterpret_cast<float4*>(a.out_norm + static_cast<size_t>(t) * H + i) =
-          make_float4(v[j].x * rinv * g.x, v[j].y * rinv * g.y, v[j].z * rinv * g.z, v[j].w * rinv * g.w);
+      const float4 y = make_float4(v[j].x * rinv * g.x, v[j].y * rinv * g.y, v[j].z * rinv * g.z, v[j].w * rinv * g.w);
+      if (a.out_norm != nullptr) *reinterpret_cast<float4*>(a.out_norm + static_cast<size_t>(t) * H + i) = y;
+      if (a.out_norm_bf16 != nullptr) {
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(y.x, y.y), hi = __floats2bfloat162_rn(y.z, y.w);
+        *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(a.out_norm_bf16) + static_cast<size_t>(t) * H + i) =
+            make_uint2(*reinterpret_cast<const unsigned*>(&lo), *reinterpret_cast<const unsigned*>(&hi));
+      }
     }
   }
 }
@@ -224,7 +230,7 @@ __global__ void __launch_bounds__(AR_THREADS) ar_twoshot_kernel(const ArArgs a) 
         if (i < a.H) *reinterpret_cast<float4*>(a.out + static_cast<size_t>(t) * a.H + i) = v[j];
       }
       // the owner normalised its rows; the others repeat the (cheap, local) norm on the broadcast sums
-      if (a.gamma != nullptr && a.out_norm != nullptr && (t % cm.nranks) != cm.rank) {
+      if (a.gamma != nullptr && (a.out_norm != nullptr || a.out_norm_bf16 != nullptr) && (t % cm.nranks) != cm.rank) {
         ArArgs b = a;
         b.resid = nullptr;
         ar_finish_row<AR_THREADS>(b, t, v, AR_MAXV, red);
@@ -337,14 +343,14 @@ using namespace ihb;
 // x: fp32, or bf16 when x_is_bf16. T <= IHB_ARC_MAX_ROWS, H % 4 == 0, H <= 8192. Launched with programmatic stream serialisation: back-to-back calls overlap the
 // launch of one with the tail of the other.
 extern "C" int ihb_allreduce_counted(const IhbComm* comm, const void* x, int x_is_bf16, const float* resid, const float* gamma,
-                                     float eps, int T, int H, float* out, float* out_norm, unsigned* counter,
-                                     unsigned* call_counter, unsigned* err, cudaStream_t stream) {
+                                     float eps, int T, int H, float* out, float* out_norm, void* out_norm_bf16,
+                                     unsigned* counter, unsigned* call_counter, unsigned* err, cudaStream_t stream) {
   if (T < 1 || T > IHB_ARC_MAX_ROWS || H < 4 || (H % 4) || H > ARC_MAXV * ARC_THREADS * 4 || comm == nullptr ||
       call_counter == nullptr) return cudaErrorInvalidValue;
   (void)counter;
   ArcArgs q;
   q.a.comm = *comm; q.a.x = reinterpret_cast<const float*>(x); q.a.resid = resid; q.a.gamma = gamma; q.a.out = out;
-  q.a.out_norm = out_norm; q.a.eps = eps; q.a.T = T; q.a.H = H; q.a.counter = counter; q.a.err = err;
+  q.a.out_norm = out_norm; q.a.out_norm_bf16 = out_norm_bf16; q.a.eps = eps; q.a.T = T; q.a.H = H; q.a.counter = counter; q.a.err = err;
   q.x_is_bf16 = x_is_bf16;
   q.call_counter = call_counter;
   cudaLaunchConfig_t cfg = {};
@@ -359,11 +365,12 @@ extern "C" int ihb_allreduce_counted(const IhbComm* comm, const void* x, int x_i
 // algo: 0 = choose by size, 1 = one-shot, 2 = two-shot. Slot region needed (floats): one-shot 2 * nranks * T * H,
 // two-shot 2 * T * H. counter: 8 unsigned, zero before the first launch.
 extern "C" int ihb_allreduce_norm(const IhbComm* comm, const float* x, const float* resid, const float* gamma, float eps,
-                                  int T, int H, float* out, float* out_norm, unsigned* counter, unsigned* err, int algo,
-                                  int grid, cudaStream_t stream) {
+                                  int T, int H, float* out, float* out_norm, void* out_norm_bf16, unsigned* counter,
+                                  unsigned* err, int algo, int grid, cudaStream_t stream) {
   if (T < 1 || H < 4 || (H % 4) || H > AR_MAXV * AR_THREADS * 4 || comm == nullptr || counter == nullptr) return cudaErrorInvalidValue;
   ArArgs a;
-  a.comm = *comm; a.x = x; a.resid = resid; a.gamma = gamma; a.out = out; a.out_norm = out_norm; a.eps = eps;
+  a.comm = *comm; a.x = x; a.resid = resid; a.gamma = gamma; a.out = out; a.out_norm = out_norm; a.out_norm_bf16 = out_norm_bf16;
+  a.eps = eps;
   a.T = T; a.H = H; a.counter = counter; a.err = err;
   const size_t bytes = static_cast<size_t>(T) * H * 4;
   if (algo == 0) algo = bytes <= (256u << 10) ? 1 : 2;

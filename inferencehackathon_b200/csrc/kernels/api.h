@@ -266,13 +266,14 @@ int ihb_dequant_bf16(const void* W, const float* scale, long long nmat, int rows
                      cudaStream_t stream);
 
 // ---- stand-alone fused all-reduce (+ residual + RMSNorm) over symmetric memory -----------------------------------------
-// x [T, H] fp32 partial of this rank -> out = sum over ranks (+ resid); out_norm = RMSNorm(out) * gamma (gamma != NULL).
+// x [T, H] fp32 partial of this rank -> out = sum over ranks (+ resid); out_norm = RMSNorm(out) * gamma (gamma != NULL);
+// out_norm_bf16 (optional): the same normed rows rounded to bf16, the input format of the tensor-core GEMM that follows.
 // algo 0 = by size, 1 = one-shot (push + one barrier, every rank adds), 2 = two-shot (row owners reduce with
 // multimem.ld_reduce or peer loads and broadcast). Slot region (floats): one-shot 2 * nranks * T * H, two-shot
 // 2 * T * H. counter: 8 unsigned words, zero before the first launch. One cooperative launch.
 int ihb_allreduce_norm(const IhbComm* comm, const float* x, const float* resid, const float* gamma, float eps, int T,
-                       int H, float* out, float* out_norm, unsigned* counter, unsigned* err, int algo, int grid,
-                       cudaStream_t stream);
+                       int H, float* out, float* out_norm, void* out_norm_bf16, unsigned* counter, unsigned* err, int algo,
+                       int grid, cudaStream_t stream);
 
 // Latency-optimal all-reduce (+ residual + RMSNorm) of a few rows: one CTA per row, plain launch; every rank ADDS its row
 // into 64-bit counted fixed-point slots on every GPU (multimem.red.add.u64 or peer reds) and waits for the contribution
@@ -282,8 +283,8 @@ int ihb_allreduce_norm(const IhbComm* comm, const float* x, const float* resid, 
 // unused. x fp32, or bf16 when x_is_bf16. T <= IHB_ARC_MAX_ROWS, H % 4 == 0, H <= 8192.
 #define IHB_ARC_MAX_ROWS 64
 int ihb_allreduce_counted(const IhbComm* comm, const void* x, int x_is_bf16, const float* resid, const float* gamma, float eps,
-                          int T, int H, float* out, float* out_norm, unsigned* counter, unsigned* call_counter, unsigned* err,
-                          cudaStream_t stream);
+                          int T, int H, float* out, float* out_norm, void* out_norm_bf16, unsigned* counter,
+                          unsigned* call_counter, unsigned* err, cudaStream_t stream);
 
 // ---- all-to-all exchange of rows over peer memory (expert-parallel dispatch / combine for multi-token windows) -----
 // Rows for destination d are pairs offsets[d] .. offsets[d + 1] of `send` (through `gather` when given). Receive region

@@ -174,7 +174,7 @@ def load(build_if_missing: bool = True) -> C.CDLL:
     lib.ihb_window_attention_scratch_floats.restype = C.c_size_t
     lib.ihb_a2a_rows.argtypes = [C.POINTER(IhbA2AArgs), C.c_int, _vp]
     lib.ihb_a2a_rows.restype = C.c_int
-    lib.ihb_allreduce_norm.argtypes = [C.POINTER(IhbComm), _vp, _vp, _vp, C.c_float, C.c_int, C.c_int, _vp, _vp, _vp, _vp,
+    lib.ihb_allreduce_norm.argtypes = [C.POINTER(IhbComm), _vp, _vp, _vp, C.c_float, C.c_int, C.c_int, _vp, _vp, _vp, _vp, _vp,
                                        C.c_int, C.c_int, _vp]
     lib.ihb_allreduce_norm.restype = C.c_int
     lib.ihb_router_topk_rows.argtypes = [_vp, _vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _vp, _vp, _vp, _vp]
@@ -187,7 +187,7 @@ def load(build_if_missing: bool = True) -> C.CDLL:
     lib.ihb_moe_combine_rows.argtypes = [_vp, _vp, _vp, C.c_int, C.c_int, C.c_int, _vp, _vp, _vp]
     lib.ihb_moe_combine_rows.restype = C.c_int
     lib.ihb_allreduce_counted.argtypes = [C.POINTER(IhbComm), _vp, C.c_int, _vp, _vp, C.c_float, C.c_int, C.c_int, _vp, _vp, _vp, _vp,
-                                          _vp, _vp]
+                                          _vp, _vp, _vp]
     lib.ihb_allreduce_counted.restype = C.c_int
     lib.ihb_dequant_bf16.argtypes = [_vp, _vp, C.c_longlong, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _vp, _vp]
     lib.ihb_dequant_bf16.restype = C.c_int
@@ -493,14 +493,15 @@ def moe_combine_rows(yg: torch.Tensor, inv: torch.Tensor, tw: torch.Tensor, k: i
 
 def allreduce_counted(comm: IhbComm, x: torch.Tensor, out: torch.Tensor, counter: torch.Tensor, call_counter: torch.Tensor,
                       err: torch.Tensor, resid: Optional[torch.Tensor] = None, gamma: Optional[torch.Tensor] = None,
-                      eps: float = 1e-6, out_norm: Optional[torch.Tensor] = None) -> None:
+                      eps: float = 1e-6, out_norm: Optional[torch.Tensor] = None,
+                      out_norm_bf16: Optional[torch.Tensor] = None) -> None:
     """Latency-optimal fused all-reduce (+ residual + RMSNorm) of ``x [T, H]`` (fp32 or bf16), ``T <= 64``: counted
     fixed-point slots, one one-way trip, no barrier (``csrc/kernels/allreduce.cu::ar_counted_kernel``). ``call_counter``:
     ``ARC_MAX_ROWS`` int32 zeros owned by the slot region (``4 * ARC_MAX_ROWS * H`` 64-bit words, zeroed); ``counter`` is
     unused (kept for signature symmetry). T may change from call to call."""
     T, H = x.shape
     check(load().ihb_allreduce_counted(C.byref(comm), x.data_ptr(), int(x.dtype == torch.bfloat16), ptr(resid), ptr(gamma), eps,
-                                       T, H, out.data_ptr(), ptr(out_norm), counter.data_ptr(), call_counter.data_ptr(),
+                                       T, H, out.data_ptr(), ptr(out_norm), ptr(out_norm_bf16), counter.data_ptr(), call_counter.data_ptr(),
                                        err.data_ptr(), stream_ptr()), "ihb_allreduce_counted")
 
 
@@ -520,9 +521,10 @@ def a2a_rows(args: IhbA2AArgs, grid: int = 32) -> None:
 
 def allreduce_norm(comm: IhbComm, x: torch.Tensor, out: torch.Tensor, counter: torch.Tensor, err: torch.Tensor,
                    resid: Optional[torch.Tensor] = None, gamma: Optional[torch.Tensor] = None, eps: float = 1e-6,
-                   out_norm: Optional[torch.Tensor] = None, algo: int = 0, grid: int = 0) -> None:
+                   out_norm: Optional[torch.Tensor] = None, algo: int = 0, grid: int = 0,
+                   out_norm_bf16: Optional[torch.Tensor] = None) -> None:
     """Fused all-reduce (+ residual + RMSNorm) of ``x [T, H]`` fp32 over the symmetric buffer described by ``comm``."""
     T, H = x.shape
     check(load().ihb_allreduce_norm(C.byref(comm), x.data_ptr(), ptr(resid), ptr(gamma), eps, T, H, out.data_ptr(),
-                                    ptr(out_norm), counter.data_ptr(), err.data_ptr(), algo, grid, stream_ptr()),
+                                    ptr(out_norm), ptr(out_norm_bf16), counter.data_ptr(), err.data_ptr(), algo, grid, stream_ptr()),
           "ihb_allreduce_norm")

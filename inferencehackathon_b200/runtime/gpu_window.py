@@ -86,24 +86,28 @@ class GpuWindow:
             self.ar_cm_small = self.ar.comm_block(self.ar_epoch, slot_offset_bytes=self.ar.extra_off)
             self.ar_calls = torch.zeros(K.ARC_MAX_ROWS, dtype=torch.int32, device=dev)
 
-    def _all_reduce(self, part: torch.Tensor, resid: torch.Tensor, gamma: Optional[torch.Tensor], tag: str):
-        """sum over ranks of ``part`` + ``resid`` -> (new residual stream, its RMSNorm * gamma or None)."""
+    def _all_reduce(self, part: torch.Tensor, resid: torch.Tensor, gamma: Optional[torch.Tensor], tag: str,
+                    want_fp32_norm: bool = True):
+        """sum over ranks of ``part`` + ``resid`` -> (new residual stream, its RMSNorm * gamma in fp32 or None, the same
+        rounded to bf16 as GEMM input or None). The bf16 copy comes out of the all-reduce kernel itself when the GEMMs
+        of this path take bf16 activations: no separate rounding launch."""
         d = self.d
         T, H = part.shape
         if self.ar is None:
             x = resid + d.comm_ref.all_reduce_world(part.clone() if d.cfg.parallel.world > 1 else part)
-            return x, None
+            return x, None, None
         out = self._buf("ar_out_" + tag, (T, H), torch.float32)
-        outn = self._buf("ar_norm_" + tag, (T, H), torch.float32) if gamma is not None else None
+        outn = self._buf("ar_norm_" + tag, (T, H), torch.float32) if (gamma is not None and (want_fp32_norm or self.fp8)) else None
+        outb = self._buf("ar_bf16_" + tag, (T, H * 2), torch.uint8) if (gamma is not None and not self.fp8) else None
         if T <= K.ARC_MAX_ROWS and H <= 8192:
             # verify windows and short prompts: one one-way trip through the switch, no barrier (9 us instead of 33 us
             # for the two-shot kernel at 16 KB on two GPUs)
             K.allreduce_counted(self.ar_cm_small, part, out, self.ar_counter, self.ar_calls, self.err, resid=resid, gamma=gamma,
-                                eps=d.cfg.model.rms_eps, out_norm=outn)
-            return out, outn
+                                eps=d.cfg.model.rms_eps, out_norm=outn, out_norm_bf16=outb)
+            return out, outn, outb
         K.allreduce_norm(self.ar_cm, part, out, self.ar_counter, self.err, resid=resid, gamma=gamma,
-                         eps=d.cfg.model.rms_eps, out_norm=outn, algo=2)
-        return out, outn
+                         eps=d.cfg.model.rms_eps, out_norm=outn, algo=2, out_norm_bf16=outb)
+        return out, outn, outb
 
     def routing(self):
         """Expert ids ``[layers, T, k]`` (int32) and weights of the last chunk that went through this path: every
@@ -272,10 +276,13 @@ class GpuWindow:
         nq, nkv, H, I, k = d.nq, d.nkv, d.H, d.I, m.top_k
         mask_u8 = mask.to(torch.uint8).contiguous() if mask is not None else None
         self.aux_taps = {}
-        xn = None                                                # RMSNorm(x) * in_ln when the last all-reduce produced it
+        xn = xb = None                                           # RMSNorm(x) * in_ln (fp32 / bf16) when the last all-reduce produced it
         n_layers = len(w.layers)
         for L, lw in enumerate(w.layers):
-            xq, xs, _ = self._quant(xn, None, "x") if xn is not None else self._quant(x, lw.in_ln, "x")
+            if xb is not None:
+                xq, xs = xb, None                                # bf16 rows straight from the all-reduce kernel
+            else:
+                xq, xs, _ = self._quant(xn, None, "x") if xn is not None else self._quant(x, lw.in_ln, "x")
             qkv = self._linear(lw.wqkv, xq, xs, T, "qkv")
             K.qk_norm_rope_rows(qkv, nq, nkv, lw.q_norm, lw.k_norm, m.rms_eps, d.cos, d.sin, pos32, slots,
                                 d.k_cache[L], d.v_cache[L], d.max_seq)
@@ -286,8 +293,10 @@ class GpuWindow:
             o = self._linear(lw.wo, aq, asc, T, "wo")
             if self.attn_scale != 1.0:
                 o.mul_(self.attn_scale)
-            x, h2 = self._all_reduce(o, x, lw.post_ln, "a" + str(L & 1))
-            if h2 is not None:
+            x, h2, hb = self._all_reduce(o, x, lw.post_ln, "a" + str(L & 1))          # the router reads h2 in fp32
+            if hb is not None:
+                hq, hs = hb, None
+            elif h2 is not None:
                 hq, hs, _ = self._quant(h2, None, "h")
             else:
                 hq, hs, h2 = self._quant(x, lw.post_ln, "h", want_norm=True)
@@ -319,7 +328,7 @@ class GpuWindow:
                 y = self._buf("ycomb", (T, H), torch.float32)
                 K.moe_combine_rows(yg, inv, tw, k, y)               # slot order: deterministic
                 nxt = w.layers[L + 1].in_ln if L + 1 < n_layers else None
-                x, xn = self._all_reduce(y, x, nxt, "m" + str(L & 1))
+                x, xn, xb = self._all_reduce(y, x, nxt, "m" + str(L & 1), want_fp32_norm=False)
             else:
                 xnew = self._buf("xres" + str(L & 1), (T, H), torch.float32)
                 K.moe_combine_rows(yg, inv, tw, k, xnew, resid=x)

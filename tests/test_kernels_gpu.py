@@ -285,10 +285,14 @@ def test_counted_allreduce_single_rank_adds_residual_and_norms(payload):
             x = x.to(torch.bfloat16)
         resid = torch.randn(T, H, device=d, generator=g)
         out, outn = torch.empty(T, H, device=d), torch.empty(T, H, device=d)
-        lib.allreduce_counted(cm, x, out, counter, calls, err, resid=resid, gamma=gamma, out_norm=outn)
+        outb = torch.empty(T, H, device=d, dtype=torch.bfloat16)
+        lib.allreduce_counted(cm, x, out, counter, calls, err, resid=resid, gamma=gamma, out_norm=outn,
+                              out_norm_bf16=outb if it % 2 == 0 else None)
         ref = x.float() + resid
         refn = ref * torch.rsqrt(ref.pow(2).mean(-1, keepdim=True) + 1e-6) * gamma
         assert float((out - ref).abs().max()) < 4e-6 * (1 + it)
         assert float((outn - refn).abs().max()) < 1e-5
+        if it % 2 == 0:                                  # the bf16 copy is the fp32 normed row, rounded to nearest
+            assert torch.equal(outb, outn.to(torch.bfloat16))
     assert int(err.item()) == 0 and calls[:8].tolist() == [9, 9, 6, 6, 6, 3, 3, 0]
     assert int(slots.abs().max()) == 0                   # every reader cleared what it consumed
