@@ -48,6 +48,8 @@ class GpuWindow:
         # GEMM operand type of this path: bf16 for bf16 models and (by default) for block-fp8 models as well
         self.bf16_copies = dec.fp8 and bool(env_flag("IHB_WINDOW_BF16", 1))
         self.fp8 = dec.fp8 and not self.bf16_copies
+        # bf16 GEMM inputs come out of the fused all-reduce kernel; IHB_WINDOW_AR_BF16=0 rounds them in a launch of its own
+        self.ar_bf16 = not self.fp8 and bool(env_flag("IHB_WINDOW_AR_BF16", 1))
         self.es = 1 if self.fp8 else 2
         dev = dec.device
         self._bf16 = {}                       # data_ptr of an fp8 weight -> its resident bf16 copy
@@ -97,8 +99,8 @@ class GpuWindow:
             x = resid + d.comm_ref.all_reduce_world(part.clone() if d.cfg.parallel.world > 1 else part)
             return x, None, None
         out = self._buf("ar_out_" + tag, (T, H), torch.float32)
-        outn = self._buf("ar_norm_" + tag, (T, H), torch.float32) if (gamma is not None and (want_fp32_norm or self.fp8)) else None
-        outb = self._buf("ar_bf16_" + tag, (T, H * 2), torch.uint8) if (gamma is not None and not self.fp8) else None
+        outn = self._buf("ar_norm_" + tag, (T, H), torch.float32) if (gamma is not None and (want_fp32_norm or not self.ar_bf16)) else None
+        outb = self._buf("ar_bf16_" + tag, (T, H * 2), torch.uint8) if (gamma is not None and self.ar_bf16) else None
         if T <= K.ARC_MAX_ROWS and H <= 8192:
             # verify windows and short prompts: one one-way trip through the switch, no barrier (9 us instead of 33 us
             # for the two-shot kernel at 16 KB on two GPUs)
