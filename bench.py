@@ -42,6 +42,8 @@ def parse_args():
     p.add_argument("--model", default="qwen3-235b-a22b")
     p.add_argument("--weights", default="fp8_block", choices=["fp8_block", "bf16"])
     p.add_argument("--prompt", type=int, default=1024)
+    p.add_argument("--kv", default="bf16", choices=["bf16", "fp8"], help="KV cache rows: bf16 (the headline), or e4m3 with a "
+                   "scale per position (half the cache bytes; runs the per-kernel pipeline instead of the persistent kernel)")
     p.add_argument("--layers", type=int, default=None, help="truncate the layer count (debug only)")
     p.add_argument("--distinct-layers", type=int, default=-1, help="-1: as many as fit")
     p.add_argument("--max-seq", type=int, default=0)
@@ -241,7 +243,7 @@ def main() -> None:
         gate = correctness_gate(args, rank, world, dev, tp, ep)
         if rank == 0:
             print("correctness gate: " + json.dumps(gate), file=sys.stderr)
-    eng = InferenceEngine.build(args.model, tp=tp, ep=ep, rank=rank, world=world, weights=args.weights, device=dev,
+    eng = InferenceEngine.build(args.model, tp=tp, ep=ep, rank=rank, world=world, weights=args.weights, kv=args.kv, device=dev,
                                 backend="cuda", max_seq=max_seq, n_layers=args.layers, distinct_layers=distinct)
     if args.hot_experts > 0:
         # imbalance run: the same change on every rank (the router is replicated); shared layer sets are scaled once
@@ -351,7 +353,7 @@ def main() -> None:
                           "parallelism": par_name, "layers": mcfg.n_layers,
                           "distinct_layer_weight_sets": distinct or mcfg.n_layers,
                           "l2": "inputs larger than L2 (per-token weight stream >> 126 MB)",
-                          "weights": args.weights, "kv": "bf16", "init_s": round(t_init, 1),
+                          "weights": args.weights, "kv": args.kv, "init_s": round(t_init, 1),
                           "router_skew": ({"hot_experts": args.hot_experts, "scale": args.hot_scale} if args.hot_experts else None)},
                "tpot_ms_p50": p50, "tpot_ms_p95": p95, "ttft_ms": ttft * 1e3,
                "ttft_cold_ms": cold * 1e3,

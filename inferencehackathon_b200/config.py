@@ -157,7 +157,7 @@ class QuantConfig:
 
     weights: str = "bf16"          # "fp32" | "bf16" | "fp8_block"
     block: int = 128
-    kv: str = "bf16"               # "fp32" | "bf16" | "fp8" (e4m3 rows with a scale per position: PyTorch path only)
+    kv: str = "bf16"               # "fp32" | "bf16" | "fp8" (e4m3 rows with a scale per position; on GPUs: the per-kernel pipeline)
 
     @property
     def weight_bytes(self) -> float:

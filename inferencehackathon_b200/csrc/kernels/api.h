@@ -123,6 +123,17 @@ int ihb_flash_decode(const float* q, const void* k_cache, const void* v_cache, i
                      const int* pos, int nsplit, float* scratch, unsigned* counters, float* out, unsigned char* out_q,
                      float* out_s, int out_fp8, int use_pdl, cudaStream_t stream);
 size_t ihb_flash_decode_scratch_floats(int nq, int nsplit);
+// The same two steps over an e4m3 KV cache: k_cache / v_cache [nkv, max_seq, 128] bytes, k_scale / v_scale
+// [nkv, max_seq] fp32 (one scale per row = amax of the row / 448, written by the append; a row reads as byte * scale).
+// The reference keeps its e4m3 cache with static per-channel scales (kernels/k1_attn_prologue.cu:524-604,
+// kernels/k2_flash_decode.cu:71-83); the per-row scale needs no calibration pass.
+int ihb_qk_norm_rope_kv8(float* qkv, int nq, int nkv, const float* q_gamma, const float* k_gamma, float eps,
+                         const float* cos_t, const float* sin_t, const int* pos, void* k_cache, void* v_cache,
+                         float* k_scale, float* v_scale, int max_seq, int use_pdl, cudaStream_t stream);
+int ihb_flash_decode_kv8(const float* q, const void* k_cache, const void* v_cache, const float* k_scale,
+                         const float* v_scale, int nq, int nkv, int max_seq, const int* pos, int nsplit, float* scratch,
+                         unsigned* counters, float* out, unsigned char* out_q, float* out_s, int out_fp8, int use_pdl,
+                         cudaStream_t stream);
 
 // ---- tensor-core linear layers (tcgen05 / TMEM / TMA) ------------------------------------------------------------
 enum { IHB_TC_LINEAR = 0, IHB_TC_GATEUP = 1, IHB_TC_DOWN = 2 };
@@ -239,6 +250,14 @@ int ihb_window_attention(const float* qkv, int qkv_stride, const void* k_cache, 
                          int max_seq, int base, int T, const unsigned char* mask, float* out, int mode, float* scratch,
                          cudaStream_t stream);
 int ihb_window_attention_splits(int nq, int nkv, int base, int T);
+// The window append and the tensor-core tiles over an e4m3 KV cache (layout as for ihb_flash_decode_kv8). Rows are
+// de-quantised on their way into shared memory; the tile loops are those of the bf16 cache.
+int ihb_qk_norm_rope_rows_kv8(float* qkv, int nq, int nkv, const float* q_gamma, const float* k_gamma, float eps,
+                              const float* cos_t, const float* sin_t, const int* positions, const int* slots, void* k_cache,
+                              void* v_cache, float* k_scale, float* v_scale, int max_seq, int T, cudaStream_t stream);
+int ihb_window_attention_kv8(const float* qkv, int qkv_stride, const void* k_cache, const void* v_cache, const float* k_scale,
+                             const float* v_scale, int nq, int nkv, int max_seq, int base, int T, const unsigned char* mask,
+                             float* out, float* scratch, cudaStream_t stream);
 size_t ihb_window_attention_scratch_floats(int nq, int nkv, int T);
 
 // ---- routing of a window of tokens on the device (moe_rows.cu) --------------------------------------------------------------------

@@ -69,14 +69,18 @@ __global__ void __launch_bounds__(256) embed_norm_kernel(const void* __restrict_
 
 // ---------------------------------------------------------------------------------------------------------------------
 // One warp per head. Lane owns channels d = lane + 32 j (j = 0..3); RoPE pairs (d, d + 64) are (j, j + 2).
+// KV8: the cache rows are e4m3 with one fp32 scale per (KV head, position) = amax of the row / 448, written here;
+// otherwise bf16 rows and the scale pointers are unused.
+template <bool KV8>
 __global__ void __launch_bounds__(32) qk_norm_rope_kv_kernel(float* __restrict__ qkv, int nq, int nkv,
                                                              const float* __restrict__ q_gamma,
                                                              const float* __restrict__ k_gamma, float eps,
                                                              const float* __restrict__ cos_t,
                                                              const float* __restrict__ sin_t,
                                                              const int* __restrict__ pos_p,
-                                                             __nv_bfloat16* __restrict__ k_cache,
-                                                             __nv_bfloat16* __restrict__ v_cache, int max_seq) {
+                                                             void* __restrict__ k_cache, void* __restrict__ v_cache,
+                                                             float* __restrict__ k_scale, float* __restrict__ v_scale,
+                                                             int max_seq) {
   pdl_wait();
   pdl_launch_dependents();
   const int head = blockIdx.x;
@@ -86,9 +90,10 @@ __global__ void __launch_bounds__(32) qk_norm_rope_kv_kernel(float* __restrict__
   if (head >= nq + nkv) {                  // V head: copy into the cache
     const int kvh = head - nq - nkv;
     const float* v = qkv + static_cast<size_t>(head) * HD;
-    __nv_bfloat16* dst = v_cache + (static_cast<size_t>(kvh) * max_seq + pos) * HD;
+    float vv[4];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) dst[lane + 32 * j] = __float2bfloat16(ld_cg_f(v + lane + 32 * j));
+    for (int j = 0; j < 4; ++j) vv[j] = ld_cg_f(v + lane + 32 * j);
+    kv_store_row<KV8>(v_cache, v_scale, static_cast<size_t>(kvh) * max_seq + pos, vv, lane);
     return;
   }
   float* x = qkv + static_cast<size_t>(head) * HD;
@@ -116,9 +121,7 @@ __global__ void __launch_bounds__(32) qk_norm_rope_kv_kernel(float* __restrict__
 #pragma unroll
     for (int j = 0; j < 4; ++j) x[lane + 32 * j] = o[j];
   } else {
-    __nv_bfloat16* dst = k_cache + (static_cast<size_t>(head - nq) * max_seq + pos) * HD;
-#pragma unroll
-    for (int j = 0; j < 4; ++j) dst[lane + 32 * j] = __float2bfloat16(o[j]);
+    kv_store_row<KV8>(k_cache, k_scale, static_cast<size_t>(head - nq) * max_seq + pos, o, lane);
   }
 }
 
@@ -130,10 +133,12 @@ constexpr int FD_WARPS = 4;
 constexpr int FD_BLOCK = FD_WARPS * 32;     // positions per CTA iteration
 constexpr int FD_REC = HD + 2;
 
-template <int GQ>
+template <int GQ, bool KV8>   // KV8: e4m3 cache rows with a scale per (KV head, position); the scores take the K scale, the
+                              // probabilities the V scale, so the inner loops stay plain FMAs on decoded bytes
 __global__ void __launch_bounds__(FD_WARPS * 32) flash_decode_kernel(
-    const float* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
-    const __nv_bfloat16* __restrict__ v_cache, int nq, int nkv, int max_seq, const int* __restrict__ pos_p,
+    const float* __restrict__ q, const void* __restrict__ k_cache, const void* __restrict__ v_cache,
+    const float* __restrict__ k_scale, const float* __restrict__ v_scale, int nq, int nkv, int max_seq,
+    const int* __restrict__ pos_p,
     int nsplit, float* __restrict__ scratch, unsigned* __restrict__ counters, float* __restrict__ out,
     uint8_t* __restrict__ out_q, float* __restrict__ out_s, int out_fp8) {
   __shared__ float red_m[FD_WARPS];
@@ -162,8 +167,11 @@ __global__ void __launch_bounds__(FD_WARPS * 32) flash_decode_kernel(
     l[g] = 0.f;
     acc[g][0] = acc[g][1] = acc[g][2] = acc[g][3] = 0.f;
   }
-  const __nv_bfloat16* kbase = k_cache + static_cast<size_t>(kvh) * max_seq * HD;
-  const __nv_bfloat16* vbase = v_cache + static_cast<size_t>(kvh) * max_seq * HD;
+  const size_t row0 = static_cast<size_t>(kvh) * max_seq;
+  const __nv_bfloat16* kbase = reinterpret_cast<const __nv_bfloat16*>(k_cache) + row0 * HD;      // bf16 rows
+  const __nv_bfloat16* vbase = reinterpret_cast<const __nv_bfloat16*>(v_cache) + row0 * HD;
+  const uint8_t* kbase8 = reinterpret_cast<const uint8_t*>(k_cache) + row0 * HD;                 // e4m3 rows
+  const uint8_t* vbase8 = reinterpret_cast<const uint8_t*>(v_cache) + row0 * HD;
 
   for (int b0 = split * FD_BLOCK; b0 < n; b0 += nsplit * FD_BLOCK) {
     const int base = b0 + warp * 32;
@@ -173,7 +181,33 @@ __global__ void __launch_bounds__(FD_WARPS * 32) flash_decode_kernel(
     float s[GQ];
 #pragma unroll
     for (int g = 0; g < GQ; ++g) s[g] = 0.f;
-    if (valid) {
+    float vsc = 0.f;                                   // V scale of this lane's position (KV8)
+    if constexpr (KV8) {
+      if (valid) {
+        const uint4* kr = reinterpret_cast<const uint4*>(kbase8 + static_cast<size_t>(p) * HD);
+        uint4 kreg[HD / 16];
+#pragma unroll
+        for (int c = 0; c < HD / 16; ++c) kreg[c] = kr[c];      // the row's 128 bytes in flight before the first FMA
+        const float ksc = k_scale[row0 + p];
+        vsc = v_scale[row0 + p];
+#pragma unroll
+        for (int c = 0; c < HD / 16; ++c) {
+          const unsigned w4[4] = {kreg[c].x, kreg[c].y, kreg[c].z, kreg[c].w};
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const float4 kf = e4m3x4_to_float4(w4[u]);
+#pragma unroll
+            for (int g = 0; g < GQ; ++g) {
+              const float4 qa = *reinterpret_cast<const float4*>(&q_s[g][c * 16 + u * 4]);
+              s[g] = fmaf(kf.x, qa.x, s[g]); s[g] = fmaf(kf.y, qa.y, s[g]);
+              s[g] = fmaf(kf.z, qa.z, s[g]); s[g] = fmaf(kf.w, qa.w, s[g]);
+            }
+          }
+        }
+#pragma unroll
+        for (int g = 0; g < GQ; ++g) s[g] *= ksc;
+      }
+    } else if (valid) {
       const uint4* kr = reinterpret_cast<const uint4*>(kbase + static_cast<size_t>(p) * HD);
       uint4 kreg[HD / 8];
 #pragma unroll
@@ -206,26 +240,47 @@ __global__ void __launch_bounds__(FD_WARPS * 32) flash_decode_kernel(
       m[g] = mnew;
       l[g] = l[g] * corr + pv;                           // per-lane partial sum, combined at the end
       acc[g][0] *= corr; acc[g][1] *= corr; acc[g][2] *= corr; acc[g][3] *= corr;
-      p_s[warp][g][lane] = pv;
+      p_s[warp][g][lane] = KV8 ? pv * vsc : pv;          // the denominator keeps the unscaled probability
     }
     __syncwarp();
     const int cnt = min(32, n - base);
-    for (int j0 = 0; j0 < cnt; j0 += 8) {
-      uint2 vreg[8];
+    if constexpr (KV8) {
+      for (int j0 = 0; j0 < cnt; j0 += 8) {
+        unsigned vreg[8];
 #pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        const int jj = min(j0 + u, cnt - 1);               // rows past the end repeat the last row; their p is 0
-        vreg[u] = *reinterpret_cast<const uint2*>(vbase + static_cast<size_t>(base + jj) * HD + lane * 4);
+        for (int u = 0; u < 8; ++u) {
+          const int jj = min(j0 + u, cnt - 1);             // rows past the end repeat the last row; their p is 0
+          vreg[u] = *reinterpret_cast<const unsigned*>(vbase8 + static_cast<size_t>(base + jj) * HD + lane * 4);
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const float4 vf = e4m3x4_to_float4(vreg[u]);
+#pragma unroll
+          for (int g = 0; g < GQ; ++g) {
+            const float pj = p_s[warp][g][j0 + u];
+            acc[g][0] = fmaf(pj, vf.x, acc[g][0]); acc[g][1] = fmaf(pj, vf.y, acc[g][1]);
+            acc[g][2] = fmaf(pj, vf.z, acc[g][2]); acc[g][3] = fmaf(pj, vf.w, acc[g][3]);
+          }
+        }
       }
+    } else {
+      for (int j0 = 0; j0 < cnt; j0 += 8) {
+        uint2 vreg[8];
 #pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        const float v0 = __uint_as_float(vreg[u].x << 16), v1 = __uint_as_float(vreg[u].x & 0xffff0000u);
-        const float v2 = __uint_as_float(vreg[u].y << 16), v3 = __uint_as_float(vreg[u].y & 0xffff0000u);
+        for (int u = 0; u < 8; ++u) {
+          const int jj = min(j0 + u, cnt - 1);               // rows past the end repeat the last row; their p is 0
+          vreg[u] = *reinterpret_cast<const uint2*>(vbase + static_cast<size_t>(base + jj) * HD + lane * 4);
+        }
 #pragma unroll
-        for (int g = 0; g < GQ; ++g) {
-          const float pj = p_s[warp][g][j0 + u];
-          acc[g][0] = fmaf(pj, v0, acc[g][0]); acc[g][1] = fmaf(pj, v1, acc[g][1]);
-          acc[g][2] = fmaf(pj, v2, acc[g][2]); acc[g][3] = fmaf(pj, v3, acc[g][3]);
+        for (int u = 0; u < 8; ++u) {
+          const float v0 = __uint_as_float(vreg[u].x << 16), v1 = __uint_as_float(vreg[u].x & 0xffff0000u);
+          const float v2 = __uint_as_float(vreg[u].y << 16), v3 = __uint_as_float(vreg[u].y & 0xffff0000u);
+#pragma unroll
+          for (int g = 0; g < GQ; ++g) {
+            const float pj = p_s[warp][g][j0 + u];
+            acc[g][0] = fmaf(pj, v0, acc[g][0]); acc[g][1] = fmaf(pj, v1, acc[g][1]);
+            acc[g][2] = fmaf(pj, v2, acc[g][2]); acc[g][3] = fmaf(pj, v3, acc[g][3]);
+          }
         }
       }
     }
@@ -343,25 +398,45 @@ extern "C" int ihb_embed_norm(const void* embed, int embed_is_bf16, const int* t
   return cudaLaunchKernelEx(&cfg, embed_norm_kernel, embed, embed_is_bf16, token, H, gamma, eps, resid, xn, xq, xs, xq_fp8);
 }
 
-extern "C" int ihb_qk_norm_rope_kv(float* qkv, int nq, int nkv, const float* q_gamma, const float* k_gamma,
-                                   float eps, const float* cos_t, const float* sin_t, const int* pos, void* k_cache,
-                                   void* v_cache, int max_seq, int use_pdl, cudaStream_t stream) {
+static int qk_norm_rope_kv_launch(float* qkv, int nq, int nkv, const float* q_gamma, const float* k_gamma, float eps,
+                                  const float* cos_t, const float* sin_t, const int* pos, void* k_cache, void* v_cache,
+                                  float* k_scale, float* v_scale, int max_seq, int use_pdl, cudaStream_t stream) {
   cudaLaunchConfig_t cfg = {};
   cudaLaunchAttribute attr[1];
   pdl_cfg(cfg, attr, dim3(nq + 2 * nkv), dim3(32), use_pdl, stream);
-  return cudaLaunchKernelEx(&cfg, qk_norm_rope_kv_kernel, qkv, nq, nkv, q_gamma, k_gamma, eps, cos_t, sin_t, pos,
-                            reinterpret_cast<__nv_bfloat16*>(k_cache), reinterpret_cast<__nv_bfloat16*>(v_cache),
-                            max_seq);
+  if (k_scale != nullptr)
+    return cudaLaunchKernelEx(&cfg, qk_norm_rope_kv_kernel<true>, qkv, nq, nkv, q_gamma, k_gamma, eps, cos_t, sin_t, pos,
+                              k_cache, v_cache, k_scale, v_scale, max_seq);
+  return cudaLaunchKernelEx(&cfg, qk_norm_rope_kv_kernel<false>, qkv, nq, nkv, q_gamma, k_gamma, eps, cos_t, sin_t, pos,
+                            k_cache, v_cache, k_scale, v_scale, max_seq);
+}
+
+extern "C" int ihb_qk_norm_rope_kv(float* qkv, int nq, int nkv, const float* q_gamma, const float* k_gamma,
+                                   float eps, const float* cos_t, const float* sin_t, const int* pos, void* k_cache,
+                                   void* v_cache, int max_seq, int use_pdl, cudaStream_t stream) {
+  return qk_norm_rope_kv_launch(qkv, nq, nkv, q_gamma, k_gamma, eps, cos_t, sin_t, pos, k_cache, v_cache, nullptr, nullptr,
+                                max_seq, use_pdl, stream);
+}
+
+// e4m3 cache rows [nkv, max_seq, 128] bytes with scales [nkv, max_seq] fp32
+extern "C" int ihb_qk_norm_rope_kv8(float* qkv, int nq, int nkv, const float* q_gamma, const float* k_gamma,
+                                    float eps, const float* cos_t, const float* sin_t, const int* pos, void* k_cache,
+                                    void* v_cache, float* k_scale, float* v_scale, int max_seq, int use_pdl,
+                                    cudaStream_t stream) {
+  if (k_scale == nullptr || v_scale == nullptr) return cudaErrorInvalidValue;
+  return qk_norm_rope_kv_launch(qkv, nq, nkv, q_gamma, k_gamma, eps, cos_t, sin_t, pos, k_cache, v_cache, k_scale, v_scale,
+                                max_seq, use_pdl, stream);
 }
 
 extern "C" size_t ihb_flash_decode_scratch_floats(int nq, int nsplit) {
   return static_cast<size_t>(nq) * nsplit * FD_REC;
 }
 
-extern "C" int ihb_flash_decode(const float* q, const void* k_cache, const void* v_cache, int nq, int nkv,
-                                int max_seq, const int* pos, int nsplit, float* scratch, unsigned* counters,
-                                float* out, unsigned char* out_q, float* out_s, int out_fp8, int use_pdl,
-                                cudaStream_t stream) {
+template <bool KV8>
+static int flash_decode_launch(const float* q, const void* k_cache, const void* v_cache, const float* k_scale,
+                               const float* v_scale, int nq, int nkv, int max_seq, const int* pos, int nsplit,
+                               float* scratch, unsigned* counters, float* out, unsigned char* out_q, float* out_s,
+                               int out_fp8, int use_pdl, cudaStream_t stream) {
   if (nq % nkv || nsplit < 1 || nsplit > 256) return cudaErrorInvalidValue;
   const int q_per_kv = nq / nkv;
   int gq = q_per_kv >= 8 ? 8 : q_per_kv;
@@ -369,14 +444,30 @@ extern "C" int ihb_flash_decode(const float* q, const void* k_cache, const void*
   cudaLaunchConfig_t cfg = {};
   cudaLaunchAttribute attr[1];
   pdl_cfg(cfg, attr, dim3(nsplit, nkv, q_per_kv / gq), dim3(FD_WARPS * 32), use_pdl, stream);
-  const __nv_bfloat16* kc = reinterpret_cast<const __nv_bfloat16*>(k_cache);
-  const __nv_bfloat16* vc = reinterpret_cast<const __nv_bfloat16*>(v_cache);
   switch (gq) {
-    case 8: return cudaLaunchKernelEx(&cfg, flash_decode_kernel<8>, q, kc, vc, nq, nkv, max_seq, pos, nsplit, scratch, counters, out, out_q, out_s, out_fp8);
-    case 4: return cudaLaunchKernelEx(&cfg, flash_decode_kernel<4>, q, kc, vc, nq, nkv, max_seq, pos, nsplit, scratch, counters, out, out_q, out_s, out_fp8);
-    case 2: return cudaLaunchKernelEx(&cfg, flash_decode_kernel<2>, q, kc, vc, nq, nkv, max_seq, pos, nsplit, scratch, counters, out, out_q, out_s, out_fp8);
-    default: return cudaLaunchKernelEx(&cfg, flash_decode_kernel<1>, q, kc, vc, nq, nkv, max_seq, pos, nsplit, scratch, counters, out, out_q, out_s, out_fp8);
+    case 8: return cudaLaunchKernelEx(&cfg, flash_decode_kernel<8, KV8>, q, k_cache, v_cache, k_scale, v_scale, nq, nkv, max_seq, pos, nsplit, scratch, counters, out, out_q, out_s, out_fp8);
+    case 4: return cudaLaunchKernelEx(&cfg, flash_decode_kernel<4, KV8>, q, k_cache, v_cache, k_scale, v_scale, nq, nkv, max_seq, pos, nsplit, scratch, counters, out, out_q, out_s, out_fp8);
+    case 2: return cudaLaunchKernelEx(&cfg, flash_decode_kernel<2, KV8>, q, k_cache, v_cache, k_scale, v_scale, nq, nkv, max_seq, pos, nsplit, scratch, counters, out, out_q, out_s, out_fp8);
+    default: return cudaLaunchKernelEx(&cfg, flash_decode_kernel<1, KV8>, q, k_cache, v_cache, k_scale, v_scale, nq, nkv, max_seq, pos, nsplit, scratch, counters, out, out_q, out_s, out_fp8);
   }
+}
+
+extern "C" int ihb_flash_decode(const float* q, const void* k_cache, const void* v_cache, int nq, int nkv,
+                                int max_seq, const int* pos, int nsplit, float* scratch, unsigned* counters,
+                                float* out, unsigned char* out_q, float* out_s, int out_fp8, int use_pdl,
+                                cudaStream_t stream) {
+  return flash_decode_launch<false>(q, k_cache, v_cache, nullptr, nullptr, nq, nkv, max_seq, pos, nsplit, scratch, counters,
+                                    out, out_q, out_s, out_fp8, use_pdl, stream);
+}
+
+// the same over an e4m3 cache ([nkv, max_seq, 128] bytes, scales [nkv, max_seq] fp32)
+extern "C" int ihb_flash_decode_kv8(const float* q, const void* k_cache, const void* v_cache, const float* k_scale,
+                                    const float* v_scale, int nq, int nkv, int max_seq, const int* pos, int nsplit,
+                                    float* scratch, unsigned* counters, float* out, unsigned char* out_q, float* out_s,
+                                    int out_fp8, int use_pdl, cudaStream_t stream) {
+  if (k_scale == nullptr || v_scale == nullptr) return cudaErrorInvalidValue;
+  return flash_decode_launch<true>(q, k_cache, v_cache, k_scale, v_scale, nq, nkv, max_seq, pos, nsplit, scratch, counters,
+                                   out, out_q, out_s, out_fp8, use_pdl, stream);
 }
 
 // ---------------------------------------------------------------------------------------------------------------------

@@ -219,6 +219,32 @@ __device__ __forceinline__ __half2 cvt_e4m3x2(unsigned short v) {
   return *reinterpret_cast<__half2*>(&r);
 }
 
+// four e4m3 bytes of one 32-bit word (lowest byte first) as floats
+__device__ __forceinline__ float4 e4m3x4_to_float4(unsigned w) {
+  const float2 a = __half22float2(cvt_e4m3x2(static_cast<unsigned short>(w & 0xffffu)));
+  const float2 b = __half22float2(cvt_e4m3x2(static_cast<unsigned short>(w >> 16)));
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+
+// One warp stores a KV-cache row of 128 channels (lane holds channels lane + 32 j). KV8: e4m3 bytes plus one fp32 scale
+// per row (amax / 448, the per-(head, position) scheme of the PyTorch cache of this package); otherwise bf16.
+template <bool KV8>
+__device__ __forceinline__ void kv_store_row(void* cache, float* scale, size_t row, const float (&x)[4], int lane) {
+  if constexpr (KV8) {
+    const float amax = warp_max(fmaxf(fmaxf(fabsf(x[0]), fabsf(x[1])), fmaxf(fabsf(x[2]), fabsf(x[3]))));
+    const float sc = fmaxf(amax, 1e-12f) / 448.f;
+    uint8_t* dst = reinterpret_cast<uint8_t*>(cache) + row * 128;
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      dst[lane + 32 * j] = static_cast<uint8_t>(__nv_cvt_float_to_fp8(x[j] / sc, __NV_SATFINITE, __NV_E4M3));
+    if (lane == 0) scale[row] = sc;
+  } else {
+    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(cache) + row * 128;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) dst[lane + 32 * j] = __float2bfloat16(x[j]);
+  }
+}
+
 // 16 e4m3 weights (one uint4) times 16 fp16 activations (two uint4: elements 0-7 and 8-15), fp32 result.
 // Products accumulate in two fp16x2 chains of four; activations are pre-scaled by the caller so that
 // |x| <= 8, which bounds each chain by 4 * 448 * 8 < 65504.

@@ -60,20 +60,23 @@ __global__ void __launch_bounds__(128) norm_quant_rows_kernel(const float* __res
 }
 
 // ---- per-head QK RMSNorm + RoPE + KV append for T tokens: grid (nq + 2 nkv, T), one warp per head -------------------------
+template <bool KV8>        // KV8: e4m3 cache rows with one fp32 scale per (KV head, slot), written here
 __global__ void __launch_bounds__(32) qk_norm_rope_rows_kernel(float* __restrict__ qkv, int nq, int nkv,
                                                                const float* __restrict__ q_gamma,
                                                                const float* __restrict__ k_gamma, float eps,
                                                                const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                                                                const int* __restrict__ positions, const int* __restrict__ slots,
-                                                               __nv_bfloat16* __restrict__ k_cache,
-                                                               __nv_bfloat16* __restrict__ v_cache, int max_seq) {
+                                                               void* __restrict__ k_cache, void* __restrict__ v_cache,
+                                                               float* __restrict__ k_scale, float* __restrict__ v_scale,
+                                                               int max_seq) {
   const int head = blockIdx.x, t = blockIdx.y, lane = threadIdx.x;
   const int pos = min(positions[t], max_seq - 1), slot = min(slots[t], max_seq - 1);
   float* x = qkv + (static_cast<size_t>(t) * (nq + 2 * nkv) + head) * WHD;
   if (head >= nq + nkv) {
-    __nv_bfloat16* dst = v_cache + (static_cast<size_t>(head - nq - nkv) * max_seq + slot) * WHD;
+    float vv[4];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) dst[lane + 32 * j] = __float2bfloat16(x[lane + 32 * j]);
+    for (int j = 0; j < 4; ++j) vv[j] = x[lane + 32 * j];
+    kv_store_row<KV8>(v_cache, v_scale, static_cast<size_t>(head - nq - nkv) * max_seq + slot, vv, lane);
     return;
   }
   const float* gamma = head < nq ? q_gamma : k_gamma;
@@ -96,9 +99,7 @@ __global__ void __launch_bounds__(32) qk_norm_rope_rows_kernel(float* __restrict
 #pragma unroll
     for (int j = 0; j < 4; ++j) x[lane + 32 * j] = o[j];
   } else {
-    __nv_bfloat16* dst = k_cache + (static_cast<size_t>(head - nq) * max_seq + slot) * WHD;
-#pragma unroll
-    for (int j = 0; j < 4; ++j) dst[lane + 32 * j] = __float2bfloat16(o[j]);
+    kv_store_row<KV8>(k_cache, k_scale, static_cast<size_t>(head - nq) * max_seq + slot, o, lane);
   }
 }
 
@@ -252,10 +253,17 @@ __device__ __forceinline__ void wm_split2(float x, float y, unsigned& hi, unsign
   lo = wm_pack_bf16(x - __bfloat162float(hx), y - __bfloat162float(hy));
 }
 
-template <int HPC>          // query heads (= warps) per CTA: 8, or 4 when 8 would leave most SMs without a CTA
+// (x, y, z, w) * s -> four bf16 in two words
+__device__ __forceinline__ uint2 wm_scaled_bf16x4(float4 v, float s) {
+  return make_uint2(wm_pack_bf16(v.x * s, v.y * s), wm_pack_bf16(v.z * s, v.w * s));
+}
+
+template <int HPC, bool KV8>   // HPC: query heads (= warps) per CTA: 8, or 4 when 8 would leave most SMs without a CTA.
+                               // KV8: e4m3 cache rows; a row is de-quantised (bytes * its scale -> bf16) on its way into
+                               // shared memory, so the tensor-core loops below are the same for both cache types
 __global__ void __launch_bounds__(HPC * 32) window_attn_mma_kernel(
-    const float* __restrict__ qkv, int qkv_stride, const __nv_bfloat16* __restrict__ k_cache,
-    const __nv_bfloat16* __restrict__ v_cache, int nq, int nkv, int max_seq, int base, int T,
+    const float* __restrict__ qkv, int qkv_stride, const void* __restrict__ k_cache, const void* __restrict__ v_cache,
+    const float* __restrict__ k_scale, const float* __restrict__ v_scale, int nq, int nkv, int max_seq, int base, int T,
     const uint8_t* __restrict__ mask, float* __restrict__ out, int nsplit, float* __restrict__ part) {
   __shared__ __align__(16) __nv_bfloat16 ks[WM_KB][WM_LD];
   __shared__ __align__(16) __nv_bfloat16 vs[WM_KB][WM_LD];
@@ -288,8 +296,11 @@ __global__ void __launch_bounds__(HPC * 32) window_attn_mma_kernel(
   for (int nd = 0; nd < 16; ++nd) o[nd][0] = o[nd][1] = o[nd][2] = o[nd][3] = 0.f;
   float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
   const int n_keys = mask != nullptr ? base + T : min(base + T, base + t0 + 16);
-  const __nv_bfloat16* kbase = k_cache + static_cast<size_t>(kvh) * max_seq * WHD;
-  const __nv_bfloat16* vbase = v_cache + static_cast<size_t>(kvh) * max_seq * WHD;
+  const size_t row0 = static_cast<size_t>(kvh) * max_seq;
+  const __nv_bfloat16* kbase = reinterpret_cast<const __nv_bfloat16*>(k_cache) + row0 * WHD;     // bf16 rows
+  const __nv_bfloat16* vbase = reinterpret_cast<const __nv_bfloat16*>(v_cache) + row0 * WHD;
+  const uint8_t* kbase8 = reinterpret_cast<const uint8_t*>(k_cache) + row0 * WHD;                // e4m3 rows
+  const uint8_t* vbase8 = reinterpret_cast<const uint8_t*>(v_cache) + row0 * WHD;
   const int blocks_per_split = ((n_keys + WM_KB - 1) / WM_KB + nsplit - 1) / nsplit;
   const int key_end = min(n_keys, (split + 1) * blocks_per_split * WM_KB);
   for (int kb0 = split * blocks_per_split * WM_KB; kb0 < key_end; kb0 += WM_KB) {
@@ -297,8 +308,18 @@ __global__ void __launch_bounds__(HPC * 32) window_attn_mma_kernel(
     for (int i = tid; i < WM_KB * 16; i += HPC * 32) {
       const int r = i >> 4, ch = i & 15;
       const int p = min(kb0 + r, n_keys - 1);          // rows past the end repeat a valid row; they are masked below
-      *reinterpret_cast<uint4*>(&ks[r][ch * 8]) = *reinterpret_cast<const uint4*>(kbase + static_cast<size_t>(p) * WHD + ch * 8);
-      *reinterpret_cast<uint4*>(&vs[r][ch * 8]) = *reinterpret_cast<const uint4*>(vbase + static_cast<size_t>(p) * WHD + ch * 8);
+      if constexpr (KV8) {
+        const uint2 kq = *reinterpret_cast<const uint2*>(kbase8 + static_cast<size_t>(p) * WHD + ch * 8);
+        const uint2 vq = *reinterpret_cast<const uint2*>(vbase8 + static_cast<size_t>(p) * WHD + ch * 8);
+        const float ksc = k_scale[row0 + p], vsc = v_scale[row0 + p];
+        const uint2 k0 = wm_scaled_bf16x4(e4m3x4_to_float4(kq.x), ksc), k1 = wm_scaled_bf16x4(e4m3x4_to_float4(kq.y), ksc);
+        const uint2 v0 = wm_scaled_bf16x4(e4m3x4_to_float4(vq.x), vsc), v1 = wm_scaled_bf16x4(e4m3x4_to_float4(vq.y), vsc);
+        *reinterpret_cast<uint4*>(&ks[r][ch * 8]) = make_uint4(k0.x, k0.y, k1.x, k1.y);
+        *reinterpret_cast<uint4*>(&vs[r][ch * 8]) = make_uint4(v0.x, v0.y, v1.x, v1.y);
+      } else {
+        *reinterpret_cast<uint4*>(&ks[r][ch * 8]) = *reinterpret_cast<const uint4*>(kbase + static_cast<size_t>(p) * WHD + ch * 8);
+        *reinterpret_cast<uint4*>(&vs[r][ch * 8]) = *reinterpret_cast<const uint4*>(vbase + static_cast<size_t>(p) * WHD + ch * 8);
+      }
     }
     __syncthreads();
     if (!active) continue;
@@ -431,9 +452,19 @@ extern "C" int ihb_qk_norm_rope_rows(float* qkv, int nq, int nkv, const float* q
                                      const float* cos_t, const float* sin_t, const int* positions, const int* slots,
                                      void* k_cache, void* v_cache, int max_seq, int T, cudaStream_t stream) {
   if (T < 1) return cudaErrorInvalidValue;
-  qk_norm_rope_rows_kernel<<<dim3(nq + 2 * nkv, T), 32, 0, stream>>>(
-      qkv, nq, nkv, q_gamma, k_gamma, eps, cos_t, sin_t, positions, slots, reinterpret_cast<__nv_bfloat16*>(k_cache),
-      reinterpret_cast<__nv_bfloat16*>(v_cache), max_seq);
+  qk_norm_rope_rows_kernel<false><<<dim3(nq + 2 * nkv, T), 32, 0, stream>>>(
+      qkv, nq, nkv, q_gamma, k_gamma, eps, cos_t, sin_t, positions, slots, k_cache, v_cache, nullptr, nullptr, max_seq);
+  return cudaGetLastError();
+}
+
+// e4m3 cache rows [nkv, max_seq, 128] bytes with scales [nkv, max_seq] fp32
+extern "C" int ihb_qk_norm_rope_rows_kv8(float* qkv, int nq, int nkv, const float* q_gamma, const float* k_gamma, float eps,
+                                         const float* cos_t, const float* sin_t, const int* positions, const int* slots,
+                                         void* k_cache, void* v_cache, float* k_scale, float* v_scale, int max_seq, int T,
+                                         cudaStream_t stream) {
+  if (T < 1 || k_scale == nullptr || v_scale == nullptr) return cudaErrorInvalidValue;
+  qk_norm_rope_rows_kernel<true><<<dim3(nq + 2 * nkv, T), 32, 0, stream>>>(
+      qkv, nq, nkv, q_gamma, k_gamma, eps, cos_t, sin_t, positions, slots, k_cache, v_cache, k_scale, v_scale, max_seq);
   return cudaGetLastError();
 }
 
@@ -463,33 +494,48 @@ extern "C" size_t ihb_window_attention_scratch_floats(int nq, int nkv, int T) {
   return static_cast<size_t>(T) * nq * window_split_bound(nq, nkv, T) * WM_REC;
 }
 
+template <bool KV8>
+static int window_attention_tiles(const float* qkv, int qkv_stride, const void* k_cache, const void* v_cache,
+                                  const float* k_scale, const float* v_scale, int nq, int nkv, int max_seq, int base, int T,
+                                  const unsigned char* mask, float* out, float* scratch, cudaStream_t stream) {
+  if (T < 1 || nq % nkv || base + T > max_seq || qkv_stride % 2) return cudaErrorInvalidValue;
+  const int q_per_kv = nq / nkv;
+  const int ctas8 = ((T + 15) / 16) * nkv * ((q_per_kv + 7) / 8);
+  // few query tiles (verify windows, short prompts): slice the keys so that the whole GPU works on them
+  const int nsplit = scratch != nullptr ? ihb_window_attention_splits(nq, nkv, base, T) : 1;
+  if (ctas8 >= 120 || q_per_kv <= 4) {
+    const dim3 grid(((T + 15) / 16) * nsplit, nkv, (q_per_kv + 7) / 8);
+    window_attn_mma_kernel<8, KV8><<<grid, 256, 0, stream>>>(qkv, qkv_stride, k_cache, v_cache, k_scale, v_scale, nq, nkv,
+                                                              max_seq, base, T, mask, out, nsplit, scratch);
+  } else {
+    const dim3 grid(((T + 15) / 16) * nsplit, nkv, (q_per_kv + 3) / 4);
+    window_attn_mma_kernel<4, KV8><<<grid, 128, 0, stream>>>(qkv, qkv_stride, k_cache, v_cache, k_scale, v_scale, nq, nkv,
+                                                              max_seq, base, T, mask, out, nsplit, scratch);
+  }
+  if (nsplit > 1) window_attn_merge_kernel<<<(T * nq + 3) / 4, 128, 0, stream>>>(scratch, nq, nsplit, T, out);
+  return cudaGetLastError();
+}
+
 extern "C" int ihb_window_attention(const float* qkv, int qkv_stride, const void* k_cache, const void* v_cache, int nq,
                                     int nkv, int max_seq, int base, int T, const unsigned char* mask, float* out, int mode,
                                     float* scratch, cudaStream_t stream) {
+  if (mode != 1)            // tensor-core tiles (the default); mode 1 keeps the per-token CUDA-core kernel
+    return window_attention_tiles<false>(qkv, qkv_stride, k_cache, v_cache, nullptr, nullptr, nq, nkv, max_seq, base, T, mask,
+                                         out, scratch, stream);
   if (T < 1 || nq % nkv || base + T > max_seq) return cudaErrorInvalidValue;
   const int q_per_kv = nq / nkv;
-  if (mode != 1) {          // tensor-core tiles (the default); mode 1 keeps the per-token CUDA-core kernel
-    if (qkv_stride % 2) return cudaErrorInvalidValue;
-    const int ctas8 = ((T + 15) / 16) * nkv * ((q_per_kv + 7) / 8);
-    // few query tiles (verify windows, short prompts): slice the keys so that the whole GPU works on them
-    const int nsplit = scratch != nullptr ? ihb_window_attention_splits(nq, nkv, base, T) : 1;
-    if (ctas8 >= 120 || q_per_kv <= 4) {
-      const dim3 grid(((T + 15) / 16) * nsplit, nkv, (q_per_kv + 7) / 8);
-      window_attn_mma_kernel<8><<<grid, 256, 0, stream>>>(qkv, qkv_stride, reinterpret_cast<const __nv_bfloat16*>(k_cache),
-                                                           reinterpret_cast<const __nv_bfloat16*>(v_cache), nq, nkv, max_seq, base, T,
-                                                           mask, out, nsplit, scratch);
-    } else {
-      const dim3 grid(((T + 15) / 16) * nsplit, nkv, (q_per_kv + 3) / 4);
-      window_attn_mma_kernel<4><<<grid, 128, 0, stream>>>(qkv, qkv_stride, reinterpret_cast<const __nv_bfloat16*>(k_cache),
-                                                           reinterpret_cast<const __nv_bfloat16*>(v_cache), nq, nkv, max_seq, base, T,
-                                                           mask, out, nsplit, scratch);
-    }
-    if (nsplit > 1) window_attn_merge_kernel<<<(T * nq + 3) / 4, 128, 0, stream>>>(scratch, nq, nsplit, T, out);
-    return cudaGetLastError();
-  }
   const dim3 grid(T, nkv, (q_per_kv + 7) / 8);
   window_attn_kernel<8><<<grid, WA_WARPS * 32, 0, stream>>>(qkv, qkv_stride, reinterpret_cast<const __nv_bfloat16*>(k_cache),
                                                            reinterpret_cast<const __nv_bfloat16*>(v_cache), nq, nkv, max_seq,
                                                            base, T, mask, out);
   return cudaGetLastError();
+}
+
+// the tensor-core tiles over an e4m3 cache ([nkv, max_seq, 128] bytes, scales [nkv, max_seq] fp32)
+extern "C" int ihb_window_attention_kv8(const float* qkv, int qkv_stride, const void* k_cache, const void* v_cache,
+                                        const float* k_scale, const float* v_scale, int nq, int nkv, int max_seq, int base,
+                                        int T, const unsigned char* mask, float* out, float* scratch, cudaStream_t stream) {
+  if (k_scale == nullptr || v_scale == nullptr) return cudaErrorInvalidValue;
+  return window_attention_tiles<true>(qkv, qkv_stride, k_cache, v_cache, k_scale, v_scale, nq, nkv, max_seq, base, T, mask, out,
+                                      scratch, stream);
 }

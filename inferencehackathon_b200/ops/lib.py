@@ -150,6 +150,10 @@ def load(build_if_missing: bool = True) -> C.CDLL:
                                         C.c_int, C.c_int, _vp]
     lib.ihb_flash_decode.argtypes = [_vp, _vp, _vp, C.c_int, C.c_int, C.c_int, _vp, C.c_int, _vp, _vp, _vp,
                                      _vp, _vp, C.c_int, C.c_int, _vp]
+    lib.ihb_qk_norm_rope_kv8.argtypes = [_vp, C.c_int, C.c_int, _vp, _vp, C.c_float, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
+                                         C.c_int, C.c_int, _vp]
+    lib.ihb_flash_decode_kv8.argtypes = [_vp, _vp, _vp, _vp, _vp, C.c_int, C.c_int, C.c_int, _vp, C.c_int, _vp, _vp, _vp,
+                                         _vp, _vp, C.c_int, C.c_int, _vp]
     lib.ihb_flash_decode_scratch_floats.argtypes = [C.c_int, C.c_int]
     lib.ihb_flash_decode_scratch_floats.restype = C.c_size_t
     lib.ihb_tc_gemm.argtypes = [C.POINTER(IhbTcArgs), C.c_int, _vp]
@@ -168,6 +172,12 @@ def load(build_if_missing: bool = True) -> C.CDLL:
     lib.ihb_window_attention.argtypes = [_vp, C.c_int, _vp, _vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _vp, _vp, C.c_int, _vp,
                                          _vp]
     lib.ihb_window_attention.restype = C.c_int
+    lib.ihb_qk_norm_rope_rows_kv8.argtypes = [_vp, C.c_int, C.c_int, _vp, _vp, C.c_float, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
+                                              C.c_int, C.c_int, _vp]
+    lib.ihb_qk_norm_rope_rows_kv8.restype = C.c_int
+    lib.ihb_window_attention_kv8.argtypes = [_vp, C.c_int, _vp, _vp, _vp, _vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _vp,
+                                             _vp, _vp, _vp]
+    lib.ihb_window_attention_kv8.restype = C.c_int
     lib.ihb_window_attention_splits.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int]
     lib.ihb_window_attention_splits.restype = C.c_int
     lib.ihb_window_attention_scratch_floats.argtypes = [C.c_int, C.c_int, C.c_int]
@@ -196,7 +206,7 @@ def load(build_if_missing: bool = True) -> C.CDLL:
     lib.ihb_mega_max_grid.argtypes = [C.POINTER(IhbMegaArgs)]
     lib.ihb_mega_max_grid.restype = C.c_int
     for name in ("ihb_gemv", "ihb_moe_gateup", "ihb_moe_down", "ihb_embed_norm", "ihb_qk_norm_rope_kv",
-                 "ihb_flash_decode"):
+                 "ihb_flash_decode", "ihb_qk_norm_rope_kv8", "ihb_flash_decode_kv8"):
         getattr(lib, name).restype = C.c_int
     _lib = lib
     return lib
@@ -290,7 +300,15 @@ def embed_norm(embed: torch.Tensor, token: torch.Tensor, gamma: torch.Tensor, ep
 
 
 def qk_norm_rope_kv(qkv: torch.Tensor, nq: int, nkv: int, q_gamma, k_gamma, eps: float, cos_t, sin_t, pos,
-                    k_cache, v_cache, max_seq: int, use_pdl: bool = False) -> None:
+                    k_cache, v_cache, max_seq: int, use_pdl: bool = False,
+                    k_scale: Optional[torch.Tensor] = None, v_scale: Optional[torch.Tensor] = None) -> None:
+    """``k_scale`` / ``v_scale`` ``[nkv, max_seq]`` fp32: the caches are e4m3 bytes with one scale per row."""
+    if k_scale is not None:
+        check(load().ihb_qk_norm_rope_kv8(qkv.data_ptr(), nq, nkv, q_gamma.data_ptr(), k_gamma.data_ptr(), eps,
+                                          cos_t.data_ptr(), sin_t.data_ptr(), pos.data_ptr(), k_cache.data_ptr(),
+                                          v_cache.data_ptr(), k_scale.data_ptr(), v_scale.data_ptr(), max_seq, int(use_pdl),
+                                          stream_ptr()), "ihb_qk_norm_rope_kv8")
+        return
     check(load().ihb_qk_norm_rope_kv(qkv.data_ptr(), nq, nkv, q_gamma.data_ptr(), k_gamma.data_ptr(), eps,
                                      cos_t.data_ptr(), sin_t.data_ptr(), pos.data_ptr(), k_cache.data_ptr(),
                                      v_cache.data_ptr(), max_seq, int(use_pdl), stream_ptr()),
@@ -303,7 +321,13 @@ def flash_decode_scratch_floats(nq: int, nsplit: int) -> int:
 
 def flash_decode(q, k_cache, v_cache, nq: int, nkv: int, max_seq: int, pos, nsplit: int, scratch, counters, out,
                  use_pdl: bool = False, out_q: Optional[torch.Tensor] = None, out_s: Optional[torch.Tensor] = None,
-                 out_fp8: bool = True) -> None:
+                 out_fp8: bool = True, k_scale: Optional[torch.Tensor] = None, v_scale: Optional[torch.Tensor] = None) -> None:
+    if k_scale is not None:                                     # e4m3 cache rows with a scale per row
+        check(load().ihb_flash_decode_kv8(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), k_scale.data_ptr(),
+                                          v_scale.data_ptr(), nq, nkv, max_seq, pos.data_ptr(), nsplit, scratch.data_ptr(),
+                                          counters.data_ptr(), out.data_ptr(), ptr(out_q), ptr(out_s), int(out_fp8),
+                                          int(use_pdl), stream_ptr()), "ihb_flash_decode_kv8")
+        return
     check(load().ihb_flash_decode(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), nq, nkv, max_seq,
                                   pos.data_ptr(), nsplit, scratch.data_ptr(), counters.data_ptr(), out.data_ptr(),
                                   ptr(out_q), ptr(out_s), int(out_fp8), int(use_pdl), stream_ptr()),
@@ -437,7 +461,14 @@ def norm_quant_rows(x: torch.Tensor, gamma: Optional[torch.Tensor], eps: float, 
 
 
 def qk_norm_rope_rows(qkv: torch.Tensor, nq: int, nkv: int, q_gamma, k_gamma, eps: float, cos_t, sin_t, positions,
-                      slots, k_cache, v_cache, max_seq: int) -> None:
+                      slots, k_cache, v_cache, max_seq: int,
+                      k_scale: Optional[torch.Tensor] = None, v_scale: Optional[torch.Tensor] = None) -> None:
+    if k_scale is not None:                                     # e4m3 cache rows with a scale per row
+        check(load().ihb_qk_norm_rope_rows_kv8(qkv.data_ptr(), nq, nkv, q_gamma.data_ptr(), k_gamma.data_ptr(), eps,
+                                               cos_t.data_ptr(), sin_t.data_ptr(), positions.data_ptr(), slots.data_ptr(),
+                                               k_cache.data_ptr(), v_cache.data_ptr(), k_scale.data_ptr(), v_scale.data_ptr(),
+                                               max_seq, qkv.shape[0], stream_ptr()), "ihb_qk_norm_rope_rows_kv8")
+        return
     check(load().ihb_qk_norm_rope_rows(qkv.data_ptr(), nq, nkv, q_gamma.data_ptr(), k_gamma.data_ptr(), eps,
                                        cos_t.data_ptr(), sin_t.data_ptr(), positions.data_ptr(), slots.data_ptr(),
                                        k_cache.data_ptr(), v_cache.data_ptr(), max_seq, qkv.shape[0], stream_ptr()),
@@ -450,13 +481,21 @@ def window_attention_scratch_floats(nq: int, nkv: int, T: int) -> int:
 
 def window_attention(qkv: torch.Tensor, k_cache, v_cache, nq: int, nkv: int, max_seq: int, base: int,
                      mask: Optional[torch.Tensor], out: torch.Tensor, mode: Optional[int] = None,
-                     scratch: Optional[torch.Tensor] = None) -> None:
+                     scratch: Optional[torch.Tensor] = None,
+                     k_scale: Optional[torch.Tensor] = None, v_scale: Optional[torch.Tensor] = None) -> None:
     """``mode`` 0: tensor-core tiles, 1: per-token CUDA-core kernel; default from ``IHB_WINDOW_ATTN`` (0). ``scratch``
-    (``window_attention_scratch_floats(nq, nkv, T)`` floats) lets short windows slice the keys over many CTAs."""
+    (``window_attention_scratch_floats(nq, nkv, T)`` floats) lets short windows slice the keys over many CTAs.
+    ``k_scale`` / ``v_scale``: the caches are e4m3 bytes with one scale per row (tensor-core tiles only)."""
     if mode is None:
         mode = int(os.environ.get("IHB_WINDOW_ATTN", "0"))
     if scratch is not None and scratch.numel() < window_attention_scratch_floats(nq, nkv, qkv.shape[0]):
         raise ValueError("window attention scratch too small")
+    if k_scale is not None:
+        check(load().ihb_window_attention_kv8(qkv.data_ptr(), qkv.shape[1], k_cache.data_ptr(), v_cache.data_ptr(),
+                                              k_scale.data_ptr(), v_scale.data_ptr(), nq, nkv, max_seq, base, qkv.shape[0],
+                                              ptr(mask), out.data_ptr(), ptr(scratch), stream_ptr()),
+              "ihb_window_attention_kv8")
+        return
     check(load().ihb_window_attention(qkv.data_ptr(), qkv.shape[1], k_cache.data_ptr(), v_cache.data_ptr(), nq, nkv,
                                       max_seq, base, qkv.shape[0], ptr(mask), out.data_ptr(), mode, ptr(scratch),
                                       stream_ptr()),

@@ -46,6 +46,14 @@ class GpuDecoder:
         self.use_tc = bool(env_flag("IHB_TC", 1))          # tensor-core linears (0: SIMT streaming GEMVs)
         # persistent whole-token kernel (tensor parallel only; expert parallel keeps the per-kernel pipeline)
         self.use_mega = bool(env_flag("IHB_MEGA", 1)) and m.n_experts <= 256
+        # e4m3 KV cache with one scale per (layer, KV head, position): half the cache bytes per context token. The append
+        # and attention kernels of the per-kernel pipeline and of the window path read it (the reference:
+        # kernels/k1_attn_prologue.cu:524-604, kernels/k2_flash_decode.cu:71-83); the persistent kernel is built for
+        # bf16 rows, so this mode runs the streaming per-kernel pipeline, whose weights the window path shares.
+        self.kv_fp8 = cfg.quant.kv == "fp8"
+        if self.kv_fp8:
+            self.use_mega = False
+            self.use_tc = False
         self.fp8 = weights.quant.weights == "fp8_block"
         self.use_graph = cfg.use_graph and bool(env_flag("IHB_GRAPH", 1))
         self.comm_ref = comm
@@ -75,8 +83,11 @@ class GpuDecoder:
         self.argmax_partial = torch.zeros(1024, dtype=torch.int64, device=dev)
         self.logits = torch.zeros(max(g.vocab_local, 1), **f32)
         kv_shape = (L, self.nkv, self.max_seq, 128)
-        self.k_cache = torch.zeros(kv_shape, dtype=torch.bfloat16, device=dev)
-        self.v_cache = torch.zeros(kv_shape, dtype=torch.bfloat16, device=dev)
+        kv_t = torch.uint8 if self.kv_fp8 else torch.bfloat16
+        self.k_cache = torch.zeros(kv_shape, dtype=kv_t, device=dev)
+        self.v_cache = torch.zeros(kv_shape, dtype=kv_t, device=dev)
+        self.k_scale = torch.zeros(kv_shape[:3], **f32) if self.kv_fp8 else None
+        self.v_scale = torch.zeros(kv_shape[:3], **f32) if self.kv_fp8 else None
         cos, sin = rope_tables(torch.arange(self.max_seq, device=dev), 128, m.rope_theta)
         self.cos, self.sin = cos.contiguous(), sin.contiguous()
         q_per_kv = self.nq // self.nkv
@@ -367,10 +378,11 @@ class GpuDecoder:
         fd_ctr = self.counters[8:]
         for L, (qkv, oproj, router, moe, lw) in enumerate(self.layer_args):
             K.gemv(qkv, pdl)
+            ks, vs = self.kv_scales(L)
             K.qk_norm_rope_kv(self.qkv, self.nq, self.nkv, lw.q_norm, lw.k_norm, m.rms_eps, self.cos, self.sin,
-                              self.pos, self.k_cache[L], self.v_cache[L], self.max_seq, pdl)
+                              self.pos, self.k_cache[L], self.v_cache[L], self.max_seq, pdl, k_scale=ks, v_scale=vs)
             K.flash_decode(self.qkv, self.k_cache[L], self.v_cache[L], self.nq, self.nkv, self.max_seq, self.pos,
-                           self.nsplit, self.fd_scratch, fd_ctr, self.attn, pdl)
+                           self.nsplit, self.fd_scratch, fd_ctr, self.attn, pdl, k_scale=ks, v_scale=vs)
             K.gemv(oproj, pdl)
             K.gemv(router, pdl)
             K.moe_gateup(moe, pdl)
@@ -616,6 +628,12 @@ class GpuDecoder:
             from .gpu_window import GpuWindow
             self._window = GpuWindow(self)
         return self._window
+
+    def kv_scales(self, L: int):
+        """(k_scale, v_scale) ``[nkv, max_seq]`` of layer ``L`` for an e4m3 cache, (None, None) for a bf16 cache."""
+        if not self.kv_fp8:
+            return None, None
+        return self.k_scale[L], self.v_scale[L]
 
     def has_window(self) -> bool:
         return (self.use_mega or not self.use_tc) and bool(env_flag("IHB_WINDOW", 1))

@@ -286,11 +286,13 @@ class GpuWindow:
             else:
                 xq, xs, _ = self._quant(xn, None, "x") if xn is not None else self._quant(x, lw.in_ln, "x")
             qkv = self._linear(lw.wqkv, xq, xs, T, "qkv")
+            ksc, vsc = d.kv_scales(L)                            # e4m3 cache rows: one scale per row, else None
             K.qk_norm_rope_rows(qkv, nq, nkv, lw.q_norm, lw.k_norm, m.rms_eps, d.cos, d.sin, pos32, slots,
-                                d.k_cache[L], d.v_cache[L], d.max_seq)
+                                d.k_cache[L], d.v_cache[L], d.max_seq, k_scale=ksc, v_scale=vsc)
             attn = self._buf("attn", (T, nq * 128), torch.float32)
             K.window_attention(qkv, d.k_cache[L], d.v_cache[L], nq, nkv, d.max_seq, base, mask_u8, attn,
-                               scratch=self._buf("attn_part", (K.window_attention_scratch_floats(nq, nkv, T),), torch.float32))
+                               scratch=self._buf("attn_part", (K.window_attention_scratch_floats(nq, nkv, T),), torch.float32),
+                               k_scale=ksc, v_scale=vsc)
             aq, asc, _ = self._quant(attn, None, "a")
             o = self._linear(lw.wo, aq, asc, T, "wo")
             if self.attn_scale != 1.0:

@@ -59,6 +59,39 @@ def test_cuda_decode_matches_torch_reference(weights, pipeline, graph, monkeypat
     eng.gpu.check_error()
 
 
+@pytest.mark.parametrize("weights", ["bf16", "fp8_block"])
+def test_e4m3_kv_cache_on_the_cuda_path_matches_the_pytorch_cache(weights):
+    """``kv="fp8"``: the window path and the per-kernel decode pipeline append e4m3 rows with a scale per position and
+    attend over them; the oracle is the PyTorch model with its own e4m3 cache of the same scheme."""
+    dev = "cuda:0"
+    ref = InferenceEngine.build("small", weights=weights, kv="fp8", device=dev, backend="torch", max_seq=256)
+    eng = InferenceEngine.build("small", weights=weights, kv="fp8", device=dev, backend="cuda", max_seq=256)
+    assert eng.gpu.kv_fp8 and not eng.gpu.use_mega and eng.gpu.has_window()
+    assert eng.gpu.k_cache.dtype == torch.uint8 and eng.gpu.k_scale.shape == eng.gpu.k_cache.shape[:3]
+    ref.model.act_mode = eng.gpu.window().act_mode
+    pr = ref.prefill(_prompt(), return_logits=True)
+    pe = eng.prefill(_prompt(), return_logits=True)
+    scale = float(pr.logits.abs().max())
+    assert float((pr.logits[0] - pe.logits[0]).abs().max()) < 0.04 * scale
+    # the rows the prompt pass wrote decode to the oracle's rows (layer 0: same inputs on both sides)
+    n = len(_prompt())
+    k_ref, v_ref = ref.cache.read(0, n)
+    k_eng = eng.gpu.k_cache[0, :, :n].view(torch.float8_e4m3fn).float() * eng.gpu.k_scale[0, :, :n, None]
+    v_eng = eng.gpu.v_cache[0, :, :n].view(torch.float8_e4m3fn).float() * eng.gpu.v_scale[0, :, :n, None]
+    assert float((k_eng - k_ref.float()).abs().max()) < 0.14 * float(k_ref.float().abs().max())
+    assert float((v_eng - v_ref.float()).abs().max()) < 0.14 * float(v_ref.float().abs().max())
+    ref.reset(); eng.reset()
+    ref.model.act_mode = None
+    a = ref.generate(_prompt(), 24)
+    pe = eng.prefill(_prompt())
+    got = [pe.next_token]
+    for t in a.tokens[:-1]:                      # teacher forcing, as in the bf16-cache test
+        got.append(eng.decode_step(t).token_id)
+    agree = sum(int(x == y) for x, y in zip(a.tokens, got))
+    assert agree >= (20 if weights == "bf16" else 15), (a.tokens, got)
+    eng.gpu.check_error()
+
+
 @pytest.mark.parametrize("mega", ["0", "1"])
 def test_graph_replay_is_deterministic(mega, monkeypatch):
     monkeypatch.setenv("IHB_MEGA", mega)

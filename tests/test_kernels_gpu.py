@@ -237,6 +237,61 @@ def test_rope_kv_and_flash_decode(nq, nkv, ctx):
     assert float((deq - out).abs().max()) <= 0.07 * float(out.abs().max()) + 1e-6
 
 
+def _fp8_rows(x):
+    """x [..., 128] fp32 -> (e4m3 bytes as uint8, scale [...] fp32): one scale per row = amax / 448."""
+    s = x.abs().amax(-1, keepdim=True).clamp_min(1e-12) / 448.0
+    q = (x / s).clamp(-448, 448).to(torch.float8_e4m3fn)
+    return q.view(torch.uint8).contiguous(), s[..., 0].contiguous()
+
+
+@pytest.mark.parametrize("nq,nkv", [(8, 1), (64, 4), (8, 2), (4, 4)])
+@pytest.mark.parametrize("ctx", [1, 77, 1024, 3000])
+def test_rope_kv_and_flash_decode_on_an_e4m3_cache(nq, nkv, ctx):
+    """The append writes the new K / V rows as e4m3 bytes with amax / 448 as the row's scale; flash decode over that cache
+    matches fp32 attention over the de-quantised rows."""
+    lib = _K()
+    max_seq = 4096
+    d = _dev()
+    g = torch.Generator(device=d).manual_seed(nq * 1000 + ctx + 7)
+    kc, ks = _fp8_rows(torch.randn(nkv, max_seq, 128, device=d, generator=g) * 2.0)
+    vc, vs = _fp8_rows(torch.randn(nkv, max_seq, 128, device=d, generator=g) * 0.5)
+    qkv = torch.randn((nq + 2 * nkv) * 128, device=d, generator=g)
+    qg = 1.0 + 0.1 * torch.randn(128, device=d, generator=g)
+    kg = 1.0 + 0.1 * torch.randn(128, device=d, generator=g)
+    pos = torch.tensor([ctx - 1], dtype=torch.int32, device=d)
+    cos, sin = rope_tables(torch.arange(max_seq, device=d), 128, 1e6)
+    cos, sin = cos.contiguous(), sin.contiguous()
+    raw = qkv.clone()
+    before_k, before_v = kc.clone(), vc.clone()
+    lib.qk_norm_rope_kv(qkv, nq, nkv, qg, kg, 1e-6, cos, sin, pos, kc, vc, max_seq, False, k_scale=ks, v_scale=vs)
+    nsplit = 5
+    scratch = torch.zeros(lib.flash_decode_scratch_floats(nq, nsplit), device=d)
+    ctrs = torch.zeros(nq, dtype=torch.int32, device=d)
+    out = torch.zeros(nq * 128, device=d)
+    for _ in range(2):
+        lib.flash_decode(qkv, kc, vc, nq, nkv, max_seq, pos, nsplit, scratch, ctrs, out, False, k_scale=ks, v_scale=vs)
+    torch.cuda.synchronize()
+    # the appended rows: only row ctx - 1 changed; its scale is amax / 448 and its bytes decode to the row within e4m3's step
+    k = raw[nq * 128:(nq + nkv) * 128].reshape(1, nkv, 128)
+    v = raw[(nq + nkv) * 128:].reshape(nkv, 128)
+    kr = apply_rope(rmsnorm(k, kg, 1e-6), cos[ctx - 1: ctx], sin[ctx - 1: ctx])[0]
+    keep = torch.ones(max_seq, dtype=torch.bool, device=d)
+    keep[ctx - 1] = False
+    assert torch.equal(kc[:, keep], before_k[:, keep]) and torch.equal(vc[:, keep], before_v[:, keep])
+    for cache, scale, want in ((kc, ks, kr), (vc, vs, v)):
+        amax = want.abs().amax(-1)
+        assert float((scale[:, ctx - 1] - amax / 448.0).abs().max()) <= 1e-5 * float(amax.max() / 448.0) + 1e-12
+        deq = cache[:, ctx - 1].view(torch.float8_e4m3fn).float() * scale[:, ctx - 1, None]
+        assert float(((deq - want).abs() - 0.0625 * want.abs()).max()) <= float(amax.max()) * 2e-3
+    kf = kc[:, :ctx].view(torch.float8_e4m3fn).float() * ks[:, :ctx, None]
+    vf = vc[:, :ctx].view(torch.float8_e4m3fn).float() * vs[:, :ctx, None]
+    qh = qkv[: nq * 128].reshape(nkv, nq // nkv, 128)
+    sc = torch.einsum("kgd,ksd->kgs", qh, kf) / math.sqrt(128)
+    ref = torch.einsum("kgs,ksd->kgd", torch.softmax(sc, -1), vf).reshape(-1)
+    assert float((out - ref).abs().max()) < 2e-3
+    assert int(ctrs.sum().item()) == 0
+
+
 def test_embed_norm_quantised_copy():
     lib = _K()
     d = _dev()

@@ -327,3 +327,66 @@ def test_window_attention_tensor_core_tiles_against_fp32(T, base, nq, nkv, maske
         K.window_attention(qkv, kc, vc, nq, nkv, max_seq, base, mu8, out, mode=mode, scratch=scr)
         torch.cuda.synchronize()
         assert float((out - want).abs().max()) < 2e-3, (mode, scr is not None)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("T,base,nq,nkv,masked", [(8, 1024, 8, 1, False), (16, 300, 64, 4, True), (70, 0, 8, 2, False),
+                                                  (128, 40, 16, 1, False)])
+def test_window_append_and_attention_on_an_e4m3_cache(T, base, nq, nkv, masked):
+    """Window rows appended as e4m3 bytes with a scale per row; the tensor-core tiles over that cache (rows de-quantised
+    to bf16 on their way into shared memory) against fp32 PyTorch on the same de-quantised rows."""
+    import math
+    from inferencehackathon_b200.models.qwen3_moe import apply_rope, rmsnorm, rope_tables
+    from inferencehackathon_b200.ops import lib as K
+    K.load()
+    d = torch.device("cuda", 0)
+    g = torch.Generator(device=d).manual_seed(T + base + 11)
+    max_seq = base + T + 5
+
+    def fp8_rows(x):
+        s = x.abs().amax(-1, keepdim=True).clamp_min(1e-12) / 448.0
+        return (x / s).clamp(-448, 448).to(torch.float8_e4m3fn).view(torch.uint8).contiguous(), s[..., 0].contiguous()
+
+    kc, ks = fp8_rows(torch.randn(nkv, max_seq, 128, device=d, generator=g) * 2.0)
+    vc, vs = fp8_rows(torch.randn(nkv, max_seq, 128, device=d, generator=g) * 0.5)
+    qkv = torch.randn(T, (nq + 2 * nkv) * 128, device=d, generator=g)
+    raw = qkv.clone()
+    qg = 1.0 + 0.1 * torch.randn(128, device=d, generator=g)
+    kg = 1.0 + 0.1 * torch.randn(128, device=d, generator=g)
+    cos, sin = rope_tables(torch.arange(max_seq, device=d), 128, 1e6)
+    cos, sin = cos.contiguous(), sin.contiguous()
+    pos = torch.arange(base, base + T, dtype=torch.int32, device=d)
+    K.qk_norm_rope_rows(qkv, nq, nkv, qg, kg, 1e-6, cos, sin, pos, pos, kc, vc, max_seq, k_scale=ks, v_scale=vs)
+    torch.cuda.synchronize()
+    # appended rows against the fp32 formula, within e4m3's step
+    k_raw = raw[:, nq * 128:(nq + nkv) * 128].reshape(T, nkv, 128)
+    v_raw = raw[:, (nq + nkv) * 128:].reshape(T, nkv, 128)
+    kr = apply_rope(rmsnorm(k_raw, kg, 1e-6), cos[base: base + T], sin[base: base + T])
+    for cache, scale, want in ((kc, ks, kr), (vc, vs, v_raw)):
+        want = want.permute(1, 0, 2)                                                   # [nkv, T, 128]
+        amax = want.abs().amax(-1)
+        assert float((scale[:, base: base + T] - amax / 448.0).abs().max()) <= 1e-5 * float(amax.max() / 448.0) + 1e-12
+        deq = cache[:, base: base + T].view(torch.float8_e4m3fn).float() * scale[:, base: base + T, None]
+        assert float(((deq - want).abs() - 0.0625 * want.abs()).max()) <= float(amax.max()) * 2e-3
+    mask = None
+    vis = torch.ones(T, base + T, dtype=torch.bool, device=d)
+    if masked:
+        mask = torch.rand(T, T, device=d, generator=g) < 0.4
+        mask |= torch.eye(T, dtype=torch.bool, device=d)
+        vis[:, base:] = mask
+    else:
+        vis[:, base:] = torch.tril(torch.ones(T, T, dtype=torch.bool, device=d))
+    n = base + T
+    kf = (kc[:, :n].view(torch.float8_e4m3fn).float() * ks[:, :n, None]).to(torch.bfloat16).float()   # as the kernel stages them
+    vf = (vc[:, :n].view(torch.float8_e4m3fn).float() * vs[:, :n, None]).to(torch.bfloat16).float()
+    q = qkv[:, : nq * 128].reshape(T, nkv, nq // nkv, 128)
+    s = torch.einsum("tkgd,ksd->tkgs", q, kf) / math.sqrt(128)
+    s = s.masked_fill(~vis[:, None, None, :], float("-inf"))
+    want = torch.einsum("tkgs,ksd->tkgd", torch.softmax(s, -1), vf).reshape(T, nq * 128)
+    mu8 = mask.to(torch.uint8).contiguous() if mask is not None else None
+    scratch = torch.full((K.window_attention_scratch_floats(nq, nkv, T),), float("nan"), device=d)
+    for scr in (None, scratch):                                       # with scratch: keys sliced over CTAs + merge
+        out = torch.full((T, nq * 128), float("nan"), device=d)
+        K.window_attention(qkv, kc, vc, nq, nkv, max_seq, base, mu8, out, mode=0, scratch=scr, k_scale=ks, v_scale=vs)
+        torch.cuda.synchronize()
+        assert float((out - want).abs().max()) < 2e-3, scr is not None
