@@ -108,20 +108,33 @@ def sweep_experts(tp: int, fp8: bool, iters: int, dev: torch.device) -> Dict:
             "rule": rule, "best": best, "rule_vs_best": round(rule["us"] / best["us"], 3), "all": rows}
 
 
-def sweep_flash_decode(tp: int, iters: int, dev: torch.device, contexts=(4096, 32768)) -> Dict:
+def _e4m3_rows(x: torch.Tensor):
+    """x [..., 128] -> (e4m3 bytes as uint8, one fp32 scale per row = amax / 448): the cache layout of ``kv="fp8"``."""
+    s = x.abs().amax(-1, keepdim=True).clamp_min(1e-12) / 448.0
+    return (x / s).clamp(-448, 448).to(torch.float8_e4m3fn).view(torch.uint8).contiguous(), s[..., 0].contiguous()
+
+
+def sweep_flash_decode(tp: int, iters: int, dev: torch.device, contexts=(4096, 32768), kv8: bool = False) -> Dict:
     """Split count of the split-KV flash-decode kernel at the head counts of one rank (64 / tp query heads, at least
-    one KV head)."""
+    one KV head); ``kv8``: over an e4m3 cache with a scale per row instead of bf16 rows."""
     from . import lib
     nq, nkv = 64 // tp, max(1, 4 // tp)
     out: Dict = {}
     g = torch.Generator(device=dev).manual_seed(2)
     sms = torch.cuda.get_device_properties(dev).multi_processor_count
     for ctx in contexts:
-        bytes_kv = 2 * nkv * ctx * 128 * 2
+        bytes_kv = 2 * nkv * ctx * (128 + 4) if kv8 else 2 * nkv * ctx * 128 * 2
         ncopies = max(2, (192 << 20) // bytes_kv + 1)
         ncopies = min(ncopies, 64)
-        kc = [torch.randn(nkv, ctx, 128, device=dev, generator=g).to(torch.bfloat16) for _ in range(ncopies)]
-        vc = [torch.randn(nkv, ctx, 128, device=dev, generator=g).to(torch.bfloat16) for _ in range(ncopies)]
+        ksc = vsc = [None] * ncopies
+        if kv8:
+            kq = [_e4m3_rows(torch.randn(nkv, ctx, 128, device=dev, generator=g)) for _ in range(ncopies)]
+            vq = [_e4m3_rows(torch.randn(nkv, ctx, 128, device=dev, generator=g)) for _ in range(ncopies)]
+            kc, ksc = [a for a, _ in kq], [b for _, b in kq]
+            vc, vsc = [a for a, _ in vq], [b for _, b in vq]
+        else:
+            kc = [torch.randn(nkv, ctx, 128, device=dev, generator=g).to(torch.bfloat16) for _ in range(ncopies)]
+            vc = [torch.randn(nkv, ctx, 128, device=dev, generator=g).to(torch.bfloat16) for _ in range(ncopies)]
         q = torch.randn(nq * 128, device=dev, generator=g)
         pos = torch.tensor([ctx - 1], dtype=torch.int32, device=dev)
         o = torch.zeros(nq * 128, device=dev)
@@ -133,7 +146,9 @@ def sweep_flash_decode(tp: int, iters: int, dev: torch.device, contexts=(4096, 3
             ctrs = torch.zeros(nq, dtype=torch.int32, device=dev)
 
             def fn(i):
-                lib.flash_decode(q, kc[i % ncopies], vc[i % ncopies], nq, nkv, ctx, pos, nsplit, scratch, ctrs, o, False)
+                j = i % ncopies
+                lib.flash_decode(q, kc[j], vc[j], nq, nkv, ctx, pos, nsplit, scratch, ctrs, o, False,
+                                 k_scale=ksc[j], v_scale=vsc[j])
             try:
                 us = _time_us(fn, iters)
             except RuntimeError:
@@ -231,6 +246,7 @@ def main(argv=None) -> int:
     ap.add_argument("--out", default="")
     ap.add_argument("--skip-experts", action="store_true")
     ap.add_argument("--gemm", action="store_true", help="only the dense tcgen05 GEMM table of the prompt path")
+    ap.add_argument("--flash-kv", action="store_true", help="only flash decode, over bf16 and over e4m3 cache rows")
     a = ap.parse_args(argv)
     from . import lib
     lib.load()
@@ -240,6 +256,15 @@ def main(argv=None) -> int:
         res["window_gemm"] = sweep_window_gemm(a.iters, dev)
         for r in res["window_gemm"]:
             print("gemm", r)
+        if a.out:
+            with open(a.out, "w") as f:
+                json.dump(res, f, indent=1)
+        return 0
+    if a.flash_kv:
+        for name, kv8 in (("bf16", False), ("e4m3", True)):
+            res["flash_decode_" + name] = sweep_flash_decode(a.tp, a.iters, dev, kv8=kv8)
+            for ctx, r in res["flash_decode_" + name].items():
+                print(f"flash-decode {name} cache, ctx {ctx}, nq {r['nq']}, nkv {r['nkv']}: best {r['best']}")
         if a.out:
             with open(a.out, "w") as f:
                 json.dump(res, f, indent=1)
