@@ -47,9 +47,24 @@ def _synthetic_telemetry(token_index: int, t_ms: float, topo: dict) -> dict:
 
 
 class VLLMBackend(Backend):
-    def __init__(self, url: Optional[str] = None, scrape_spec: bool = True):
+    def __init__(self, url: Optional[str] = None, scrape_spec: bool = True, routing_sock: Optional[str] = None):
         self.url = url or VLLM_URL
         self.scrape_spec = scrape_spec
+        # a vLLM started through serve/vllm_tools.py streams its routers' choices over this socket; without it the
+        # telemetry cycles through the placement
+        sock = routing_sock if routing_sock is not None else os.environ.get("VLLM_ROUTING_SOCK", "")
+        self.feed = None
+        if sock:
+            from .vllm_tools import RoutingFeedReader
+            self.feed = RoutingFeedReader(sock)
+
+    def _telemetry(self, n: int, t_ms: float, topo: dict) -> dict:
+        if self.feed is not None:
+            from .vllm_tools import telemetry_from_feed
+            tel = telemetry_from_feed(self.feed, n, t_ms, topo, all_layers=bool(os.environ.get("X_TELEMETRY_ALL_LAYERS")))
+            if tel is not None:
+                return tel
+        return _synthetic_telemetry(n, t_ms, topo)
 
     def stream(self, req: ChatRequest, topo: dict) -> Iterator[dict]:
         body = json.dumps({"model": os.environ.get("VLLM_MODEL", "qwen3-235b-fp8"),
@@ -83,7 +98,7 @@ class VLLMBackend(Backend):
                     if chunk.get("choices", [{}])[0].get("delta", {}).get("content"):
                         now = time.time()
                         t_first = t_first or now
-                        chunk["x_telemetry"] = _synthetic_telemetry(n, 1e3 * (now - t0), topo)
+                        chunk["x_telemetry"] = self._telemetry(n, 1e3 * (now - t0), topo)
                         n += 1
                     yield chunk
                 if done:
