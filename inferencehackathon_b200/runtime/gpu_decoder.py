@@ -54,6 +54,9 @@ class GpuDecoder:
         if self.kv_fp8:
             self.use_mega = False
             self.use_tc = False
+        if not self.use_mega and cfg.parallel.ep > 1 and cfg.parallel.world > 1:
+            raise ValueError("expert parallelism on GPUs runs inside the persistent kernel; the per-kernel pipelines "
+                             "(IHB_MEGA=0, kv='fp8') are tensor-parallel only")
         self.fp8 = weights.quant.weights == "fp8_block"
         self.use_graph = cfg.use_graph and bool(env_flag("IHB_GRAPH", 1))
         self.comm_ref = comm
