@@ -373,3 +373,102 @@ def test_counted_slots_with_too_few_parities_lose_or_mix_contributions():
 def test_counted_slots_without_clearing_cannot_be_reused():
     bad, agents = _run_counted(2, 2, layers=6, seed=0, n_parities=4, clear_after_barrier=False)
     assert bad > 0 or any(a["err"] for a in agents)
+
+
+# ---- counted accumulation as a stand-alone launch (ar_counted_kernel) -----------------------------------------------------------
+def _run_standalone_counted(n_ranks, n_rows, row_counts, seed, n_parities=4, dead_rank=None, dead_after=0):
+    """Model of the small-message all-reduce kernel that the window path launches per collective. An agent is one
+    (rank, row): in every call that covers its row it adds its partial into the row's word on every GPU (the adds land
+    one at a time, at any later step, in any order), polls ITS OWN GPU's word until it has counted n_ranks
+    contributions, checks the sum, clears the word (it is the word's only reader) and bumps the row's call count, which
+    selects the parity of the row's next call. ``row_counts[k]`` rows take part in call k (the same sequence on every
+    rank). Rows progress independently here; on the GPU the calls of a rank are ordered by the stream, which only removes
+    interleavings. Returns (violations, agents)."""
+    rng = random.Random(seed)
+    mem = [[[[0, 0] for _ in range(n_rows)] for _ in range(n_parities)] for _ in range(n_ranks)]   # [gpu][parity][row]
+    inflight = []
+    agents = []
+    for r in range(n_ranks):
+        for t in range(n_rows):
+            mine = [k for k, T in enumerate(row_counts) if T > t]          # the calls this row takes part in
+            agents.append(dict(r=r, t=t, calls=mine, done=0, pc="push", spins=0, err=None))
+    live = [i for i, a in enumerate(agents) if a["calls"]]
+    bad = 0
+
+    def value(k, rank, row):
+        return (k + 1) * 1000 + rank * 10 + row
+
+    while live or inflight:
+        if inflight and (not live or rng.random() < 0.5):
+            g, p, t, v = inflight.pop(rng.randrange(len(inflight)))
+            mem[g][p][t][0] += 1
+            mem[g][p][t][1] += v
+            continue
+        i = rng.choice(live)
+        a = agents[i]
+        r, t = a["r"], a["t"]
+        k = a["calls"][a["done"]]                                           # global index of the row's current call
+        par = a["done"] % n_parities                                        # the row's own call count picks the parity
+        if a["pc"] == "push":
+            if dead_rank == r and a["done"] >= dead_after:
+                live.remove(i)                                              # this rank makes no further calls
+                continue
+            for g in range(n_ranks):
+                inflight.append((g, par, t, value(k, r, t)))
+            a["pc"] = "read"
+        else:
+            cnt, tot = mem[r][par][t]
+            if cnt > n_ranks:
+                bad += 1
+            if cnt >= n_ranks:
+                if tot != sum(value(k, q, t) for q in range(n_ranks)):
+                    bad += 1
+                mem[r][par][t] = [0, 0]
+                a["done"] += 1
+                a["spins"] = 0
+                a["pc"] = "push"
+                if a["done"] == len(a["calls"]):
+                    live.remove(i)
+            else:
+                a["spins"] += 1
+                if a["spins"] > 4000:                                       # bounded wait: an error status, not a hang
+                    a["err"] = "peer time-out"
+                    live.remove(i)
+    return bad, agents
+
+
+@pytest.mark.parametrize("n_ranks", [1, 2, 4, 8])
+def test_standalone_counted_all_reduce_with_changing_row_counts(n_ranks):
+    """Every call is complete and exact although the number of rows changes from call to call, the adds of a fast rank
+    land while a slow rank still reads the previous call, and nothing but the words themselves synchronises the ranks."""
+    for seed in range(6):
+        rng = random.Random(100 + seed)
+        row_counts = [rng.choice([1, 2, 5]) for _ in range(12)]
+        bad, agents = _run_standalone_counted(n_ranks, 5, row_counts, seed)
+        assert bad == 0
+        assert all(a["err"] is None and a["done"] == len(a["calls"]) for a in agents)
+
+
+def test_standalone_counted_all_reduce_needs_more_than_one_parity():
+    """With a single slot per row a fast rank's add of call n + 1 lands in the word a slow rank has not read yet: the
+    model sees a count above the number of ranks, a mixed sum, or a contribution wiped by the late clear (a wait that
+    runs out). Two parities are already safe for this protocol (a rank adds call n + 2 only after every rank has
+    contributed n + 1, i.e. has read and cleared n); the kernel keeps four."""
+    broken = 0
+    for seed in range(30):
+        bad, agents = _run_standalone_counted(2, 2, [2] * 8, seed, n_parities=1)
+        broken += int(bad > 0 or any(a["err"] for a in agents))
+    assert broken > 0
+    for seed in range(10):
+        bad, agents = _run_standalone_counted(4, 2, [2] * 8, seed, n_parities=2)
+        assert bad == 0 and all(a["err"] is None for a in agents)
+
+
+def test_standalone_counted_all_reduce_with_a_rank_that_stops_calling_ends_with_a_status():
+    bad, agents = _run_standalone_counted(4, 2, [2] * 6, seed=1, dead_rank=2, dead_after=3)
+    assert bad == 0
+    for a in agents:
+        if a["r"] == 2:
+            assert a["done"] == 3 and a["err"] is None
+        else:
+            assert a["err"] == "peer time-out" and a["done"] == 3          # all calls before the stop completed everywhere
