@@ -43,3 +43,4 @@ def test_bench_flags_parse():
     finally:
         sys.argv = old
     assert d.gpus == 1 and d.impl == "ours" and d.model == "qwen3-235b-a22b" and d.plan == "tp"
+    assert d.kv == "bf16" and d.steps_per_launch == 1                     # the headline keeps bf16 KV rows, one token per launch
