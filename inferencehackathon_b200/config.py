@@ -108,6 +108,11 @@ class ParallelConfig:
     ep: int = 1
     rank: int = 0
     world: int = 1
+    # Ranks that share one KV head (tp above the number of KV heads) and split its cache rows between them: rank i of
+    # such a group keeps the rows r with r % kv_share == i and the group merges its partial attention results. 1: every
+    # rank keeps all rows of its KV head (the layout of the reference, kernels/decode_step_tp8.cu:153-160, and of the CUDA
+    # pipelines here). PyTorch path only.
+    kv_share: int = 1
 
     @property
     def plan(self) -> str:
@@ -145,6 +150,8 @@ class ParallelConfig:
             raise ValueError("tp must divide the expert intermediate size")
         if self.tp > cfg.n_kv_heads and self.tp % cfg.n_kv_heads:
             raise ValueError("tp above n_kv_heads must be a multiple of it (KV heads replicate)")
+        if self.kv_share > 1 and (self.tp <= cfg.n_kv_heads or self.kv_share != self.tp // cfg.n_kv_heads):
+            raise ValueError("kv_share must equal tp / n_kv_heads (the ranks that hold the same KV head)")
 
 
 @dataclass(frozen=True)

@@ -107,6 +107,19 @@ class TorchKV:
             buf[L, :, start:start + T] = (x.float() / s).clamp(-448, 448).to(torch.float8_e4m3fn)
             sc[L, :, start:start + T] = s
 
+    def write_rows(self, L: int, rows: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> None:
+        """k, v ``[nkv, R, hd]`` -> the (not necessarily contiguous) rows ``rows[R]`` of layer ``L``."""
+        if rows.numel() == 0:
+            return
+        if not self.fp8:
+            self.k[L][:, rows] = k.to(self.k.dtype)
+            self.v[L][:, rows] = v.to(self.v.dtype)
+            return
+        for buf, sc, x in ((self.k, self.k_scale, k), (self.v, self.v_scale, v)):
+            s = x.float().abs().amax(dim=-1, keepdim=True).clamp_min(1e-12) / 448.0
+            buf[L][:, rows] = (x.float() / s).clamp(-448, 448).to(torch.float8_e4m3fn)
+            sc[L][:, rows] = s
+
     def read(self, L: int, n: int):
         """Rows ``0 .. n`` of layer ``L`` as (k, v) in a float type."""
         if not self.fp8:
@@ -134,6 +147,36 @@ def _attention(q: torch.Tensor, kc: torch.Tensor, vc: torch.Tensor, positions: t
     p = torch.softmax(scores, dim=-1)
     out = torch.einsum("kgts,ksd->kgtd", p, vc.float())
     return out.permute(2, 0, 1, 3).reshape(T, nq * hd)
+
+
+def _attention_partial(q: torch.Tensor, kc: torch.Tensor, vc: torch.Tensor, visible: torch.Tensor):
+    """Attention of ``q[T, nh, hd]`` over SOME rows ``kc / vc [R, hd]`` of one KV head (``visible[T, R]``): the
+    un-normalised output ``acc[T, nh, hd]`` with its running maximum ``m[T, nh]`` and denominator ``l[T, nh]``, i.e. the
+    record a split-KV kernel writes per split. Rows a query does not see contribute nothing; a query that sees no row
+    returns ``m = -inf, l = 0, acc = 0``."""
+    T, nh, hd = q.shape
+    if kc.shape[0] == 0:
+        z = q.new_zeros(T, nh, dtype=torch.float32)
+        return q.new_zeros(T, nh, hd, dtype=torch.float32), z - float("inf"), z
+    scores = torch.einsum("thd,sd->ths", q.float(), kc.float()) * (hd ** -0.5)
+    scores = scores.masked_fill(~visible[:, None, :], float("-inf"))
+    m = scores.amax(-1)
+    p = torch.exp(scores - torch.where(torch.isinf(m), torch.zeros_like(m), m)[..., None])
+    p = torch.where(visible[:, None, :], p, torch.zeros_like(p))
+    return torch.einsum("ths,sd->thd", p, vc.float()), m, p.sum(-1)
+
+
+def _merge_partials(parts) -> torch.Tensor:
+    """[(acc, m, l), ...] of disjoint row sets -> normalised attention output ``[T, nh, hd]`` (the merge a split-KV
+    kernel does across its splits, here across the ranks that share a KV head)."""
+    M = torch.stack([m for _, m, _ in parts]).amax(0)
+    num = torch.zeros_like(parts[0][0])
+    den = torch.zeros_like(parts[0][2])
+    for acc, m, l in parts:
+        f = torch.where(torch.isinf(m), torch.zeros_like(m), torch.exp(m - M))
+        num = num + acc * f[..., None]
+        den = den + l * f
+    return num / den[..., None]
 
 
 def _experts_local(h: torch.Tensor, lw: LayerWeights, idx: torch.Tensor, w: torch.Tensor, expert0: int,
@@ -178,7 +221,11 @@ class Qwen3MoE:
 
     def new_cache(self, max_seq: int, dtype=torch.float32, device=None) -> TorchKV:
         device = device if device is not None else self.w.embed.device
-        return TorchKV(self.cfg.n_layers, self.geom.nkv_local, max_seq, self.cfg.head_dim, dtype, device)
+        share = self.par.kv_share
+        rows = max_seq if share <= 1 else (max_seq + share - 1) // share      # a rank keeps every share-th row of its KV head
+        kv = TorchKV(self.cfg.n_layers, self.geom.nkv_local, rows, self.cfg.head_dim, dtype, device)
+        kv.max_seq = max_seq                                                 # positions it covers (``len`` counts positions)
+        return kv
 
     # ---------------------------------------------------------------------------------------------------------
     def _moe(self, L: int, h: torch.Tensor, lw: LayerWeights, record: bool) -> torch.Tensor:
@@ -258,9 +305,12 @@ class Qwen3MoE:
             v = qkv[:, (nq + nkv) * hd:].reshape(T, nkv, hd)
             q = apply_rope(rmsnorm(q, lw.q_norm, cfg.rms_eps), cos, sin)
             k = apply_rope(rmsnorm(k, lw.k_norm, cfg.rms_eps), cos, sin)
-            cache.write(L, start, k.permute(1, 0, 2), v.permute(1, 0, 2))
-            kc, vc = cache.read(L, start + T)
-            attn = _attention(q, kc, vc, positions, tree_mask)
+            if self.par.kv_share > 1:
+                attn = self._attention_kv_split(L, q, k, v, cache, start, positions, tree_mask)
+            else:
+                cache.write(L, start, k.permute(1, 0, 2), v.permute(1, 0, 2))
+                kc, vc = cache.read(L, start + T)
+                attn = _attention(q, kc, vc, positions, tree_mask)
             o = fake_quant_act(attn, self.act_mode) @ lw.wo.dequant().t()
             x = x + self.comm.all_reduce_tp(o)
             h2 = rmsnorm(x, lw.post_ln, cfg.rms_eps)
@@ -270,6 +320,36 @@ class Qwen3MoE:
         if commit:
             cache.len = start + T
         return rmsnorm(x, self.w.final_norm, cfg.rms_eps)
+
+    def _attention_kv_split(self, L: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cache: TorchKV, start: int,
+                            positions: torch.Tensor, tree_mask: Optional[torch.Tensor]) -> torch.Tensor:
+        """Context-parallel attention for the ranks that share one KV head (tp above the number of KV heads; the
+        reference replicates the head's whole cache on them, kernels/decode_step_tp8.cu:153-160). Rank i of the group
+        keeps cache rows r with r % kv_share == i, stored compactly at r // kv_share: 1 / kv_share of the head's KV bytes
+        per rank. Per layer: the group gathers its query heads (every rank needs all of them for its rows), each rank
+        attends over its own rows and produces un-normalised partials (acc, m, l), the group gathers the partials and
+        every rank merges those of its own heads: the split-KV merge, across GPUs."""
+        share = self.par.kv_share
+        me = self.par.tp_rank % share
+        T, nq, hd = q.shape
+        slots = torch.arange(start, start + T, device=q.device)
+        own_new = (slots % share) == me
+        cache.write_rows(L, slots[own_new] // share, k[own_new].permute(1, 0, 2), v[own_new].permute(1, 0, 2))
+        n_rows = (start + T - me + share - 1) // share if start + T > me else 0    # rows r < start + T with r % share == me
+        kc, vc = cache.read(L, n_rows)
+        own_slots = torch.arange(n_rows, device=q.device) * share + me
+        visible = own_slots[None, :] <= positions[:, None]                         # as in _attention, on this rank's rows
+        if tree_mask is not None:
+            in_window = own_slots >= start
+            visible = visible.clone()
+            visible[:, in_window] = tree_mask[:, own_slots[in_window] - start]
+        q_all = torch.cat(self.comm.all_gather_kv(q.float()), dim=1)               # [T, share * nq, hd], heads in rank order
+        acc, m, l = _attention_partial(q_all, kc[0], vc[0], visible)
+        packed = torch.cat([acc, m[..., None], l[..., None]], dim=-1)              # one record per (token, head)
+        recs = self.comm.all_gather_kv(packed)
+        mine = slice(me * nq, (me + 1) * nq)
+        out = _merge_partials([(r[:, mine, :hd], r[:, mine, hd], r[:, mine, hd + 1]) for r in recs])
+        return out.reshape(T, nq * hd)
 
     def logits(self, hidden: torch.Tensor) -> torch.Tensor:
         """Full-vocabulary logits ``[T, V]`` (gathered from the vocabulary shards)."""

@@ -25,6 +25,7 @@ class Collectives:
         self.par = par
         self.world_group = None
         self.tp_group = None
+        self.kv_group = None
         self.n_collectives = 0
         if par.world > 1:
             if not dist.is_initialized():
@@ -39,6 +40,13 @@ class Collectives:
                     grp = dist.new_group(ranks)
                     if par.rank in ranks:
                         self.tp_group = grp
+            if par.kv_share > 1:
+                # consecutive ranks of a tensor-parallel group hold the same KV head: one subgroup per head
+                for g0 in range(0, par.world, par.kv_share):
+                    ranks = list(range(g0, g0 + par.kv_share))
+                    grp = dist.new_group(ranks)
+                    if par.rank in ranks:
+                        self.kv_group = grp
 
     # tensor parallel -------------------------------------------------------------------------------------
     def all_reduce_tp(self, x: torch.Tensor) -> torch.Tensor:
@@ -46,6 +54,15 @@ class Collectives:
             self.n_collectives += 1
             dist.all_reduce(x, op=dist.ReduceOp.SUM, group=self.tp_group)
         return x
+
+    def all_gather_kv(self, x: torch.Tensor) -> List[torch.Tensor]:
+        """``x`` of every rank that shares this rank's KV head, in rank order (``kv_share`` tensors)."""
+        if self.par.kv_share <= 1 or self.par.world == 1:
+            return [x]
+        self.n_collectives += 1
+        out = [torch.empty_like(x) for _ in range(self.par.kv_share)]
+        dist.all_gather(out, x.contiguous(), group=self.kv_group)
+        return out
 
     def all_reduce_world(self, x: torch.Tensor) -> torch.Tensor:
         if self.par.world > 1:

@@ -127,15 +127,18 @@ class InferenceEngine:
               weights: str = "fp32", kv: Optional[str] = None, device="cpu", backend: str = "auto",
               max_seq: int = 2048, seed: int = 0, n_layers: Optional[int] = None, distinct_layers: int = 0,
               state_dict=None, checkpoint: Optional[str] = None, comm: str = "auto",
-              use_graph: bool = True, same_weights_in_every_layout: bool = False) -> "InferenceEngine":
+              use_graph: bool = True, same_weights_in_every_layout: bool = False,
+              kv_seq_split: bool = False) -> "InferenceEngine":
         """Public constructor. Weight source, in order: ``state_dict`` (HF names), ``checkpoint`` (safetensors
         directory), else random init (host-side and layout-independent for small models, streamed on the
         device otherwise: per-rank random streams, fast, but a sharded engine then holds other numbers than the
         one-GPU engine; ``same_weights_in_every_layout`` generates every full tensor on the device from a seed derived
-        from its name and slices it, for comparisons across layouts)."""
+        from its name and slices it, for comparisons across layouts). ``kv_seq_split`` (PyTorch path): the ranks that
+        share a KV head split its cache rows between them instead of replicating them."""
         mcfg = get_model_config(model, n_layers)
         world = world if world is not None else max(tp, ep)
-        par = ParallelConfig(tp=tp, ep=ep, rank=rank, world=world)
+        share = tp // mcfg.n_kv_heads if (kv_seq_split and tp > mcfg.n_kv_heads) else 1
+        par = ParallelConfig(tp=tp, ep=ep, rank=rank, world=world, kv_share=share)
         par.validate(mcfg)
         q = QuantConfig(weights=weights, kv=kv or ("fp32" if weights == "fp32" else "bf16"))
         ecfg = EngineConfig(model=mcfg, parallel=par, quant=q, max_seq=max_seq, seed=seed, backend=backend,

@@ -54,6 +54,9 @@ class GpuDecoder:
         if self.kv_fp8:
             self.use_mega = False
             self.use_tc = False
+        if cfg.parallel.kv_share > 1:
+            raise ValueError("the CUDA pipelines keep all rows of a shared KV head on every rank; kv_seq_split is a "
+                             "feature of the PyTorch path")
         if not self.use_mega and cfg.parallel.ep > 1 and cfg.parallel.world > 1:
             raise ValueError("expert parallelism on GPUs runs inside the persistent kernel; the per-kernel pipelines "
                              "(IHB_MEGA=0, kv='fp8') are tensor-parallel only")

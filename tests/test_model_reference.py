@@ -71,3 +71,35 @@ def test_fp8_kv_cache_on_the_pytorch_path_tracks_the_fp32_cache():
     a = ref.generate(prompt, 8).tokens
     b = q8.generate(prompt, 8).tokens
     assert sum(int(x == y) for x, y in zip(a, b)) >= 6
+
+
+def test_partial_attention_records_merge_to_full_attention():
+    """Attention over disjoint row sets, returned as (acc, m, l) records and merged, equals attention over all rows:
+    causal and with a tree mask, including a query that sees no row of one set."""
+    from inferencehackathon_b200.models.qwen3_moe import _attention, _attention_partial, _merge_partials
+    g = torch.Generator().manual_seed(5)
+    T, nh, hd, start = 5, 4, 32, 9
+    S = start + T
+    q = torch.randn(T, nh, hd, generator=g)
+    kc, vc = torch.randn(1, S, hd, generator=g), torch.randn(1, S, hd, generator=g)
+    positions = torch.arange(start, S)
+    for mask in (None, torch.tril(torch.ones(T, T, dtype=torch.bool)) & (torch.rand(T, T, generator=g) < 0.7)
+                 | torch.eye(T, dtype=torch.bool)):
+        want = _attention(q, kc, vc, positions, mask).reshape(T, nh, hd)
+        visible = torch.arange(S)[None, :] <= positions[:, None]
+        if mask is not None:
+            visible = visible.clone()
+            visible[:, start:] = mask
+        for share in (2, 3):
+            parts = []
+            for me in range(share):
+                rows = torch.arange(me, S, share)
+                parts.append(_attention_partial(q, kc[0, rows], vc[0, rows], visible[:, rows]))
+            assert torch.allclose(_merge_partials(parts), want, atol=1e-5, rtol=1e-5)
+    # a set that no query sees, and an empty set, contribute nothing
+    none = _attention_partial(q, kc[0, :3], vc[0, :3], torch.zeros(T, 3, dtype=torch.bool))
+    assert torch.isinf(none[1]).all() and float(none[2].abs().sum()) == 0.0
+    full = _attention_partial(q, kc[0], vc[0], torch.arange(S)[None, :] <= positions[:, None])
+    empty = _attention_partial(q, kc[0, :0], vc[0, :0], torch.zeros(T, 0, dtype=torch.bool))
+    assert torch.allclose(_merge_partials([full, none, empty]), _attention(q, kc, vc, positions, None).reshape(T, nh, hd),
+                          atol=1e-5, rtol=1e-5)
