@@ -209,7 +209,8 @@ def _build_engine_backend() -> Backend:
     model = os.environ.get("ENGINE_MODEL", "tiny")
     device = os.environ.get("ENGINE_DEVICE", "cpu")
     weights = os.environ.get("ENGINE_WEIGHTS", "fp32" if device == "cpu" else "fp8_block")
-    eng = InferenceEngine.build(model, weights=weights, device=device, max_seq=int(os.environ.get("ENGINE_MAX_SEQ", "1024")))
+    eng = InferenceEngine.build(model, weights=weights, kv=os.environ.get("ENGINE_KV") or None, device=device,
+                                max_seq=int(os.environ.get("ENGINE_MAX_SEQ", "1024")))
     return EngineBackend(eng)
 
 

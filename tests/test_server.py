@@ -181,3 +181,14 @@ def test_metrics_endpoint_counts_tokens_and_speculation():
     # non-streaming requests are counted too
     c.post("/v1/chat/completions", json=dict(body, stream=False))
     assert "ihb:requests_total 2.0" in c.get("/metrics").text
+
+
+def test_engine_backend_can_run_on_an_e4m3_kv_cache(monkeypatch):
+    """``ENGINE_KV=fp8`` builds the served engine with e4m3 KV rows (scale per position); the stream still carries real
+    router ids."""
+    from inferencehackathon_b200.serve import backends as bk
+    monkeypatch.setenv("ENGINE_MODEL", "tiny")
+    monkeypatch.setenv("ENGINE_DEVICE", "cpu")
+    monkeypatch.setenv("ENGINE_KV", "fp8")
+    be = bk._build_engine_backend()
+    assert be.engine.cfg.quant.kv == "fp8" and be.engine.cache.fp8
