@@ -50,10 +50,12 @@ class TPOT:
 # vLLM bf16 TP8 on 8xH100 as decomposed by the reference (85.7 tok/s)
 MEASURED_BASELINE = TPOT(overhead_ms=7.00, comms_ms=3.00, weight_ms=1.56, kv_ms=0.10)
 MEASURED_BASELINE_TOK_S = 85.7
-# this engine on 8 B200 (persistent kernel, block-fp8 weights, context 1024): 5.43 ms per token; comms = what the two
-# all-reduces per layer cost beyond the same phases on one GPU, weight = bytes at the measured copy bandwidth
-B200_MEASURED = TPOT(overhead_ms=3.77, comms_ms=1.22, weight_ms=0.42, kv_ms=0.02)
-B200_MEASURED_TOK_S = 184.1
+# this engine on 8 B200 (persistent kernel, block-fp8 weights, context 1024): 3.744 ms per token. comms = what the two
+# all-reduces per layer (~1.4 us each) and the arg-max exchange (~8 us) cost beyond the same phases on one GPU,
+# weight = 2.80 GB per rank at the measured 6.56 TB/s copy bandwidth, kv = 47 MB per rank; overhead = the rest, i.e. the
+# latency chain of the phases (six hand-overs per layer and the serial work between them)
+B200_MEASURED = TPOT(overhead_ms=3.03, comms_ms=0.27, weight_ms=0.43, kv_ms=0.01)
+B200_MEASURED_TOK_S = 267.1
 
 
 def corroborate_weight(cluster: Optional[Cluster] = None) -> dict:

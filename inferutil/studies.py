@@ -129,16 +129,16 @@ class Terms:
         return 1000.0 / self.tpot_ms
 
 
-B200_MEASURED_START = Terms(overhead=3.77, comms=1.22, weight=0.42, kv=0.02)   # 5.43 ms: 8 GPUs, persistent kernel
-# (comms: 94 layers x 13 us that the two all-reduces cost beyond the same phases on one GPU; weight: bytes at the
-# measured copy bandwidth; overhead: the rest, i.e. phase latencies)
+B200_MEASURED_START = Terms(overhead=3.03, comms=0.27, weight=0.43, kv=0.01)   # 3.74 ms: 8 GPUs, persistent kernel
+# (comms: 94 layers x 2 x 1.4 us that the all-reduces cost beyond the same phases on one GPU, plus the arg-max exchange;
+# weight: bytes at the measured copy bandwidth; overhead: the rest, i.e. 94 x ~32 us of phase latencies)
 
 DEFAULT_RUNGS: List[Tuple[str, Dict[str, float]]] = [
-    ("attention merge and logits handed over as tagged values too (no barrier, no atomics)", {"overhead": 3.3}),
-    ("skew between GPUs absorbed by prefetching two phases ahead", {"comms": 0.8}),
-    ("dense weights of the next layer staged in L2 during the expert phase", {"overhead": 2.6}),
-    ("fp4 expert weights", {"weight": 0.27}),
-    ("speculative decoding, tau 2.5 at verify cost 1.25", {"spec": 2.0}),
+    ("hand-overs inside thread-block clusters through distributed shared memory (12 L2 round trips per layer -> 6)", {"overhead": 2.75}),
+    ("o_proj starts on the attention blocks that have arrived (no wait for the last block)", {"overhead": 2.5}),
+    ("several tokens per cooperative launch in generation loops (13 us launch boundary per token)", {"overhead": 2.49}),
+    ("fp4 expert weights", {"weight": 0.28}),
+    ("speculative decoding, tau 2.5 at verify cost 1.25 (needs a verify window near one decode step; today ~4)", {"spec": 2.0}),
 ]
 
 
@@ -199,7 +199,7 @@ def predict_matrix(efficiency: float = 0.46, gpu: str = "B200-SXM-180GB", collec
 
 # ---- speculative decoding: unified predictor and tree-shape search ------------------------------------------------------------------
 def spec_predict(floor: float, alpha: float, width: int, depth: int, layout: str = "tp", n_ranks: int = 8,
-                 draft_ms_per_step: float = 0.0, decode_step_ms: float = 5.43, temperature: float = 0.0,
+                 draft_ms_per_step: float = 0.0, decode_step_ms: float = 3.74, temperature: float = 0.0,
                  overlap: float = 0.0, n_experts: int = 128, top_k: int = 8) -> dict:
     """speedup = E[emitted] / (verify cost + draft cost). Sampling lowers acceptance (about 0.8x at temperature
     0.7); on expert parallelism the busiest-rank factor of the expert term falls toward 1 as the union fills."""
@@ -330,6 +330,34 @@ def validate_routing_model(trials: int = 4000, n_experts: int = 128, top_k: int 
 
 
 # ---- CLI ----------------------------------------------------------------------------------------------------------------------------------------
+# ---- strong-scaling fit ------------------------------------------------------------------------------------------------------------
+# this engine, Qwen3-235B-A22B block-fp8, context 1024, ms per token at 1 / 2 / 4 / 8 B200s (persistent kernel)
+B200_SCALING_MS = ((1, 8.14), (2, 6.23), (4, 4.52), (8, 3.744))
+
+
+def scaling_fit(points: Sequence[Tuple[int, float]] = B200_SCALING_MS, bytes_per_token: float = 21.7e9,
+                hbm_bw: float = 6.5616e12, n_layers: int = 94) -> dict:
+    """Least-squares fit of ``t(N) = a * (bytes / N) / bw + fixed`` to measured ms per token at N GPUs: ``a`` is the
+    inverse bandwidth efficiency of the byte-proportional part (1 = streaming at the measured copy bandwidth) and
+    ``fixed`` the part that more GPUs do not shrink (the per-layer latency chain plus the head and the token turn-around),
+    reported per layer. Also: the time each term takes at every N, and what N GPUs would give with the fixed part halved."""
+    xs = [bytes_per_token / n / hbm_bw * 1e3 for n, _ in points]            # ms of HBM time at the copy bandwidth
+    ys = [ms for _, ms in points]
+    k = len(points)
+    mx, my = sum(xs) / k, sum(ys) / k
+    sxx = sum((x - mx) ** 2 for x in xs)
+    a = sum((x - mx) * (y - my) for x, y in zip(xs, ys)) / sxx if sxx > 0 else 0.0
+    fixed = my - a * mx
+    rows = []
+    for (n, ms), x in zip(points, xs):
+        pred = a * x + fixed
+        rows.append({"n_gpus": n, "measured_ms": ms, "fit_ms": pred, "byte_part_ms": a * x, "fixed_ms": fixed,
+                     "fixed_share": fixed / pred, "tok_s": 1000.0 / ms, "tok_s_if_fixed_halves": 1000.0 / (a * x + fixed / 2)})
+    return {"bandwidth_efficiency": 1.0 / a if a > 0 else float("inf"), "fixed_ms": fixed,
+            "fixed_us_per_layer": fixed * 1e3 / n_layers, "rows": rows,
+            "max_fit_error_ms": max(abs(r["fit_ms"] - r["measured_ms"]) for r in rows)}
+
+
 def _table(rows: List[dict]) -> str:
     if not rows:
         return ""
@@ -351,9 +379,9 @@ def main(argv=None) -> int:
     s = sub.add_parser("floor", help="back the floor share out of (k, tau, S) triples")
     s.add_argument("triples", nargs="+", help="k:tau:S")
     s = sub.add_parser("reconcile", help="which per-collective latency fits the measured step time")
-    s.add_argument("--tpot-ms", type=float, default=5.43)
+    s.add_argument("--tpot-ms", type=float, default=3.74)
     s.add_argument("--collectives", type=int, default=188)
-    s.add_argument("--weight-floor-ms", type=float, default=0.42)
+    s.add_argument("--weight-floor-ms", type=float, default=0.43)
     s.add_argument("--efficiency", type=float, default=0.45)
     s.add_argument("--candidates", type=float, nargs="+", default=[3, 5, 10, 16, 25, 35])
     sub.add_parser("ladder", help="tok/s after each lever")
@@ -379,6 +407,8 @@ def main(argv=None) -> int:
     s.add_argument("--collective-us", type=float, default=10.0); s.add_argument("--refresh", type=int, default=2)
     s = sub.add_parser("routing-check", help="Monte-Carlo check of the union / busiest-rank formulas")
     s.add_argument("--trials", type=int, default=2000)
+    s = sub.add_parser("scaling-fit", help="byte-proportional and fixed part of ms per token over the GPU count")
+    s.add_argument("points", nargs="*", help="N:ms pairs (default: this engine's measured 1 / 2 / 4 / 8 B200 figures)")
     s = sub.add_parser("spec-analyze", help="S, tau, V and the go/no-go from one speculative run")
     s.add_argument("--base", type=float, required=True); s.add_argument("--spec", type=float, required=True)
     s.add_argument("--accepted", type=float, required=True); s.add_argument("--drafts", type=float, required=True)
@@ -410,6 +440,12 @@ def main(argv=None) -> int:
         print(json.dumps(stale_tp_ceiling(collective_us=a.collective_us, refresh_every=a.refresh), indent=1))
     elif a.cmd == "routing-check":
         print(json.dumps(validate_routing_model(a.trials), indent=1))
+    elif a.cmd == "scaling-fit":
+        pts = [(int(t.split(":")[0]), float(t.split(":")[1])) for t in a.points] or B200_SCALING_MS
+        r = scaling_fit(pts)
+        print(f"byte part streams at {100 * r['bandwidth_efficiency']:.0f} % of the copy bandwidth; fixed part "
+              f"{r['fixed_ms']:.2f} ms = {r['fixed_us_per_layer']:.1f} us per layer; worst fit error {r['max_fit_error_ms']:.2f} ms")
+        print(_table(r["rows"]))
     elif a.cmd == "spec-analyze":
         print(json.dumps(spec_analyze(a.base, a.spec, a.accepted, a.drafts, a.positions, a.floor), indent=1))
     return 0

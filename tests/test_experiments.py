@@ -170,7 +170,7 @@ def test_union_reconcile_ladder_and_tree():
     rows = studies.comms_reconcile(11.67, 188, 1.56, 0.19, [5, 16, 35, 60])
     assert [r["consistent"] for r in rows] == [True, True, False, False]
     lad = studies.ladder()
-    assert lad[0]["tok_s"] == pytest.approx(1000.0 / 5.43) and all(b["tok_s"] > a["tok_s"] for a, b in zip(lad, lad[1:]))
+    assert lad[0]["tok_s"] == pytest.approx(1000.0 / 3.74) and all(b["tok_s"] > a["tok_s"] for a, b in zip(lad, lad[1:]))
     hi = studies.tree_optimizer(0.9, 0.7)[0]
     lo = studies.tree_optimizer(0.0, 0.7)[0]
     assert hi["positions"] > lo["positions"]                       # a floor-bound step favours large trees
@@ -219,3 +219,17 @@ def test_window_group_table_covers_every_pair_once():
         assert torch.all(covered == 1)                                # every (token, slot) pair exactly once
         assert torch.all(groups[ng:, 2] == 0)                         # unused entries are empty
         assert torch.equal(torch.sort(order).values, torch.arange(pairs))
+
+
+def test_scaling_fit_separates_the_byte_part_from_the_fixed_part():
+    # exact data from t = 1.5 * x + 3.0 is recovered
+    bw, by = 6.5616e12, 21.7e9
+    pts = [(n, 1.5 * by / n / bw * 1e3 + 3.0) for n in (1, 2, 4, 8)]
+    r = studies.scaling_fit(pts, by, bw)
+    assert r["bandwidth_efficiency"] == pytest.approx(1 / 1.5) and r["fixed_ms"] == pytest.approx(3.0)
+    assert r["max_fit_error_ms"] < 1e-9 and r["fixed_us_per_layer"] == pytest.approx(3000.0 / 94)
+    # the measured points: the part that GPUs do not shrink is most of the token at 8 GPUs
+    m = studies.scaling_fit()
+    assert 2.5 < m["fixed_ms"] < 3.6 and m["rows"][-1]["fixed_share"] > 0.75 and m["max_fit_error_ms"] < 0.7
+    assert m["rows"][-1]["tok_s_if_fixed_halves"] > 1.5 * m["rows"][-1]["tok_s"]
+    assert studies.main(["scaling-fit"]) == 0 and studies.main(["scaling-fit", "1:8.0", "2:5.0", "4:3.5"]) == 0
