@@ -17,9 +17,6 @@ ENGINE_PROFILES = {
                 "forward_tpot_ms": 8.61, "collective_us": 9.35, "weight_dtype": "fp8"},
     "vllm": {"label": "vLLM", "ttft_ms": 110.0, "per_tok_ms": 11.7, "spec_enabled": False, "proposed": 1,
              "forward_tpot_ms": 11.7, "collective_us": 17.0, "weight_dtype": "bf16"},
-    # this engine as measured on 8 B200s (Qwen3-235B-A22B block-fp8, 1024-token prompt): paces the mock like the real thing
-    "b200moe": {"label": "b200moe", "ttft_ms": 65.5, "per_tok_ms": 3.74, "spec_enabled": False, "proposed": 1,
-                "forward_tpot_ms": 3.74, "collective_us": 1.4, "weight_dtype": "fp8"},
 }
 
 
