@@ -74,7 +74,10 @@ class DecodeBreakdown:
 
 def decode_latency(cfg: MoEConfig, cluster: Cluster, *, plan: str = "hybrid", dtype_bytes: int = 2,
                    kv_dtype_bytes: int = 2, seq_len: int = 32768, tp: int | None = None, ep: int | None = None,
-                   ideal_routing: bool = False, measured_max_experts: float | None = None) -> DecodeBreakdown:
+                   ideal_routing: bool = False, measured_max_experts: float | None = None,
+                   kv_seq_split: bool = False) -> DecodeBreakdown:
+    """``kv_seq_split``: the ranks that share a KV head (tp above the number of KV heads) split its cache rows between them
+    instead of replicating them (two more small exchanges per layer, counted in ``comms``)."""
     gpu, n = cluster.gpu, cluster.n_gpus
     tp, ep = tp or n, ep or n
     layers = cfg.n_layers
@@ -104,6 +107,9 @@ def decode_latency(cfg: MoEConfig, cluster: Cluster, *, plan: str = "hybrid", dt
     else:
         raise ValueError(f"unknown plan {plan!r}")
     shards = n if plan == "floor" else min(tp, cfg.n_kv_heads)
+    if kv_seq_split and plan != "floor" and tp > cfg.n_kv_heads:
+        shards = tp                                        # every rank reads 1 / tp of the KV bytes
+        comms += 2 * layers * gpu.collective_latency_s     # query gather + partial-record exchange inside a head's group
     kv_s = seq_len * cfg.kv_bytes_per_token(kv_dtype_bytes) / shards / gpu.hbm_bw
     flops = 2 * cfg.active_params + 4 * cfg.n_heads * cfg.head_dim * seq_len
     peak = gpu.fp8_flops if dtype_bytes < 2 else gpu.bf16_flops

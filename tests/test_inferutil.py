@@ -212,3 +212,24 @@ def test_b200_measured_baseline_is_consistent():
     assert abs(1000.0 / total - O.B200_MEASURED_TOK_S) < 1.0
     final, steps = O.optimize(b)
     assert (final.overhead_ms + final.comms_ms + final.weight_ms + final.kv_ms) <= total
+
+
+def test_kv_row_split_trades_kv_bytes_for_two_exchanges_per_layer():
+    import dataclasses
+    from inferutil.hardware import GPUS, Cluster
+    from inferutil.latency import decode_latency
+    from inferutil.model import QWEN3_235B
+    g = dataclasses.replace(GPUS["B200-SXM-180GB"], collective_latency_s=1.4e-6)
+    c = Cluster(g, 8)
+    kw = dict(plan="tp", dtype_bytes=1, kv_dtype_bytes=2)
+    rep = decode_latency(QWEN3_235B, c, seq_len=32768, **kw)
+    spl = decode_latency(QWEN3_235B, c, seq_len=32768, kv_seq_split=True, **kw)
+    assert spl.kv_read_s == rep.kv_read_s / 2                      # 4 KV heads on 8 ranks: two ranks per head
+    assert spl.comms_s == rep.comms_s * 2 and spl.total_s > rep.total_s          # does not pay at 32 K tokens ...
+    long_rep = decode_latency(QWEN3_235B, c, seq_len=131072, **kw)
+    long_spl = decode_latency(QWEN3_235B, c, seq_len=131072, kv_seq_split=True, **kw)
+    assert long_spl.total_s < long_rep.total_s                     # ... but does at 128 K
+    # no effect where every rank already owns whole KV heads
+    c4 = Cluster(g, 4)
+    assert decode_latency(QWEN3_235B, c4, seq_len=32768, kv_seq_split=True, **kw).total_s == \
+        decode_latency(QWEN3_235B, c4, seq_len=32768, **kw).total_s
