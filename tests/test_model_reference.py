@@ -103,3 +103,19 @@ def test_partial_attention_records_merge_to_full_attention():
     empty = _attention_partial(q, kc[0, :0], vc[0, :0], torch.zeros(T, 0, dtype=torch.bool))
     assert torch.allclose(_merge_partials([full, none, empty]), _attention(q, kc, vc, positions, None).reshape(T, nh, hd),
                           atol=1e-5, rtol=1e-5)
+
+
+def test_torch_kv_scattered_rows_match_contiguous_writes():
+    """``write_rows`` (rows anywhere in the cache) stores what ``write`` stores for the same rows: bf16 and e4m3 + scale."""
+    from inferencehackathon_b200.models.qwen3_moe import TorchKV
+    g = torch.Generator().manual_seed(1)
+    k, v = torch.randn(2, 6, 32, generator=g), torch.randn(2, 6, 32, generator=g)
+    for dtype in (torch.bfloat16, torch.float8_e4m3fn):
+        a, b = TorchKV(1, 2, 16, 32, dtype, "cpu"), TorchKV(1, 2, 16, 32, dtype, "cpu")
+        a.write(0, 3, k, v)
+        b.write_rows(0, torch.tensor([3, 4, 5]), k[:, :3], v[:, :3])
+        b.write_rows(0, torch.tensor([8, 6, 7]), k[:, [5, 3, 4]], v[:, [5, 3, 4]])       # any order
+        b.write_rows(0, torch.tensor([], dtype=torch.long), k[:, :0], v[:, :0])          # nothing to write
+        ka, va = a.read(0, 9)
+        kb, vb = b.read(0, 9)
+        assert torch.equal(ka.float(), kb.float()) and torch.equal(va.float(), vb.float())
