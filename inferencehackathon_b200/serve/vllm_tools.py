@@ -292,6 +292,8 @@ class FusedSmallAllReduce:
         self.group_fn = group_fn                   # returns the process group to reduce over (default: the world group)
         self.hidden: Optional[int] = None          # the slot layout depends on the row width: fixed by the first call
         self._ready = False
+        self.n_calls = 0
+        self.check_every = 256                     # calls between two reads of the device error word (a read synchronises)
 
     def _setup(self, device: torch.device) -> None:
         import torch.distributed as dist
@@ -325,7 +327,17 @@ class FusedSmallAllReduce:
             self.hidden = int(t.shape[1])
         out = torch.empty(t.shape, dtype=torch.float32, device=t.device)
         self.K.allreduce_counted(self.cm, t, out, self.counter, self.calls, self.err)
+        self.n_calls += 1
+        if self.n_calls % self.check_every == 0:
+            self.check()
         return out if t.dtype == torch.float32 else out.to(t.dtype)
+
+    def check(self) -> None:
+        """Raise if a bounded device-side wait gave up (a rank that stopped calling): the sums since then are not valid."""
+        if self._ready:
+            code = int(self.err.item())
+            if code:
+                raise RuntimeError(f"fused all-reduce: device-side wait gave up ({self.K.ERR_NAMES.get(code, code)})")
 
 
 def patch_tensor_parallel_all_reduce(target, fused=None, name: str = "tensor_model_parallel_all_reduce",
