@@ -126,6 +126,13 @@ class EngineBackend(Backend):
         self._lock = threading.Lock()
         self._gpu_of = lambda e: expert_gpu(e, engine.cfg.model, engine.cfg.parallel)
         self.healthy = True
+        # ROUTE_PIPELINE=1: every token's real routing drives the native predictor + prefetch scheduler; the turn's
+        # x_summary then carries their hit rates (what an expert-prefetch scheme would have achieved on this turn)
+        self.pipeline = None
+        if os.environ.get("ROUTE_PIPELINE"):
+            from ..routing.pipeline import RoutingPipeline
+            m = engine.cfg.model
+            self.pipeline = RoutingPipeline(m.n_layers, m.n_experts, m.top_k, n_gpus=max(engine.cfg.parallel.world, 1))
 
     def placement_fn(self):
         return self._gpu_of
@@ -187,9 +194,12 @@ class EngineBackend(Backend):
         yield {"x_summary": {"engine": self.label, "ttft_ms": round(1e3 * pre.seconds, 3), "decode_tok_per_s": rate,
                              "prefill_tokens": len(prompt), "completion_tokens": len(tokens),
                              "spec_enabled": self.spec is not None,
-                             "spec_accept_rate": round(accepted / proposed, 3) if proposed else 0.0, **extra}}
+                             "spec_accept_rate": round(accepted / proposed, 3) if proposed else 0.0, **extra,
+                             **({"route_prediction": self.pipeline.stats()} if self.pipeline is not None else {})}}
 
     def _chunk(self, req, i, token, t_ms, routes, proposed, accepted) -> dict:
+        if self.pipeline is not None and routes:
+            self.pipeline.on_token({r.layer: r.experts for r in routes})
         return {"id": "chatcmpl-b200", "object": "chat.completion.chunk", "model": req.model,
                 "choices": [{"index": 0, "delta": {"content": self.tok.piece(int(token))}, "finish_reason": None}],
                 "x_telemetry": {"token_index": i, "t_ms": round(t_ms, 4), "experts": self._routes(routes, i),

@@ -181,3 +181,43 @@ def test_trace_collector_bounded_and_drain():
     tc.push(3, np.zeros(4), np.zeros(3))
     tc.clear()
     assert tc.n_traces() == 0
+
+
+def test_live_pipeline_scores_predictions_against_real_routing():
+    """Routing records in, Markov predictions + prefetch actions out: high hit rate on structured routing, the chance
+    rate on random routing, actions for the GPUs that hold the predicted experts."""
+    import random
+    from inferencehackathon_b200.routing.pipeline import RoutingPipeline
+    L, E, k = 6, 32, 4
+
+    def run(structured, sink=None):
+        rng = random.Random(0)
+        p = RoutingPipeline(L, E, k, n_gpus=4, warmup_tokens=8, sink=sink)
+        for _ in range(150):
+            cur = rng.sample(range(E), k)
+            tok = {}
+            for layer in range(L):
+                tok[layer] = cur
+                cur = ([(e + 1) % E if rng.random() < 0.9 else rng.randrange(E) for e in cur] if structured
+                       else rng.sample(range(E), k))
+            p.on_token(tok)
+        return p
+
+    good, rand = run(True), run(False)
+    gs, rs = good.stats(), rand.stats()
+    assert gs["tokens"] == 150 and gs["records"] == 150 * L
+    assert gs["prefetch_hit_rate"] > 0.6 and gs["mean_layer_hit_rate"] > 0.6
+    assert rs["prefetch_hit_rate"] < 0.3                                   # chance is k / E = 0.125
+    acts = good.scheduler.drain()
+    assert acts and all(a.gpu_id == good.placement.gpu_for(a.layer, a.expert_id) for a in acts[:50])
+    assert {a.kind for a in acts} == {"WarmExpert", "EarlyDispatch"}
+    seen = []
+    run(True, sink=seen.append)
+    assert len(seen) > 100 and seen[0].layer >= 1                          # predictions are for the NEXT layer
+    # nothing is predicted during warm-up or for the layer after the last one
+    p = RoutingPipeline(L, E, k, warmup_tokens=2)
+    assert p.on_layer(0, [1, 2, 3, 4]) is None
+    for _ in range(3):
+        for layer in range(L):
+            out = p.on_layer(layer, [layer, layer + 1, layer + 2, layer + 3])
+    assert out is None

@@ -192,3 +192,22 @@ def test_engine_backend_can_run_on_an_e4m3_kv_cache(monkeypatch):
     monkeypatch.setenv("ENGINE_KV", "fp8")
     be = bk._build_engine_backend()
     assert be.engine.cfg.quant.kv == "fp8" and be.engine.cache.fp8
+
+
+def test_engine_backend_reports_route_prediction_when_the_pipeline_is_on(monkeypatch):
+    """``ROUTE_PIPELINE=1``: the routing of every streamed token drives the native Markov predictor and prefetch
+    scheduler, and the turn's summary says how many predicted experts were really selected."""
+    from fastapi.testclient import TestClient
+    from inferencehackathon_b200 import TINY
+    from inferencehackathon_b200.runtime.engine import InferenceEngine
+    from inferencehackathon_b200.serve.app import create_app
+    eng = InferenceEngine.build("tiny", weights="fp32", max_seq=128)
+    body = {"messages": [{"role": "user", "content": "route me"}], "max_tokens": 12, "temperature": 0.0}
+    plain = json.loads(_frames(TestClient(create_app(bk.EngineBackend(eng))).post("/v1/chat/completions", json=body).text)[-2])
+    assert "route_prediction" not in plain["x_summary"]
+    monkeypatch.setenv("ROUTE_PIPELINE", "1")
+    backend = bk.EngineBackend(eng)
+    frames = _frames(TestClient(create_app(backend)).post("/v1/chat/completions", json=body).text)
+    rp = json.loads(frames[-2])["x_summary"]["route_prediction"]
+    assert rp["tokens"] == 12 and rp["records"] == 12 * TINY.n_layers
+    assert rp["prefetched"] > 0 and 0.0 <= rp["prefetch_hit_rate"] <= 1.0 and rp["hits"] <= rp["prefetched"]
