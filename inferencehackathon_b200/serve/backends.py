@@ -54,9 +54,17 @@ class VLLMBackend(Backend):
         # telemetry cycles through the placement
         sock = routing_sock if routing_sock is not None else os.environ.get("VLLM_ROUTING_SOCK", "")
         self.feed = None
+        self.pipeline = None
         if sock:
             from .vllm_tools import RoutingFeedReader
-            self.feed = RoutingFeedReader(sock)
+            on_record = None
+            if os.environ.get("ROUTE_PIPELINE"):
+                # the fed routing also drives the native predictor + prefetch scheduler (x_summary.route_prediction)
+                from ..routing.pipeline import RoutingPipeline
+                self.pipeline = RoutingPipeline(int(os.environ.get("VLLM_NUM_LAYERS", "94")),
+                                                int(os.environ.get("VLLM_NUM_EXPERTS", "128")), 8)
+                on_record = lambda _tok, layer, experts: self.pipeline.on_layer(layer, experts)   # noqa: E731
+            self.feed = RoutingFeedReader(sock, on_record=on_record)
 
     def _telemetry(self, n: int, t_ms: float, topo: dict) -> dict:
         if self.feed is not None:
@@ -110,7 +118,8 @@ class VLLMBackend(Backend):
         extra = summary_fields(round(1000.0 / rate, 2), rate, weight_dtype="bf16", collective_us=17.0) if rate > 0 else {}
         yield {"x_summary": {"ttft_ms": round(1e3 * ttft, 1), "decode_tok_per_s": rate,
                              "prefill_tokens": sum(len(m.content.split()) for m in req.messages),
-                             "completion_tokens": n, "spec_accept_rate": spec["accept_rate"], **extra}}
+                             "completion_tokens": n, "spec_accept_rate": spec["accept_rate"], **extra,
+                             **({"route_prediction": self.pipeline.stats()} if self.pipeline is not None else {})}}
 
 
 class EngineBackend(Backend):

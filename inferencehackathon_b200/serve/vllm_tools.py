@@ -194,8 +194,10 @@ class RoutingFeedReader:
     """Reads the feed in a background thread and keeps the records of the most recent tokens. Connects lazily and keeps
     retrying: the server may start before vLLM does."""
 
-    def __init__(self, path: str = DEFAULT_SOCK, keep_tokens: int = 64, retry_s: float = 0.5):
+    def __init__(self, path: str = DEFAULT_SOCK, keep_tokens: int = 64, retry_s: float = 0.5,
+                 on_record: Optional[Callable[[int, int, List[int]], None]] = None):
         self.path, self.retry_s = path, retry_s
+        self.on_record = on_record                 # called in the reader thread with (token, layer, experts) of every record
         self._by_token: "collections.OrderedDict[int, Dict[int, List[int]]]" = collections.OrderedDict()
         self._keep = keep_tokens
         self._lock = threading.Lock()
@@ -246,6 +248,8 @@ class RoutingFeedReader:
             row[layer] = experts
             while len(self._by_token) > self._keep:
                 self._by_token.popitem(last=False)
+        if self.on_record is not None:
+            self.on_record(tok, layer, experts)
 
     def latest_token(self) -> Optional[int]:
         with self._lock:

@@ -182,3 +182,22 @@ def test_vllm_backend_uses_the_feed_when_it_has_records(tmp_path):
     assert be._telemetry(1, 2.0, topo)["experts"] == [{"layer": 0, "expert_id": 3, "gpu": 3}, {"layer": 0, "expert_id": 9, "gpu": 1}]
     be.feed.close()
     feed.close()
+
+
+def test_fed_routing_drives_the_prediction_pipeline(tmp_path, monkeypatch):
+    from inferencehackathon_b200.serve import backends as bk
+    monkeypatch.setenv("ROUTE_PIPELINE", "1")
+    monkeypatch.setenv("VLLM_NUM_LAYERS", "4")
+    monkeypatch.setenv("VLLM_NUM_EXPERTS", "16")
+    path = str(tmp_path / "p.sock")
+    feed = vt.RoutingFeed(path).start()
+    be = bk.VLLMBackend(scrape_spec=False, routing_sock=path)
+    assert _wait(feed.connected)
+    for tok in range(12):                                                   # every layer shifts the experts by one
+        for layer in range(4):
+            feed.send({"token": tok, "layer": layer, "experts": [(tok + layer + j) % 16 for j in range(8)]})
+    assert _wait(lambda: be.pipeline.records == 48)
+    st = be.pipeline.stats()
+    assert st["tokens"] == 12 and st["prefetched"] > 0 and st["prefetch_hit_rate"] > 0.5
+    be.feed.close()
+    feed.close()
