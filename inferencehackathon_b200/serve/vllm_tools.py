@@ -378,11 +378,17 @@ def patch_tensor_parallel_all_reduce(target, fused=None, name: str = "tensor_mod
 
 
 # ---- launcher -----------------------------------------------------------------------------------------------------------------------
-def build_serve_argv(model: str, tp: int = 8, port: int = 8001, extra: Optional[List[str]] = None) -> List[str]:
-    """Command line handed to vLLM's ``serve`` (the flags the reference launcher passes, tools/start_vllm.py:124-132)."""
+def build_serve_argv(model: str, tp: int = 8, port: int = 8001, extra: Optional[List[str]] = None,
+                     eager: bool = True) -> List[str]:
+    """Command line handed to vLLM's ``serve`` (the flags the reference launcher passes, tools/start_vllm.py:124-132).
+    ``eager``: add ``--enforce-eager``; the gate hook reads expert ids back to the host, which neither a compiled graph
+    nor a CUDA-graph capture allows (under capture the hook stays silent)."""
+    extra = list(extra or [])
     argv = ["vllm", "serve", model, "--tensor-parallel-size", str(tp), "--port", str(port),
             "--chat-template-content-format", "string"]
-    return argv + list(extra or [])
+    if eager and "--enforce-eager" not in extra:
+        argv.append("--enforce-eager")
+    return argv + extra
 
 
 def main(argv=None) -> int:
@@ -394,11 +400,13 @@ def main(argv=None) -> int:
     ap.add_argument("--top-k", type=int, default=8)
     ap.add_argument("--fused-allreduce", action="store_true", help="decode-sized tensor-parallel all-reduces go through this "
                     "package's counted NVSwitch kernel")
+    ap.add_argument("--graphs", action="store_true", help="do not add --enforce-eager (the routing feed then only reports "
+                    "steps that run outside CUDA graphs)")
     ap.add_argument("--print-only", action="store_true", help="print the vLLM command line and exit")
     a, extra = ap.parse_known_args(argv)
     if not a.model:
         ap.error("--model (or VLLM_MODEL_PATH) is required")
-    serve_argv = build_serve_argv(a.model, a.tp, a.port, extra)
+    serve_argv = build_serve_argv(a.model, a.tp, a.port, extra, eager=not a.graphs)
     if a.print_only:
         print(" ".join(serve_argv))
         return 0

@@ -162,7 +162,8 @@ def test_fused_all_reduce_refuses_what_the_kernel_cannot_take():
 
 def test_launcher_command_line(capsys):
     argv = vt.build_serve_argv("/models/q", tp=4, port=9000, extra=["--enforce-eager"])
-    assert argv[:3] == ["vllm", "serve", "/models/q"] and "--enforce-eager" in argv
+    assert argv[:3] == ["vllm", "serve", "/models/q"] and argv.count("--enforce-eager") == 1
+    assert "--enforce-eager" in vt.build_serve_argv("/m") and "--enforce-eager" not in vt.build_serve_argv("/m", eager=False)
     assert argv[argv.index("--tensor-parallel-size") + 1] == "4" and argv[argv.index("--port") + 1] == "9000"
     assert vt.main(["--model", "/models/q", "--tp", "2", "--print-only", "--max-model-len", "4096"]) == 0
     out = capsys.readouterr().out
