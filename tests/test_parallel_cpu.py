@@ -102,3 +102,18 @@ def test_tree_verify_window_with_split_kv_rows():
     for logits, n in run_cpu_ranks(_tree_window, 4, (4, True)):
         assert n == ref_len == len(PROMPT)
         assert torch.allclose(logits, ref_logits, atol=5e-4, rtol=1e-4)
+
+
+def _fp8_kv_logits(rank, world, split):
+    e = InferenceEngine.build("tiny", tp=4, rank=rank, world=world, weights="fp32", kv="fp8", max_seq=128, kv_seq_split=split)
+    return e.prefill(PROMPT, return_logits=True).logits[0].clone()
+
+
+def test_split_kv_rows_with_an_e4m3_cache_match_the_replicated_e4m3_cache():
+    """The row split stores the same quantised rows (one scale per row), only on different ranks. The merge sums in
+    another order, and a 1e-7 difference in a later layer's K / V can move an element across an e4m3 rounding boundary,
+    so the logits agree to a few 1e-4 rather than to fp32 round-off; a wrong row, scale or merge would be off by 1e-1."""
+    rep = run_cpu_ranks(_fp8_kv_logits, 4, (False,))
+    spl = run_cpu_ranks(_fp8_kv_logits, 4, (True,))
+    for a, b in zip(rep, spl):
+        assert float((a - b).abs().max()) < 5e-3 * max(1.0, float(a.abs().max()))
