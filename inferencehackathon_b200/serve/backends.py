@@ -228,9 +228,16 @@ def _build_engine_backend() -> Backend:
     model = os.environ.get("ENGINE_MODEL", "tiny")
     device = os.environ.get("ENGINE_DEVICE", "cpu")
     weights = os.environ.get("ENGINE_WEIGHTS", "fp32" if device == "cpu" else "fp8_block")
+    # ENGINE_CHECKPOINT: a directory of Hugging Face safetensors shards (else random weights of the named architecture);
+    # ENGINE_TOKENIZER: a Hugging Face tokenizer directory (else the reversible byte mapping)
     eng = InferenceEngine.build(model, weights=weights, kv=os.environ.get("ENGINE_KV") or None, device=device,
-                                max_seq=int(os.environ.get("ENGINE_MAX_SEQ", "1024")))
-    return EngineBackend(eng)
+                                max_seq=int(os.environ.get("ENGINE_MAX_SEQ", "1024")),
+                                checkpoint=os.environ.get("ENGINE_CHECKPOINT") or None)
+    tok = None
+    if os.environ.get("ENGINE_TOKENIZER"):
+        from .tokenizer import HFTokenizer
+        tok = HFTokenizer(os.environ["ENGINE_TOKENIZER"])
+    return EngineBackend(eng, tokenizer=tok)
 
 
 def get_backend() -> Backend:

@@ -211,3 +211,45 @@ def test_engine_backend_reports_route_prediction_when_the_pipeline_is_on(monkeyp
     rp = json.loads(frames[-2])["x_summary"]["route_prediction"]
     assert rp["tokens"] == 12 and rp["records"] == 12 * TINY.n_layers
     assert rp["prefetched"] > 0 and 0.0 <= rp["prefetch_hit_rate"] <= 1.0 and rp["hits"] <= rp["prefetched"]
+
+
+def test_served_engine_can_use_a_hugging_face_tokenizer_directory(tmp_path, monkeypatch):
+    """``ENGINE_TOKENIZER`` points at a tokenizer directory; a tiny word-level tokenizer is built here, offline."""
+    from tokenizers import Tokenizer, models, pre_tokenizers
+    from transformers import PreTrainedTokenizerFast
+    words = ["[UNK]", "route", "me", "to", "the", "experts", "please"]
+    t = Tokenizer(models.WordLevel({w: i for i, w in enumerate(words)}, unk_token="[UNK]"))
+    t.pre_tokenizer = pre_tokenizers.Whitespace()
+    PreTrainedTokenizerFast(tokenizer_object=t, unk_token="[UNK]").save_pretrained(str(tmp_path))
+    monkeypatch.setenv("ENGINE_MODEL", "tiny")
+    monkeypatch.setenv("ENGINE_DEVICE", "cpu")
+    monkeypatch.setenv("ENGINE_TOKENIZER", str(tmp_path))
+    be = bk._build_engine_backend()
+    assert be.tok.encode("route me please") == [1, 2, 6] and be.tok.decode([3, 4, 5]).split() == ["to", "the", "experts"]
+    from fastapi.testclient import TestClient
+    from inferencehackathon_b200.serve.app import create_app
+    frames = _frames(TestClient(create_app(be)).post("/v1/chat/completions", json={
+        "messages": [{"role": "user", "content": "route me to the experts"}], "max_tokens": 4, "temperature": 0.0}).text)
+    summ = json.loads(frames[-2])["x_summary"]
+    assert summ["prefill_tokens"] == 5 and summ["completion_tokens"] == 4
+
+
+def test_served_engine_loads_a_safetensors_checkpoint_directory(tmp_path, monkeypatch):
+    """``ENGINE_CHECKPOINT``: the served engine reads Hugging Face safetensors shards instead of drawing random weights."""
+    import torch
+    from safetensors.torch import save_file
+    from inferencehackathon_b200.config import get_model_config
+    from inferencehackathon_b200.models.weights import random_state_dict
+    from inferencehackathon_b200.runtime.engine import InferenceEngine
+    sd = random_state_dict(get_model_config("tiny"), 11)
+    save_file({k: v.contiguous() for k, v in sd.items()}, str(tmp_path / "model.safetensors"))
+    monkeypatch.setenv("ENGINE_MODEL", "tiny")
+    monkeypatch.setenv("ENGINE_DEVICE", "cpu")
+    monkeypatch.setenv("ENGINE_CHECKPOINT", str(tmp_path))
+    be = bk._build_engine_backend()
+    ref = InferenceEngine.build("tiny", weights="fp32", state_dict=sd)
+    other = InferenceEngine.build("tiny", weights="fp32")                  # seed 0: another model
+    prompt = [3, 1, 4, 1, 5, 9, 2, 6]
+    got = be.engine.prefill(prompt, return_logits=True).logits
+    assert torch.equal(got, ref.prefill(prompt, return_logits=True).logits)
+    assert not torch.equal(got, other.prefill(prompt, return_logits=True).logits)
