@@ -253,3 +253,17 @@ def test_served_engine_loads_a_safetensors_checkpoint_directory(tmp_path, monkey
     got = be.engine.prefill(prompt, return_logits=True).logits
     assert torch.equal(got, ref.prefill(prompt, return_logits=True).logits)
     assert not torch.equal(got, other.prefill(prompt, return_logits=True).logits)
+
+
+def test_package_command_line_generates_and_reports(capsys):
+    from inferencehackathon_b200.__main__ import main
+    assert main(["generate", "--model", "tiny", "--prompt", "abc", "--max-new", "6", "--kv", "fp8", "--json"]) == 0
+    out = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert out["prompt_tokens"] == 3 and out["new_tokens"] == 6 and out["kv"] == "fp8" and out["backend"] == "torch"
+    assert out["ttft_ms"] > 0 and out["decode_tok_per_s"] > 0 and isinstance(out["text"], str)
+    assert main(["generate", "--prompt", "x" * 40, "--max-seq", "32"]) == 2          # no room left: refused with a reason
+    capsys.readouterr()
+    assert main(["info"]) == 0
+    info = json.loads(capsys.readouterr().out)
+    assert set(info["native_libraries"]) == {"libihb_kernels.so", "libihb_ctrl.so"}
+    assert info["presets"]["qwen3-235b-a22b"]["experts"] == 128 and info["presets"]["tiny"]["layers"] == 4
