@@ -307,3 +307,50 @@ def test_route_aware_select_and_union():
     ex = [[10, 11, 12], [1, 2, 3]]
     assert sp.route_aware_select(lps, ex, u, 0.0) == 0
     assert sp.route_aware_select(lps, ex, u, 0.5) == 1
+
+
+# ---- property-based checks (hypothesis) ---------------------------------------------------------------------------------------------
+from hypothesis import given, settings, strategies as st   # noqa: E402
+
+
+@settings(max_examples=120, deadline=None)
+@given(st.integers(2, 24), st.integers(1, 8), st.integers(0, 2 ** 31 - 1))
+def test_greedy_chain_accept_is_the_longest_matching_prefix_plus_the_targets_token(vocab, k, seed):
+    """For any logits and any draft, greedy acceptance emits exactly: the drafted tokens up to the first position where
+    the draft differs from the arg-max of the row that scores it, then that row's arg-max (or the bonus row's after a
+    full accept); the random numbers and the draft's log-probabilities play no part."""
+    rng = np.random.default_rng(seed)
+    rows = rng.standard_normal((k + 1, vocab)).astype(np.float32)
+    best = rows.argmax(1)
+    draft = [int(best[p]) if rng.random() < 0.7 else int(rng.integers(vocab)) for p in range(k)]
+    n = 0
+    while n < k and draft[n] == int(best[n]):
+        n += 1
+    toks, nacc = sp.accept_chain(rows, draft, (-rng.random(k)).tolist(), rng.random(k + 1).tolist(), temperature=0.0)
+    assert nacc == n and toks == draft[:n] + [int(best[n])]
+    # the same through the tree walk over a chain-shaped tree, and through the full-distribution variant
+    q = np.full((k, vocab), 1.0 / vocab, np.float32)
+    toks_full, nacc_full = sp.accept_chain_full(rows, draft, q, rng.random(k + 1).tolist(), temperature=0.0)
+    assert (toks_full, nacc_full) == (toks, nacc)
+
+
+@settings(max_examples=60, deadline=None)
+@given(st.lists(st.integers(0, 1000), min_size=1, max_size=12), st.integers(1, 64))
+def test_tree_builder_rows_are_exactly_the_ancestor_chains(raw_parents, context_len):
+    """For any tree given as parent indices (node 0 = the last committed token, a parent precedes its child): a draft
+    node sees exactly itself and its draft ancestors, its RoPE position is context_len + depth - 1, and its CSR slot list
+    is that chain, root side first, with node i in cache slot context_len + i - 1."""
+    parent = [-1] + [p % i for i, p in enumerate(raw_parents) if i > 0]
+    n = len(parent)
+    mask = sp.tree_mask(parent)
+    pos, off, slots = sp.tree_attn_build(parent, context_len)
+    assert mask.shape == (n - 1, n - 1) and int(pos[0]) == context_len - 1 and int(off[0]) == int(off[1]) if n > 1 else True
+    for i in range(1, n):
+        chain, j = [], i
+        while j > 0:
+            chain.append(j)
+            j = parent[j]
+        chain.reverse()                                                     # root side first, self last
+        assert {c + 1 for c in range(n - 1) if mask[i - 1, c]} == set(chain)
+        assert int(pos[i]) == context_len + len(chain) - 1
+        assert slots[off[i]:off[i + 1]].tolist() == [context_len + a - 1 for a in chain]
