@@ -105,11 +105,65 @@ double imbalance_of(const std::vector<double>& load) {
 
 }  // namespace
 
+// helpers of the placement optimiser (see ihb_placement_optimize)
+namespace {
+struct Candidate {
+  std::vector<int> prim, rep;
+  double peak = 0.0;
+};
+
+double peak_of(const unsigned* c, int n_experts, int n_gpus, const std::vector<int>& prim, const std::vector<int>& rep,
+               std::vector<double>* loads) {
+  std::vector<double> load(n_gpus, 0.0);
+  for (int e = 0; e < n_experts; ++e) {
+    if (rep[e] >= 0) { load[prim[e]] += 0.5 * c[e]; load[rep[e]] += 0.5 * c[e]; }
+    else load[prim[e]] += c[e];
+  }
+  if (loads != nullptr) *loads = load;
+  return *std::max_element(load.begin(), load.end());
+}
+
+Candidate place_lpt(const unsigned* c, int n_experts, int n_gpus, const std::vector<char>& hot) {
+  struct Item { double w; int e; };
+  std::vector<Item> items;
+  for (int e = 0; e < n_experts; ++e) {
+    if (hot[e]) { items.push_back({0.5 * c[e], e}); items.push_back({0.5 * c[e], e}); }
+    else items.push_back({static_cast<double>(c[e]), e});
+  }
+  std::stable_sort(items.begin(), items.end(), [](const Item& a, const Item& b) { return a.w > b.w; });
+  Candidate out;
+  out.prim.assign(n_experts, -1);
+  out.rep.assign(n_experts, -1);
+  std::vector<double> load(n_gpus, 0.0);
+  for (const Item& it : items) {
+    int best = -1;
+    for (int g = 0; g < n_gpus; ++g) {
+      if (g == out.prim[it.e]) continue;                 // the second half of a hot expert goes to another GPU
+      if (best < 0 || load[g] < load[best]) best = g;
+    }
+    if (out.prim[it.e] < 0) out.prim[it.e] = best; else out.rep[it.e] = best;
+    load[best] += it.w;
+  }
+  out.peak = peak_of(c, n_experts, n_gpus, out.prim, out.rep, nullptr);
+  return out;
+}
+}  // namespace
+
 extern "C" {
 
 // ---- placement -------------------------------------------------------------------------------------------------------
 // counts [n_layers][n_experts]; out_primary / out_replica [n_layers][n_experts] (replica -1 = none);
 // out_stats = {round-robin mean imbalance, optimised mean imbalance, improvement %, replicated expert-layers}.
+//
+// Per layer three candidate placements are built and the one with the lowest peak load is kept:
+//  (a) longest-processing-time: heaviest expert first onto the least-loaded GPU, no replicas;
+//  (b) the same with every hot expert (count > hot_mult x the layer mean) split into two halves that are placed as
+//      separate items on two different GPUs (primary = home of the first half, replica = home of the second), so a
+//      replica is PLACED by load like any other item instead of being bolted on afterwards;
+//  (c) round robin (expert % n_gpus), the layout to beat.
+// Ties go to (b), then (a): a layer never ends up with a higher peak than round robin, and never with a replica that
+// raises its peak. (The reference places by (a) and then always gives a hot expert a replica on the least-loaded other
+// GPU, engine/src/routing/optimizer.rs:61-232; on skewed counts that step can undo the balance (a) had reached.)
 void ihb_placement_optimize(const unsigned* counts, int n_layers, int n_experts, int n_gpus, double hot_mult,
                             int* out_primary, int* out_replica, double* out_stats) {
   double rr_total = 0.0, opt_total = 0.0;
@@ -118,43 +172,39 @@ void ihb_placement_optimize(const unsigned* counts, int n_layers, int n_experts,
     const unsigned* c = counts + static_cast<size_t>(l) * n_experts;
     int* prim = out_primary + static_cast<size_t>(l) * n_experts;
     int* rep = out_replica + static_cast<size_t>(l) * n_experts;
-    std::vector<double> rr(n_gpus, 0.0);
-    for (int e = 0; e < n_experts; ++e) rr[e % n_gpus] += c[e];
-    rr_total += imbalance_of(rr);
+    Candidate rr;
+    rr.prim.resize(n_experts);
+    rr.rep.assign(n_experts, -1);
+    for (int e = 0; e < n_experts; ++e) rr.prim[e] = e % n_gpus;
+    std::vector<double> rr_load;
+    rr.peak = peak_of(c, n_experts, n_gpus, rr.prim, rr.rep, &rr_load);
+    rr_total += imbalance_of(rr_load);
 
-    // heaviest expert first onto the least-loaded GPU
-    std::vector<int> order(n_experts);
-    std::iota(order.begin(), order.end(), 0);
-    std::stable_sort(order.begin(), order.end(), [&](int a, int b) { return c[a] > c[b]; });
-    std::vector<uint64_t> load(n_gpus, 0);
-    for (int e : order) {
-      const int g = static_cast<int>(std::min_element(load.begin(), load.end()) - load.begin());
-      prim[e] = g;
-      load[g] += c[e];
-    }
-    // experts far above the layer mean get a second home that takes half their traffic
     uint64_t total = 0;
-    for (int e = 0; e < n_experts; ++e) { total += c[e]; rep[e] = -1; }
+    for (int e = 0; e < n_experts; ++e) total += c[e];
+    std::vector<char> none(n_experts, 0), hot(n_experts, 0);
+    bool any_hot = false;
     if (total > 0 && n_gpus > 1) {
-      const unsigned threshold = static_cast<unsigned>(hot_mult * (static_cast<double>(total) / n_experts));
-      for (int e : order) {
-        if (c[e] <= threshold) break;
-        int best = -1;
-        for (int g = 0; g < n_gpus; ++g)
-          if (g != prim[e] && (best < 0 || load[g] < load[best])) best = g;
-        rep[e] = best;
-        const uint64_t half = c[e] / 2;
-        load[best] += half;
-        load[prim[e]] -= std::min(load[prim[e]], half);
-        ++replicated;
+      const double threshold = hot_mult * (static_cast<double>(total) / n_experts);
+      for (int e = 0; e < n_experts; ++e) {
+        hot[e] = static_cast<double>(c[e]) > threshold;
+        any_hot = any_hot || hot[e];
       }
     }
-    std::vector<double> opt(n_gpus, 0.0);
-    for (int e = 0; e < n_experts; ++e) {
-      if (rep[e] >= 0) { opt[prim[e]] += 0.5 * c[e]; opt[rep[e]] += 0.5 * c[e]; }
-      else opt[prim[e]] += c[e];
+    Candidate best = place_lpt(c, n_experts, n_gpus, none);
+    if (any_hot) {
+      Candidate split = place_lpt(c, n_experts, n_gpus, hot);
+      if (split.peak <= best.peak) best = split;
     }
+    if (rr.peak < best.peak) best = rr;
+    std::vector<double> opt;
+    peak_of(c, n_experts, n_gpus, best.prim, best.rep, &opt);
     opt_total += imbalance_of(opt);
+    for (int e = 0; e < n_experts; ++e) {
+      prim[e] = best.prim[e];
+      rep[e] = best.rep[e];
+      replicated += rep[e] >= 0;
+    }
   }
   const double mean_rr = n_layers ? rr_total / n_layers : 1.0, mean_opt = n_layers ? opt_total / n_layers : 1.0;
   out_stats[0] = mean_rr;

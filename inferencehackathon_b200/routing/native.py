@@ -169,9 +169,12 @@ class PlacementMap:
 
 
 def optimize_placement(activation_counts, n_gpus: int, hot_mult: float = 2.0) -> Tuple[PlacementMap, Dict]:
-    """Per layer: heaviest expert first onto the least-loaded GPU, then experts firing more than ``hot_mult`` x the
-    layer mean get a replica (taking half their traffic) on the least-loaded other GPU. Returns the map and the
-    JSON document ``{placement, replicas, stats}``. Reference: engine/src/routing/optimizer.rs:61-232."""
+    """Per layer the best of three placements by peak GPU load: heaviest expert first onto the least-loaded GPU; the
+    same with every expert firing more than ``hot_mult`` x the layer mean split into two halves placed on two GPUs
+    (primary + replica, each taking half its traffic); round robin. A layer therefore never ends up above round robin,
+    nor with a replica that raises its peak. Returns the map and the JSON document ``{placement, replicas, stats}``.
+    Reference: engine/src/routing/optimizer.rs:61-232 (heaviest first, then a replica for every hot expert on the
+    least-loaded other GPU, which on skewed counts can undo the balance)."""
     counts = np.ascontiguousarray(activation_counts, dtype=np.uint32)
     n_layers, n_experts = counts.shape
     prim = np.zeros((n_layers, n_experts), np.int32)

@@ -221,3 +221,38 @@ def test_live_pipeline_scores_predictions_against_real_routing():
         for layer in range(L):
             out = p.on_layer(layer, [layer, layer + 1, layer + 2, layer + 3])
     assert out is None
+
+
+from hypothesis import given, settings, strategies as st   # noqa: E402
+
+
+@settings(max_examples=60, deadline=None)
+@given(st.integers(1, 4), st.sampled_from([8, 16, 32]), st.sampled_from([2, 4, 8]), st.integers(0, 2 ** 31 - 1))
+def test_placement_optimiser_invariants(n_layers, n_experts, n_gpus, seed):
+    """For any activation counts: every expert has exactly one primary GPU in range, a replica (if any) sits on another
+    GPU, the greedy placement never loads the busiest GPU more than round robin does (with replicas taking half of a
+    hot expert's traffic), and the JSON document round-trips."""
+    rng = np.random.default_rng(seed)
+    counts = (rng.pareto(1.2, size=(n_layers, n_experts)) * 50).astype(np.uint32)
+    pm, doc = rt.optimize_placement(counts, n_gpus)
+    prim, rep = np.asarray(pm.primary).reshape(n_layers, n_experts), np.asarray(pm.replica).reshape(n_layers, n_experts)
+    assert prim.min() >= 0 and prim.max() < n_gpus
+    has = rep >= 0
+    assert (rep[has] < n_gpus).all() and (rep[has] != prim[has]).all()
+    for layer in range(n_layers):
+        load = np.zeros(n_gpus)
+        rr = np.zeros(n_gpus)
+        for e in range(n_experts):
+            c = float(counts[layer, e])
+            if rep[layer, e] >= 0:
+                load[prim[layer, e]] += c / 2
+                load[rep[layer, e]] += c / 2
+            else:
+                load[prim[layer, e]] += c
+            rr[e % n_gpus] += c
+        assert load.max() <= rr.max() + 1e-6
+        assert abs(load.sum() - rr.sum()) < 1e-6 * max(1.0, rr.sum())
+    back = rt.PlacementMap.from_json(doc, n_gpus)
+    assert np.array_equal(np.asarray(back.primary), np.asarray(pm.primary))
+    assert np.array_equal(np.asarray(back.replica), np.asarray(pm.replica))
+    assert doc["stats"]["optimized_mean_imbalance"] <= doc["stats"]["round_robin_mean_imbalance"] + 1e-9
