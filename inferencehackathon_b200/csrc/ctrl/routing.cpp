@@ -15,6 +15,13 @@
 #include <vector>
 
 namespace {
+// expert ids wrap into [0, n) the way the placement lookups of the Python side do (id % n), negatives included:
+// a stray id must never index outside a table
+inline size_t wrap_id(int id, int n) {
+  const int m = id % n;
+  return static_cast<size_t>(m < 0 ? m + n : m);
+}
+
 
 float dotf(const float* a, const float* b, int n) {
   float s = 0.f;
@@ -56,10 +63,10 @@ struct Predictor {
     return true;
   }
   bool markov_scores(int layer, const int* cur, int n_cur, std::vector<float>& s) const {
-    if (!has_markov || layer + 1 >= n_layers || cur == nullptr || n_cur <= 0) return false;
+    if (!has_markov || layer < 0 || layer + 1 >= n_layers || cur == nullptr || n_cur <= 0) return false;
     s.assign(n_experts, 0.f);
     for (int i = 0; i < n_cur; ++i) {
-      const float* row = &markov[layer][static_cast<size_t>(cur[i] % n_experts) * n_experts];
+      const float* row = &markov[layer][wrap_id(cur[i], n_experts) * n_experts];
       float sum = 0.f;
       for (int j = 0; j < n_experts; ++j) sum += row[j];
       for (int j = 0; j < n_experts; ++j) s[j] += row[j] / sum;
@@ -261,7 +268,7 @@ void ihb_pred_markov_observe(void* h, int layer, const int* experts_l, int n_l, 
   if (!p->has_markov || layer < 0 || layer + 1 >= p->n_layers) return;
   for (int i = 0; i < n_l; ++i)
     for (int j = 0; j < n_l1; ++j)
-      p->markov[layer][static_cast<size_t>(experts_l[i] % p->n_experts) * p->n_experts + experts_l1[j] % p->n_experts] += 1.f;
+      p->markov[layer][wrap_id(experts_l[i], p->n_experts) * p->n_experts + wrap_id(experts_l1[j], p->n_experts)] += 1.f;
 }
 
 // kind: 0 proxy, 1 learned linear, 2 Markov, 3 ensemble (weights[3], each component L2-normalised before mixing).
@@ -319,7 +326,11 @@ void ihb_sched_set_sink(void* h, ihb_prefetch_sink_fn fn, void* ctx, int record)
 
 int ihb_sched_gpus_for(void* h, int layer, int expert, int* out_replica) {
   auto* s = static_cast<Scheduler*>(h);
-  const size_t i = static_cast<size_t>(layer) * s->n_experts + expert % s->n_experts;
+  if (layer < 0 || layer >= s->n_layers) {
+    if (out_replica) *out_replica = -1;
+    return -1;
+  }
+  const size_t i = static_cast<size_t>(layer) * s->n_experts + wrap_id(expert, s->n_experts);
   if (out_replica) *out_replica = s->replica[i];
   return s->primary[i];
 }
@@ -330,7 +341,7 @@ int ihb_sched_on_prediction(void* h, int layer, const int* experts, int n) {
   if (layer < 0 || layer >= s->n_layers) return 0;
   int issued = 0;
   for (int i = 0; i < n; ++i) {
-    const size_t at = static_cast<size_t>(layer) * s->n_experts + experts[i] % s->n_experts;
+    const size_t at = static_cast<size_t>(layer) * s->n_experts + wrap_id(experts[i], s->n_experts);
     const int homes[2] = {s->primary[at], s->replica[at]};
     for (int g : homes) {
       if (g < 0) continue;
@@ -341,15 +352,19 @@ int ihb_sched_on_prediction(void* h, int layer, const int* experts, int n) {
   }
   s->prefetched += n;
   s->pending.push_back({layer, std::vector<int>(experts, experts + n)});
+  while (s->pending.size() > 4 * static_cast<size_t>(s->n_layers) + 4) s->pending.pop_front();   // never grows without bound
   return issued;
 }
 
 void ihb_sched_on_layer_complete(void* h, int layer, const int* actual, int n) {
   auto* s = static_cast<Scheduler*>(h);
-  if (s->pending.empty() || s->pending.front().layer != layer) return;
-  for (int e : s->pending.front().experts)
+  // score the oldest pending prediction for this layer; predictions queued before it were for layers whose routing
+  // never arrived (a skipped layer, a stream that restarted): they stay counted as prefetched and are dropped
+  auto it = std::find_if(s->pending.begin(), s->pending.end(), [layer](const auto& p) { return p.layer == layer; });
+  if (it == s->pending.end()) return;
+  for (int e : it->experts)
     if (std::find(actual, actual + n, e) != actual + n) ++s->hits;
-  s->pending.pop_front();
+  s->pending.erase(s->pending.begin(), it + 1);
 }
 
 float ihb_sched_hit_rate(void* h) {
@@ -385,10 +400,12 @@ void ihb_acc_record(void* h, int layer, const int* predicted, int n_pred, const 
 }
 float ihb_acc_hit_rate(void* h, int layer) {
   auto* a = static_cast<Accuracy*>(h);
+  if (layer < 0 || layer >= a->n_layers) return 0.f;
   return a->total[layer] ? static_cast<float>(a->hits[layer]) / static_cast<float>(a->total[layer]) : 0.f;
 }
 unsigned long long ihb_acc_tokens(void* h, int layer) {
   auto* a = static_cast<Accuracy*>(h);
+  if (layer < 0 || layer >= a->n_layers) return 0;
   return a->top_k ? a->total[layer] / a->top_k : 0;
 }
 float ihb_acc_mean_hit_rate(void* h) {

@@ -256,3 +256,46 @@ def test_placement_optimiser_invariants(n_layers, n_experts, n_gpus, seed):
     assert np.array_equal(np.asarray(back.primary), np.asarray(pm.primary))
     assert np.array_equal(np.asarray(back.replica), np.asarray(pm.replica))
     assert doc["stats"]["optimized_mean_imbalance"] <= doc["stats"]["round_robin_mean_imbalance"] + 1e-9
+
+
+@settings(max_examples=50, deadline=None)
+@given(st.integers(2, 5), st.sampled_from([8, 16]), st.integers(1, 4), st.integers(0, 2 ** 31 - 1))
+def test_scheduler_and_predictor_invariants_on_arbitrary_routing(n_layers, n_experts, k, seed):
+    """Any routing stream, including out-of-range ids, repeated layers and layers out of order: counters stay consistent
+    (hits <= prefetched, rates in [0, 1]), a Markov prediction names distinct experts in range (its Laplace prior lets
+    it name experts it has not seen yet), once a transition dominates it is predicted, actions only name GPUs that hold
+    the expert, and nothing reads or writes outside a table (this test also runs under ASan in ops/sanitize_ctrl.py)."""
+    rng = np.random.default_rng(seed)
+    pm = rt.PlacementMap.round_robin(n_layers, 4, n_experts)
+    sched = rt.PrefetchScheduler(pm)
+    pred = rt.RoutePredictor(n_layers, 1, n_experts)
+    pred.enable_markov()
+    acc = rt.AccuracyTracker(n_layers, k)
+    seen_after = {}
+    prev = None
+    for _ in range(60):
+        layer = int(rng.integers(-1, n_layers + 1))                          # sometimes out of range
+        experts = [int(e) for e in rng.integers(-2, n_experts + 2, size=k)]    # sometimes out of range
+        if prev is not None and prev[0] == layer - 1 and 0 <= prev[0] < n_layers - 1:
+            pred.markov_observe(prev[0], prev[1], experts)
+            for a in prev[1]:
+                if 0 <= a < n_experts:
+                    seen_after.setdefault((prev[0], a), set()).update(e for e in experts if 0 <= e < n_experts)
+        sched.on_layer_complete(layer, experts)
+        if 0 <= layer < n_layers - 1:
+            p = pred.predict(layer, None, current_experts=experts, top_k=k, kind=rt.MARKOV)
+            assert len(set(p.experts)) == len(p.experts) <= k and p.layer == layer + 1
+            assert all(0 <= e < n_experts for e in p.experts)
+            if p.experts:
+                sched.on_prediction(p)
+                acc.record(p, layer + 1, experts)
+        prev = (layer, experts)
+    assert 0 <= sched.total_hits() <= sched.total_prefetched()
+    assert 0.0 <= sched.hit_rate() <= 1.0 and 0.0 <= acc.mean_hit_rate() <= 1.0
+    for a in sched.drain():
+        assert 0 <= a.layer < n_layers and a.gpu_id in [g for g in pm.gpus_for(a.layer, a.expert_id) if g is not None]
+    # a transition observed many times wins over the prior
+    for _ in range(40):
+        pred.markov_observe(0, [1], [n_experts - 1])
+    assert pred.predict(0, None, current_experts=[1], top_k=1, kind=rt.MARKOV).experts == [n_experts - 1]
+    assert acc.hit_rate(-1) == 0.0 and acc.hit_rate(n_layers + 3) == 0.0
