@@ -58,15 +58,24 @@ int sample_from(const std::vector<float>& p, float u) {
   return last;
 }
 
+// A drafted id outside the vocabulary (a drafter bug, a stale id map) has target probability 0: it is never accepted and
+// never used as an index.
+inline bool in_vocab(int x, int vocab) { return x >= 0 && x < vocab; }
+
 // residual of target p against a drafter that put probability q on token x only
-int sample_residual_point(std::vector<float> p, int x, float q, float u) {
-  if (x >= 0 && x < static_cast<int>(p.size())) p[x] = std::max(0.f, p[x] - q);
+int sample_residual_point(const std::vector<float>& target, int x, float q, float u) {
+  std::vector<float> p = target;
+  if (in_vocab(x, static_cast<int>(p.size()))) p[x] = std::max(0.f, p[x] - q);
   double total = 0.0;
   for (float v : p) total += v;
-  if (total < 1e-9) {   // degenerate: drafter mass covers the target mass
-    p[x] = 1.f;
-  }
+  if (total < 1e-9) return sample_from(target, u);   // degenerate: the drafter's mass covers the target's (all of it on x)
   return sample_from(p, u);
+}
+
+// parent of node n for the tree walks below: an index that is not a node, or the node itself, counts as the root
+inline int parent_of(const int* parent, int n, int n_nodes) {
+  const int p = parent[n];
+  return (p >= 0 && p < n_nodes && p != n) ? p : 0;
 }
 
 }  // namespace
@@ -81,7 +90,7 @@ int ihb_spec_accept(const float* target_logits, int vocab, int k, const int* dra
     softmax_row(target_logits + static_cast<size_t>(pos) * vocab, vocab, temperature, p);
     const int x = draft_tokens[pos];
     const float q = std::exp(draft_logprobs[pos]);
-    const float ratio = q > 0.f ? std::min(1.f, p[x] / q) : 1.f;
+    const float ratio = !in_vocab(x, vocab) ? 0.f : q > 0.f ? std::min(1.f, p[x] / q) : 1.f;
     if (rng_u[pos] < ratio) {
       out_tokens[accepted++] = x;
       continue;
@@ -106,7 +115,7 @@ int ihb_spec_accept_full(const float* target_logits, int vocab, int k, const int
     softmax_row(target_logits + static_cast<size_t>(pos) * vocab, vocab, temperature, p);
     const float* q = draft_probs + static_cast<size_t>(pos) * vocab;
     const int x = draft_tokens[pos];
-    const float ratio = q[x] > 0.f ? std::min(1.f, p[x] / q[x]) : 1.f;
+    const float ratio = !in_vocab(x, vocab) ? 0.f : q[x] > 0.f ? std::min(1.f, p[x] / q[x]) : 1.f;
     if (rng_u[pos] < ratio) {
       out_tokens[accepted++] = x;
       continue;
@@ -149,12 +158,13 @@ int ihb_spec_accept_multi(const float* target_logits, int vocab, int n_drafters,
       if (!alive[d]) continue;
       const int x = draft_tokens[d * k + pos];
       const float q = std::exp(draft_logprobs[d * k + pos]);
-      const float ratio = q > 0.f ? std::min(1.f, resid[x] / q) : 1.f;
+      const bool ok = in_vocab(x, vocab);
+      const float ratio = !ok ? 0.f : q > 0.f ? std::min(1.f, resid[x] / q) : 1.f;
       if (ratio > best_ratio) { best_ratio = ratio; best = d; }
       if (rng_u[ui++] < ratio) {
         taken = d;
       } else {                                   // SpecInfer-style: remove this drafter's mass, renormalise
-        resid[x] = std::max(0.f, resid[x] - q);
+        if (ok) resid[x] = std::max(0.f, resid[x] - q);
         double s = 0.0;
         for (float v : resid) s += v;
         if (s > 1e-12) for (float& v : resid) v = static_cast<float>(v / s);
@@ -198,10 +208,10 @@ int ihb_spec_accept_tree(int n_nodes, const int* tokens, const int* parent, cons
     for (int c : order) {
       const int x = tokens[c];
       const float q = std::exp(draft_logprob[c]);
-      const float px = (x >= 0 && x < vocab) ? p[x] : 0.f;
-      const float a = q > 0.f ? std::min(1.f, px / q) : 1.f;
+      const bool ok = in_vocab(x, vocab);
+      const float a = !ok ? 0.f : q > 0.f ? std::min(1.f, p[x] / q) : 1.f;
       if (next_u() < a) { go = c; break; }
-      if (x >= 0 && x < vocab) p[x] = std::max(0.f, p[x] - q);
+      if (ok) p[x] = std::max(0.f, p[x] - q);
       double s = 0.0;
       for (float v : p) s += v;
       if (s > 1e-12) for (float& v : p) v = static_cast<float>(v / s);
@@ -224,11 +234,13 @@ int ihb_tree_attn_build(int n_nodes, const int* parent, int context_len, int* ou
   int w = 0;
   out_anc_off[0] = 0;
   for (int i = 0; i < n_nodes; ++i) {
+    // a walk of more than n_nodes steps means the parent array has a cycle: it is cut there
     int depth = 0;
-    for (int n = i; n != 0; n = parent[n]) ++depth;
+    for (int n = i; n != 0 && depth < n_nodes; n = parent_of(parent, n, n_nodes)) ++depth;
     out_pos_id[i] = context_len + depth - 1;
     const int start = w;
-    for (int n = i; n != 0; n = parent[n]) out_anc_slots[w++] = context_len + (n - 1);
+    int steps = 0;
+    for (int n = i; n != 0 && steps < depth; n = parent_of(parent, n, n_nodes), ++steps) out_anc_slots[w++] = context_len + (n - 1);
     std::reverse(out_anc_slots + start, out_anc_slots + w);
     out_anc_off[i + 1] = w;
   }
@@ -240,8 +252,11 @@ int ihb_tree_attn_build(int n_nodes, const int* parent, int context_len, int* ou
 void ihb_tree_mask(int n_nodes, const int* parent, unsigned char* mask) {
   const int m = n_nodes - 1;
   std::memset(mask, 0, static_cast<size_t>(m) * m);
-  for (int i = 1; i < n_nodes; ++i)
-    for (int n = i; n != 0; n = parent[n]) mask[static_cast<size_t>(i - 1) * m + (n - 1)] = 1;
+  for (int i = 1; i < n_nodes; ++i) {
+    int steps = 0;
+    for (int n = i; n != 0 && steps < n_nodes; n = parent_of(parent, n, n_nodes), ++steps)
+      mask[static_cast<size_t>(i - 1) * m + (n - 1)] = 1;
+  }
 }
 
 // Top-m draft candidates: target token ids through d2t, log-probabilities from the DRAFT-space log-softmax.

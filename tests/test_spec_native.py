@@ -354,3 +354,57 @@ def test_tree_builder_rows_are_exactly_the_ancestor_chains(raw_parents, context_
         assert {c + 1 for c in range(n - 1) if mask[i - 1, c]} == set(chain)
         assert int(pos[i]) == context_len + len(chain) - 1
         assert slots[off[i]:off[i + 1]].tolist() == [context_len + a - 1 for a in chain]
+
+
+@settings(max_examples=150, deadline=None)
+@given(st.integers(2, 12), st.integers(1, 6), st.sampled_from([0.0, 0.3, 1.0, 7.5]), st.integers(0, 2 ** 31 - 1))
+def test_acceptance_routines_stay_in_bounds_on_adversarial_input(vocab, k, temperature, seed):
+    """Drafted token ids outside the vocabulary, log-probabilities of minus infinity, uniforms of exactly 0 and 1 and
+    huge logits: every routine returns tokens inside the vocabulary, accepts at most k drafts, emits n_accepted + 1
+    tokens, and touches no memory outside its arguments (this test also runs under ASan in ops/sanitize_ctrl.py)."""
+    rng = np.random.default_rng(seed)
+    rows = (rng.standard_normal((k + 1, vocab)) * rng.choice([1.0, 50.0])).astype(np.float32)
+    draft = [int(t) for t in rng.integers(-3, vocab + 3, size=k)]          # some ids are not in the vocabulary
+    lps = [float(x) for x in rng.choice([0.0, -0.5, -30.0, -np.inf], size=k)]
+    u = [float(x) for x in rng.choice([0.0, 1.0, 0.5, 0.999999], size=k + 1)]
+    toks, nacc = sp.accept_chain(rows, draft, lps, u, temperature=temperature)
+    assert 0 <= nacc <= k and len(toks) == nacc + 1 and all(0 <= t < vocab for t in toks[nacc:])
+    assert toks[:nacc] == draft[:nacc] and all(0 <= t < vocab for t in toks[:nacc])   # an id outside the vocabulary is never accepted
+    q = rng.random((k, vocab)).astype(np.float32)
+    q /= q.sum(1, keepdims=True)
+    toks, nacc = sp.accept_chain_full(rows, draft, q, u, temperature=temperature)
+    assert 0 <= nacc <= k and len(toks) == nacc + 1 and all(0 <= t < vocab for t in toks)
+    # a chain-shaped tree and a bushy tree over the same ids
+    chain = sp.SpecTree.chain(0, draft, lps)
+    trows = (rng.standard_normal((chain.n_nodes, vocab)) * 5).astype(np.float32)
+    toks, nodes = sp.accept_tree(chain, trows, [float(x) for x in rng.random(4 * chain.n_nodes + 4)], temperature=temperature)
+    assert 1 <= len(toks) <= k + 1 and len(nodes) == len(toks) - 1 and all(0 <= t < vocab for t in toks)
+    bushy = sp.SpecTree.root(0)
+    for i in range(k):
+        bushy.add(int(rng.integers(0, bushy.n_nodes)), draft[i], lps[i])
+    brows = (rng.standard_normal((bushy.n_nodes, vocab)) * 5).astype(np.float32)
+    toks, nodes = sp.accept_tree(bushy, brows, [float(x) for x in rng.random(4 * bushy.n_nodes + 4)], temperature=temperature)
+    assert 1 <= len(toks) <= k + 1 and all(0 <= t < vocab for t in toks)
+    assert all(bushy.parent[b] == a for a, b in zip([0] + nodes, nodes))    # the accepted nodes form a root path
+    # several drafters
+    n = 2
+    mt = np.stack([rows, rows[::-1].copy()])
+    md = rng.integers(-2, vocab + 2, size=(n, k))
+    res = sp.accept_multi(mt, md, np.zeros((n, k), np.float32), [float(x) for x in rng.random(n * k + 1)], temperature=temperature)
+    assert 0 <= res.n_accepted <= k and len(res.tokens) == res.n_accepted + 1 and all(0 <= t < vocab for t in res.tokens)
+
+
+@settings(max_examples=80, deadline=None)
+@given(st.lists(st.integers(-3, 14), min_size=1, max_size=12), st.integers(1, 32))
+def test_tree_builder_terminates_on_malformed_parent_arrays(parent, context_len):
+    """Parents that are negative, out of range, self-referencing or cyclic: the builder and the mask return (a walk is
+    cut after n steps, an invalid parent counts as the root), every position stays within context_len - 1 + n and every
+    slot within the draft rows."""
+    n = len(parent)
+    pos, off, slots = sp.tree_attn_build(parent, context_len)
+    mask = sp.tree_mask(parent)
+    assert mask.shape == (max(n - 1, 0), max(n - 1, 0))
+    assert all(context_len - 1 <= int(p) <= context_len - 1 + n for p in pos)
+    assert all(context_len <= int(s) < context_len + n for s in slots) and int(off[-1]) == len(slots)
+    for i in range(1, n):
+        assert mask[i - 1, i - 1]                                           # a node always sees itself
