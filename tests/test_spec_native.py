@@ -408,3 +408,48 @@ def test_tree_builder_terminates_on_malformed_parent_arrays(parent, context_len)
     assert all(context_len <= int(s) < context_len + n for s in slots) and int(off[-1]) == len(slots)
     for i in range(1, n):
         assert mask[i - 1, i - 1]                                           # a node always sees itself
+
+
+@settings(max_examples=100, deadline=None)
+@given(st.integers(1, 10), st.integers(0, 2 ** 31 - 1))
+def test_cost_models_and_selection_on_arbitrary_input(k, seed):
+    """Verify-depth planner, tree-shape model, route-aware selection and the draft-candidate mapping with arbitrary
+    (also out-of-range, negative or empty) ids and extreme parameters: results stay in range and finite."""
+    rng = np.random.default_rng(seed)
+    probs = rng.random(k).tolist()
+    experts = [[int(e) for e in rng.integers(-5, 5000, size=int(rng.integers(0, 9)))] for _ in range(k)]
+    plan = sp.adaptive_verify_depth(probs, experts, floor_fraction=float(rng.choice([0.0, 0.5, 0.86, 1.0])))
+    assert 1 <= plan.depth <= k and np.isfinite([plan.emitted, plan.cost, plan.value]).all() and plan.cost > 0
+    assert plan.union_size <= sum(len(e) for e in experts[: plan.depth])
+    # fewer experts per position than positions (a short list): treated as empty, no read past the list
+    assert 1 <= sp.adaptive_verify_depth(probs, experts[: k // 2]).depth <= k
+    shape = sp.tree_shape_optimal(float(rng.uniform(1.0, 9.0)), float(rng.uniform(0.05, 1.0)),
+                                  node_budget=int(rng.integers(1, 200)), max_branch=int(rng.integers(1, 9)),
+                                  max_depth=int(rng.integers(1, 9)))
+    assert shape.branch >= 1 and shape.depth >= 1 and np.isfinite([shape.emitted, shape.speedup]).all()
+    for p in (0.0, 0.3, 1.0):
+        for b in (1, 4):
+            assert 0.0 <= sp.level_advance_prob(p, b) <= 1.0 + 1e-6
+    union = sp.ExpertUnion([int(e) for e in rng.integers(-10, 9000, size=12)])
+    idx = sp.route_aware_select((-rng.random(k) * 5).tolist(), experts, union, float(rng.choice([0.0, 0.5, 100.0])))
+    assert 0 <= idx < k
+    dv = int(rng.integers(1, 12))
+    d2t = rng.integers(0, 50, size=dv).astype(np.int32)
+    toks, lps = sp.draft_top_candidates(rng.standard_normal(dv) * rng.choice([1.0, 80.0]), int(rng.integers(1, 20)), d2t)
+    assert 1 <= len(toks) <= dv and all(t in set(d2t.tolist()) for t in toks)
+    assert all(np.isfinite(lp) and lp <= 1e-5 for lp in lps) and lps == sorted(lps, reverse=True)
+
+
+@settings(max_examples=40, deadline=None)
+@given(st.lists(st.integers(-2, 8), min_size=2, max_size=7), st.integers(0, 5), st.integers(0, 2 ** 31 - 1))
+def test_tree_attention_oracle_is_finite_on_any_parent_array(parent, ctx, seed):
+    """The fp32 tree-attention oracle with malformed parent arrays (negative, out of range, cycles) and an empty
+    context: it returns, the root row stays zero and every other row is finite."""
+    rng = np.random.default_rng(seed)
+    n, n_q, n_kv, hd = len(parent), 4, 2, 8
+    q = rng.standard_normal((n, n_q, hd)).astype(np.float32)
+    out = sp.sdpa_tree_ref(parent, ctx, q, rng.standard_normal((n_kv, ctx, hd)).astype(np.float32),
+                           rng.standard_normal((n_kv, ctx, hd)).astype(np.float32),
+                           rng.standard_normal((n, n_kv, hd)).astype(np.float32),
+                           rng.standard_normal((n, n_kv, hd)).astype(np.float32), np.ones(hd, np.float32), np.ones(hd, np.float32))
+    assert out.shape == q.shape and np.isfinite(out).all() and not out[0].any()
