@@ -210,3 +210,66 @@ def test_k_split_rule_of_the_window_gemms():
     for tiles, nkb, T in [(10, 64, 8), (72, 64, 16), (32, 16, 8), (1, 3, 1)]:
         ks = GpuWindow._k_split(_W, tiles, nkb, T)
         assert 1 <= ks <= min(nkb, 16)
+
+
+# ---- property-based checks ------------------------------------------------------------------------------------------------------------
+from hypothesis import given, settings, strategies as st   # noqa: E402
+
+
+@settings(max_examples=60, deadline=None)
+@given(st.integers(1, 70), st.integers(1, 90), st.sampled_from([8, 16, 32]), st.sampled_from([8, 16, 32]), st.integers(0, 2 ** 31 - 1))
+def test_block_quantisation_round_trip_and_sub_matrix_scales(rows, K, rb, kb, seed):
+    """Any matrix size (not a multiple of the block), any block shape: de-quantised values are within half an e4m3 step of
+    the input relative to the block's largest value, and the scales of any block-aligned-or-not sub-matrix, re-blocked by
+    ``reblock_scales``, de-quantise that sub-matrix to the same numbers as the full matrix does."""
+    from inferencehackathon_b200.models.quant import dequant_block, quant_block, reblock_scales
+    g = torch.Generator().manual_seed(seed)
+    w = torch.randn(rows, K, generator=g) * torch.rand(1, generator=g) * 10
+    qw = quant_block(w, rb, kb)
+    deq = dequant_block(qw.data, qw.scale, rb, kb)
+    assert deq.shape == w.shape
+    amax_blocks = qw.scale.repeat_interleave(rb, 0)[:rows].repeat_interleave(kb, 1)[:, :K] * 448.0
+    assert float(((deq - w).abs() / amax_blocks).max()) <= 2 ** -4 + 1e-6          # e4m3: 3 mantissa bits
+    r0 = int(torch.randint(0, rows, (1,), generator=g))
+    k0 = int(torch.randint(0, K, (1,), generator=g))
+    nr = int(torch.randint(1, rows - r0 + 1, (1,), generator=g))
+    nk = int(torch.randint(1, K - k0 + 1, (1,), generator=g))
+    sub, rb2, kb2 = reblock_scales(qw.scale, rb, kb, r0, nr, k0, nk)
+    assert rb % rb2 == 0 and kb % kb2 == 0
+    deq_sub = dequant_block(qw.data[r0:r0 + nr, k0:k0 + nk], sub, rb2, kb2)
+    assert torch.equal(deq_sub, deq[r0:r0 + nr, k0:k0 + nk])
+
+
+@settings(max_examples=80, deadline=None)
+@given(st.sampled_from(["tiny", "small", "qwen3-30b-a3b", "qwen3-235b-a22b"]), st.sampled_from([1, 2, 4, 8]),
+       st.sampled_from(["tp", "ep", "hybrid"]), st.sampled_from([1, 2, 4]))
+def test_shards_of_all_ranks_tile_every_dimension_exactly_once(model, world, plan, attn_tp):
+    """For every valid layout: the ranks' query heads, expert-intermediate columns / experts and vocabulary rows
+    partition their ranges (no gap, no overlap), and every KV head is held by the ranks whose query heads use it."""
+    from inferencehackathon_b200.models.weights import shard_geometry
+    cfg = get_model_config(model)
+    tp, ep = {"tp": (world, 1), "ep": (1, world), "hybrid": (min(attn_tp, world), world)}[plan]
+    if world == 1:
+        tp, ep = 1, 1
+    try:
+        geoms = [shard_geometry(cfg, ParallelConfig(tp=tp, ep=ep, rank=r, world=world)) for r in range(world)]
+    except ValueError:
+        return                                                              # a layout the model's shapes do not allow
+    vocab = sorted((g.vocab0, g.vocab0 + g.vocab_local) for g in geoms)
+    assert vocab[0][0] == 0 and all(a[1] == b[0] for a, b in zip(vocab, vocab[1:])) and vocab[-1][1] == cfg.vocab
+    groups = world // tp                                                    # attention is replicated across tp groups
+    heads = sorted((g.q_head0, g.q_head0 + g.nq_local) for g in geoms)
+    for h in range(cfg.n_q_heads):
+        assert sum(1 for a, b in heads if a <= h < b) == groups
+    q_per_kv = cfg.n_q_heads // cfg.n_kv_heads
+    for g in geoms:
+        used = {h // q_per_kv for h in range(g.q_head0, g.q_head0 + g.nq_local)}
+        assert used <= set(range(g.kv_head0, g.kv_head0 + g.nkv_local))
+    if ep > 1:
+        ex = sorted((g.expert0, g.expert0 + g.n_experts_local) for g in geoms)
+        assert ex[0][0] == 0 and all(a[1] == b[0] for a, b in zip(ex, ex[1:])) and ex[-1][1] == cfg.n_experts
+        assert all(g.inter_local == cfg.moe_inter and g.inter0 == 0 for g in geoms)
+    else:
+        cols = sorted((g.inter0, g.inter0 + g.inter_local) for g in geoms)
+        assert cols[0][0] == 0 and all(a[1] == b[0] for a, b in zip(cols, cols[1:])) and cols[-1][1] == cfg.moe_inter
+        assert all(g.n_experts_local == cfg.n_experts for g in geoms)
