@@ -226,3 +226,23 @@ def test_tree_beam_budget_and_spec_bench_cli(capsys):
     line = _json.loads(capsys.readouterr().out.strip().splitlines()[-1])
     assert line["ngram"]["lossless"] and line["eagle_tree"]["lossless"]
     assert line["ngram"]["forwards_per_token"] <= 1.0 + 1e-9
+
+
+from hypothesis import HealthCheck, given, settings, strategies as st   # noqa: E402
+
+
+@settings(max_examples=12, deadline=None, suppress_health_check=[HealthCheck.function_scoped_fixture])
+@given(st.integers(1, 7), st.integers(1, 3), st.integers(1, 3), st.integers(2, 20), st.integers(0, 10 ** 6))
+def test_greedy_speculation_is_lossless_for_any_depth_drafter_order_and_prompt(tiny, depth, n, min_n, block, seed):
+    """The central invariant, over random draft depths, n-gram orders and prompts (repetitive enough that drafts get
+    accepted, random enough that many get rejected): greedy speculative decoding emits exactly plain greedy decoding's
+    tokens, with no more target forwards than tokens."""
+    eng = tiny[0]
+    rng = np.random.default_rng(seed)
+    prompt = (rng.integers(0, 2048, block).tolist() * 3)[: 40] + rng.integers(0, 2048, 3).tolist()
+    plain = eng.generate(prompt, 12).tokens
+    r = D.EngineRunner(eng)
+    se = D.SpecEngine(r, D.ChainDrafterPool([ngram.NGramDrafter(max(n, min_n), min_n=min(n, min_n))]),
+                      D.SpecConfig(depth, 2048, 0.0))
+    out, _tel = se.decode(prompt, D.DecodeStop(12), D.Rng(seed))
+    assert out == plain and r.forwards <= 12
