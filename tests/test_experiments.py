@@ -233,3 +233,31 @@ def test_scaling_fit_separates_the_byte_part_from_the_fixed_part():
     assert 2.5 < m["fixed_ms"] < 3.6 and m["rows"][-1]["fixed_share"] > 0.75 and m["max_fit_error_ms"] < 0.7
     assert m["rows"][-1]["tok_s_if_fixed_halves"] > 1.5 * m["rows"][-1]["tok_s"]
     assert studies.main(["scaling-fit"]) == 0 and studies.main(["scaling-fit", "1:8.0", "2:5.0", "4:3.5"]) == 0
+
+
+from hypothesis import given, settings, strategies as st   # noqa: E402
+
+
+@settings(max_examples=80, deadline=None)
+@given(st.integers(1, 300), st.sampled_from([1, 4, 16, 128]), st.sampled_from([16, 32, 64]), st.integers(0, 2 ** 31 - 1))
+def test_expert_group_table_oracle_tiles_every_pair_exactly_once(pairs, n_experts, nt, seed):
+    """The oracle of the device group-table kernel, for any routing: the groups are contiguous runs of the pairs sorted by
+    expert, each within one expert and at most ``nt`` rows long, together they cover every pair once, the entries past
+    ``n_groups`` are empty, and the shape-only bound G is never exceeded."""
+    import torch
+    from inferencehackathon_b200.runtime.gpu_window import GpuWindow
+    g = torch.Generator().manual_seed(seed)
+    skew = torch.rand(n_experts, generator=g) ** 3 + 1e-3                  # a few hot experts, many cold ones
+    flat_e = torch.multinomial(skew, pairs, replacement=True, generator=g)
+    order, groups, n_groups, gmax = GpuWindow._group_table(flat_e, n_experts, nt)
+    n = int(n_groups[0])
+    assert groups.shape == (gmax, 4) and n <= gmax
+    sorted_e = flat_e[order]
+    assert torch.equal(sorted_e, torch.sort(flat_e).values) and sorted(order.tolist()) == list(range(pairs))
+    covered = 0
+    for e, first, rows, _ in groups[:n].tolist():
+        assert 1 <= rows <= nt and first == covered                         # consecutive, no gap, no overlap
+        assert bool((sorted_e[first:first + rows] == e).all())
+        covered += rows
+    assert covered == pairs
+    assert int(groups[n:, 2].sum()) == 0
