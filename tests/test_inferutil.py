@@ -233,3 +233,33 @@ def test_kv_row_split_trades_kv_bytes_for_two_exchanges_per_layer():
     c4 = Cluster(g, 4)
     assert decode_latency(QWEN3_235B, c4, seq_len=32768, kv_seq_split=True, **kw).total_s == \
         decode_latency(QWEN3_235B, c4, seq_len=32768, **kw).total_s
+
+
+from hypothesis import given, settings, strategies as st   # noqa: E402
+
+
+@settings(max_examples=40, deadline=None)
+@given(st.integers(1, 3), st.sampled_from([8, 16]), st.sampled_from([2, 4, 8]), st.integers(0, 2 ** 31 - 1))
+def test_co_activation_partition_places_every_expert_once_with_even_counts(n_layers, n_experts, n_gpus, seed):
+    """For any co-activation history: every (layer, expert) gets one GPU in range, every GPU holds exactly
+    n_experts / n_gpus experts of a layer, and the edge weight between GPUs plus the weight kept inside GPUs is the
+    graph's total (nothing counted twice)."""
+    import random
+    from inferutil.routing import CoActGraph, greedy_partition, placement_stats, round_robin_placement
+    rng = random.Random(seed)
+    g = CoActGraph(n_experts=n_experts, n_layers=n_layers)
+    for _ in range(60):
+        for layer in range(n_layers):
+            g.add_token_step(layer, rng.sample(range(n_experts), 4))
+    pl = greedy_partition(g, n_gpus=n_gpus, n_experts=n_experts, n_layers=n_layers)
+    assert sorted(pl) == list(range(n_layers * n_experts)) and all(0 <= v < n_gpus for v in pl.values())
+    for layer in range(n_layers):
+        per_gpu = [0] * n_gpus
+        for e in range(n_experts):
+            per_gpu[pl[g.node_id(layer, e)]] += 1
+        assert per_gpu == [n_experts // n_gpus] * n_gpus
+    cross = g.cross_gpu_weight(pl)
+    assert 0 <= cross <= g.total_edge_weight()
+    rr = round_robin_placement(n_gpus, n_experts, n_layers)
+    st_g, st_r = placement_stats(g, pl, "greedy"), placement_stats(g, rr, "rr")
+    assert st_g["label"] == "greedy" and st_r["label"] == "rr"

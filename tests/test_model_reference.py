@@ -119,3 +119,49 @@ def test_torch_kv_scattered_rows_match_contiguous_writes():
         ka, va = a.read(0, 9)
         kb, vb = b.read(0, 9)
         assert torch.equal(ka.float(), kb.float()) and torch.equal(va.float(), vb.float())
+
+
+from hypothesis import given, settings, strategies as st   # noqa: E402
+
+
+@settings(max_examples=80, deadline=None)
+@given(st.integers(2, 40), st.sampled_from([0.0, 0.2, 1.0, 3.0]), st.integers(0, 12), st.sampled_from([1.0, 0.9, 0.5, 0.05]),
+       st.integers(0, 2 ** 31 - 1))
+def test_sampler_distribution_invariants(vocab, temperature, top_k, top_p, seed):
+    """For any logits and settings: the distribution sums to one, greedy is a point mass on the arg-max, top-k keeps at
+    most k tokens (the k largest), top-p keeps the smallest prefix of the sorted distribution whose mass reaches p, and
+    a draw always comes from the support."""
+    from inferencehackathon_b200.runtime.sampler import Sampler, SamplingParams
+    g = torch.Generator().manual_seed(seed)
+    logits = torch.randn(vocab, generator=g) * 3
+    s = Sampler(SamplingParams(temperature=temperature, top_k=top_k, top_p=top_p, seed=seed))
+    p = s.probs(logits)
+    assert p.shape == logits.shape and abs(float(p.sum()) - 1.0) < 1e-5 and float(p.min()) >= 0.0
+    support = set(torch.nonzero(p).flatten().tolist())
+    if temperature <= 0.0:
+        assert support == {int(logits.argmax())}
+    else:
+        if top_k and top_k < vocab:
+            assert support <= set(torch.topk(logits, top_k).indices.tolist())           # random logits have no ties
+        if top_p < 1.0:
+            ref = Sampler(SamplingParams(temperature=temperature, top_k=top_k, top_p=1.0)).probs(logits)
+            sp_, si = torch.sort(ref, descending=True)
+            before = sp_.cumsum(0) - sp_
+            assert support == set(si[before < top_p].tolist())
+        assert int(logits.argmax()) in support
+    assert int(s.sample(logits)) in support
+
+
+@settings(max_examples=60, deadline=None)
+@given(st.text(alphabet=st.characters(min_codepoint=32, max_codepoint=126), min_size=0, max_size=40),
+       st.sampled_from([256, 2048, 151936]))
+def test_byte_tokenizer_round_trips_printable_text(text, vocab):
+    from inferencehackathon_b200.serve.tokenizer import ByteTokenizer
+    tok = ByteTokenizer(vocab)
+    ids = tok.encode(text)
+    assert ids and all(0 <= i < vocab for i in ids)
+    if text:
+        assert tok.decode(ids) == text
+    # ids outside the printable range still map to distinct readable pieces
+    pieces = {tok.piece(i) for i in (0, 5, 127, 200, vocab - 1)}
+    assert len(pieces) == len({0, 5, 127, 200, vocab - 1})
