@@ -246,3 +246,35 @@ def test_greedy_speculation_is_lossless_for_any_depth_drafter_order_and_prompt(t
                       D.SpecConfig(depth, 2048, 0.0))
     out, _tel = se.decode(prompt, D.DecodeStop(12), D.Rng(seed))
     assert out == plain and r.forwards <= 12
+
+
+def _ngram_oracle(ctx, k, n, min_n):
+    L = len(ctx)
+    for g in range(min(n, L), min_n - 1, -1):
+        suffix = ctx[L - g:]
+        for end in range(L - 1, g - 1, -1):                                 # latest earlier occurrence first
+            if ctx[end - g:end] == suffix:
+                return ctx[end:end + k]
+    return []
+
+
+@settings(max_examples=150, deadline=None)
+@given(st.integers(1, 4), st.integers(1, 4), st.integers(1, 6),
+       st.lists(st.tuples(st.sampled_from(["extend", "rollback", "replace"]), st.integers(1, 9), st.integers(0, 2 ** 31 - 1)),
+                min_size=1, max_size=12))
+def test_ngram_drafter_with_incremental_index_equals_a_rescan(n, min_n, k, ops):
+    """One drafter instance across any sequence of context extensions, rollbacks and rewrites (what speculative rounds
+    with rejections produce): its proposal always equals a from-scratch scan for the latest earlier match."""
+    n, min_n = max(n, min_n), min(n, min_n)
+    d = ngram.NGramDrafter(n, min_n=min_n)
+    ctx = []
+    for op, amount, seed in ops:
+        rng = np.random.default_rng(seed)
+        if op == "extend":
+            ctx = ctx + rng.integers(0, 3, amount).tolist()                 # a tiny vocabulary: matches are frequent
+        elif op == "rollback":
+            ctx = ctx[: max(0, len(ctx) - amount)]
+        else:
+            cut = max(0, len(ctx) - amount)
+            ctx = ctx[:cut] + rng.integers(0, 3, amount).tolist()           # the tail is rewritten with other tokens
+        assert d.propose(ctx, k) == _ngram_oracle(ctx, k, n, min_n)
