@@ -267,3 +267,20 @@ def test_package_command_line_generates_and_reports(capsys):
     info = json.loads(capsys.readouterr().out)
     assert set(info["native_libraries"]) == {"libihb_kernels.so", "libihb_ctrl.so"}
     assert info["presets"]["qwen3-235b-a22b"]["experts"] == 128 and info["presets"]["tiny"]["layers"] == 4
+
+
+from hypothesis import given, settings, strategies as st   # noqa: E402
+
+
+@settings(max_examples=150, deadline=None)
+@given(st.text(max_size=300), st.text(max_size=300))
+def test_metric_scrape_parser_never_raises_and_keeps_rates_in_range(before, after):
+    """Arbitrary scrape text (truncated lines, odd numbers, binary junk) around the counters: the parser returns finite
+    numbers, an accept rate in [0, 1] and tau >= 1."""
+    import math
+    from inferencehackathon_b200.serve.spec_metrics import accept_stats, cumulative_accept
+    head = 'vllm:spec_decode_num_accepted_tokens_total{model="m"} 12\nvllm:spec_decode_num_drafts_total 20\n'
+    for b, a in ((before, after), (head + before, head + after), (before, head + after)):
+        for r in (accept_stats(b, a), cumulative_accept(a)):
+            assert all(math.isfinite(float(v)) for v in r.values())
+            assert 0.0 <= r["accept_rate"] <= 1.0 and r["tau"] >= 1.0 and r["accepted"] >= 0.0 and r["drafts"] >= 0.0
