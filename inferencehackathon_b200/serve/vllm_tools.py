@@ -238,9 +238,11 @@ class RoutingFeedReader:
     def _take(self, line: bytes) -> None:
         try:
             rec = json.loads(line)
+            if not isinstance(rec, dict):
+                return
             tok, layer, experts = int(rec.get("token", 0)), int(rec["layer"]), [int(e) for e in rec["experts"]]
-        except (ValueError, KeyError, TypeError):
-            return
+        except (ValueError, KeyError, TypeError, OverflowError, RecursionError):
+            return                              # a malformed line must not end the reader thread
         with self._lock:
             self.records += 1
             self._recent.append({"token": tok, "layer": layer, "experts": experts})

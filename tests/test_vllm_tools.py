@@ -202,3 +202,25 @@ def test_fed_routing_drives_the_prediction_pipeline(tmp_path, monkeypatch):
     assert st["tokens"] == 12 and st["prefetched"] > 0 and st["prefetch_hit_rate"] > 0.5
     be.feed.close()
     feed.close()
+
+
+def test_reader_survives_any_line():
+    """Lines that are not records (JSON of another shape, numbers that do not fit, binary junk) are skipped."""
+    from hypothesis import given, settings, strategies as st
+
+    reader = vt.RoutingFeedReader("/nonexistent/never.sock", retry_s=10.0)
+
+    @settings(max_examples=200, deadline=None)
+    @given(st.one_of(st.binary(max_size=60), st.sampled_from([b"[1,2]", b"3", b"null", b'"x"', b'{"layer":1}',
+                                                                b'{"layer":"a","experts":[1]}', b'{"layer":1,"experts":7}',
+                                                                b'{"layer":1e999,"experts":[1]}', b'{"layer":1,"experts":[[]]}',
+                                                                b'{"token":null,"layer":2,"experts":[1]}'])))
+    def feed(line):
+        before = reader.records
+        reader._take(line)
+        assert reader.records in (before, before + 1)
+
+    feed()
+    reader._take(b'{"token": 3, "layer": 1, "experts": [4, 5]}')
+    assert reader.layers_of(3) == {1: [4, 5]}
+    reader.close()
