@@ -41,8 +41,23 @@ def _load_placement(num_layers: int, experts_per_layer: int, num_gpus: int, path
                 table = json.load(f)["placement"]
     except Exception:
         table = {}
-    return {str(L): {str(e): int(table.get(str(L), {}).get(str(e), e % num_gpus)) for e in range(experts_per_layer)}
-            for L in range(num_layers)}
+    if not isinstance(table, dict):
+        table = {}
+
+    def gpu_of(L: int, e: int) -> int:
+        # a file written for another model or GPU count, or damaged: entries that are missing, not integers or name a
+        # GPU that is not there fall back to round robin one by one
+        row = table.get(str(L))
+        v = row.get(str(e)) if isinstance(row, dict) else None
+        if isinstance(v, bool) or not isinstance(v, (int, float, str)):
+            return e % num_gpus
+        try:
+            g = int(v)
+        except (ValueError, OverflowError):
+            return e % num_gpus
+        return g if 0 <= g < num_gpus else e % num_gpus
+
+    return {str(L): {str(e): gpu_of(L, e) for e in range(experts_per_layer)} for L in range(num_layers)}
 
 
 def build_topology(num_layers: int = 94, experts_per_layer: int = 128, placement_fn=None) -> dict:

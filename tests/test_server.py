@@ -284,3 +284,25 @@ def test_metric_scrape_parser_never_raises_and_keeps_rates_in_range(before, afte
         for r in (accept_stats(b, a), cumulative_accept(a)):
             assert all(math.isfinite(float(v)) for v in r.values())
             assert 0.0 <= r["accept_rate"] <= 1.0 and r["tau"] >= 1.0 and r["accepted"] >= 0.0 and r["drafts"] >= 0.0
+
+
+_json_values = st.recursive(st.none() | st.booleans() | st.integers(-5, 20) | st.floats(allow_nan=False, allow_infinity=True) | st.text(max_size=4),
+                            lambda c: st.lists(c, max_size=3) | st.dictionaries(st.sampled_from(["0", "1", "2", "placement", "x"]), c, max_size=4),
+                            max_leaves=12)
+
+
+@settings(max_examples=120, deadline=None)
+@given(_json_values)
+def test_placement_file_of_any_shape_yields_a_complete_in_range_table(tmp_path_factory, doc):
+    """Whatever JSON the placement file holds (another model's table, wrong types, GPUs that are not there), the topology
+    has one GPU in range for every (layer, expert); valid entries are kept, the rest fall back to round robin."""
+    from pathlib import Path
+    from inferencehackathon_b200.serve.topology import _load_placement
+    path = Path(tmp_path_factory.mktemp("pl")) / "placement.json"
+    path.write_text(json.dumps({"placement": doc}) if not isinstance(doc, float) else json.dumps({"placement": None}))
+    table = _load_placement(3, 4, 2, path)
+    assert sorted(table) == ["0", "1", "2"]
+    for L, row in table.items():
+        assert sorted(row) == ["0", "1", "2", "3"] and all(isinstance(g, int) and 0 <= g < 2 for g in row.values())
+    if isinstance(doc, dict) and isinstance(doc.get("1"), dict) and doc["1"].get("2") in (0, 1) and not isinstance(doc["1"].get("2"), bool):
+        assert table["1"]["2"] == doc["1"]["2"]
