@@ -153,18 +153,30 @@ class PlacementMap:
 
     @classmethod
     def from_json(cls, obj: Dict, n_gpus: Optional[int] = None) -> "PlacementMap":
-        pl = obj["placement"]
-        n_layers = len(pl)
-        n_experts = max(len(v) for v in pl.values())
-        prim = np.zeros((n_layers, n_experts), np.int32)
+        """Inverse of :meth:`to_json`. Layers or experts a document leaves out are placed round robin; anything that is
+        not a table of non-negative integers raises ``ValueError`` (never an index or type error from the inside)."""
+        try:
+            pl = obj["placement"]
+            rows = {int(l): {int(e): int(g) for e, g in row.items()} for l, row in pl.items()}
+            reps = {int(l): {int(e): int(g) for e, g in row.items()} for l, row in (obj.get("replicas") or {}).items()}
+        except (KeyError, TypeError, ValueError, AttributeError, OverflowError) as err:
+            raise ValueError(f"not a placement document: {type(err).__name__}: {err}") from None
+        ids = [l for l in rows] + [e for r in rows.values() for e in r] + [g for r in rows.values() for g in r.values()]
+        ids += [l for l in reps] + [e for r in reps.values() for e in r] + [g for r in reps.values() for g in r.values()]
+        if not rows or not any(rows.values()) or min(ids) < 0 or max(ids) > 1 << 20:
+            raise ValueError("not a placement document: empty, or an id that is negative or absurdly large")
+        n_layers = max(list(rows) + list(reps)) + 1
+        n_experts = max(e for r in list(rows.values()) + list(reps.values()) for e in r) + 1
+        stated = obj.get("stats", {}).get("n_gpus") if isinstance(obj.get("stats"), dict) else None
+        ng = int(n_gpus or stated or max(g for r in rows.values() for g in r.values()) + 1)
+        prim = (np.arange(n_experts, dtype=np.int32)[None, :] % ng).repeat(n_layers, 0)
         rep = np.full((n_layers, n_experts), -1, np.int32)
-        for l, row in pl.items():
+        for l, row in rows.items():
             for e, g in row.items():
-                prim[int(l), int(e)] = g
-        for l, row in obj.get("replicas", {}).items():
+                prim[l, e] = g
+        for l, row in reps.items():
             for e, g in row.items():
-                rep[int(l), int(e)] = g
-        ng = n_gpus or int(obj.get("stats", {}).get("n_gpus", prim.max() + 1))
+                rep[l, e] = g
         return cls(prim, rep, ng)
 
 

@@ -299,3 +299,22 @@ def test_scheduler_and_predictor_invariants_on_arbitrary_routing(n_layers, n_exp
         pred.markov_observe(0, [1], [n_experts - 1])
     assert pred.predict(0, None, current_experts=[1], top_k=1, kind=rt.MARKOV).experts == [n_experts - 1]
     assert acc.hit_rate(-1) == 0.0 and acc.hit_rate(n_layers + 3) == 0.0
+
+
+_doc_values = st.recursive(st.none() | st.booleans() | st.integers(-3, 40) | st.text(alphabet="0123456789x-", max_size=3),
+                           lambda c: st.lists(c, max_size=3) | st.dictionaries(st.sampled_from(["0", "1", "3", "x", "placement", "replicas", "stats", "n_gpus"]), c, max_size=4),
+                           max_leaves=14)
+
+
+@settings(max_examples=200, deadline=None)
+@given(_doc_values)
+def test_placement_document_reader_accepts_or_refuses_cleanly(doc):
+    """Any JSON-like document: the reader returns a complete map (missing entries round robin) or raises ValueError."""
+    try:
+        pm = rt.PlacementMap.from_json(doc if isinstance(doc, dict) else {"placement": doc})
+    except ValueError:
+        return
+    prim, rep = np.asarray(pm.primary), np.asarray(pm.replica)
+    assert prim.shape == rep.shape and prim.ndim == 2 and prim.size > 0 and prim.min() >= 0 and rep.min() >= -1
+    back = rt.PlacementMap.from_json(pm.to_json(), pm.n_gpus)
+    assert np.array_equal(np.asarray(back.primary), prim) and np.array_equal(np.asarray(back.replica), rep)
