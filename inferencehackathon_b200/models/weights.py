@@ -302,9 +302,37 @@ def _common_rb(sizes, block: int) -> int:
 def shard_state_dict(source, cfg: ModelConfig, par: ParallelConfig, quant: QuantConfig,
                      device="cpu", small_dtype=torch.float32) -> ModelWeights:
     """Build one rank's :class:`ModelWeights` from a full HF-named state dict or safetensors directory."""
-    get = _Getter(source)
+    raw = _Getter(source)
     geom = shard_geometry(cfg, par)
     hd, H = cfg.head_dim, cfg.hidden
+    I, E = cfg.moe_inter, cfg.n_experts
+    suffix_shape = {"q_proj.weight": (cfg.n_q_heads * hd, H), "k_proj.weight": (cfg.n_kv_heads * hd, H),
+                    "v_proj.weight": (cfg.n_kv_heads * hd, H), "o_proj.weight": (H, cfg.n_q_heads * hd),
+                    "gate_proj.weight": (I, H), "up_proj.weight": (I, H), "down_proj.weight": (H, I),
+                    "mlp.gate.weight": (E, H), "input_layernorm.weight": (H,), "post_attention_layernorm.weight": (H,),
+                    "q_norm.weight": (hd,), "k_norm.weight": (hd,), "model.norm.weight": (H,),
+                    "model.embed_tokens.weight": (cfg.vocab, H), "lm_head.weight": (cfg.vocab, H)}
+
+    def _check(name: str, t: torch.Tensor) -> torch.Tensor:
+        # a checkpoint of another architecture fails here, with the tensor's name, not deep inside a concatenation
+        for suffix, shape in suffix_shape.items():
+            if name.endswith(suffix) and tuple(t.shape) != shape:
+                raise ValueError(f"{name}: shape {tuple(t.shape)} in the checkpoint, {shape} for {cfg.name}")
+        return t
+
+    class _Checked:
+        has = staticmethod(raw.has)
+
+        @staticmethod
+        def get(name):
+            return _check(name, raw.get(name))
+
+        @staticmethod
+        def weight(name):
+            w, sc = raw.weight(name)
+            return _check(name, w), sc
+
+    get = _Checked
     qr0, qrows = geom.q_head0 * hd, geom.nq_local * hd
     kr0, krows = geom.kv_head0 * hd, geom.nkv_local * hd
     # row-stacked tensors need one block height that divides every part (and shard offsets)

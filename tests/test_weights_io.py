@@ -273,3 +273,22 @@ def test_shards_of_all_ranks_tile_every_dimension_exactly_once(model, world, pla
         cols = sorted((g.inter0, g.inter0 + g.inter_local) for g in geoms)
         assert cols[0][0] == 0 and all(a[1] == b[0] for a, b in zip(cols, cols[1:])) and cols[-1][1] == cfg.moe_inter
         assert all(g.n_experts_local == cfg.n_experts for g in geoms)
+
+
+def test_checkpoint_of_another_shape_is_refused_with_the_tensors_name():
+    cfg = get_model_config("tiny")
+    sd = random_state_dict(cfg, 0)
+    one, q = ParallelConfig(), QuantConfig(weights="fp32", kv="fp32")
+    name = "model.layers.1.mlp.experts.3.up_proj.weight"
+    bad = dict(sd)
+    bad[name] = bad[name][:, :-1]
+    with pytest.raises(ValueError, match="experts.3.up_proj.weight.*shape"):
+        shard_state_dict(bad, cfg, one, q)
+    bad = dict(sd)
+    bad["model.layers.0.self_attn.q_norm.weight"] = torch.ones(cfg.head_dim * 2)
+    with pytest.raises(ValueError, match="q_norm"):
+        shard_state_dict(bad, cfg, one, q)
+    missing = dict(sd)
+    del missing[name]
+    with pytest.raises(KeyError, match="up_proj"):
+        shard_state_dict(missing, cfg, one, q)
