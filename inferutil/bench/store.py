@@ -5,6 +5,7 @@ from __future__ import annotations
 import csv
 import json
 import os
+import warnings
 from dataclasses import asdict, dataclass
 from typing import Optional
 
@@ -59,7 +60,14 @@ def load_all(name: str, results_dir: str) -> list:
     if not os.path.isdir(folder):
         return []
     names = sorted(n for n in os.listdir(folder) if n.endswith(".json") and not n.endswith(".manifest.json"))
-    return [load_run(os.path.join(folder, n)) for n in names]
+    runs = []
+    for n in names:
+        try:
+            runs.append(load_run(os.path.join(folder, n)))
+        except (OSError, ValueError, KeyError, TypeError, AttributeError) as e:
+            # one truncated or foreign file must not hide the other runs of the experiment
+            warnings.warn(f"skipping unreadable run file {os.path.join(folder, n)}: {type(e).__name__}: {e}")
+    return runs
 
 
 def load_latest(name: str, results_dir: str):

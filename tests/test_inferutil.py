@@ -263,3 +263,19 @@ def test_co_activation_partition_places_every_expert_once_with_even_counts(n_lay
     rr = round_robin_placement(n_gpus, n_experts, n_layers)
     st_g, st_r = placement_stats(g, pl, "greedy"), placement_stats(g, rr, "rr")
     assert st_g["label"] == "greedy" and st_r["label"] == "rr"
+
+
+def test_an_unreadable_run_file_does_not_hide_the_other_runs(tmp_path):
+    import warnings
+    cfgb = B.BenchConfig("rt", "tp", 2, 2, 8, 1, prompt_tokens=32, decode_tokens=8, repeats=2, warmup_steps=1)
+    res = B.run_benchmark(B.MockEngine(CFG, H100, jitter=0.0, seed=1), cfgb, CFG, H100)
+    for rid in ("a1", "c3"):
+        B.write_run(B.RunRecord(rid, cfgb, {"gpu": "H100-SXM-80GB", "n_gpus": 8}, res), str(tmp_path))
+    folder = tmp_path / "rt"
+    (folder / "b2.json").write_text('{"runid": "b2", "config": {"name"')       # a write that was cut short
+    (folder / "b4.json").write_text('[1, 2, 3]')                               # not a run record at all
+    with warnings.catch_warnings(record=True) as seen:
+        warnings.simplefilter("always")
+        runs = B.load_all("rt", str(tmp_path))
+    assert [r.runid for r in runs] == ["a1", "c3"] and len(seen) == 2
+    assert B.load_latest("rt", str(tmp_path)).runid == "c3"
