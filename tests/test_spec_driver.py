@@ -278,3 +278,23 @@ def test_ngram_drafter_with_incremental_index_equals_a_rescan(n, min_n, k, ops):
             cut = max(0, len(ctx) - amount)
             ctx = ctx[:cut] + rng.integers(0, 3, amount).tolist()           # the tail is rewritten with other tokens
         assert d.propose(ctx, k) == _ngram_oracle(ctx, k, n, min_n)
+
+
+@settings(max_examples=8, deadline=None, suppress_health_check=[HealthCheck.function_scoped_fixture])
+@given(st.integers(1, 3), st.integers(1, 3), st.integers(1, 4), st.integers(0, 10 ** 6))
+def test_tree_speculation_with_an_untrained_head_is_lossless_for_any_tree_shape(tiny, branch, depth, chain_depth, seed):
+    """An EAGLE-style head with random weights drafts badly, which is the point: whatever tree shape it proposes and
+    however few of its nodes are accepted, the greedy output equals plain greedy decoding."""
+    eng = tiny[0]
+    rng = np.random.default_rng(seed)
+    prompt = rng.integers(0, 2048, 20).tolist()
+    plain = eng.generate(prompt, 10).tokens
+    aux = default_aux_layers(eng.cfg.model.n_layers)
+    r = D.EngineRunner(eng, aux_layers=aux)
+    torch.manual_seed(seed)
+    head = EagleHead(EagleHeadConfig(hidden=256, n_heads=4, n_kv_heads=2, head_dim=32, draft_vocab=512, target_vocab=2048),
+                     eng.weights.embed)
+    head.bind(r)
+    e3 = D.Eagle3Engine(D.RouteAwareDrafter(head, 0.0), r, D.Eagle3Config(chain_depth, 2, 2048, 0.86))
+    out, _ = e3.decode(prompt, D.DecodeStop(10), D.Rng(seed), tree=(branch, depth))
+    assert out == plain
